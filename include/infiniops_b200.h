@@ -1,0 +1,200 @@
+/*
+ * infiniops_b200.h -- C ABI of the B200 (sm_100a) int4 weight-only linear and
+ * mixture-of-experts kernels.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream
+ * (`cudaStream_t` passed as `void*`, NULL = legacy default stream), launches
+ * asynchronously on that stream on the CURRENT device, allocates nothing and
+ * returns an `iob_status`.  The C++ `infini::ops` operators and the Python
+ * module `infini.ops` shipped with this library are thin callers of these
+ * functions.
+ *
+ * Each declaration names the reference interface it stands in for (paths are
+ * relative to the InfiniOps source tree).
+ */
+#ifndef INFINIOPS_B200_H_
+#define INFINIOPS_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+  IOB_OK = 0,
+  IOB_INVALID_ARGUMENT = 1, /* a shape / pointer / attribute the op cannot accept */
+  IOB_UNSUPPORTED = 2,      /* valid for the reference, not implemented here */
+  IOB_CUDA_ERROR = 3,       /* a CUDA runtime call or launch failed */
+  IOB_SCRATCH_TOO_SMALL = 4 /* caller-provided scratch smaller than *_scratch_bytes() */
+} iob_status;
+
+/* Element types, for pointers whose type is chosen at run time. */
+typedef enum {
+  IOB_F32 = 0,
+  IOB_F16 = 1,
+  IOB_BF16 = 2,
+  IOB_I32 = 3,
+  IOB_I64 = 4,
+  IOB_U32 = 5
+} iob_dtype;
+
+/* Quantised weight types (the two 4-bit types of
+ * src/base/moe_wna16_marlin_gemm.h:172-184). */
+#define IOB_QTYPE_UINT4B8 1125899907892224LL /* GPTQ symmetric: w = (q - 8) * s      */
+#define IOB_QTYPE_UINT4 1125899906843648LL   /* AWQ: w = (q - z) * s, z in `b_zeros` */
+
+/* Text of the last non-OK status returned on the calling thread. */
+const char* infiniops_b200_last_error(void);
+
+/* Library version string. */
+const char* infiniops_b200_version(void);
+
+/* ---- weight repacking -------------------------------------------------------------------- */
+
+/* GPTQ-packed int32 [K/pf, N] (pf = 32/num_bits; field i of a word = row pf*(k/pf)+i),
+ * optional act-order row permutation `perm` (int32 [K], NULL = none), into the
+ * Marlin tile layout int32 [K/16, N*16/pf].  num_bits 4 or 8; K % 16 == 0 (32 with
+ * `is_a_8bit`), N % 64 == 0; `perm` is not accepted together with `is_a_8bit`.
+ * Replaces: GptqMarlinRepack::operator(), src/base/gptq_marlin_repack.h:34-37
+ * (implemented in the reference by vLLM `_C::gptq_marlin_repack`,
+ * src/linked/torch/nvidia/ops/gptq_marlin_repack/vllm.cc:15-24). */
+int infiniops_b200_gptq_marlin_repack(const int32_t* b_q_weight, const int32_t* perm,
+                                      int64_t size_k, int64_t size_n, int num_bits,
+                                      int is_a_8bit, int32_t* out, void* stream);
+
+/* AWQ-packed int32 [K, N/pf] (logical column j of a word in field (0,4,1,5,2,6,3,7)[j]
+ * for 4 bits, (0,2,1,3)[j] for 8) into the same Marlin tile layout.
+ * Replaces: AwqMarlinRepack::operator(), src/base/awq_marlin_repack.h:32-34
+ * (vLLM `_C::awq_marlin_repack`, src/linked/torch/nvidia/ops/awq_marlin_repack/vllm.cc:15-23). */
+int infiniops_b200_awq_marlin_repack(const int32_t* b_q_weight, int64_t size_k, int64_t size_n,
+                                     int num_bits, int is_a_8bit, int32_t* out, void* stream);
+
+/* ---- routers ------------------------------------------------------------------------------- */
+
+/* Softmax over experts, then top-k on softmax+bias; weights are the un-biased softmax
+ * (optionally renormalised), ties go to the smaller expert index, rows flagged in
+ * `is_padding` get index -1, token_expert_indices[t, r] = r * T + t.
+ * gating [T, E] of `gating_dtype` (F32/F16/BF16); bias float [E] or NULL; is_padding
+ * uint8 [T] or NULL; topk_weights float [T, k]; topk_indices [T, k] of `index_dtype`
+ * (I32/U32/I64); token_expert_indices int32 [T, k].
+ * Replaces: TopkSoftmax::operator(), src/base/topk_softmax.h:38-43 and the kernel
+ * src/native/cuda/ops/topk_softmax/kernel.cuh:93-182. */
+int infiniops_b200_topk_softmax(const void* gating_output, int gating_dtype, const float* bias,
+                                const uint8_t* is_padding, int renormalize, float* topk_weights,
+                                void* topk_indices, int index_dtype, int32_t* token_expert_indices,
+                                int64_t num_tokens, int64_t num_experts, int64_t topk,
+                                void* stream);
+
+/* Group-limited top-k (DeepSeek style): score = x or sigmoid(x) rounded to the score type,
+ * selection score = score + bias rounded to the score type, group score = sum of the two
+ * largest selection scores of the group, `topk_group` best groups kept, `topk` best
+ * finite experts inside them; values = un-biased score, optionally renormalised
+ * (/(sum + 1e-20)) and scaled.  scores [T, E] of `scores_dtype`, bias [E] of `bias_dtype`
+ * (both F32/F16/BF16); topk_values float [T, k]; topk_indices int32 [T, k].
+ * scoring_func: 0 = none, 1 = sigmoid.
+ * Replaces: GroupedTopk::operator(), src/base/grouped_topk.h:39-45 and the kernel
+ * src/native/cuda/nvidia/ops/grouped_topk/kernel.cuh:143-261. */
+int infiniops_b200_grouped_topk(const void* scores, int scores_dtype, const void* bias,
+                                int bias_dtype, int64_t num_tokens, int64_t num_experts,
+                                int64_t num_expert_group, int64_t topk_group, int64_t topk,
+                                int renormalize, double routed_scaling_factor, int scoring_func,
+                                float* topk_values, int32_t* topk_indices, void* stream);
+
+/* ---- token sort / pad ---------------------------------------------------------------------- */
+
+/* Bytes of scratch `infiniops_b200_moe_align_block_size` needs for `numel` routing ids
+ * (0 for small inputs that one thread block handles). */
+size_t infiniops_b200_moe_align_block_size_scratch_bytes(int64_t numel, int64_t num_experts);
+
+/* Groups the flat routing ids 0..numel-1 by (mapped) expert, keeping ascending order inside
+ * an expert, pads every expert's run to a multiple of `block_size` with the value `numel`,
+ * writes the expert of every block (unused blocks -1) and the padded total.
+ * topk_ids int32 [numel]; expert_map int32 [num_experts] or NULL; ids outside
+ * [0, num_experts) or mapped outside it are dropped.  Every element of `sorted_token_ids`
+ * [sorted_size] and `experts_ids` [experts_size] is written.
+ * `scratch` may be NULL when *_scratch_bytes() is 0; its contents need no initialisation.
+ * Replaces: MoeAlignBlockSize::operator(), src/base/moe_align_block_size.h:37-45 and the
+ * kernel src/native/cuda/nvidia/ops/moe_align_block_size/kernel.cuh:23-78. */
+int infiniops_b200_moe_align_block_size(const int32_t* topk_ids, const int32_t* expert_map,
+                                        int64_t numel, int64_t num_experts, int64_t block_size,
+                                        int32_t* sorted_token_ids, int64_t sorted_size,
+                                        int32_t* experts_ids, int64_t experts_size,
+                                        int32_t* num_tokens_post_pad, void* scratch,
+                                        size_t scratch_bytes, void* stream);
+
+/* ---- activation and combine ------------------------------------------------------------------ */
+
+/* out[..., j] = silu(in[..., j]) * in[..., H + j]; fp32 math, one rounding.
+ * `ndim` <= 8; shape is the OUTPUT shape ([..., H]); strides in elements; the last
+ * dimension of both tensors must have stride 1.  dtype F32/F16/BF16.
+ * Replaces: SiluAndMul::operator(), src/base/silu_and_mul.h:36 and the kernel
+ * src/native/cuda/ops/silu_and_mul/kernel.cuh:31-81. */
+int infiniops_b200_silu_and_mul(const void* input, void* out, int dtype, int ndim,
+                                const int64_t* out_shape, const int64_t* input_strides,
+                                const int64_t* out_strides, void* stream);
+
+/* out[t, h] = sum over slots s of in[t, s, h] (fp32 accumulation, slot order), skipping
+ * slots whose id in `topk_ids` is negative, or -- with `expert_map` -- not below
+ * `expert_map_size` or mapped to a negative value.  Input strides in elements, any
+ * non-negative values; output contiguous [T, H].  topk_ids of `ids_dtype` (I32/I64) or NULL.
+ * Replaces: MoeSum::operator() (both overloads), src/base/moe_sum.h:132-138 and the kernel
+ * src/native/cuda/ops/moe_sum/kernel.cuh:10-48. */
+int infiniops_b200_moe_sum(const void* input, int dtype, int64_t num_tokens, int64_t topk,
+                           int64_t hidden, int64_t in_stride_t, int64_t in_stride_s,
+                           int64_t in_stride_h, const void* topk_ids, int ids_dtype,
+                           int64_t ids_stride_t, int64_t ids_stride_s, const int32_t* expert_map,
+                           int64_t expert_map_size, int64_t expert_map_stride, void* out,
+                           void* stream);
+
+/* ---- W4A16 GEMM ------------------------------------------------------------------------------ */
+
+/* Bytes of scratch the dense GEMM needs for an [M, K] x [K, N] problem on the current
+ * device (partial sums of K-split tiles and their arrival counters). */
+size_t infiniops_b200_marlin_gemm_scratch_bytes(int64_t size_m, int64_t size_n, int64_t size_k);
+
+/* C[M, N] = A[M, K] * dequant(W)[K, N] (+ bias[N]), fp32 accumulation, C in A's type.
+ * a: [M, K] F16/BF16 row-major.  b_q_weight: Marlin layout int32 [K/16, 2N] as produced by
+ * the repack functions above (4-bit).  b_scales: [G, N] in A's type, plain row-major,
+ * G = K / group_size (group_size a multiple of 16 that divides K; G = 1 for per-channel).  b_zeros: int32 [G, N/8],
+ * field j of a word = column 8*(n/8)+j, required for IOB_QTYPE_UINT4 and NULL for
+ * IOB_QTYPE_UINT4B8.  b_bias: [N] in A's type or NULL.  K % 64 == 0, N % 64 == 0.
+ * `scratch` must hold *_scratch_bytes(); its first use must find the counter area zeroed
+ * (cudaMemset once after allocation); every call leaves it zeroed again.
+ * The reference has no dense Marlin GEMM operator; this follows the argument set of its MoE
+ * form (src/base/moe_wna16_marlin_gemm.h:18-34) without the routing arguments, and the value
+ * semantics of tests/test_moe_wna16_gemm.py:397-404,437. */
+int infiniops_b200_marlin_gemm(const void* a, int a_dtype, const int32_t* b_q_weight,
+                               const void* b_bias, const void* b_scales, const int32_t* b_zeros,
+                               int64_t b_type_id, int64_t size_m, int64_t size_n, int64_t size_k,
+                               int64_t num_groups, void* out, void* scratch, size_t scratch_bytes,
+                               void* stream);
+
+/* Bytes of scratch the routed (MoE) GEMM needs. */
+size_t infiniops_b200_moe_wna16_marlin_gemm_scratch_bytes(int64_t size_m, int64_t top_k,
+                                                          int64_t size_n, int64_t size_k,
+                                                          int64_t num_experts,
+                                                          int64_t moe_block_size);
+
+/* Routed GEMM: for every block b of `moe_block_size` entries of `sorted_token_ids` below
+ * `num_tokens_past_padded[0]`, with e = expert_ids[b] >= 0, and every entry r < M*top_k of
+ * the block: out[r, :] = A[r / top_k, :] * dequant(W[e]) (+ bias[e]) (* topk_weights[r] when
+ * `mul_topk_weights`).  Rows of `out` that no entry names are left untouched.
+ * a: [M, K]; b_q_weight: [E, K/16, 2N]; b_scales: [E, G, N]; b_zeros: [E, G, N/8] or NULL;
+ * b_bias: [E, N] or NULL; topk_weights float [M*top_k]; out: [M*top_k, N].
+ * Replaces: MoeWna16MarlinGemm::operator(), src/base/moe_wna16_marlin_gemm.h:71-85
+ * (vLLM `_moe_C::moe_wna16_marlin_gemm`, src/linked/torch/nvidia/ops/moe_wna16_marlin_gemm/vllm.h:53-93). */
+int infiniops_b200_moe_wna16_marlin_gemm(
+    const void* a, int a_dtype, const int32_t* b_q_weight, const void* b_bias,
+    const void* b_scales, const int32_t* b_zeros, const int32_t* sorted_token_ids,
+    const int32_t* expert_ids, const int32_t* num_tokens_past_padded, const float* topk_weights,
+    int64_t moe_block_size, int64_t top_k, int mul_topk_weights, int64_t b_type_id,
+    int64_t size_m, int64_t size_n, int64_t size_k, int64_t num_groups, int64_t num_experts,
+    int64_t sorted_size, void* out, void* scratch, size_t scratch_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* INFINIOPS_B200_H_ */

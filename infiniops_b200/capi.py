@@ -1,0 +1,179 @@
+"""ctypes view of ``libinfiniops_b200.so`` (the C ABI declared in ``include/infiniops_b200.h``).
+
+The functions here take torch tensors only to read ``data_ptr()`` / shapes / strides; the
+arithmetic is entirely in the CUDA library.  There is no fallback: if the library is
+missing or a call returns a non-zero status, an exception is raised.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import pathlib
+
+import torch
+
+_LIB_PATH = pathlib.Path(__file__).resolve().parent / "lib" / "libinfiniops_b200.so"
+
+F32, F16, BF16, I32, I64, U32 = range(6)
+QTYPE_UINT4B8 = 1125899907892224
+QTYPE_UINT4 = 1125899906843648
+
+_DTYPE = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16, torch.int32: I32,
+          torch.int64: I64, torch.uint32: U32}
+
+_vp, _i64, _int, _sz, _dbl = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_size_t, ctypes.c_double
+
+# name -> (restype, argtypes); every name must also be declared in include/infiniops_b200.h
+PROTOTYPES = {
+    "infiniops_b200_last_error": (ctypes.c_char_p, []),
+    "infiniops_b200_version": (ctypes.c_char_p, []),
+    "infiniops_b200_gptq_marlin_repack": (_int, [_vp, _vp, _i64, _i64, _int, _int, _vp, _vp]),
+    "infiniops_b200_awq_marlin_repack": (_int, [_vp, _i64, _i64, _int, _int, _vp, _vp]),
+    "infiniops_b200_topk_softmax": (_int, [_vp, _int, _vp, _vp, _int, _vp, _vp, _int, _vp, _i64, _i64, _i64, _vp]),
+    "infiniops_b200_grouped_topk": (_int, [_vp, _int, _vp, _int, _i64, _i64, _i64, _i64, _i64, _int, _dbl, _int,
+                                           _vp, _vp, _vp]),
+    "infiniops_b200_moe_align_block_size_scratch_bytes": (_sz, [_i64, _i64]),
+    "infiniops_b200_moe_align_block_size": (_int, [_vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp, _i64, _vp, _vp,
+                                                   _sz, _vp]),
+    "infiniops_b200_silu_and_mul": (_int, [_vp, _vp, _int, _int, _vp, _vp, _vp, _vp]),
+    "infiniops_b200_moe_sum": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _i64, _i64, _vp, _int, _i64, _i64, _vp,
+                                      _i64, _i64, _vp, _vp]),
+    "infiniops_b200_marlin_gemm_scratch_bytes": (_sz, [_i64, _i64, _i64]),
+    "infiniops_b200_marlin_gemm": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp,
+                                          _sz, _vp]),
+    "infiniops_b200_moe_wna16_marlin_gemm_scratch_bytes": (_sz, [_i64, _i64, _i64, _i64, _i64, _i64]),
+    "infiniops_b200_moe_wna16_marlin_gemm": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
+                                                    _int, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _sz,
+                                                    _vp]),
+}
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """Load the CUDA library, or fail loudly: there is no CPU or PyTorch fallback."""
+    global _lib
+    if _lib is None:
+        if not _LIB_PATH.exists():
+            raise RuntimeError(f"{_LIB_PATH} is missing: run `python -m infiniops_b200.build` "
+                               "(the operators have no fallback implementation)")
+        handle = ctypes.CDLL(str(_LIB_PATH))
+        for name, (restype, argtypes) in PROTOTYPES.items():
+            fn = getattr(handle, name)
+            fn.restype, fn.argtypes = restype, argtypes
+        _lib = handle
+    return _lib
+
+
+class Error(RuntimeError):
+    pass
+
+
+def _check(status: int) -> None:
+    if status != 0:
+        raise Error(f"status {status}: {lib().infiniops_b200_last_error().decode()}")
+
+
+def _ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream(stream) -> ctypes.c_void_p:
+    if stream is None:
+        stream = torch.cuda.current_stream().cuda_stream
+    return ctypes.c_void_p(stream)
+
+
+_scratch: dict = {}
+
+
+def scratch(device, nbytes: int) -> torch.Tensor:
+    """A zero-initialised per-device scratch buffer that only grows (test / bench convenience)."""
+    key = torch.device(device).index
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _scratch[key] = buf
+    return buf
+
+
+def gptq_marlin_repack(b_q_weight, perm, size_k, size_n, num_bits, is_a_8bit, out, stream=None):
+    p = perm if perm is not None and perm.numel() else None
+    _check(lib().infiniops_b200_gptq_marlin_repack(_ptr(b_q_weight), _ptr(p), size_k, size_n, num_bits,
+                                                   int(is_a_8bit), _ptr(out), _stream(stream)))
+
+
+def awq_marlin_repack(b_q_weight, size_k, size_n, num_bits, is_a_8bit, out, stream=None):
+    _check(lib().infiniops_b200_awq_marlin_repack(_ptr(b_q_weight), size_k, size_n, num_bits, int(is_a_8bit),
+                                                  _ptr(out), _stream(stream)))
+
+
+def topk_softmax(gating, bias, is_padding, renormalize, topk_weights, topk_indices, token_expert_indices,
+                 stream=None):
+    t, e = gating.shape
+    _check(lib().infiniops_b200_topk_softmax(_ptr(gating), _DTYPE[gating.dtype], _ptr(bias), _ptr(is_padding),
+                                             int(renormalize), _ptr(topk_weights), _ptr(topk_indices),
+                                             _DTYPE[topk_indices.dtype], _ptr(token_expert_indices), t, e,
+                                             topk_weights.shape[1], _stream(stream)))
+
+
+def grouped_topk(scores, bias, num_expert_group, topk_group, topk, renormalize, routed_scaling_factor,
+                 scoring_func, topk_values, topk_indices, stream=None):
+    t, e = scores.shape
+    _check(lib().infiniops_b200_grouped_topk(_ptr(scores), _DTYPE[scores.dtype], _ptr(bias), _DTYPE[bias.dtype], t,
+                                             e, num_expert_group, topk_group, topk, int(renormalize),
+                                             float(routed_scaling_factor), scoring_func, _ptr(topk_values),
+                                             _ptr(topk_indices), _stream(stream)))
+
+
+def moe_align_block_size(topk_ids, expert_map, num_experts, block_size, sorted_token_ids, experts_ids,
+                         num_tokens_post_pad, stream=None):
+    numel = topk_ids.numel()
+    need = lib().infiniops_b200_moe_align_block_size_scratch_bytes(numel, num_experts)
+    buf = scratch(topk_ids.device, need) if need else None
+    _check(lib().infiniops_b200_moe_align_block_size(_ptr(topk_ids), _ptr(expert_map), numel, num_experts,
+                                                     block_size, _ptr(sorted_token_ids), sorted_token_ids.numel(),
+                                                     _ptr(experts_ids), experts_ids.numel(),
+                                                     _ptr(num_tokens_post_pad), _ptr(buf),
+                                                     0 if buf is None else buf.numel(), _stream(stream)))
+
+
+def silu_and_mul(x, out, stream=None):
+    nd = out.dim()
+    arr = ctypes.c_int64 * nd
+    _check(lib().infiniops_b200_silu_and_mul(_ptr(x), _ptr(out), _DTYPE[x.dtype], nd, arr(*out.shape),
+                                             arr(*x.stride()), arr(*out.stride()), _stream(stream)))
+
+
+def moe_sum(x, out, topk_ids=None, expert_map=None, stream=None):
+    t, k, h = x.shape
+    st, ss, sh = x.stride()
+    ids_t, ids_s = (0, 0) if topk_ids is None else topk_ids.stride()
+    _check(lib().infiniops_b200_moe_sum(_ptr(x), _DTYPE[x.dtype], t, k, h, st, ss, sh, _ptr(topk_ids),
+                                        I32 if topk_ids is None else _DTYPE[topk_ids.dtype], ids_t, ids_s,
+                                        _ptr(expert_map), 0 if expert_map is None else expert_map.numel(),
+                                        0 if expert_map is None else expert_map.stride(0), _ptr(out),
+                                        _stream(stream)))
+
+
+def marlin_gemm(a, b_q_weight, b_bias, b_scales, b_zeros, b_type_id, size_m, size_n, size_k, out, stream=None,
+                scratch_buf=None):
+    need = lib().infiniops_b200_marlin_gemm_scratch_bytes(size_m, size_n, size_k)
+    buf = scratch_buf if scratch_buf is not None else scratch(a.device, need)
+    _check(lib().infiniops_b200_marlin_gemm(_ptr(a), _DTYPE[a.dtype], _ptr(b_q_weight), _ptr(b_bias), _ptr(b_scales),
+                                            _ptr(b_zeros), b_type_id, size_m, size_n, size_k, b_scales.shape[-2],
+                                            _ptr(out), _ptr(buf), buf.numel(), _stream(stream)))
+
+
+def moe_wna16_marlin_gemm(a, b_q_weight, b_bias, b_scales, b_zeros, sorted_token_ids, expert_ids,
+                          num_tokens_past_padded, topk_weights, moe_block_size, top_k, mul_topk_weights, b_type_id,
+                          size_m, size_n, size_k, out, stream=None, scratch_buf=None):
+    e = b_q_weight.shape[0]
+    need = lib().infiniops_b200_moe_wna16_marlin_gemm_scratch_bytes(size_m, top_k, size_n, size_k, e,
+                                                                    moe_block_size)
+    buf = scratch_buf if scratch_buf is not None else scratch(a.device, need)
+    _check(lib().infiniops_b200_moe_wna16_marlin_gemm(
+        _ptr(a), _DTYPE[a.dtype], _ptr(b_q_weight), _ptr(b_bias), _ptr(b_scales), _ptr(b_zeros),
+        _ptr(sorted_token_ids), _ptr(expert_ids), _ptr(num_tokens_past_padded), _ptr(topk_weights), moe_block_size,
+        top_k, int(mul_topk_weights), b_type_id, size_m, size_n, size_k, b_scales.shape[-2], e,
+        sorted_token_ids.numel(), _ptr(out), _ptr(buf), buf.numel(), _stream(stream)))

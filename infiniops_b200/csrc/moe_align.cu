@@ -1,0 +1,262 @@
+// moe_align_block_size: stable grouping of routing ids by expert, padded to blocks.
+//
+// The ids are cut into chunks of 1024 (one per thread block, one id per thread).  Inside a
+// chunk a thread finds its stable rank among the ids of the same expert from a warp
+// `match.any` ballot plus a per-warp / per-expert count table in shared memory -- no atomics
+// on the ordering path, so the result is deterministic and equals the ascending-index order
+// a serial scan would give.  Up to 1024 ids the whole operator is ONE launch of ONE block.
+// Beyond that, a counting launch leaves per-chunk histograms in scratch, its last-arriving
+// block (an atomic ticket, no spinning) turns them into offsets, and a second launch scatters.
+#include "common.cuh"
+
+namespace iob {
+namespace {
+
+constexpr int kChunk = 1024;
+constexpr int kWarps = kChunk / 32;
+constexpr unsigned kFull = 0xffffffffu;
+
+__device__ __forceinline__ int MapExpert(int id, const int32_t* expert_map, int num_experts) {
+  if (id < 0 || id >= num_experts) return -1;
+  if (expert_map != nullptr) id = expert_map[id];
+  return id >= 0 && id < num_experts ? id : -1;
+}
+
+struct Smem {
+  uint16_t* warp_count;  // [kWarps][num_experts]: per-warp counts, then exclusive prefixes over warps
+  int* expert_base;      // [num_experts]: first padded position of every expert
+  int* expert_total;     // [num_experts]: ids routed to every expert
+  int* warp_sums;        // [kWarps] scratch of the block scan
+};
+
+__device__ __forceinline__ Smem CarveSmem(unsigned char* raw, int num_experts) {
+  Smem s;
+  const int table = ((kWarps * num_experts + 1) & ~1);
+  s.warp_count = reinterpret_cast<uint16_t*>(raw);
+  s.expert_base = reinterpret_cast<int*>(raw + static_cast<size_t>(table) * sizeof(uint16_t));
+  s.expert_total = s.expert_base + num_experts;
+  s.warp_sums = s.expert_total + num_experts;
+  return s;
+}
+
+size_t SmemBytes(int64_t num_experts) {
+  const size_t table = ((kWarps * num_experts + 1) & ~1);
+  return table * sizeof(uint16_t) + (2 * num_experts + kWarps) * sizeof(int);
+}
+
+// Stable rank of this thread's id among the chunk's ids with the same expert.  On return
+// s.warp_count[w][e] holds the number of such ids in warps before w, and `chunk_total(e)`
+// has been handed to `emit` for every expert.
+template <typename Emit>
+__device__ __forceinline__ int ChunkRank(const Smem& s, int expert, int num_experts, Emit emit) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  for (int i = tid; i < kWarps * num_experts; i += kChunk) s.warp_count[i] = 0;
+  __syncthreads();
+  const unsigned same = __match_any_sync(kFull, expert);
+  const int rank_in_warp = __popc(same & ((1u << lane) - 1u));
+  if (expert >= 0 && rank_in_warp == 0) {
+    s.warp_count[warp * num_experts + expert] = static_cast<uint16_t>(__popc(same));
+  }
+  __syncthreads();
+  for (int e = tid; e < num_experts; e += kChunk) {
+    int run = 0;
+#pragma unroll 8
+    for (int w = 0; w < kWarps; ++w) {
+      const int c = s.warp_count[w * num_experts + e];
+      s.warp_count[w * num_experts + e] = static_cast<uint16_t>(run);
+      run += c;
+    }
+    emit(e, run);
+  }
+  __syncthreads();
+  return expert >= 0 ? s.warp_count[warp * num_experts + expert] + rank_in_warp : 0;
+}
+
+// From s.expert_total: padded exclusive scan -> s.expert_base, block owners -> experts_ids,
+// padded total -> num_tokens_post_pad.  Requires num_experts <= kChunk.
+__device__ __forceinline__ void PadAndPublish(const Smem& s, int num_experts, int block_size,
+                                              int32_t* experts_ids, int32_t* num_tokens_post_pad) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int count = tid < num_experts ? s.expert_total[tid] : 0;
+  const int padded = (count + block_size - 1) / block_size * block_size;
+  int incl = padded;
+#pragma unroll
+  for (int offset = 1; offset < 32; offset <<= 1) {
+    const int up = __shfl_up_sync(kFull, incl, offset);
+    if (lane >= offset) incl += up;
+  }
+  if (lane == 31) s.warp_sums[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    int v = s.warp_sums[lane];
+#pragma unroll
+    for (int offset = 1; offset < 32; offset <<= 1) {
+      const int up = __shfl_up_sync(kFull, v, offset);
+      if (lane >= offset) v += up;
+    }
+    s.warp_sums[lane] = v;  // inclusive over warps
+  }
+  __syncthreads();
+  const int before = warp == 0 ? 0 : s.warp_sums[warp - 1];
+  if (tid < num_experts) s.expert_base[tid] = before + incl - padded;
+  const int total = s.warp_sums[kWarps - 1];
+  __syncthreads();
+  if (tid == 0) *num_tokens_post_pad = total;
+  // Owner of block b = last expert whose base is <= b * block_size.
+  for (int b = tid; b < total / block_size; b += kChunk) {
+    const int pos = b * block_size;
+    int lo = 0, hi = num_experts;  // first expert with base > pos
+    while (lo < hi) {
+      const int mid = (lo + hi) >> 1;
+      if (s.expert_base[mid] <= pos) lo = mid + 1; else hi = mid;
+    }
+    experts_ids[b] = lo - 1;
+  }
+}
+
+__device__ __forceinline__ void FillOutputs(int32_t* sorted_token_ids, int64_t sorted_size,
+                                            int32_t* experts_ids, int64_t experts_size, int numel) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kChunk;
+  const int64_t start = static_cast<int64_t>(blockIdx.x) * kChunk + threadIdx.x;
+  for (int64_t i = start; i < sorted_size; i += stride) sorted_token_ids[i] = numel;
+  for (int64_t i = start; i < experts_size; i += stride) experts_ids[i] = -1;
+}
+
+// Whole operator in one block (numel <= kChunk).
+__global__ void __launch_bounds__(kChunk)
+AlignSingleBlockKernel(const int32_t* __restrict__ topk_ids, const int32_t* __restrict__ expert_map,
+                       int numel, int num_experts, int block_size, int32_t* __restrict__ sorted_token_ids,
+                       int64_t sorted_size, int32_t* __restrict__ experts_ids, int64_t experts_size,
+                       int32_t* __restrict__ num_tokens_post_pad) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const Smem s = CarveSmem(smem_raw, num_experts);
+  FillOutputs(sorted_token_ids, sorted_size, experts_ids, experts_size, numel);
+  const int tid = threadIdx.x;
+  const int expert = tid < numel ? MapExpert(topk_ids[tid], expert_map, num_experts) : -1;
+  const int rank = ChunkRank(s, expert, num_experts, [&](int e, int total) { s.expert_total[e] = total; });
+  PadAndPublish(s, num_experts, block_size, experts_ids, num_tokens_post_pad);
+  __syncthreads();
+  if (expert >= 0) sorted_token_ids[s.expert_base[expert] + rank] = tid;
+}
+
+// Scratch layout (int32): [0] ticket, [1 .. E] expert_base, then [chunks][E] histograms.
+__global__ void __launch_bounds__(kChunk)
+AlignCountKernel(const int32_t* __restrict__ topk_ids, const int32_t* __restrict__ expert_map, int numel,
+                 int num_experts, int block_size, int32_t* __restrict__ sorted_token_ids,
+                 int64_t sorted_size, int32_t* __restrict__ experts_ids, int64_t experts_size,
+                 int32_t* __restrict__ num_tokens_post_pad, int32_t* __restrict__ scratch) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ int is_last;
+  const Smem s = CarveSmem(smem_raw, num_experts);
+  FillOutputs(sorted_token_ids, sorted_size, experts_ids, experts_size, numel);
+  const int tid = threadIdx.x;
+  const int idx = blockIdx.x * kChunk + tid;
+  const int expert = idx < numel ? MapExpert(topk_ids[idx], expert_map, num_experts) : -1;
+  int32_t* hist = scratch + 1 + num_experts;
+  ChunkRank(s, expert, num_experts,
+            [&](int e, int total) { hist[static_cast<int64_t>(blockIdx.x) * num_experts + e] = total; });
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) is_last = atomicAdd(scratch, 1) == static_cast<int>(gridDim.x) - 1;
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  // Exclusive prefix over chunks, in place; totals to shared memory.
+  for (int e = tid; e < num_experts; e += kChunk) {
+    int run = 0;
+    for (unsigned c = 0; c < gridDim.x; ++c) {
+      const int64_t at = static_cast<int64_t>(c) * num_experts + e;
+      const int v = hist[at];
+      hist[at] = run;
+      run += v;
+    }
+    s.expert_total[e] = run;
+  }
+  __syncthreads();
+  PadAndPublish(s, num_experts, block_size, experts_ids, num_tokens_post_pad);
+  __syncthreads();
+  for (int e = tid; e < num_experts; e += kChunk) scratch[1 + e] = s.expert_base[e];
+  if (tid == 0) scratch[0] = 0;
+}
+
+__global__ void __launch_bounds__(kChunk)
+AlignScatterKernel(const int32_t* __restrict__ topk_ids, const int32_t* __restrict__ expert_map, int numel,
+                   int num_experts, int32_t* __restrict__ sorted_token_ids,
+                   const int32_t* __restrict__ scratch) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const Smem s = CarveSmem(smem_raw, num_experts);
+  const int idx = blockIdx.x * kChunk + threadIdx.x;
+  const int expert = idx < numel ? MapExpert(topk_ids[idx], expert_map, num_experts) : -1;
+  const int rank = ChunkRank(s, expert, num_experts, [](int, int) {});
+  if (expert >= 0) {
+    const int32_t* hist = scratch + 1 + num_experts;
+    const int at = scratch[1 + expert] + hist[static_cast<int64_t>(blockIdx.x) * num_experts + expert] + rank;
+    sorted_token_ids[at] = idx;
+  }
+}
+
+template <typename Kernel>
+int AllowSmem(Kernel kernel, size_t bytes) {
+  if (bytes > 48 * 1024) {
+    const cudaError_t err =
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes));
+    if (err != cudaSuccess) return Fail(IOB_CUDA_ERROR, "moe_align_block_size: %s", cudaGetErrorString(err));
+  }
+  return IOB_OK;
+}
+
+}  // namespace
+}  // namespace iob
+
+extern "C" size_t infiniops_b200_moe_align_block_size_scratch_bytes(int64_t numel, int64_t num_experts) {
+  if (numel <= iob::kChunk) return 0;
+  const int64_t chunks = (numel + iob::kChunk - 1) / iob::kChunk;
+  return static_cast<size_t>(1 + num_experts + chunks * num_experts) * sizeof(int32_t);
+}
+
+extern "C" int infiniops_b200_moe_align_block_size(const int32_t* topk_ids, const int32_t* expert_map,
+                                                   int64_t numel, int64_t num_experts, int64_t block_size,
+                                                   int32_t* sorted_token_ids, int64_t sorted_size,
+                                                   int32_t* experts_ids, int64_t experts_size,
+                                                   int32_t* num_tokens_post_pad, void* scratch,
+                                                   size_t scratch_bytes, void* stream) {
+  using namespace iob;
+  IOB_REQUIRE(num_experts > 0 && num_experts < 1024, "moe_align_block_size: requires `num_experts` in [1, 1023]");
+  IOB_REQUIRE(block_size > 0 && block_size <= INT32_MAX, "moe_align_block_size: requires a positive `block_size`");
+  IOB_REQUIRE(numel >= 0 && numel <= INT32_MAX, "moe_align_block_size: requires int32-addressable token indices");
+  int64_t need_sorted = numel + num_experts * (block_size - 1);
+  if (numel < num_experts) need_sorted = numel * block_size < need_sorted ? numel * block_size : need_sorted;
+  const int64_t need_blocks = (need_sorted + block_size - 1) / block_size;
+  IOB_REQUIRE(need_sorted <= INT32_MAX, "moe_align_block_size: requires int32-addressable padded indices");
+  IOB_REQUIRE(sorted_size >= need_sorted && experts_size >= need_blocks,
+              "moe_align_block_size: output tensors are too small");
+  IOB_REQUIRE(num_tokens_post_pad != nullptr && (sorted_size == 0 || sorted_token_ids != nullptr) &&
+                  (experts_size == 0 || experts_ids != nullptr) && (numel == 0 || topk_ids != nullptr),
+              "moe_align_block_size: null tensor pointer");
+  auto s = static_cast<cudaStream_t>(stream);
+  const size_t smem = SmemBytes(num_experts);
+  const int n = static_cast<int>(numel), e = static_cast<int>(num_experts), bs = static_cast<int>(block_size);
+  if (numel <= kChunk) {
+    if (const int rc = AllowSmem(AlignSingleBlockKernel, smem)) return rc;
+    AlignSingleBlockKernel<<<1, kChunk, smem, s>>>(topk_ids, expert_map, n, e, bs, sorted_token_ids, sorted_size,
+                                                  experts_ids, experts_size, num_tokens_post_pad);
+    return CheckLaunch("moe_align_block_size launch");
+  }
+  const size_t need = infiniops_b200_moe_align_block_size_scratch_bytes(numel, num_experts);
+  if (scratch == nullptr || scratch_bytes < need) {
+    return Fail(IOB_SCRATCH_TOO_SMALL, "moe_align_block_size: needs %zu bytes of scratch, got %zu", need,
+                scratch_bytes);
+  }
+  auto* scratch_i32 = static_cast<int32_t*>(scratch);
+  const unsigned chunks = static_cast<unsigned>((numel + kChunk - 1) / kChunk);
+  if (cudaMemsetAsync(scratch_i32, 0, sizeof(int32_t), s) != cudaSuccess) {
+    return Fail(IOB_CUDA_ERROR, "moe_align_block_size: ticket reset failed");
+  }
+  if (const int rc = AllowSmem(AlignCountKernel, smem)) return rc;
+  if (const int rc = AllowSmem(AlignScatterKernel, smem)) return rc;
+  AlignCountKernel<<<chunks, kChunk, smem, s>>>(topk_ids, expert_map, n, e, bs, sorted_token_ids, sorted_size,
+                                               experts_ids, experts_size, num_tokens_post_pad, scratch_i32);
+  if (const int rc = CheckLaunch("moe_align_block_size count launch")) return rc;
+  AlignScatterKernel<<<chunks, kChunk, smem, s>>>(topk_ids, expert_map, n, e, sorted_token_ids, scratch_i32);
+  return CheckLaunch("moe_align_block_size scatter launch");
+}
