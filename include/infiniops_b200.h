@@ -127,8 +127,9 @@ int infiniops_b200_moe_align_block_size(const int32_t* topk_ids, const int32_t* 
 /* ---- activation and combine ------------------------------------------------------------------ */
 
 /* out[..., j] = silu(in[..., j]) * in[..., H + j]; fp32 math, one rounding.
- * `ndim` <= 8; shape is the OUTPUT shape ([..., H]); strides in elements; the last
- * dimension of both tensors must have stride 1.  dtype F32/F16/BF16.
+ * `ndim` <= 8; shape is the OUTPUT shape ([..., H]); strides in elements, any non-negative
+ * values (16-byte vector accesses are used when the last stride is 1 and rows are aligned).
+ * dtype F32/F16/BF16.
  * Replaces: SiluAndMul::operator(), src/base/silu_and_mul.h:36 and the kernel
  * src/native/cuda/ops/silu_and_mul/kernel.cuh:31-81. */
 int infiniops_b200_silu_and_mul(const void* input, void* out, int dtype, int ndim,
@@ -149,6 +150,13 @@ int infiniops_b200_moe_sum(const void* input, int dtype, int64_t num_tokens, int
                            void* stream);
 
 /* ---- W4A16 GEMM ------------------------------------------------------------------------------ */
+
+/* The GEMM kernels bound every on-device wait.  If one expires (it never should) the kernel
+ * records a non-zero code in the first int of its scratch buffer and returns early, leaving
+ * the output incomplete.  This helper copies that int back on `stream`, synchronises the
+ * stream and returns it (0 = no wait ever expired, -1 = the copy failed).
+ * No counterpart in the reference. */
+int infiniops_b200_scratch_status(const void* scratch, void* stream);
 
 /* Bytes of scratch the dense GEMM needs for an [M, K] x [K, N] problem on the current
  * device (partial sums of K-split tiles and their arrival counters). */

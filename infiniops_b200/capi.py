@@ -38,6 +38,7 @@ PROTOTYPES = {
     "infiniops_b200_silu_and_mul": (_int, [_vp, _vp, _int, _int, _vp, _vp, _vp, _vp]),
     "infiniops_b200_moe_sum": (_int, [_vp, _int, _i64, _i64, _i64, _i64, _i64, _i64, _vp, _int, _i64, _i64, _vp,
                                       _i64, _i64, _vp, _vp]),
+    "infiniops_b200_scratch_status": (_int, [_vp, _vp]),
     "infiniops_b200_marlin_gemm_scratch_bytes": (_sz, [_i64, _i64, _i64]),
     "infiniops_b200_marlin_gemm": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp,
                                           _sz, _vp]),
@@ -87,9 +88,11 @@ def _stream(stream) -> ctypes.c_void_p:
 _scratch: dict = {}
 
 
-def scratch(device, nbytes: int) -> torch.Tensor:
-    """A zero-initialised per-device scratch buffer that only grows (test / bench convenience)."""
-    key = torch.device(device).index
+def scratch(device, nbytes: int, tag: str = "gemm") -> torch.Tensor:
+    """A zero-initialised scratch buffer per (device, purpose) that only grows (test / bench
+    convenience).  The GEMM keeps counters it expects to find zeroed, so it never shares a
+    buffer with the token sort."""
+    key = (torch.device(device).index, tag)
     buf = _scratch.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
@@ -130,7 +133,7 @@ def moe_align_block_size(topk_ids, expert_map, num_experts, block_size, sorted_t
                          num_tokens_post_pad, stream=None):
     numel = topk_ids.numel()
     need = lib().infiniops_b200_moe_align_block_size_scratch_bytes(numel, num_experts)
-    buf = scratch(topk_ids.device, need) if need else None
+    buf = scratch(topk_ids.device, need, "align") if need else None
     _check(lib().infiniops_b200_moe_align_block_size(_ptr(topk_ids), _ptr(expert_map), numel, num_experts,
                                                      block_size, _ptr(sorted_token_ids), sorted_token_ids.numel(),
                                                      _ptr(experts_ids), experts_ids.numel(),
@@ -154,6 +157,11 @@ def moe_sum(x, out, topk_ids=None, expert_map=None, stream=None):
                                         _ptr(expert_map), 0 if expert_map is None else expert_map.numel(),
                                         0 if expert_map is None else expert_map.stride(0), _ptr(out),
                                         _stream(stream)))
+
+
+def scratch_status(buf, stream=None) -> int:
+    """0 unless a bounded on-device wait of a GEMM kernel using `buf` ever expired."""
+    return lib().infiniops_b200_scratch_status(_ptr(buf), _stream(stream))
 
 
 def marlin_gemm(a, b_q_weight, b_bias, b_scales, b_zeros, b_type_id, size_m, size_n, size_k, out, stream=None,

@@ -1,0 +1,872 @@
+// W4A16 GEMM for sm_100a: dense (marlin_gemm) and routed (moe_wna16_marlin_gemm).
+//
+// Orientation.  The product is computed transposed, D[n, m] = sum_k W[k, n] * A[m, k], so the
+// 128 weight columns of a tile are the M dimension of a tcgen05 MMA (one TMEM lane each) and
+// the tokens are its N dimension (16..256).  The dequantised weights are the MMA's A operand
+// and live in TENSOR MEMORY; the activations are the B operand in shared memory (K-major,
+// 128-byte swizzle, written by TMA); the fp32 accumulator is in tensor memory too.
+//
+// Why tensor memory for the weights: the Marlin layout stores, per 32-bit word, exactly the
+// fragment a thread of an m16n8k16 MMA would hold (two columns 8 apart, k pairs {2c,2c+1} and
+// {2c+8,2c+9}).  `tcgen05.st.16x128b` has the same thread<->element map, so a word goes
+// global -> shared (bulk copy, still packed) -> one 8-byte shared load -> lop3/sub/mul in
+// registers -> tensor memory, without any shuffle and without ever writing 16-bit weights to
+// shared memory (which would cost 4x the bytes of the int4 stream on the store and again on the
+// MMA's operand fetch).
+//
+// Pipeline per thread block (one per SM, persistent):
+//   warp 0      producer: bulk copies of packed weights / scales / zero points and one TMA
+//               tensor copy of the activation tile per 64-k stage, mbarrier completion
+//   warp 1      MMA issuer (one thread) + owner of the tensor-memory allocation
+//   warps 2..   dequantisers (one or two sets of 4 warps; a warp owns a 32-lane quarter)
+//   last 4      epilogue: accumulator -> registers -> bias / routing weight -> global
+//
+// Work split (stream-K): the tiles x k-stages grid is cut into equal contiguous ranges, one
+// per thread block.  A tile whose k range is shared by several blocks is finished by the block
+// that arrives last at the tile's counter (no waiting on other blocks): every sharer writes its
+// fp32 partial to scratch, the last one adds them in a fixed order, so results do not depend
+// on arrival order.
+//
+// Every wait on an mbarrier is bounded; on expiry the block raises a flag in scratch (see
+// infiniops_b200_scratch_status), lets copies in flight land, frees tensor memory and returns.
+#include <cuda.h>
+
+#include <algorithm>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace iob {
+namespace {
+
+constexpr int kTileN = 128;              // weight columns per tile (= UMMA M)
+constexpr int kBlockK = 64;              // k per pipeline stage
+constexpr int kAStages = 4;              // tensor-memory stages of dequantised weights
+constexpr int kAStageCols = kBlockK / 2; // 32-bit columns per stage (two 16-bit values each)
+constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr int kHeaderBytes = 256;        // scratch: status word first, then tile counters
+
+constexpr int kErrFull = 1, kErrEmpty = 2, kErrAFull = 3, kErrAEmpty = 4, kErrDFull = 5, kErrDEmpty = 6;
+
+__host__ __device__ constexpr int StagesFor(int tok) {
+  return tok <= 16 ? 12 : tok <= 32 ? 10 : tok <= 64 ? 8 : tok <= 128 ? 6 : 5;
+}
+__host__ __device__ constexpr int AccStagesFor(int tok) { return tok <= 128 ? 2 : 1; }
+__host__ __device__ constexpr int StageBytes(int tok) { return tok * 128 + 4096 + 1024; }
+__host__ __device__ constexpr int TmemColsFor(int tok) {
+  const int need = AccStagesFor(tok) * tok + kAStages * kAStageCols;
+  return need <= 32 ? 32 : need <= 64 ? 64 : need <= 128 ? 128 : need <= 256 ? 256 : 512;
+}
+
+struct GemmParams {
+  const uint32_t* wq;      // [E][K/16][2N]
+  const void* scales;      // [E][G][N]
+  const uint32_t* zeros;   // [E][G][N/8] or null
+  const void* bias;        // [E][N] or null
+  void* out;               // [rows][N]
+  float* partial;          // [2 * grid][tok][128]
+  int* counters;           // [tiles]
+  int* status;
+  int m, n, k, groups, group_size;
+  // routed form only
+  const int32_t* sorted_ids;
+  const int32_t* expert_ids;
+  const int32_t* num_post_pad;
+  const float* topk_weights;
+  int top_k, block_size, mul_weights, out_rows;
+};
+
+// ---- PTX wrappers ------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t SmemAddr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void MbarInit(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void MbarArrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void MbarExpectTx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool MbarTryWait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false when the block is giving up (this wait expired, or another did).
+__device__ __forceinline__ bool MbarWait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                         int code) {
+  for (uint32_t spin = 0;; ++spin) {
+    if (MbarTryWait(bar, parity)) return true;
+    if ((spin & 0xff) == 0xff) {
+      if (*abort_flag) return false;
+      if (spin > kSpinLimit) {
+        *abort_flag = 1;
+        atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void BulkLoad(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void TmaLoad2D(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+          dst),
+      "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void TcFenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void TcFenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void TcCommit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]; A is 128 x 16 (16-bit, two per column), B is N x 16 K-major.
+__device__ __forceinline__ void MmaTs(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                      uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}" ::"r"(
+          d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void TmemStore16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.16x128b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(
+          taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+      "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void TmemLoad16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void TmemWaitLd() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void TmemWaitSt() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void NamedBarrierUnused(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ uint32_t Lop3AndOr(uint32_t a, uint32_t and_mask, uint32_t or_mask) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(and_mask), "r"(or_mask));
+  return r;
+}
+
+// ---- 16-bit type traits ------------------------------------------------------------------------
+template <typename T>
+struct Half2Of;
+template <>
+struct Half2Of<__half> {
+  using type = __half2;
+  static constexpr uint32_t kMagic = 0x64006400u;  // 1024.0 in both halves
+  static constexpr float kBase = 1024.0f;
+  static constexpr uint32_t kFormat = 0;  // instruction-descriptor code of the operand type
+};
+template <>
+struct Half2Of<__nv_bfloat16> {
+  using type = __nv_bfloat162;
+  static constexpr uint32_t kMagic = 0x43004300u;  // 128.0 in both halves
+  static constexpr float kBase = 128.0f;
+  static constexpr uint32_t kFormat = 1;
+};
+template <typename T>
+__device__ __forceinline__ uint32_t Splat(float v) {
+  using H2 = typename Half2Of<T>::type;
+  const T h = FromFloat<T>(v);
+  H2 p;
+  p.x = h;
+  p.y = h;
+  return *reinterpret_cast<uint32_t*>(&p);
+}
+template <typename T>
+__device__ __forceinline__ uint32_t SplatRaw(T h) {
+  using H2 = typename Half2Of<T>::type;
+  H2 p;
+  p.x = h;
+  p.y = h;
+  return *reinterpret_cast<uint32_t*>(&p);
+}
+// ((magic | nibbles) - zero_magic) * scale, both halves; exact until the final multiply.
+template <typename T>
+__device__ __forceinline__ uint32_t Dequant2(uint32_t shifted_word, uint32_t zero_magic, uint32_t scale2) {
+  using H2 = typename Half2Of<T>::type;
+  const uint32_t biased = Lop3AndOr(shifted_word, 0x000F000Fu, Half2Of<T>::kMagic);
+  const H2 centred = __hsub2(*reinterpret_cast<const H2*>(&biased), *reinterpret_cast<const H2*>(&zero_magic));
+  const H2 scaled = __hmul2(centred, *reinterpret_cast<const H2*>(&scale2));
+  return *reinterpret_cast<const uint32_t*>(&scaled);
+}
+
+// ---- work walker ------------------------------------------------------------------------------
+struct Segment {
+  int tile, n_tile, m_tile, k_begin, k_end;
+};
+struct Walker {
+  long long u, u_end;
+  int k_stages, m_tiles;
+  __device__ __forceinline__ bool Next(Segment& s) {
+    if (u >= u_end) return false;
+    s.tile = static_cast<int>(u / k_stages);
+    s.k_begin = static_cast<int>(u - static_cast<long long>(s.tile) * k_stages);
+    const long long left = u_end - u;
+    s.k_end = left < k_stages - s.k_begin ? s.k_begin + static_cast<int>(left) : k_stages;
+    s.n_tile = s.tile / m_tiles;
+    s.m_tile = s.tile - s.n_tile * m_tiles;
+    u += s.k_end - s.k_begin;
+    return true;
+  }
+};
+__device__ __forceinline__ long long RangeStart(long long block, long long total, long long grid) {
+  return block * total / grid;
+}
+// Block whose range holds unit u (largest b with RangeStart(b) <= u).
+__device__ __forceinline__ int OwnerOf(long long u, long long total, long long grid) {
+  return static_cast<int>(((u + 1) * grid - 1) / total);
+}
+
+template <int kTok, int kSets>
+struct Shared {
+  static constexpr int kStages = StagesFor(kTok);
+  static constexpr int kAcc = AccStagesFor(kTok);
+  uint64_t full[kStages], empty[kStages];
+  uint64_t a_full[kAStages], a_empty[kAStages];
+  uint64_t d_full[kAcc], d_empty[kAcc];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <typename T, int kTok, bool kZeros, bool kMoe, int kSets>
+__global__ void __launch_bounds__((6 + 4 * kSets) * 32, 1)
+W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const GemmParams p) {
+  using Sh = Shared<kTok, kSets>;
+  constexpr int kStages = Sh::kStages;
+  constexpr int kAcc = Sh::kAcc;
+  constexpr int kStage = StageBytes(kTok);
+  constexpr int kActBytes = kTok * 128;
+  constexpr int kTmemCols = TmemColsFor(kTok);
+  constexpr int kDequantWarps = 4 * kSets;
+  constexpr uint32_t kIdesc = (1u << 4) | (Half2Of<T>::kFormat << 7) | (Half2Of<T>::kFormat << 10) |
+                              (static_cast<uint32_t>(kTok >> 3) << 17) | (static_cast<uint32_t>(kTileN >> 4) << 24);
+
+  extern __shared__ unsigned char smem_dyn[];
+  __shared__ Sh sh;
+  unsigned char* stages =
+      reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+  const uint32_t stages_addr = SmemAddr(stages);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int* abort_flag = &sh.abort_flag;
+
+  const int k_stages = p.k / kBlockK;
+  const int n_tiles = (p.n + kTileN - 1) / kTileN;
+  int m_tiles;
+  if constexpr (kMoe) {
+    m_tiles = *p.num_post_pad / p.block_size;
+  } else {
+    m_tiles = (p.m + kTok - 1) / kTok;
+  }
+  const long long total_units = static_cast<long long>(n_tiles) * m_tiles * k_stages;
+  const long long grid = gridDim.x;
+  const long long u_begin = RangeStart(blockIdx.x, total_units, grid);
+  const long long u_end = RangeStart(blockIdx.x + 1, total_units, grid);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      MbarInit(SmemAddr(&sh.full[i]), 1);
+      MbarInit(SmemAddr(&sh.empty[i]), 5);
+    }
+    for (int i = 0; i < kAStages; ++i) {
+      MbarInit(SmemAddr(&sh.a_full[i]), 4);
+      MbarInit(SmemAddr(&sh.a_empty[i]), 1);
+    }
+    for (int i = 0; i < kAcc; ++i) {
+      MbarInit(SmemAddr(&sh.d_full[i]), 1);
+      MbarInit(SmemAddr(&sh.d_empty[i]), 4);
+    }
+    sh.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(SmemAddr(&sh.tmem_base)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  TcFenceBefore();
+  __syncthreads();
+  TcFenceAfter();
+  const uint32_t tmem_base = sh.tmem_base;
+  const uint32_t tmem_d = tmem_base;                  // accumulators: columns [0, kAcc * kTok)
+  const uint32_t tmem_a = tmem_base + kAcc * kTok;    // weights: kAStages x 32 columns
+
+  if (warp == 0) {
+    // ================= producer =================
+    if (lane == 0) {
+      Walker walk{u_begin, u_end, k_stages, m_tiles};
+      Segment seg;
+      uint32_t it = 0;
+      bool alive = true;
+      while (alive && walk.Next(seg)) {
+        int expert = 0;
+        if constexpr (kMoe) {
+          expert = p.expert_ids[seg.m_tile];
+          if (expert < 0) continue;
+        }
+        const int n0 = seg.n_tile * kTileN;
+        const int n_valid = min(kTileN, p.n - n0);
+        const int row0 = kMoe ? seg.m_tile * p.block_size : seg.m_tile * kTok;
+        const uint32_t* wq = p.wq + static_cast<size_t>(expert) * (p.k / 16) * (2 * static_cast<size_t>(p.n));
+        const T* scales = static_cast<const T*>(p.scales) + static_cast<size_t>(expert) * p.groups * p.n;
+        const uint32_t* zeros = kZeros ? p.zeros + static_cast<size_t>(expert) * p.groups * (p.n / 8) : nullptr;
+        const uint32_t tx = kActBytes + 4 * (n_valid * 8) + n_valid * 2 + (kZeros ? n_valid / 2 : 0);
+        for (int ks = seg.k_begin; ks < seg.k_end; ++ks, ++it) {
+          const int s = it % kStages;
+          const uint32_t full = SmemAddr(&sh.full[s]);
+          if (!MbarWait(SmemAddr(&sh.empty[s]), ((it / kStages) & 1) ^ 1, abort_flag, p.status, kErrEmpty)) {
+            alive = false;
+            break;
+          }
+          MbarExpectTx(full, tx);
+          const uint32_t base = stages_addr + s * kStage;
+          TmaLoad2D(base, &a_map, ks * kBlockK, row0, full);
+#pragma unroll
+          for (int kt = 0; kt < 4; ++kt) {
+            BulkLoad(base + kActBytes + kt * 1024, wq + static_cast<size_t>(ks * 4 + kt) * (2 * p.n) + 2 * n0,
+                     n_valid * 8, full);
+          }
+          const int g = ks * kBlockK / p.group_size;
+          BulkLoad(base + kActBytes + 4096, scales + static_cast<size_t>(g) * p.n + n0, n_valid * 2, full);
+          if constexpr (kZeros) {
+            BulkLoad(base + kActBytes + 4096 + 256, zeros + static_cast<size_t>(g) * (p.n / 8) + n0 / 8, n_valid / 2,
+                     full);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ================= MMA issuer =================
+    if (lane == 0) {
+      Walker walk{u_begin, u_end, k_stages, m_tiles};
+      Segment seg;
+      uint32_t it = 0, seg_idx = 0;
+      bool alive = true;
+      while (alive && walk.Next(seg)) {
+        if constexpr (kMoe) {
+          if (p.expert_ids[seg.m_tile] < 0) continue;
+        }
+        const int acc = seg_idx % kAcc;
+        if (!MbarWait(SmemAddr(&sh.d_empty[acc]), ((seg_idx / kAcc) & 1) ^ 1, abort_flag, p.status, kErrDEmpty)) break;
+        TcFenceAfter();
+        const uint32_t d_addr = tmem_d + acc * kTok;
+        for (int ks = seg.k_begin; ks < seg.k_end; ++ks, ++it) {
+          const int s = it % kStages, a = it % kAStages;
+          if (!MbarWait(SmemAddr(&sh.full[s]), (it / kStages) & 1, abort_flag, p.status, kErrFull) ||
+              !MbarWait(SmemAddr(&sh.a_full[a]), (it / kAStages) & 1, abort_flag, p.status, kErrAFull)) {
+            alive = false;
+            break;
+          }
+          TcFenceAfter();
+          const uint32_t act = stages_addr + s * kStage;
+          const uint64_t desc0 = static_cast<uint64_t>((act >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) |
+                                 (1ull << 46) | (2ull << 61);
+#pragma unroll
+          for (int j = 0; j < kBlockK / 16; ++j) {
+            MmaTs(d_addr, tmem_a + a * kAStageCols + 8 * j, desc0 + 2 * j, kIdesc,
+                  (ks > seg.k_begin || j > 0) ? 1u : 0u);
+          }
+          TcCommit(SmemAddr(&sh.empty[s]));
+          TcCommit(SmemAddr(&sh.a_empty[a]));
+        }
+        if (!alive) break;
+        TcCommit(SmemAddr(&sh.d_full[acc]));
+        ++seg_idx;
+      }
+    }
+  } else if (warp < 2 + kDequantWarps) {
+    // ================= dequantisers =================
+    const int set = (warp - 2) / 4;
+    const int q = warp & 3;  // tensor-memory lane quarter this warp may touch
+    Walker walk{u_begin, u_end, k_stages, m_tiles};
+    Segment seg;
+    uint32_t it = 0;
+    bool alive = true;
+    // symmetric types: implicit zero point 8
+    const uint32_t zero_sym = Splat<T>(Half2Of<T>::kBase + 8.0f);
+    while (alive && walk.Next(seg)) {
+      if constexpr (kMoe) {
+        if (p.expert_ids[seg.m_tile] < 0) continue;
+      }
+      for (int ks = seg.k_begin; ks < seg.k_end; ++ks, ++it) {
+        if (static_cast<int>(it % kSets) != set) continue;
+        const int s = it % kStages, a = it % kAStages;
+        if (!MbarWait(SmemAddr(&sh.full[s]), (it / kStages) & 1, abort_flag, p.status, kErrFull) ||
+            !MbarWait(SmemAddr(&sh.a_empty[a]), ((it / kAStages) & 1) ^ 1, abort_flag, p.status, kErrAEmpty)) {
+          alive = false;
+          break;
+        }
+        TcFenceAfter();
+        const unsigned char* base = stages + s * kStage + kActBytes;
+        const uint32_t* words = reinterpret_cast<const uint32_t*>(base);
+        const T* scale_row = reinterpret_cast<const T*>(base + 4096);
+        const uint32_t* zero_row = reinterpret_cast<const uint32_t*>(base + 4096 + 256);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          // sub-block sb = 2q + h covers tile columns [16 sb, 16 sb + 16); this thread owns
+          // columns c0 = 16 sb + lane / 4 and c0 + 8.
+          const int sb = 2 * q + h;
+          const int c0 = 16 * sb + (lane >> 2);
+          const uint32_t s_lo = SplatRaw<T>(scale_row[c0]);
+          const uint32_t s_hi = SplatRaw<T>(scale_row[c0 + 8]);
+          uint32_t z_lo = zero_sym, z_hi = zero_sym;
+          if constexpr (kZeros) {
+            const uint32_t shift = 4 * (lane >> 2);
+            z_lo = Splat<T>(Half2Of<T>::kBase + static_cast<float>((zero_row[2 * sb] >> shift) & 0xF));
+            z_hi = Splat<T>(Half2Of<T>::kBase + static_cast<float>((zero_row[2 * sb + 1] >> shift) & 0xF));
+          }
+          uint32_t regs[16];
+#pragma unroll
+          for (int kt = 0; kt < 4; ++kt) {
+            // word of chunk (kt, sb / 4), lane, sub-tile sb % 4
+            const uint32_t w = words[kt * 256 + (sb >> 2) * 128 + lane * 4 + (sb & 3)];
+            regs[4 * kt + 0] = Dequant2<T>(w, z_lo, s_lo);        // column c0,     k pair lane % 4
+            regs[4 * kt + 1] = Dequant2<T>(w >> 8, z_hi, s_hi);   // column c0 + 8, k pair lane % 4
+            regs[4 * kt + 2] = Dequant2<T>(w >> 4, z_lo, s_lo);   // column c0,     k pair lane % 4 + 4
+            regs[4 * kt + 3] = Dequant2<T>(w >> 12, z_hi, s_hi);  // column c0 + 8, k pair lane % 4 + 4
+          }
+          TmemStore16(tmem_a + (static_cast<uint32_t>(32 * q + 16 * h) << 16) + a * kAStageCols, regs);
+        }
+        TmemWaitSt();
+        TcFenceBefore();
+        __syncwarp();
+        if (lane == 0) {
+          MbarArrive(SmemAddr(&sh.a_full[a]));
+          MbarArrive(SmemAddr(&sh.empty[s]));
+        }
+      }
+    }
+  } else {
+    // ================= epilogue =================
+    const int q = warp & 3;
+    Walker walk{u_begin, u_end, k_stages, m_tiles};
+    Segment seg;
+    uint32_t seg_idx = 0;
+    T* out = static_cast<T*>(p.out);
+    while (walk.Next(seg)) {
+      int expert = 0;
+      if constexpr (kMoe) {
+        expert = p.expert_ids[seg.m_tile];
+        if (expert < 0) continue;
+      }
+      const int acc = seg_idx % kAcc;
+      if (!MbarWait(SmemAddr(&sh.d_full[acc]), (seg_idx / kAcc) & 1, abort_flag, p.status, kErrDFull)) break;
+      TcFenceAfter();
+      const int n_local = 32 * q + lane;
+      const int n = seg.n_tile * kTileN + n_local;
+      const bool n_ok = n < p.n;
+      const int row0 = kMoe ? seg.m_tile * p.block_size : seg.m_tile * kTok;
+      const int m_valid = kMoe ? p.block_size : min(kTok, p.m - row0);
+      const bool whole = seg.k_begin == 0 && seg.k_end == k_stages;
+      const uint32_t d_addr = tmem_d + acc * kTok + (static_cast<uint32_t>(32 * q) << 16);
+      float bias_v = 0.0f;
+      if (p.bias != nullptr && n_ok) bias_v = ToFloat<T>(static_cast<const T*>(p.bias)[static_cast<size_t>(expert) * p.n + n]);
+
+      // Writes one finished value; `j` is the token column of the tile.
+      auto emit = [&](int j, float v) {
+        v += bias_v;
+        if constexpr (kMoe) {
+          const int id = p.sorted_ids[row0 + j];
+          if (id < p.out_rows) {
+            if (p.mul_weights) v *= p.topk_weights[id];
+            out[static_cast<size_t>(id) * p.n + n] = FromFloat<T>(v);
+          }
+        } else {
+          out[static_cast<size_t>(row0 + j) * p.n + n] = FromFloat<T>(v);
+        }
+      };
+
+      const bool first_of_block = walk.u - (seg.k_end - seg.k_begin) == u_begin;
+      float* my_partial = p.partial + (static_cast<size_t>(2 * blockIdx.x + (first_of_block ? 0 : 1)) * kTok) * kTileN;
+#pragma unroll 1
+      for (int c = 0; c < kTok; c += 16) {
+        if (c >= m_valid) break;
+        uint32_t r[16];
+        TmemLoad16(d_addr + c, r);
+        TmemWaitLd();
+        if (whole) {
+          if (n_ok) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              if (c + j < m_valid) emit(c + j, __uint_as_float(r[j]));
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) my_partial[static_cast<size_t>(c + j) * kTileN + n_local] = __uint_as_float(r[j]);
+        }
+      }
+      // The accumulator is in registers / memory now: hand it back to the MMA warp.
+      TcFenceBefore();
+      __syncwarp();
+      if (lane == 0) MbarArrive(SmemAddr(&sh.d_empty[acc]));
+      ++seg_idx;
+
+      if (!whole) {
+        // Each lane quarter of the tile has its own arrival counter, so the four epilogue
+        // warps never have to meet at a barrier: the warp that arrives last for its quarter
+        // (over all blocks sharing the tile) sums that quarter.
+        const long long tile_u0 = static_cast<long long>(seg.tile) * k_stages;
+        const int first_block = OwnerOf(tile_u0, total_units, grid);
+        const int last_block = OwnerOf(tile_u0 + k_stages - 1, total_units, grid);
+        int* counter = p.counters + 4 * static_cast<size_t>(seg.tile) + q;
+        __threadfence();
+        __syncwarp();
+        int ticket = 0;
+        if (lane == 0) ticket = atomicAdd(counter, 1);
+        ticket = __shfl_sync(0xffffffffu, ticket, 0);
+        if (ticket == last_block - first_block) {
+          __threadfence();
+          if (n_ok) {
+            for (int j = 0; j < m_valid; ++j) {
+              float v = 0.0f;
+              for (int b = first_block; b <= last_block; ++b) {
+                // a block's first segment uses slot 2b, any later one slot 2b + 1
+                const bool is_first = RangeStart(b, total_units, grid) >= tile_u0;
+                const float* src =
+                    p.partial + (static_cast<size_t>(2 * b + (is_first ? 0 : 1)) * kTok + j) * kTileN + n_local;
+                v += __ldcg(src);
+              }
+              emit(j, v);
+            }
+          }
+          if (lane == 0) *counter = 0;
+        }
+      }
+    }
+  }
+
+  // ---- teardown -----------------------------------------------------------------------------
+  if (*abort_flag) {
+    // give copies in flight time to land before shared memory is released
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+  }
+  TcFenceBefore();
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// Copies the routed rows of `a` into scratch in sorted order so a TMA box of consecutive rows
+// is one routing block.
+template <typename T>
+__global__ void GatherRowsKernel(const T* __restrict__ a, T* __restrict__ gathered,
+                                 const int32_t* __restrict__ sorted_ids, const int32_t* __restrict__ num_post_pad,
+                                 int k, int top_k, int out_rows) {
+  const int rows = *num_post_pad;
+  const int vec_per_row = k / 8;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const int id = sorted_ids[row];
+    uint4* dst = reinterpret_cast<uint4*>(gathered + static_cast<size_t>(row) * k);
+    if (id < out_rows) {
+      const uint4* src = reinterpret_cast<const uint4*>(a + static_cast<size_t>(id / top_k) * k);
+      for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x) dst[i] = src[i];
+    } else {
+      for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x) dst[i] = make_uint4(0, 0, 0, 0);
+    }
+  }
+}
+
+// ---- host side ----------------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn GetEncode() {
+  static EncodeFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) != cudaSuccess ||
+        result != cudaDriverEntryPointSuccess) {
+      return static_cast<EncodeFn>(nullptr);
+    }
+    return reinterpret_cast<EncodeFn>(ptr);
+  }();
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr;
+  int64_t rows, cols;
+  int box_rows, dtype;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows && dtype == o.dtype;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr);
+    h ^= static_cast<size_t>(k.rows) * 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
+    h ^= static_cast<size_t>(k.cols) * 0xC2B2AE3D27D4EB4Full + (h << 6) + (h >> 2);
+    h ^= static_cast<size_t>(k.box_rows * 4 + k.dtype) + (h << 6) + (h >> 2);
+    return h;
+  }
+};
+
+// Tensor map of a row-major [rows, cols] 16-bit matrix with a [box_rows, 64] box, 128-byte swizzle.
+int ActivationMap(const void* ptr, int64_t rows, int64_t cols, int box_rows, int dtype, CUtensorMap* out) {
+  static thread_local std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  const MapKey key{ptr, rows, cols, box_rows, dtype};
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return IOB_OK;
+  }
+  EncodeFn encode = GetEncode();
+  if (encode == nullptr) return Fail(IOB_CUDA_ERROR, "W4A16 GEMM: cuTensorMapEncodeTiled is not available");
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+  const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult rc = encode(out, dtype == IOB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                             2, const_cast<void*>(ptr), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) return Fail(IOB_CUDA_ERROR, "W4A16 GEMM: tensor map encode failed (%d)", static_cast<int>(rc));
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *out);
+  return IOB_OK;
+}
+
+int TokenTile(int64_t m) { return m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : m <= 128 ? 128 : 256; }
+
+size_t Align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+
+struct ScratchPlan {
+  size_t counters_off, partial_off, gathered_off, total;
+};
+ScratchPlan PlanScratch(int64_t tiles, int tok, int64_t gathered_bytes) {
+  ScratchPlan plan;
+  plan.counters_off = kHeaderBytes;
+  plan.partial_off = Align256(plan.counters_off + static_cast<size_t>(4) * tiles * sizeof(int));
+  plan.gathered_off = Align256(plan.partial_off + static_cast<size_t>(2) * NumSms() * tok * kTileN * sizeof(float));
+  plan.total = Align256(plan.gathered_off + gathered_bytes);
+  return plan;
+}
+
+template <typename T, int kTok, bool kZeros, bool kMoe>
+int LaunchKernel(const CUtensorMap& map, const GemmParams& p, int grid, cudaStream_t stream) {
+  constexpr int kSets = kTok <= 64 ? 2 : 1;
+  auto kernel = W4A16GemmKernel<T, kTok, kZeros, kMoe, kSets>;
+  constexpr int smem = StagesFor(kTok) * StageBytes(kTok) + 1024;
+  static thread_local bool configured[64] = {};
+  int device = 0;
+  cudaGetDevice(&device);
+  if (device < 0 || device >= 64 || !configured[device]) {
+    const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (err != cudaSuccess) return Fail(IOB_CUDA_ERROR, "W4A16 GEMM: %s", cudaGetErrorString(err));
+    if (device >= 0 && device < 64) configured[device] = true;
+  }
+  kernel<<<grid, (6 + 4 * kSets) * 32, smem, stream>>>(map, p);
+  return CheckLaunch("W4A16 GEMM launch");
+}
+
+template <typename T, bool kZeros, bool kMoe>
+int DispatchTok(int tok, const CUtensorMap& map, const GemmParams& p, int grid, cudaStream_t stream) {
+  switch (tok) {
+    case 16: return LaunchKernel<T, 16, kZeros, kMoe>(map, p, grid, stream);
+    case 32: return LaunchKernel<T, 32, kZeros, kMoe>(map, p, grid, stream);
+    case 64: return LaunchKernel<T, 64, kZeros, kMoe>(map, p, grid, stream);
+    default: break;
+  }
+  if constexpr (!kMoe) {
+    if (tok == 128) return LaunchKernel<T, 128, kZeros, kMoe>(map, p, grid, stream);
+    if (tok == 256) return LaunchKernel<T, 256, kZeros, kMoe>(map, p, grid, stream);
+  }
+  return Fail(IOB_UNSUPPORTED, "W4A16 GEMM: no kernel for a token tile of %d", tok);
+}
+
+template <bool kMoe>
+int Dispatch(int a_dtype, bool zeros, int tok, const CUtensorMap& map, const GemmParams& p, int grid,
+             cudaStream_t stream) {
+  if (a_dtype == IOB_BF16) {
+    return zeros ? DispatchTok<__nv_bfloat16, true, kMoe>(tok, map, p, grid, stream)
+                 : DispatchTok<__nv_bfloat16, false, kMoe>(tok, map, p, grid, stream);
+  }
+  return zeros ? DispatchTok<__half, true, kMoe>(tok, map, p, grid, stream)
+               : DispatchTok<__half, false, kMoe>(tok, map, p, grid, stream);
+}
+
+int CheckProblem(const char* op, const void* a, int a_dtype, const void* wq, const void* scales, const void* zeros,
+                 int64_t b_type_id, int64_t m, int64_t n, int64_t k, int64_t groups, const void* out) {
+  IOB_REQUIRE(a && wq && scales && out, "%s: null tensor pointer", op);
+  IOB_REQUIRE(a_dtype == IOB_F16 || a_dtype == IOB_BF16, "%s: requires float16 or bfloat16 `a`", op);
+  IOB_REQUIRE(m > 0 && n > 0 && k > 0 && k % 16 == 0 && n % 64 == 0, "%s: received unsupported dimensions", op);
+  IOB_REQUIRE(m <= INT32_MAX && n <= INT32_MAX && k <= INT32_MAX, "%s: dimensions exceed int32", op);
+  if (b_type_id != IOB_QTYPE_UINT4B8 && b_type_id != IOB_QTYPE_UINT4) {
+    return Fail(IOB_UNSUPPORTED, "%s: only the 4-bit weight types uint4b8 and uint4 are implemented", op);
+  }
+  IOB_REQUIRE((zeros != nullptr) == (b_type_id == IOB_QTYPE_UINT4),
+              "%s: zero points are required for uint4 and not accepted for uint4b8", op);
+  IOB_REQUIRE(groups > 0 && k % groups == 0, "%s: `size_k` must be a multiple of the number of scale groups", op);
+  if (k % kBlockK != 0 || (k / groups) % kBlockK != 0) {
+    return Fail(IOB_UNSUPPORTED, "%s: needs `size_k` and the group size to be multiples of 64", op);
+  }
+  IOB_REQUIRE(reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(wq) % 16 == 0 &&
+                  reinterpret_cast<uintptr_t>(scales) % 16 == 0 && reinterpret_cast<uintptr_t>(zeros) % 16 == 0,
+              "%s: tensors must be 16-byte aligned", op);
+  return IOB_OK;
+}
+
+}  // namespace
+}  // namespace iob
+
+extern "C" int infiniops_b200_scratch_status(const void* scratch, void* stream) {
+  int code = 0;
+  auto s = static_cast<cudaStream_t>(stream);
+  if (cudaMemcpyAsync(&code, scratch, sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+      cudaStreamSynchronize(s) != cudaSuccess) {
+    return -1;
+  }
+  return code;
+}
+
+extern "C" size_t infiniops_b200_marlin_gemm_scratch_bytes(int64_t size_m, int64_t size_n, int64_t size_k) {
+  using namespace iob;
+  (void)size_k;
+  const int tok = TokenTile(size_m);
+  const int64_t tiles = ((size_n + kTileN - 1) / kTileN) * ((size_m + tok - 1) / tok);
+  return PlanScratch(tiles, tok, 0).total;
+}
+
+extern "C" int infiniops_b200_marlin_gemm(const void* a, int a_dtype, const int32_t* b_q_weight, const void* b_bias,
+                                          const void* b_scales, const int32_t* b_zeros, int64_t b_type_id,
+                                          int64_t size_m, int64_t size_n, int64_t size_k, int64_t num_groups,
+                                          void* out, void* scratch, size_t scratch_bytes, void* stream) {
+  using namespace iob;
+  if (const int rc = CheckProblem("marlin_gemm", a, a_dtype, b_q_weight, b_scales, b_zeros, b_type_id, size_m, size_n,
+                                  size_k, num_groups, out)) {
+    return rc;
+  }
+  const int tok = TokenTile(size_m);
+  const int64_t n_tiles = (size_n + kTileN - 1) / kTileN, m_tiles = (size_m + tok - 1) / tok;
+  const ScratchPlan plan = PlanScratch(n_tiles * m_tiles, tok, 0);
+  if (scratch == nullptr || scratch_bytes < plan.total) {
+    return Fail(IOB_SCRATCH_TOO_SMALL, "marlin_gemm: needs %zu bytes of scratch, got %zu", plan.total, scratch_bytes);
+  }
+  CUtensorMap map;
+  if (const int rc = ActivationMap(a, size_m, size_k, tok, a_dtype, &map)) return rc;
+  auto* base = static_cast<unsigned char*>(scratch);
+  GemmParams p{};
+  p.wq = reinterpret_cast<const uint32_t*>(b_q_weight);
+  p.scales = b_scales;
+  p.zeros = reinterpret_cast<const uint32_t*>(b_zeros);
+  p.bias = b_bias;
+  p.out = out;
+  p.partial = reinterpret_cast<float*>(base + plan.partial_off);
+  p.counters = reinterpret_cast<int*>(base + plan.counters_off);
+  p.status = reinterpret_cast<int*>(base);
+  p.m = static_cast<int>(size_m);
+  p.n = static_cast<int>(size_n);
+  p.k = static_cast<int>(size_k);
+  p.groups = static_cast<int>(num_groups);
+  p.group_size = static_cast<int>(size_k / num_groups);
+  const int64_t units = n_tiles * m_tiles * (size_k / kBlockK);
+  const int grid = static_cast<int>(units < NumSms() ? units : NumSms());
+  return Dispatch<false>(a_dtype, b_zeros != nullptr, tok, map, p, grid, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" size_t infiniops_b200_moe_wna16_marlin_gemm_scratch_bytes(int64_t size_m, int64_t top_k, int64_t size_n,
+                                                                     int64_t size_k, int64_t num_experts,
+                                                                     int64_t moe_block_size) {
+  using namespace iob;
+  int64_t sorted = size_m * top_k + num_experts * (moe_block_size - 1);
+  if (size_m * top_k < num_experts) sorted = std::min(sorted, size_m * top_k * moe_block_size);
+  const int tok = TokenTile(moe_block_size);
+  const int64_t blocks = (sorted + moe_block_size - 1) / moe_block_size;
+  const int64_t tiles = ((size_n + kTileN - 1) / kTileN) * blocks;
+  // one extra box of rows so the last block's TMA box stays inside the buffer's tensor map
+  return PlanScratch(tiles, tok, (sorted + tok) * size_k * 2).total;
+}
+
+extern "C" int infiniops_b200_moe_wna16_marlin_gemm(
+    const void* a, int a_dtype, const int32_t* b_q_weight, const void* b_bias, const void* b_scales,
+    const int32_t* b_zeros, const int32_t* sorted_token_ids, const int32_t* expert_ids,
+    const int32_t* num_tokens_past_padded, const float* topk_weights, int64_t moe_block_size, int64_t top_k,
+    int mul_topk_weights, int64_t b_type_id, int64_t size_m, int64_t size_n, int64_t size_k, int64_t num_groups,
+    int64_t num_experts, int64_t sorted_size, void* out, void* scratch, size_t scratch_bytes, void* stream) {
+  using namespace iob;
+  const char* op = "moe_wna16_marlin_gemm";
+  if (const int rc = CheckProblem(op, a, a_dtype, b_q_weight, b_scales, b_zeros, b_type_id, size_m, size_n, size_k,
+                                  num_groups, out)) {
+    return rc;
+  }
+  IOB_REQUIRE(sorted_token_ids && expert_ids && num_tokens_past_padded, "%s: received invalid routing metadata", op);
+  IOB_REQUIRE(top_k > 0 && num_experts > 0 && size_m <= INT32_MAX / top_k, "%s: output dimensions overflow", op);
+  IOB_REQUIRE(moe_block_size == 8 || (moe_block_size >= 16 && moe_block_size <= 64 && moe_block_size % 16 == 0),
+              "%s: received an unsupported `moe_block_size`", op);
+  IOB_REQUIRE(!mul_topk_weights || topk_weights != nullptr, "%s: received invalid top-k weights", op);
+  if (moe_block_size == 8) return Fail(IOB_UNSUPPORTED, "%s: `moe_block_size` 8 is not implemented", op);
+  const int tok = TokenTile(moe_block_size);
+  // rows the routing can occupy at most (the bound the sort operator guarantees)
+  int64_t sorted_cap = size_m * top_k + num_experts * (moe_block_size - 1);
+  if (size_m * top_k < num_experts) sorted_cap = std::min(sorted_cap, size_m * top_k * moe_block_size);
+  IOB_REQUIRE(sorted_size >= sorted_cap, "%s: `sorted_token_ids` is smaller than the padded routing can be", op);
+  const int64_t blocks = (sorted_cap + moe_block_size - 1) / moe_block_size;
+  const int64_t n_tiles = (size_n + kTileN - 1) / kTileN;
+  const ScratchPlan plan = PlanScratch(n_tiles * blocks, tok, (sorted_cap + tok) * size_k * 2);
+  if (scratch == nullptr || scratch_bytes < plan.total) {
+    return Fail(IOB_SCRATCH_TOO_SMALL, "%s: needs %zu bytes of scratch, got %zu", op, plan.total, scratch_bytes);
+  }
+  auto s = static_cast<cudaStream_t>(stream);
+  auto* base = static_cast<unsigned char*>(scratch);
+  void* gathered = base + plan.gathered_off;
+  const int out_rows = static_cast<int>(size_m * top_k);
+  const int gather_grid = static_cast<int>(std::min<int64_t>(sorted_cap, 4 * NumSms()));
+  if (a_dtype == IOB_BF16) {
+    GatherRowsKernel<__nv_bfloat16><<<gather_grid, 256, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(a), static_cast<__nv_bfloat16*>(gathered), sorted_token_ids,
+        num_tokens_past_padded, static_cast<int>(size_k), static_cast<int>(top_k), out_rows);
+  } else {
+    GatherRowsKernel<__half><<<gather_grid, 256, 0, s>>>(static_cast<const __half*>(a), static_cast<__half*>(gathered),
+                                                        sorted_token_ids, num_tokens_past_padded,
+                                                        static_cast<int>(size_k), static_cast<int>(top_k), out_rows);
+  }
+  if (const int rc = CheckLaunch("moe_wna16_marlin_gemm gather launch")) return rc;
+  CUtensorMap map;
+  if (const int rc = ActivationMap(gathered, sorted_cap + tok, size_k, tok, a_dtype, &map)) return rc;
+  GemmParams p{};
+  p.wq = reinterpret_cast<const uint32_t*>(b_q_weight);
+  p.scales = b_scales;
+  p.zeros = reinterpret_cast<const uint32_t*>(b_zeros);
+  p.bias = b_bias;
+  p.out = out;
+  p.partial = reinterpret_cast<float*>(base + plan.partial_off);
+  p.counters = reinterpret_cast<int*>(base + plan.counters_off);
+  p.status = reinterpret_cast<int*>(base);
+  p.m = static_cast<int>(size_m);
+  p.n = static_cast<int>(size_n);
+  p.k = static_cast<int>(size_k);
+  p.groups = static_cast<int>(num_groups);
+  p.group_size = static_cast<int>(size_k / num_groups);
+  p.sorted_ids = sorted_token_ids;
+  p.expert_ids = expert_ids;
+  p.num_post_pad = num_tokens_past_padded;
+  p.topk_weights = topk_weights;
+  p.top_k = static_cast<int>(top_k);
+  p.block_size = static_cast<int>(moe_block_size);
+  p.mul_weights = mul_topk_weights;
+  p.out_rows = out_rows;
+  return Dispatch<true>(a_dtype, b_zeros != nullptr, tok, map, p, NumSms(), s);
+}
