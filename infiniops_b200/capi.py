@@ -92,7 +92,8 @@ def scratch(device, nbytes: int, tag: str = "gemm") -> torch.Tensor:
     """A zero-initialised scratch buffer per (device, purpose) that only grows (test / bench
     convenience).  The GEMM keeps counters it expects to find zeroed, so it never shares a
     buffer with the token sort."""
-    key = (torch.device(device).index, tag)
+    index = torch.device(device).index
+    key = (torch.cuda.current_device() if index is None else index, tag)
     buf = _scratch.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)

@@ -15,10 +15,11 @@
 // MMA's operand fetch).
 //
 // Pipeline per thread block (one per SM, persistent):
-//   warp 0      producer: bulk copies of packed weights / scales / zero points and one TMA
-//               tensor copy of the activation tile per 64-k stage, mbarrier completion
+//   warp 0      producer: per 128-k stage one TMA tensor copy of the packed weights, two of the
+//               activation tile, bulk copies of scales / zero points; mbarrier completion;
+//               several lanes issue for consecutive stages at once
 //   warp 1      MMA issuer (one thread) + owner of the tensor-memory allocation
-//   warps 2..   dequantisers (one or two sets of 4 warps; a warp owns a 32-lane quarter)
+//   warps 2..   dequantisers (two or three sets of 4 warps; a warp owns a 32-lane quarter)
 //   last 4      epilogue: accumulator -> registers -> bias / routing weight -> global
 //
 // Work split (stream-K): the tiles x k-stages grid is cut into equal contiguous ranges, one
@@ -40,21 +41,34 @@ namespace iob {
 namespace {
 
 constexpr int kTileN = 128;              // weight columns per tile (= UMMA M)
-constexpr int kBlockK = 64;              // k per pipeline stage
+constexpr int kBlockK = 128;             // k per pipeline stage (two 64-k activation atoms)
 constexpr int kAStages = 4;              // tensor-memory stages of dequantised weights
 constexpr int kAStageCols = kBlockK / 2; // 32-bit columns per stage (two 16-bit values each)
-constexpr uint32_t kSpinLimit = 1u << 22;
-constexpr int kHeaderBytes = 256;        // scratch: status word first, then tile counters
+// Polls before a wait gives up.  A failed try_wait returns after a hardware time-out of a few
+// microseconds, so this is a few hundred milliseconds -- far beyond any legitimate wait.
+constexpr uint32_t kSpinLimit = 1u << 16;
+constexpr int kHeaderBytes = 256;        // scratch: status word first, then arrival counters
+constexpr int kMaxGrid = 1024;           // counters are laid out for at most this many thread blocks
 
 constexpr int kErrFull = 1, kErrEmpty = 2, kErrAFull = 3, kErrAEmpty = 4, kErrDFull = 5, kErrDEmpty = 6;
 
 __host__ __device__ constexpr int StagesFor(int tok) {
-  return tok <= 16 ? 12 : tok <= 32 ? 10 : tok <= 64 ? 8 : tok <= 128 ? 6 : 5;
+  // as many as fit beside the barriers in 227 KB: decode needs ~90 KB of weights in flight per SM
+  // to cover HBM latency at full rate
+  return tok <= 16 ? 14 : tok <= 32 ? 12 : tok <= 64 ? 8 : tok <= 128 ? 5 : 3;
 }
+// Sets of four dequantiser warps; a set takes every kSets-th stage.
+__host__ __device__ constexpr int SetsFor(int tok) { return tok <= 64 ? 3 : 2; }
 __host__ __device__ constexpr int AccStagesFor(int tok) { return tok <= 128 ? 2 : 1; }
-__host__ __device__ constexpr int StageBytes(int tok) { return tok * 128 + 4096 + 1024; }
+// activations (two swizzle atoms of tok x 128 B) | packed weights 8 KB | 2 scale rows | 2 zero rows
+__host__ __device__ constexpr int StageBytes(int tok) { return tok * 256 + 8192 + 1024; }
+// MMA-issuing threads.  One thread cannot keep the tensor pipe busy when a stage is only a few
+// hundred cycles of MMA work (its barrier wait and commits are not overlapped), so small token
+// tiles use two issuers on alternating stages, each with its own accumulator; the epilogue adds
+// the two in a fixed order.
+__host__ __device__ constexpr int IssuersFor(int tok) { return tok <= 64 ? 2 : 1; }
 __host__ __device__ constexpr int TmemColsFor(int tok) {
-  const int need = AccStagesFor(tok) * tok + kAStages * kAStageCols;
+  const int need = AccStagesFor(tok) * IssuersFor(tok) * tok + kAStages * kAStageCols;
   return need <= 32 ? 32 : need <= 64 ? 64 : need <= 128 ? 128 : need <= 256 ? 256 : 512;
 }
 
@@ -65,7 +79,7 @@ struct GemmParams {
   const void* bias;        // [E][N] or null
   void* out;               // [rows][N]
   float* partial;          // [2 * grid][tok][128]
-  int* counters;           // [tiles]
+  int* counters;           // [kMaxGrid][4]: one per (first block of a split tile, lane quarter)
   int* status;
   int m, n, k, groups, group_size;
   // routed form only
@@ -99,18 +113,58 @@ __device__ __forceinline__ bool MbarTryWait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false when the block is giving up (this wait expired, or another did).
 __device__ __forceinline__ bool MbarWait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                         int code) {
+                                         int code, int detail = 0) {
   for (uint32_t spin = 0;; ++spin) {
     if (MbarTryWait(bar, parity)) return true;
     if ((spin & 0xff) == 0xff) {
       if (*abort_flag) return false;
       if (spin > kSpinLimit) {
         *abort_flag = 1;
-        atomicCAS(status, 0, code);
+        // first expiry wins: code, then who and where (block, thread, caller's detail word)
+        if (atomicCAS(status, 0, code) == 0) {
+          status[1] = static_cast<int>(blockIdx.x);
+          status[2] = static_cast<int>(threadIdx.x);
+          status[3] = detail;
+        }
         return false;
       }
     }
   }
+}
+// Warp-collective form: one lane polls, the warp learns the outcome through the shuffle (which is
+// also the warp barrier that orders the other lanes' reads after the wait).  Many threads polling
+// the same mbarrier slow every other barrier operation of the block, including TMA completions.
+// `relaxed` waits (not on the critical path) back off between polls.
+__device__ __forceinline__ bool MbarWaitWarp(unsigned mask, int leader, uint32_t bar, uint32_t parity,
+                                             volatile int* abort_flag, int* status, int code, bool relaxed = false,
+                                             int detail = 0) {
+  int ok = 1;
+  if (static_cast<int>(threadIdx.x & 31) == leader) {
+    if (relaxed) {
+      for (int quick = 0; quick < 4 && !(ok = MbarTryWait(bar, parity)); ++quick) {
+      }
+      uint32_t spin = 0;
+      while (!ok) {
+        __nanosleep(128);
+        ok = MbarTryWait(bar, parity);
+        if (!ok && ((++spin & 0xff) == 0xff)) {
+          if (*abort_flag) break;
+          if (spin > kSpinLimit) {
+            *abort_flag = 1;
+            if (atomicCAS(status, 0, code) == 0) {
+              status[1] = static_cast<int>(blockIdx.x);
+              status[2] = static_cast<int>(threadIdx.x);
+              status[3] = detail;
+            }
+            break;
+          }
+        }
+      }
+    } else {
+      ok = MbarWait(bar, parity, abort_flag, status, code, detail);
+    }
+  }
+  return __shfl_sync(mask, ok, leader) != 0;
 }
 __device__ __forceinline__ void BulkLoad(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
@@ -158,6 +212,19 @@ __device__ __forceinline__ void TmemWaitLd() { asm volatile("tcgen05.wait::ld.sy
 __device__ __forceinline__ void TmemWaitSt() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void NamedBarrierUnused(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ void LdShared64(uint32_t addr, uint32_t& a, uint32_t& b) {
+  asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(a), "=r"(b) : "r"(addr));
+}
+__device__ __forceinline__ uint32_t LdShared32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t LdSharedU16(uint32_t addr) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+  return v;
 }
 __device__ __forceinline__ uint32_t Lop3AndOr(uint32_t a, uint32_t and_mask, uint32_t or_mask) {
   uint32_t r;
@@ -218,7 +285,7 @@ struct Walker {
   int k_stages, m_tiles;
   __device__ __forceinline__ bool Next(Segment& s) {
     if (u >= u_end) return false;
-    s.tile = static_cast<int>(u / k_stages);
+    s.tile = static_cast<int>(static_cast<unsigned>(u) / static_cast<unsigned>(k_stages));
     s.k_begin = static_cast<int>(u - static_cast<long long>(s.tile) * k_stages);
     const long long left = u_end - u;
     s.k_end = left < k_stages - s.k_begin ? s.k_begin + static_cast<int>(left) : k_stages;
@@ -228,12 +295,18 @@ struct Walker {
     return true;
   }
 };
+// First unit of a block's range: floor(block * total / grid).  Written with the quotient and
+// remainder of total / grid so that no 64-bit division is needed (block, grid <= 1024).
 __device__ __forceinline__ long long RangeStart(long long block, long long total, long long grid) {
-  return block * total / grid;
+  const unsigned t = static_cast<unsigned>(total), g = static_cast<unsigned>(grid), b = static_cast<unsigned>(block);
+  const unsigned quot = t / g, rem = t - quot * g;
+  return static_cast<long long>(b * quot + b * rem / g);
 }
-// Block whose range holds unit u (largest b with RangeStart(b) <= u).
+// Block whose range holds unit u (largest b with RangeStart(b) <= u): floor(((u + 1) * grid - 1) / total).
 __device__ __forceinline__ int OwnerOf(long long u, long long total, long long grid) {
-  return static_cast<int>(((u + 1) * grid - 1) / total);
+  const unsigned long long num = (static_cast<unsigned long long>(u) + 1) * static_cast<unsigned>(grid) - 1;
+  if (num < (1ull << 32)) return static_cast<int>(static_cast<unsigned>(num) / static_cast<unsigned>(total));
+  return static_cast<int>(num / static_cast<unsigned long long>(total));
 }
 
 template <int kTok, int kSets>
@@ -248,15 +321,22 @@ struct Shared {
 };
 
 template <typename T, int kTok, bool kZeros, bool kMoe, int kSets>
-__global__ void __launch_bounds__((6 + 4 * kSets) * 32, 1)
-W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const GemmParams p) {
+__global__ void __launch_bounds__((5 + IssuersFor(kTok) + 4 * kSets) * 32, 1)
+W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap w_map,
+                const GemmParams p) {
   using Sh = Shared<kTok, kSets>;
   constexpr int kStages = Sh::kStages;
   constexpr int kAcc = Sh::kAcc;
   constexpr int kStage = StageBytes(kTok);
-  constexpr int kActBytes = kTok * 128;
+  constexpr int kAtomBytes = kTok * 128;  // one 64-k activation atom
+  constexpr int kActBytes = 2 * kAtomBytes;
+  // The lanes of a pass wait for each other, so a pass must stay well below the ring size or the
+  // ring would drain between passes.
+  constexpr int kProdLanes = kStages >= 12 ? 4 : kStages >= 5 ? 2 : 1;
   constexpr int kTmemCols = TmemColsFor(kTok);
   constexpr int kDequantWarps = 4 * kSets;
+  constexpr int kIssuers = IssuersFor(kTok);
+  constexpr int kFirstDq = 1 + kIssuers;  // warp 0 producer, then the issuers, dequantisers, epilogue
   constexpr uint32_t kIdesc = (1u << 4) | (Half2Of<T>::kFormat << 7) | (Half2Of<T>::kFormat << 10) |
                               (static_cast<uint32_t>(kTok >> 3) << 17) | (static_cast<uint32_t>(kTileN >> 4) << 24);
 
@@ -278,9 +358,13 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const GemmParams p) {
     m_tiles = (p.m + kTok - 1) / kTok;
   }
   const long long total_units = static_cast<long long>(n_tiles) * m_tiles * k_stages;
-  const long long grid = gridDim.x;
-  const long long u_begin = RangeStart(blockIdx.x, total_units, grid);
-  const long long u_end = RangeStart(blockIdx.x + 1, total_units, grid);
+  // Never more ranges than units: an empty range between two sharers of a tile would break the
+  // arrival count of the tile.  Surplus blocks get nothing to do.
+  const long long grid = total_units < static_cast<long long>(gridDim.x) ? (total_units > 0 ? total_units : 1)
+                                                                          : static_cast<long long>(gridDim.x);
+  const bool idle = static_cast<long long>(blockIdx.x) >= grid || total_units == 0;
+  const long long u_begin = idle ? 0 : RangeStart(blockIdx.x, total_units, grid);
+  const long long u_end = idle ? 0 : RangeStart(blockIdx.x + 1, total_units, grid);
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
@@ -292,11 +376,15 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const GemmParams p) {
       MbarInit(SmemAddr(&sh.a_empty[i]), 1);
     }
     for (int i = 0; i < kAcc; ++i) {
-      MbarInit(SmemAddr(&sh.d_full[i]), 1);
+      MbarInit(SmemAddr(&sh.d_full[i]), kIssuers);
       MbarInit(SmemAddr(&sh.d_empty[i]), 4);
     }
     sh.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (threadIdx.x == 32) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&a_map) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&w_map) : "memory");
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(SmemAddr(&sh.tmem_base)),
@@ -308,16 +396,21 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const GemmParams p) {
   __syncthreads();
   TcFenceAfter();
   const uint32_t tmem_base = sh.tmem_base;
-  const uint32_t tmem_d = tmem_base;                  // accumulators: columns [0, kAcc * kTok)
-  const uint32_t tmem_a = tmem_base + kAcc * kTok;    // weights: kAStages x 32 columns
+  const uint32_t tmem_d = tmem_base;  // accumulators: kAcc stages x kIssuers x kTok columns
+  const uint32_t tmem_a = tmem_base + kAcc * kIssuers * kTok;  // weights: kAStages x 64 columns
 
   if (warp == 0) {
     // ================= producer =================
-    if (lane == 0) {
+    // SIMT over stages: lane j issues every copy of k-step (base + j), so up to kProdLanes stages
+    // are requested per pass of the loop instead of one (each mbarrier / TMA instruction costs a
+    // shared-memory round trip, which one thread alone cannot hide).
+    if (lane < kProdLanes) {
+      constexpr unsigned kMask = (1u << kProdLanes) - 1u;
       Walker walk{u_begin, u_end, k_stages, m_tiles};
       Segment seg;
       uint32_t it = 0;
       bool alive = true;
+      const int rows = p.group_size == 64 ? 2 : 1;  // scale / zero rows a stage needs
       while (alive && walk.Next(seg)) {
         int expert = 0;
         if constexpr (kMoe) {
@@ -327,37 +420,51 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const GemmParams p) {
         const int n0 = seg.n_tile * kTileN;
         const int n_valid = min(kTileN, p.n - n0);
         const int row0 = kMoe ? seg.m_tile * p.block_size : seg.m_tile * kTok;
-        const uint32_t* wq = p.wq + static_cast<size_t>(expert) * (p.k / 16) * (2 * static_cast<size_t>(p.n));
-        const T* scales = static_cast<const T*>(p.scales) + static_cast<size_t>(expert) * p.groups * p.n;
-        const uint32_t* zeros = kZeros ? p.zeros + static_cast<size_t>(expert) * p.groups * (p.n / 8) : nullptr;
-        const uint32_t tx = kActBytes + 4 * (n_valid * 8) + n_valid * 2 + (kZeros ? n_valid / 2 : 0);
-        for (int ks = seg.k_begin; ks < seg.k_end; ++ks, ++it) {
-          const int s = it % kStages;
-          const uint32_t full = SmemAddr(&sh.full[s]);
-          if (!MbarWait(SmemAddr(&sh.empty[s]), ((it / kStages) & 1) ^ 1, abort_flag, p.status, kErrEmpty)) {
+        const int w_row0 = expert * (p.k / 16);
+        const T* scales = static_cast<const T*>(p.scales) + static_cast<size_t>(expert) * p.groups * p.n + n0;
+        const uint32_t* zeros =
+            kZeros ? p.zeros + static_cast<size_t>(expert) * p.groups * (p.n / 8) + n0 / 8 : nullptr;
+        // the weight box is always counted in full (columns past N arrive as zeros)
+        const uint32_t tx = kActBytes + 8192 + rows * (n_valid * 2 + (kZeros ? n_valid / 2 : 0));
+        for (int ks0 = seg.k_begin; ks0 < seg.k_end; ks0 += kProdLanes) {
+          const int ks = ks0 + lane;
+          const uint32_t my_it = it + lane;
+          int ok = 1;
+          if (ks < seg.k_end) {
+            const int s = my_it % kStages;
+            const uint32_t full = SmemAddr(&sh.full[s]);
+            ok = MbarWait(SmemAddr(&sh.empty[s]), ((my_it / kStages) & 1) ^ 1, abort_flag, p.status, kErrEmpty,
+                          static_cast<int>(my_it));
+            if (ok) {
+              const uint32_t base = stages_addr + s * kStage;
+              const int g = ks * kBlockK / p.group_size;
+              MbarExpectTx(full, tx);
+              TmaLoad2D(base, &a_map, ks * kBlockK, row0, full);
+              TmaLoad2D(base + kAtomBytes, &a_map, ks * kBlockK + 64, row0, full);
+              TmaLoad2D(base + kActBytes, &w_map, 2 * n0, w_row0 + ks * 8, full);
+              for (int r = 0; r < rows; ++r) {
+                BulkLoad(base + kActBytes + 8192 + r * 256, scales + static_cast<size_t>(g + r) * p.n, n_valid * 2,
+                         full);
+                if constexpr (kZeros) {
+                  BulkLoad(base + kActBytes + 8192 + 512 + r * 64, zeros + static_cast<size_t>(g + r) * (p.n / 8),
+                           n_valid / 2, full);
+                }
+              }
+            }
+          }
+          if (!__all_sync(kMask, ok)) {
             alive = false;
             break;
           }
-          MbarExpectTx(full, tx);
-          const uint32_t base = stages_addr + s * kStage;
-          TmaLoad2D(base, &a_map, ks * kBlockK, row0, full);
-#pragma unroll
-          for (int kt = 0; kt < 4; ++kt) {
-            BulkLoad(base + kActBytes + kt * 1024, wq + static_cast<size_t>(ks * 4 + kt) * (2 * p.n) + 2 * n0,
-                     n_valid * 8, full);
-          }
-          const int g = ks * kBlockK / p.group_size;
-          BulkLoad(base + kActBytes + 4096, scales + static_cast<size_t>(g) * p.n + n0, n_valid * 2, full);
-          if constexpr (kZeros) {
-            BulkLoad(base + kActBytes + 4096 + 256, zeros + static_cast<size_t>(g) * (p.n / 8) + n0 / 8, n_valid / 2,
-                     full);
-          }
+          it += min(kProdLanes, seg.k_end - ks0);
         }
       }
     }
-  } else if (warp == 1) {
-    // ================= MMA issuer =================
+  } else if (warp <= kIssuers) {
+    // ================= MMA issuers =================
     if (lane == 0) {
+      const int me = warp - 1;  // takes the stages with it % kIssuers == me
+      int first_it = -1, last_it = -1;
       Walker walk{u_begin, u_end, k_stages, m_tiles};
       Segment seg;
       uint32_t it = 0, seg_idx = 0;
@@ -367,13 +474,22 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const GemmParams p) {
           if (p.expert_ids[seg.m_tile] < 0) continue;
         }
         const int acc = seg_idx % kAcc;
-        if (!MbarWait(SmemAddr(&sh.d_empty[acc]), ((seg_idx / kAcc) & 1) ^ 1, abort_flag, p.status, kErrDEmpty)) break;
+        if (!MbarWait(SmemAddr(&sh.d_empty[acc]), ((seg_idx / kAcc) & 1) ^ 1, abort_flag, p.status, kErrDEmpty,
+                      static_cast<int>(seg_idx))) {
+          break;
+        }
         TcFenceAfter();
-        const uint32_t d_addr = tmem_d + acc * kTok;
+        const uint32_t d_addr = tmem_d + (acc * kIssuers + me) * kTok;
+        bool issued = false;
         for (int ks = seg.k_begin; ks < seg.k_end; ++ks, ++it) {
+          if (static_cast<int>(it % kIssuers) != me) continue;
+          last_it = static_cast<int>(it);
+          if (first_it < 0) first_it = last_it;
           const int s = it % kStages, a = it % kAStages;
-          if (!MbarWait(SmemAddr(&sh.full[s]), (it / kStages) & 1, abort_flag, p.status, kErrFull) ||
-              !MbarWait(SmemAddr(&sh.a_full[a]), (it / kAStages) & 1, abort_flag, p.status, kErrAFull)) {
+          // `a_full` is raised by warps that waited for this stage's copies themselves, so it
+          // also covers the activation tile.
+          if (!MbarWait(SmemAddr(&sh.a_full[a]), (it / kAStages) & 1, abort_flag, p.status, kErrAFull,
+                        static_cast<int>(it))) {
             alive = false;
             break;
           }
@@ -383,27 +499,51 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const GemmParams p) {
                                  (1ull << 46) | (2ull << 61);
 #pragma unroll
           for (int j = 0; j < kBlockK / 16; ++j) {
-            MmaTs(d_addr, tmem_a + a * kAStageCols + 8 * j, desc0 + 2 * j, kIdesc,
-                  (ks > seg.k_begin || j > 0) ? 1u : 0u);
+            // 16-k slab j: atom j / 4, 32 bytes per slab inside the 128-byte swizzled row
+            const uint64_t desc = desc0 + static_cast<uint64_t>((j >> 2) * (kAtomBytes >> 4) + 2 * (j & 3));
+            MmaTs(d_addr, tmem_a + a * kAStageCols + 8 * j, desc, kIdesc, (issued || j > 0) ? 1u : 0u);
           }
+          issued = true;
           TcCommit(SmemAddr(&sh.empty[s]));
           TcCommit(SmemAddr(&sh.a_empty[a]));
         }
         if (!alive) break;
-        TcCommit(SmemAddr(&sh.d_full[acc]));
+        // an issuer without a stage in this segment still has to count as arrived
+        if (issued) {
+          TcCommit(SmemAddr(&sh.d_full[acc]));
+        } else {
+          MbarArrive(SmemAddr(&sh.d_full[acc]));
+        }
         ++seg_idx;
       }
+      // Drain: the commits of the last stages are arrivals nobody waits for any more.  They are
+      // asynchronous; if the block exited with one still on its way, it could land in the
+      // barriers of the next block that gets this shared memory.  So see them arrive first.
+      if (alive && last_it >= 0) {
+        for (int d = 0; d * kIssuers < kStages; ++d) {  // only stages not reused since
+          const int step = last_it - d * kIssuers;
+          if (step < first_it) break;
+          if (!MbarWait(SmemAddr(&sh.empty[step % kStages]), (step / kStages) & 1, abort_flag, p.status, kErrEmpty, step)) {
+            break;
+          }
+          if (d * kIssuers < kAStages &&
+              !MbarWait(SmemAddr(&sh.a_empty[step % kAStages]), (step / kAStages) & 1, abort_flag, p.status, kErrAEmpty,
+                        step)) {
+            break;
+          }
+        }
+      }
     }
-  } else if (warp < 2 + kDequantWarps) {
+  } else if (warp < kFirstDq + kDequantWarps) {
     // ================= dequantisers =================
-    const int set = (warp - 2) / 4;
+    const int set = (warp - kFirstDq) / 4;
     const int q = warp & 3;  // tensor-memory lane quarter this warp may touch
     Walker walk{u_begin, u_end, k_stages, m_tiles};
     Segment seg;
     uint32_t it = 0;
     bool alive = true;
     // symmetric types: implicit zero point 8
-    const uint32_t zero_sym = Splat<T>(Half2Of<T>::kBase + 8.0f);
+    const uint32_t zero_sym = Half2Of<T>::kMagic | 0x00080008u;
     while (alive && walk.Next(seg)) {
       if constexpr (kMoe) {
         if (p.expert_ids[seg.m_tile] < 0) continue;
@@ -411,41 +551,52 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const GemmParams p) {
       for (int ks = seg.k_begin; ks < seg.k_end; ++ks, ++it) {
         if (static_cast<int>(it % kSets) != set) continue;
         const int s = it % kStages, a = it % kAStages;
-        if (!MbarWait(SmemAddr(&sh.full[s]), (it / kStages) & 1, abort_flag, p.status, kErrFull) ||
-            !MbarWait(SmemAddr(&sh.a_empty[a]), ((it / kAStages) & 1) ^ 1, abort_flag, p.status, kErrAEmpty)) {
+        if (!MbarWaitWarp(0xffffffffu, 0, SmemAddr(&sh.full[s]), (it / kStages) & 1, abort_flag, p.status, kErrFull,
+                          false, static_cast<int>(it)) ||
+            !MbarWaitWarp(0xffffffffu, 0, SmemAddr(&sh.a_empty[a]), ((it / kAStages) & 1) ^ 1, abort_flag, p.status,
+                          kErrAEmpty, false, static_cast<int>(it))) {
           alive = false;
           break;
         }
         TcFenceAfter();
-        const unsigned char* base = stages + s * kStage + kActBytes;
-        const uint32_t* words = reinterpret_cast<const uint32_t*>(base);
-        const T* scale_row = reinterpret_cast<const T*>(base + 4096);
-        const uint32_t* zero_row = reinterpret_cast<const uint32_t*>(base + 4096 + 256);
+        // Explicit shared-space loads (32-bit addresses) keep these off the generic-address path.
+        const uint32_t wbase = stages_addr + s * kStage + kActBytes;
+        const uint32_t sbase = wbase + 8192, zbase = wbase + 8192 + 512;
+        // The thread's words for sub-blocks 2q and 2q + 1 of a 16-k slab are adjacent: one 8-byte load.
+        const uint32_t waddr = wbase + ((q >> 1) * 128 + lane * 4 + 2 * (q & 1)) * 4;
+        const int row_step = p.group_size == 64 ? 1 : 0;  // second 64 k use the next scale row
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          // sub-block sb = 2q + h covers tile columns [16 sb, 16 sb + 16); this thread owns
-          // columns c0 = 16 sb + lane / 4 and c0 + 8.
-          const int sb = 2 * q + h;
-          const int c0 = 16 * sb + (lane >> 2);
-          const uint32_t s_lo = SplatRaw<T>(scale_row[c0]);
-          const uint32_t s_hi = SplatRaw<T>(scale_row[c0 + 8]);
-          uint32_t z_lo = zero_sym, z_hi = zero_sym;
-          if constexpr (kZeros) {
-            const uint32_t shift = 4 * (lane >> 2);
-            z_lo = Splat<T>(Half2Of<T>::kBase + static_cast<float>((zero_row[2 * sb] >> shift) & 0xF));
-            z_hi = Splat<T>(Half2Of<T>::kBase + static_cast<float>((zero_row[2 * sb + 1] >> shift) & 0xF));
-          }
-          uint32_t regs[16];
+        for (int half = 0; half < 2; ++half) {
+          uint32_t w[4][2];
 #pragma unroll
-          for (int kt = 0; kt < 4; ++kt) {
-            // word of chunk (kt, sb / 4), lane, sub-tile sb % 4
-            const uint32_t w = words[kt * 256 + (sb >> 2) * 128 + lane * 4 + (sb & 3)];
-            regs[4 * kt + 0] = Dequant2<T>(w, z_lo, s_lo);        // column c0,     k pair lane % 4
-            regs[4 * kt + 1] = Dequant2<T>(w >> 8, z_hi, s_hi);   // column c0 + 8, k pair lane % 4
-            regs[4 * kt + 2] = Dequant2<T>(w >> 4, z_lo, s_lo);   // column c0,     k pair lane % 4 + 4
-            regs[4 * kt + 3] = Dequant2<T>(w >> 12, z_hi, s_hi);  // column c0 + 8, k pair lane % 4 + 4
+          for (int kt = 0; kt < 4; ++kt) LdShared64(waddr + (half * 4 + kt) * 1024, w[kt][0], w[kt][1]);
+          const int row = half * row_step;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            // sub-block sb = 2q + h covers tile columns [16 sb, 16 sb + 16); this thread owns
+            // columns c0 = 16 sb + lane / 4 and c0 + 8.
+            const int sb = 2 * q + h;
+            const int c0 = 16 * sb + (lane >> 2);
+            const uint32_t s_lo = LdSharedU16(sbase + row * 256 + 2 * c0) * 0x10001u;
+            const uint32_t s_hi = LdSharedU16(sbase + row * 256 + 2 * (c0 + 8)) * 0x10001u;
+            // magic | z is the 16-bit float (base + z) for z < 16, the same trick as for the weights
+            uint32_t z_lo = zero_sym, z_hi = zero_sym;
+            if constexpr (kZeros) {
+              const uint32_t shift = 4 * (lane >> 2);
+              z_lo = Half2Of<T>::kMagic | (((LdShared32(zbase + row * 64 + 8 * sb) >> shift) & 0xFu) * 0x10001u);
+              z_hi = Half2Of<T>::kMagic | (((LdShared32(zbase + row * 64 + 8 * sb + 4) >> shift) & 0xFu) * 0x10001u);
+            }
+            uint32_t regs[16];
+#pragma unroll
+            for (int kt = 0; kt < 4; ++kt) {
+              const uint32_t word = w[kt][h];
+              regs[4 * kt + 0] = Dequant2<T>(word, z_lo, s_lo);        // column c0,     k pair lane % 4
+              regs[4 * kt + 1] = Dequant2<T>(word >> 8, z_hi, s_hi);   // column c0 + 8, k pair lane % 4
+              regs[4 * kt + 2] = Dequant2<T>(word >> 4, z_lo, s_lo);   // column c0,     k pair lane % 4 + 4
+              regs[4 * kt + 3] = Dequant2<T>(word >> 12, z_hi, s_hi);  // column c0 + 8, k pair lane % 4 + 4
+            }
+            TmemStore16(tmem_a + (static_cast<uint32_t>(32 * q + 16 * h) << 16) + a * kAStageCols + half * 32, regs);
           }
-          TmemStore16(tmem_a + (static_cast<uint32_t>(32 * q + 16 * h) << 16) + a * kAStageCols, regs);
         }
         TmemWaitSt();
         TcFenceBefore();
@@ -461,7 +612,7 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const GemmParams p) {
     const int q = warp & 3;
     Walker walk{u_begin, u_end, k_stages, m_tiles};
     Segment seg;
-    uint32_t seg_idx = 0;
+    uint32_t seg_idx = 0, it = 0;
     T* out = static_cast<T*>(p.out);
     while (walk.Next(seg)) {
       int expert = 0;
@@ -470,7 +621,10 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const GemmParams p) {
         if (expert < 0) continue;
       }
       const int acc = seg_idx % kAcc;
-      if (!MbarWait(SmemAddr(&sh.d_full[acc]), (seg_idx / kAcc) & 1, abort_flag, p.status, kErrDFull)) break;
+      if (!MbarWaitWarp(0xffffffffu, 0, SmemAddr(&sh.d_full[acc]), (seg_idx / kAcc) & 1, abort_flag, p.status,
+                        kErrDFull, /*relaxed=*/true, static_cast<int>(seg_idx))) {
+        break;
+      }
       TcFenceAfter();
       const int n_local = 32 * q + lane;
       const int n = seg.n_tile * kTileN + n_local;
@@ -478,7 +632,15 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const GemmParams p) {
       const int row0 = kMoe ? seg.m_tile * p.block_size : seg.m_tile * kTok;
       const int m_valid = kMoe ? p.block_size : min(kTok, p.m - row0);
       const bool whole = seg.k_begin == 0 && seg.k_end == k_stages;
-      const uint32_t d_addr = tmem_d + acc * kTok + (static_cast<uint32_t>(32 * q) << 16);
+      const uint32_t d_addr = tmem_d + acc * kIssuers * kTok + (static_cast<uint32_t>(32 * q) << 16);
+      // which issuers contributed to this segment (they alternate stages, counted by `it`)
+      const int n_steps = seg.k_end - seg.k_begin;
+      bool present[kIssuers];
+#pragma unroll
+      for (int j = 0; j < kIssuers; ++j) {
+        present[j] = n_steps >= kIssuers || static_cast<int>((j + kIssuers - it % kIssuers) % kIssuers) < n_steps;
+      }
+      it += n_steps;
       float bias_v = 0.0f;
       if (p.bias != nullptr && n_ok) bias_v = ToFloat<T>(static_cast<const T*>(p.bias)[static_cast<size_t>(expert) * p.n + n]);
 
@@ -497,12 +659,28 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const GemmParams p) {
       };
 
       const bool first_of_block = walk.u - (seg.k_end - seg.k_begin) == u_begin;
-      float* my_partial = p.partial + (static_cast<size_t>(2 * blockIdx.x + (first_of_block ? 0 : 1)) * kTok) * kTileN;
+      // partial slot layout: [128 tile columns][kTok tokens], so a thread's tokens are contiguous
+      float* my_partial =
+          p.partial + (static_cast<size_t>(2 * blockIdx.x + (first_of_block ? 0 : 1)) * kTileN + n_local) * kTok;
 #pragma unroll 1
       for (int c = 0; c < kTok; c += 16) {
         if (c >= m_valid) break;
         uint32_t r[16];
-        TmemLoad16(d_addr + c, r);
+        if (present[0]) {
+          TmemLoad16(d_addr + c, r);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) r[j] = 0u;
+        }
+        if constexpr (kIssuers == 2) {
+          if (present[1]) {
+            uint32_t r1[16];
+            TmemLoad16(d_addr + kTok + c, r1);
+            TmemWaitLd();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r1[j]));
+          }
+        }
         TmemWaitLd();
         if (whole) {
           if (n_ok) {
@@ -513,7 +691,9 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const GemmParams p) {
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) my_partial[static_cast<size_t>(c + j) * kTileN + n_local] = __uint_as_float(r[j]);
+          for (int j = 0; j < 16; j += 4) {
+            *reinterpret_cast<uint4*>(my_partial + c + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+          }
         }
       }
       // The accumulator is in registers / memory now: hand it back to the MMA warp.
@@ -529,7 +709,8 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const GemmParams p) {
         const long long tile_u0 = static_cast<long long>(seg.tile) * k_stages;
         const int first_block = OwnerOf(tile_u0, total_units, grid);
         const int last_block = OwnerOf(tile_u0 + k_stages - 1, total_units, grid);
-        int* counter = p.counters + 4 * static_cast<size_t>(seg.tile) + q;
+        // A split tile is identified by the first block working on it: no two split tiles share one.
+        int* counter = p.counters + 4 * first_block + q;
         __threadfence();
         __syncwarp();
         int ticket = 0;
@@ -538,16 +719,41 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const GemmParams p) {
         if (ticket == last_block - first_block) {
           __threadfence();
           if (n_ok) {
-            for (int j = 0; j < m_valid; ++j) {
-              float v = 0.0f;
-              for (int b = first_block; b <= last_block; ++b) {
-                // a block's first segment uses slot 2b, any later one slot 2b + 1
-                const bool is_first = RangeStart(b, total_units, grid) >= tile_u0;
-                const float* src =
-                    p.partial + (static_cast<size_t>(2 * b + (is_first ? 0 : 1)) * kTok + j) * kTileN + n_local;
-                v += __ldcg(src);
+            // a block's first segment uses slot 2b, any later one slot 2b + 1
+            auto slot_of = [&](int b) -> const float* {
+              const bool is_first = RangeStart(b, total_units, grid) >= tile_u0;
+              return p.partial + (static_cast<size_t>(2 * b + (is_first ? 0 : 1)) * kTileN + n_local) * kTok;
+            };
+            for (int c = 0; c < m_valid; c += 16) {
+              float sum[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) sum[j] = 0.0f;
+              // two sharers per round: their 8 loads are all in flight together; the additions
+              // stay in ascending block order, so the result does not depend on who arrived last
+              for (int b = first_block; b <= last_block; b += 2) {
+                float4 v[2][4];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                  const bool on = b + u <= last_block;
+                  const float4* src = reinterpret_cast<const float4*>(slot_of(on ? b + u : b) + c);
+#pragma unroll
+                  for (int x = 0; x < 4; ++x) v[u][x] = on ? __ldcg(src + x) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+#pragma unroll
+                  for (int x = 0; x < 4; ++x) {
+                    sum[4 * x + 0] += v[u][x].x;
+                    sum[4 * x + 1] += v[u][x].y;
+                    sum[4 * x + 2] += v[u][x].z;
+                    sum[4 * x + 3] += v[u][x].w;
+                  }
+                }
               }
-              emit(j, v);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (c + j < m_valid) emit(c + j, sum[j]);
+              }
             }
           }
           if (lane == 0) *counter = 0;
@@ -609,9 +815,10 @@ EncodeFn GetEncode() {
 struct MapKey {
   const void* ptr;
   int64_t rows, cols;
-  int box_rows, dtype;
+  int box_rows, box_cols, kind;
   bool operator==(const MapKey& o) const {
-    return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows && dtype == o.dtype;
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows && box_cols == o.box_cols &&
+           kind == o.kind;
   }
 };
 struct MapKeyHash {
@@ -619,15 +826,20 @@ struct MapKeyHash {
     size_t h = reinterpret_cast<size_t>(k.ptr);
     h ^= static_cast<size_t>(k.rows) * 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
     h ^= static_cast<size_t>(k.cols) * 0xC2B2AE3D27D4EB4Full + (h << 6) + (h >> 2);
-    h ^= static_cast<size_t>(k.box_rows * 4 + k.dtype) + (h << 6) + (h >> 2);
+    h ^= static_cast<size_t>((k.box_rows * 1024 + k.box_cols) * 4 + k.kind) + (h << 6) + (h >> 2);
     return h;
   }
 };
 
-// Tensor map of a row-major [rows, cols] 16-bit matrix with a [box_rows, 64] box, 128-byte swizzle.
-int ActivationMap(const void* ptr, int64_t rows, int64_t cols, int box_rows, int dtype, CUtensorMap* out) {
+constexpr int kMapF16 = 0, kMapBf16 = 1, kMapWords = 2;
+
+// Tensor map of a row-major [rows, cols] matrix with a [box_rows, box_cols] box.  16-bit kinds use
+// the 128-byte swizzle (activation tiles, box_cols = 64); 32-bit words are copied unswizzled.
+// Encoded maps are cached per thread: encoding costs microseconds of host time.
+int TensorMap2D(const void* ptr, int64_t rows, int64_t cols, int box_rows, int box_cols, int kind,
+                CUtensorMap* out) {
   static thread_local std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-  const MapKey key{ptr, rows, cols, box_rows, dtype};
+  const MapKey key{ptr, rows, cols, box_rows, box_cols, kind};
   auto it = cache.find(key);
   if (it != cache.end()) {
     *out = it->second;
@@ -635,18 +847,31 @@ int ActivationMap(const void* ptr, int64_t rows, int64_t cols, int box_rows, int
   }
   EncodeFn encode = GetEncode();
   if (encode == nullptr) return Fail(IOB_CUDA_ERROR, "W4A16 GEMM: cuTensorMapEncodeTiled is not available");
+  const int elem_bytes = kind == kMapWords ? 4 : 2;
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
-  const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * elem_bytes};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
   const cuuint32_t elem[2] = {1, 1};
-  const CUresult rc = encode(out, dtype == IOB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
-                             2, const_cast<void*>(ptr), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const CUtensorMapDataType type = kind == kMapWords  ? CU_TENSOR_MAP_DATA_TYPE_INT32
+                                   : kind == kMapBf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                      : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUresult rc = encode(out, type, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             kind == kMapWords ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (rc != CUDA_SUCCESS) return Fail(IOB_CUDA_ERROR, "W4A16 GEMM: tensor map encode failed (%d)", static_cast<int>(rc));
   if (cache.size() > 4096) cache.clear();
   cache.emplace(key, *out);
   return IOB_OK;
+}
+
+int ActivationMap(const void* ptr, int64_t rows, int64_t cols, int box_rows, int dtype, CUtensorMap* out) {
+  return TensorMap2D(ptr, rows, cols, box_rows, 64, dtype == IOB_BF16 ? kMapBf16 : kMapF16, out);
+}
+
+// Packed weights [E * K/16, 2N] words, box = 8 rows (128 k) x 256 words (128 columns).
+int WeightMap(const void* ptr, int64_t experts, int64_t k, int64_t n, CUtensorMap* out) {
+  return TensorMap2D(ptr, experts * (k / 16), 2 * n, 8, 256, kMapWords, out);
 }
 
 int TokenTile(int64_t m) { return m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : m <= 128 ? 128 : 256; }
@@ -659,15 +884,19 @@ struct ScratchPlan {
 ScratchPlan PlanScratch(int64_t tiles, int tok, int64_t gathered_bytes) {
   ScratchPlan plan;
   plan.counters_off = kHeaderBytes;
-  plan.partial_off = Align256(plan.counters_off + static_cast<size_t>(4) * tiles * sizeof(int));
+  // Fixed positions whatever the problem: the counters must never overlap an area that some
+  // other call fills with data, because every call relies on finding them zero.
+  (void)tiles;
+  plan.partial_off = Align256(plan.counters_off + static_cast<size_t>(4) * kMaxGrid * sizeof(int));
   plan.gathered_off = Align256(plan.partial_off + static_cast<size_t>(2) * NumSms() * tok * kTileN * sizeof(float));
   plan.total = Align256(plan.gathered_off + gathered_bytes);
   return plan;
 }
 
 template <typename T, int kTok, bool kZeros, bool kMoe>
-int LaunchKernel(const CUtensorMap& map, const GemmParams& p, int grid, cudaStream_t stream) {
-  constexpr int kSets = kTok <= 64 ? 2 : 1;
+int LaunchKernel(const CUtensorMap& map, const CUtensorMap& w_map, const GemmParams& p, int grid,
+                 cudaStream_t stream) {
+  constexpr int kSets = SetsFor(kTok);
   auto kernel = W4A16GemmKernel<T, kTok, kZeros, kMoe, kSets>;
   constexpr int smem = StagesFor(kTok) * StageBytes(kTok) + 1024;
   static thread_local bool configured[64] = {};
@@ -678,34 +907,35 @@ int LaunchKernel(const CUtensorMap& map, const GemmParams& p, int grid, cudaStre
     if (err != cudaSuccess) return Fail(IOB_CUDA_ERROR, "W4A16 GEMM: %s", cudaGetErrorString(err));
     if (device >= 0 && device < 64) configured[device] = true;
   }
-  kernel<<<grid, (6 + 4 * kSets) * 32, smem, stream>>>(map, p);
+  kernel<<<grid, (5 + IssuersFor(kTok) + 4 * kSets) * 32, smem, stream>>>(map, w_map, p);
   return CheckLaunch("W4A16 GEMM launch");
 }
 
 template <typename T, bool kZeros, bool kMoe>
-int DispatchTok(int tok, const CUtensorMap& map, const GemmParams& p, int grid, cudaStream_t stream) {
+int DispatchTok(int tok, const CUtensorMap& map, const CUtensorMap& w_map, const GemmParams& p, int grid,
+                cudaStream_t stream) {
   switch (tok) {
-    case 16: return LaunchKernel<T, 16, kZeros, kMoe>(map, p, grid, stream);
-    case 32: return LaunchKernel<T, 32, kZeros, kMoe>(map, p, grid, stream);
-    case 64: return LaunchKernel<T, 64, kZeros, kMoe>(map, p, grid, stream);
+    case 16: return LaunchKernel<T, 16, kZeros, kMoe>(map, w_map, p, grid, stream);
+    case 32: return LaunchKernel<T, 32, kZeros, kMoe>(map, w_map, p, grid, stream);
+    case 64: return LaunchKernel<T, 64, kZeros, kMoe>(map, w_map, p, grid, stream);
     default: break;
   }
   if constexpr (!kMoe) {
-    if (tok == 128) return LaunchKernel<T, 128, kZeros, kMoe>(map, p, grid, stream);
-    if (tok == 256) return LaunchKernel<T, 256, kZeros, kMoe>(map, p, grid, stream);
+    if (tok == 128) return LaunchKernel<T, 128, kZeros, kMoe>(map, w_map, p, grid, stream);
+    if (tok == 256) return LaunchKernel<T, 256, kZeros, kMoe>(map, w_map, p, grid, stream);
   }
   return Fail(IOB_UNSUPPORTED, "W4A16 GEMM: no kernel for a token tile of %d", tok);
 }
 
 template <bool kMoe>
-int Dispatch(int a_dtype, bool zeros, int tok, const CUtensorMap& map, const GemmParams& p, int grid,
-             cudaStream_t stream) {
+int Dispatch(int a_dtype, bool zeros, int tok, const CUtensorMap& map, const CUtensorMap& w_map,
+             const GemmParams& p, int grid, cudaStream_t stream) {
   if (a_dtype == IOB_BF16) {
-    return zeros ? DispatchTok<__nv_bfloat16, true, kMoe>(tok, map, p, grid, stream)
-                 : DispatchTok<__nv_bfloat16, false, kMoe>(tok, map, p, grid, stream);
+    return zeros ? DispatchTok<__nv_bfloat16, true, kMoe>(tok, map, w_map, p, grid, stream)
+                 : DispatchTok<__nv_bfloat16, false, kMoe>(tok, map, w_map, p, grid, stream);
   }
-  return zeros ? DispatchTok<__half, true, kMoe>(tok, map, p, grid, stream)
-               : DispatchTok<__half, false, kMoe>(tok, map, p, grid, stream);
+  return zeros ? DispatchTok<__half, true, kMoe>(tok, map, w_map, p, grid, stream)
+               : DispatchTok<__half, false, kMoe>(tok, map, w_map, p, grid, stream);
 }
 
 int CheckProblem(const char* op, const void* a, int a_dtype, const void* wq, const void* scales, const void* zeros,
@@ -720,8 +950,8 @@ int CheckProblem(const char* op, const void* a, int a_dtype, const void* wq, con
   IOB_REQUIRE((zeros != nullptr) == (b_type_id == IOB_QTYPE_UINT4),
               "%s: zero points are required for uint4 and not accepted for uint4b8", op);
   IOB_REQUIRE(groups > 0 && k % groups == 0, "%s: `size_k` must be a multiple of the number of scale groups", op);
-  if (k % kBlockK != 0 || (k / groups) % kBlockK != 0) {
-    return Fail(IOB_UNSUPPORTED, "%s: needs `size_k` and the group size to be multiples of 64", op);
+  if (k % kBlockK != 0 || ((k / groups) != 64 && (k / groups) % kBlockK != 0)) {
+    return Fail(IOB_UNSUPPORTED, "%s: needs `size_k` to be a multiple of 128 and the group size 64 or a multiple of 128", op);
   }
   IOB_REQUIRE(reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(wq) % 16 == 0 &&
                   reinterpret_cast<uintptr_t>(scales) % 16 == 0 && reinterpret_cast<uintptr_t>(zeros) % 16 == 0,
@@ -767,6 +997,8 @@ extern "C" int infiniops_b200_marlin_gemm(const void* a, int a_dtype, const int3
   }
   CUtensorMap map;
   if (const int rc = ActivationMap(a, size_m, size_k, tok, a_dtype, &map)) return rc;
+  CUtensorMap w_map;
+  if (const int rc = WeightMap(b_q_weight, 1, size_k, size_n, &w_map)) return rc;
   auto* base = static_cast<unsigned char*>(scratch);
   GemmParams p{};
   p.wq = reinterpret_cast<const uint32_t*>(b_q_weight);
@@ -784,7 +1016,7 @@ extern "C" int infiniops_b200_marlin_gemm(const void* a, int a_dtype, const int3
   p.group_size = static_cast<int>(size_k / num_groups);
   const int64_t units = n_tiles * m_tiles * (size_k / kBlockK);
   const int grid = static_cast<int>(units < NumSms() ? units : NumSms());
-  return Dispatch<false>(a_dtype, b_zeros != nullptr, tok, map, p, grid, static_cast<cudaStream_t>(stream));
+  return Dispatch<false>(a_dtype, b_zeros != nullptr, tok, map, w_map, p, grid, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" size_t infiniops_b200_moe_wna16_marlin_gemm_scratch_bytes(int64_t size_m, int64_t top_k, int64_t size_n,
@@ -846,6 +1078,8 @@ extern "C" int infiniops_b200_moe_wna16_marlin_gemm(
   if (const int rc = CheckLaunch("moe_wna16_marlin_gemm gather launch")) return rc;
   CUtensorMap map;
   if (const int rc = ActivationMap(gathered, sorted_cap + tok, size_k, tok, a_dtype, &map)) return rc;
+  CUtensorMap w_map;
+  if (const int rc = WeightMap(b_q_weight, num_experts, size_k, size_n, &w_map)) return rc;
   GemmParams p{};
   p.wq = reinterpret_cast<const uint32_t*>(b_q_weight);
   p.scales = b_scales;
@@ -868,5 +1102,5 @@ extern "C" int infiniops_b200_moe_wna16_marlin_gemm(
   p.block_size = static_cast<int>(moe_block_size);
   p.mul_weights = mul_topk_weights;
   p.out_rows = out_rows;
-  return Dispatch<true>(a_dtype, b_zeros != nullptr, tok, map, p, NumSms(), s);
+  return Dispatch<true>(a_dtype, b_zeros != nullptr, tok, map, w_map, p, NumSms(), s);
 }

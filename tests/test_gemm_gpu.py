@@ -59,9 +59,9 @@ def test_config2_gate_up_shape():
 
 
 @pytest.mark.parametrize("m,k,n,group,dtype,zeros", (
-    (3, 64, 64, 64, torch.float16, False),      # one k stage, half-width tile
+    (3, 128, 64, 64, torch.float16, False),     # one k stage, half-width tile, two groups in it
     (17, 128, 192, 128, torch.bfloat16, True),  # ragged tile in n, token tile 32
-    (100, 256, 320, 64, torch.float16, True),   # token tile 128, two groups per 128 k
+    (100, 256, 320, 64, torch.float16, True),   # token tile 128, group size 64
     (130, 512, 128, -1, torch.bfloat16, False), # per-channel scales, token tile 256, ragged rows
     (300, 1024, 256, 128, torch.bfloat16, True),  # two token tiles
     (64, 8192, 64, 128, torch.float16, False),  # one tile shared by many blocks along k
@@ -100,7 +100,7 @@ def test_repeatable_and_scratch_left_clean():
         assert torch.equal(_gemm(a, q, scales, zeros, "awq"), first)
     buf = capi.scratch("cuda", 0)
     need = capi.lib().infiniops_b200_marlin_gemm_scratch_bytes(16, 4096, 4096)
-    header = buf[:256 + 4 * 4 * 32].view(torch.int32)
+    header = buf[:256 + 4 * 4 * 1024].view(torch.int32)  # status word and arrival counters
     assert int(header.abs().sum()) == 0 and need <= buf.numel()
 
 
