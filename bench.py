@@ -184,7 +184,7 @@ def run_ours(args):
     for phase in range(phases):
         step(phase)
     torch.cuda.synchronize()
-    assert capi.scratch_status(scratch) == 0
+    assert capi.scratch_status(scratch) == 0, f"a GEMM kernel gave up on a wait: {scratch[:192].view(torch.int32).tolist()}"
 
     # The step as CUDA graphs, one per weight copy rotation, so replays keep rotating the weights.
     graphs = []
@@ -220,7 +220,7 @@ def run_ours(args):
         barrier()
         time.sleep(0.15)
     elapsed_ms = start.elapsed_time(stop)
-    assert capi.scratch_status(scratch) == 0, "a GEMM kernel gave up on a wait"
+    assert capi.scratch_status(scratch) == 0, f"a GEMM kernel gave up on a wait: {scratch[:192].view(torch.int32).tolist()}"
 
     # ---- end to end through the operator call with host buffers -------------------------------
     host_in = {key: t.cpu().pin_memory() for key, t in acts.items()}

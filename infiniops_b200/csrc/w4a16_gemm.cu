@@ -42,7 +42,6 @@ namespace {
 
 constexpr int kTileN = 128;              // weight columns per tile (= UMMA M)
 constexpr int kBlockK = 128;             // k per pipeline stage (two 64-k activation atoms)
-constexpr int kAStages = 4;              // tensor-memory stages of dequantised weights
 constexpr int kAStageCols = kBlockK / 2; // 32-bit columns per stage (two 16-bit values each)
 // Polls before a wait gives up.  A failed try_wait returns after a hardware time-out of a few
 // microseconds, so this is a few hundred milliseconds -- far beyond any legitimate wait.
@@ -53,12 +52,21 @@ constexpr int kMaxGrid = 1024;           // counters are laid out for at most th
 constexpr int kErrFull = 1, kErrEmpty = 2, kErrAFull = 3, kErrAEmpty = 4, kErrDFull = 5, kErrDEmpty = 6;
 
 __host__ __device__ constexpr int StagesFor(int tok) {
-  // as many as fit beside the barriers in 227 KB: decode needs ~90 KB of weights in flight per SM
-  // to cover HBM latency at full rate
-  return tok <= 16 ? 14 : tok <= 32 ? 12 : tok <= 64 ? 8 : tok <= 128 ? 5 : 3;
+  // As many as fit in 227 KB (decode needs ~90 KB of weights in flight per SM to cover HBM
+  // latency at full rate) -- and a multiple of SetsFor(tok), see there.
+  return tok <= 32 ? 12 : tok <= 64 ? 8 : tok <= 128 ? 4 : 3;
 }
 // Sets of four dequantiser warps; a set takes every kSets-th stage.
-__host__ __device__ constexpr int SetsFor(int tok) { return tok <= 64 ? 3 : 2; }
+//
+// Both ring sizes (shared-memory stages, tensor-memory weight stages) are multiples of the number
+// of sets, so that a given ring slot is always served by the same set.  mbarrier waits carry one
+// parity bit, which is only sound while a waiter is never more than one phase ahead of the
+// barrier; a set that has itself produced phase k of a slot cannot reach the wait for phase k+1
+// early, but a set that meets the slot for the first time could -- and would read the stale
+// parity as "done".
+__host__ __device__ constexpr int SetsFor(int tok) { return tok <= 32 ? 3 : tok <= 128 ? 2 : 3; }
+// Tensor-memory stages of dequantised weights (64 columns each).
+__host__ __device__ constexpr int AStagesFor(int tok) { return tok <= 32 ? 6 : tok <= 128 ? 4 : 3; }
 __host__ __device__ constexpr int AccStagesFor(int tok) { return tok <= 128 ? 2 : 1; }
 // activations (two swizzle atoms of tok x 128 B) | packed weights 8 KB | 2 scale rows | 2 zero rows
 __host__ __device__ constexpr int StageBytes(int tok) { return tok * 256 + 8192 + 1024; }
@@ -68,7 +76,7 @@ __host__ __device__ constexpr int StageBytes(int tok) { return tok * 256 + 8192 
 // the two in a fixed order.
 __host__ __device__ constexpr int IssuersFor(int tok) { return tok <= 64 ? 2 : 1; }
 __host__ __device__ constexpr int TmemColsFor(int tok) {
-  const int need = AccStagesFor(tok) * IssuersFor(tok) * tok + kAStages * kAStageCols;
+  const int need = AccStagesFor(tok) * IssuersFor(tok) * tok + AStagesFor(tok) * kAStageCols;
   return need <= 32 ? 32 : need <= 64 ? 64 : need <= 128 ? 128 : need <= 256 ? 256 : 512;
 }
 
@@ -111,21 +119,33 @@ __device__ __forceinline__ bool MbarTryWait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Post-mortem aid: when a block gives up, every warp of that block that was blocked in a wait
+// leaves (wait code, detail) in the scratch header at ints [8 + 2 * warp, 9 + 2 * warp].
+__device__ __forceinline__ void NoteBlockedWarp(int* status, int code, int detail) {
+  if (reinterpret_cast<volatile int*>(status)[1] == static_cast<int>(blockIdx.x)) {
+    status[8 + 2 * (threadIdx.x >> 5)] = code;
+    status[9 + 2 * (threadIdx.x >> 5)] = detail;
+  }
+}
 // Bounded wait.  Returns false when the block is giving up (this wait expired, or another did).
 __device__ __forceinline__ bool MbarWait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
                                          int code, int detail = 0) {
   for (uint32_t spin = 0;; ++spin) {
     if (MbarTryWait(bar, parity)) return true;
     if ((spin & 0xff) == 0xff) {
-      if (*abort_flag) return false;
+      if (*abort_flag) {
+        NoteBlockedWarp(status, code, detail);
+        return false;
+      }
       if (spin > kSpinLimit) {
-        *abort_flag = 1;
         // first expiry wins: code, then who and where (block, thread, caller's detail word)
         if (atomicCAS(status, 0, code) == 0) {
           status[1] = static_cast<int>(blockIdx.x);
           status[2] = static_cast<int>(threadIdx.x);
           status[3] = detail;
+          __threadfence();
         }
+        *abort_flag = 1;
         return false;
       }
     }
@@ -148,14 +168,18 @@ __device__ __forceinline__ bool MbarWaitWarp(unsigned mask, int leader, uint32_t
         __nanosleep(128);
         ok = MbarTryWait(bar, parity);
         if (!ok && ((++spin & 0xff) == 0xff)) {
-          if (*abort_flag) break;
+          if (*abort_flag) {
+            NoteBlockedWarp(status, code, detail);
+            break;
+          }
           if (spin > kSpinLimit) {
-            *abort_flag = 1;
             if (atomicCAS(status, 0, code) == 0) {
               status[1] = static_cast<int>(blockIdx.x);
               status[2] = static_cast<int>(threadIdx.x);
               status[3] = detail;
+              __threadfence();
             }
+            *abort_flag = 1;
             break;
           }
         }
@@ -314,6 +338,7 @@ struct Shared {
   static constexpr int kStages = StagesFor(kTok);
   static constexpr int kAcc = AccStagesFor(kTok);
   uint64_t full[kStages], empty[kStages];
+  static constexpr int kAStages = AStagesFor(kTok);
   uint64_t a_full[kAStages], a_empty[kAStages];
   uint64_t d_full[kAcc], d_empty[kAcc];
   uint32_t tmem_base;
@@ -327,6 +352,9 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
   using Sh = Shared<kTok, kSets>;
   constexpr int kStages = Sh::kStages;
   constexpr int kAcc = Sh::kAcc;
+  constexpr int kAStages = Sh::kAStages;
+  static_assert(kStages % kSets == 0 && kAStages % kSets == 0, "a ring slot must always meet the same dequantiser set");
+  static_assert(kStages % IssuersFor(kTok) == 0 && kAStages % IssuersFor(kTok) == 0, "a ring slot must always meet the same issuer");
   constexpr int kStage = StageBytes(kTok);
   constexpr int kAtomBytes = kTok * 128;  // one 64-k activation atom
   constexpr int kActBytes = 2 * kAtomBytes;
