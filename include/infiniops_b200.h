@@ -179,6 +179,24 @@ int infiniops_b200_marlin_gemm(const void* a, int a_dtype, const int32_t* b_q_we
                                int64_t num_groups, void* out, void* scratch, size_t scratch_bytes,
                                void* stream);
 
+/* The same dense GEMM for callers that have no device memory to lend and may not allocate any:
+ * an engine whose arena already owns the whole GPU, or code that only runs while its host is
+ * recording work and cudaMalloc is off limits.  The scratch is a 10 MiB array inside the library
+ * image (every GPU that loads the library holds it until the process ends); this call allocates
+ * nothing, on the device or through any library.  Limits: problems whose
+ * infiniops_b200_marlin_gemm_scratch_bytes() exceeds 10 MiB -- more than 64 activation rows on a
+ * 148-SM GPU -- are refused with IOB_SCRATCH_TOO_SMALL.  The first call on each device looks up
+ * the array's device address (cudaGetSymbolAddress), so make that first call outside any stream
+ * capture.  All calls share the one array: calls that can overlap on the GPU (different streams,
+ * no dependency) race on it and must be serialised by the caller; the split-K counters are
+ * cleared on `stream` at the start of every call.  Arguments as infiniops_b200_marlin_gemm.
+ * This entry point has no counterpart in the reference. */
+int infiniops_b200_marlin_gemm_static_scratch(const void* a, int a_dtype, const int32_t* b_q_weight,
+                                              const void* b_bias, const void* b_scales,
+                                              const int32_t* b_zeros, int64_t b_type_id,
+                                              int64_t size_m, int64_t size_n, int64_t size_k,
+                                              int64_t num_groups, void* out, void* stream);
+
 /* Bytes of scratch the routed (MoE) GEMM needs. */
 size_t infiniops_b200_moe_wna16_marlin_gemm_scratch_bytes(int64_t size_m, int64_t top_k,
                                                           int64_t size_n, int64_t size_k,

@@ -42,6 +42,8 @@ PROTOTYPES = {
     "infiniops_b200_marlin_gemm_scratch_bytes": (_sz, [_i64, _i64, _i64]),
     "infiniops_b200_marlin_gemm": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp,
                                           _sz, _vp]),
+    "infiniops_b200_marlin_gemm_static_scratch": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64,
+                                                         _vp, _vp]),
     "infiniops_b200_moe_wna16_marlin_gemm_scratch_bytes": (_sz, [_i64, _i64, _i64, _i64, _i64, _i64]),
     "infiniops_b200_moe_wna16_marlin_gemm": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64,
                                                     _int, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _vp, _vp, _sz,
@@ -172,6 +174,15 @@ def marlin_gemm(a, b_q_weight, b_bias, b_scales, b_zeros, b_type_id, size_m, siz
     _check(lib().infiniops_b200_marlin_gemm(_ptr(a), _DTYPE[a.dtype], _ptr(b_q_weight), _ptr(b_bias), _ptr(b_scales),
                                             _ptr(b_zeros), b_type_id, size_m, size_n, size_k, b_scales.shape[-2],
                                             _ptr(out), _ptr(buf), buf.numel(), _stream(stream)))
+
+
+def marlin_gemm_static_scratch(a, b_q_weight, b_bias, b_scales, b_zeros, b_type_id, size_m, size_n, size_k, out,
+                               stream=None):
+    """The dense GEMM on the library's built-in scratch array: for callers that cannot allocate
+    device memory.  Nothing is allocated here either (no torch tensor is created)."""
+    _check(lib().infiniops_b200_marlin_gemm_static_scratch(_ptr(a), _DTYPE[a.dtype], _ptr(b_q_weight), _ptr(b_bias),
+                                                           _ptr(b_scales), _ptr(b_zeros), b_type_id, size_m, size_n,
+                                                           size_k, b_scales.shape[-2], _ptr(out), _stream(stream)))
 
 
 def moe_wna16_marlin_gemm(a, b_q_weight, b_bias, b_scales, b_zeros, sorted_token_ids, expert_ids,

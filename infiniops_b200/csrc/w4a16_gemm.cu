@@ -33,6 +33,7 @@
 #include <cuda.h>
 
 #include <algorithm>
+#include <mutex>
 #include <unordered_map>
 
 #include "common.cuh"
@@ -1131,4 +1132,72 @@ extern "C" int infiniops_b200_moe_wna16_marlin_gemm(
   p.mul_weights = mul_topk_weights;
   p.out_rows = out_rows;
   return Dispatch<true>(a_dtype, b_zeros != nullptr, tok, map, w_map, p, NumSms(), s);
+}
+
+// ---- dense GEMM for callers that may not allocate device memory ---------------------------------
+//
+// Some hosts of this library cannot hand the GEMM a scratch buffer: an engine that gave all of
+// the device's memory to its own arena at start-up and has no per-operator workspace to lend, or
+// a plug-in that is only ever called from inside a region where cudaMalloc is not allowed (for
+// example while the engine records its decode step).  For them the split-K scratch lives inside
+// the library image itself, in the array below.  Every GPU that loads the library carries these
+// 10 MiB until the process exits, which is why the size is kept to what decode-sized problems
+// need: at most 64 rows of activations on a 148-SM part (the plan is 9.3 MiB there).
+namespace iob {
+namespace {
+
+constexpr size_t kStaticScratchBytes = 10u << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code `g_static_scratch` is only a handle for the symbol, not a device address, so the
+// address each device gave the array is looked up once (with that device current) and kept.
+int StaticScratchAddress(void** out) {
+  static std::mutex mutex;
+  static void* address[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) {
+    return Fail(IOB_CUDA_ERROR, "marlin_gemm_static_scratch: cannot identify the current device");
+  }
+  std::lock_guard<std::mutex> lock(mutex);
+  if (address[device] == nullptr) {
+    void* ptr = nullptr;
+    const cudaError_t err = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (err != cudaSuccess || ptr == nullptr) {
+      return Fail(IOB_CUDA_ERROR, "marlin_gemm_static_scratch: cudaGetSymbolAddress failed: %s",
+                  cudaGetErrorString(err));
+    }
+    address[device] = ptr;
+  }
+  *out = address[device];
+  return IOB_OK;
+}
+
+}  // namespace
+}  // namespace iob
+
+extern "C" int infiniops_b200_marlin_gemm_static_scratch(const void* a, int a_dtype, const int32_t* b_q_weight,
+                                                         const void* b_bias, const void* b_scales,
+                                                         const int32_t* b_zeros, int64_t b_type_id, int64_t size_m,
+                                                         int64_t size_n, int64_t size_k, int64_t num_groups,
+                                                         void* out, void* stream) {
+  using namespace iob;
+  const size_t need = infiniops_b200_marlin_gemm_scratch_bytes(size_m, size_n, size_k);
+  if (size_m <= 0 || need > kStaticScratchBytes) {
+    return Fail(IOB_SCRATCH_TOO_SMALL,
+                "marlin_gemm_static_scratch: a problem with %lld rows needs %zu bytes of scratch but the built-in "
+                "buffer holds %zu (about 64 rows); call infiniops_b200_marlin_gemm with a buffer of your own",
+                static_cast<long long>(size_m), need, kStaticScratchBytes);
+  }
+  void* scratch = nullptr;
+  if (const int rc = StaticScratchAddress(&scratch)) return rc;
+  // All calls share the buffer and find what the previous one left.  The arrival counters must
+  // start at zero: a completed call leaves them so, but one that gave up on a wait may not, so
+  // they are cleared on the stream first (a memset node, not an allocation).  The partial sums
+  // are written before they are read and need no clearing.
+  if (cudaMemsetAsync(static_cast<unsigned char*>(scratch) + kHeaderBytes, 0, 4 * kMaxGrid * sizeof(int),
+                      static_cast<cudaStream_t>(stream)) != cudaSuccess) {
+    return Fail(IOB_CUDA_ERROR, "marlin_gemm_static_scratch: clearing the counters failed");
+  }
+  return infiniops_b200_marlin_gemm(a, a_dtype, b_q_weight, b_bias, b_scales, b_zeros, b_type_id, size_m, size_n,
+                                    size_k, num_groups, out, scratch, kStaticScratchBytes, stream);
 }
