@@ -51,6 +51,23 @@ const char* infiniops_b200_last_error(void);
 /* Library version string. */
 const char* infiniops_b200_version(void);
 
+/* ---- runtime helpers (for hosts that do not link the CUDA runtime themselves) ------------------- */
+
+/* Makes `device` the current CUDA device (no-op if negative or already current) and reports the
+ * previous one, so that a caller can restore it afterwards.
+ * Replaces: the DeviceGuard of the reference's launchers,
+ * src/native/cuda/nvidia/ops/moe_sum/kernel.cu:14-41. */
+int infiniops_b200_swap_device(int device, int* previous);
+
+/* A zero-initialised scratch buffer of at least `bytes` on the current device, owned by the
+ * library, one per (calling thread, device, purpose); purpose 0 = GEMM, 1 = token sort.  It only
+ * grows; growing ALLOCATES (cudaMalloc + cudaMemset, frees the old buffer) and therefore must not
+ * happen during stream capture -- size it once up front.  Returns NULL on failure.  This is what the
+ * C++ / Python operators fall back to when the Handle carries no workspace; the kernel entry points
+ * themselves never allocate.  No counterpart in the reference (its operators that need device
+ * scratch allocate it in their constructors, src/native/cuda/ops/silu_and_mul/kernel.h:19-46). */
+void* infiniops_b200_thread_scratch(int purpose, size_t bytes);
+
 /* ---- weight repacking -------------------------------------------------------------------- */
 
 /* GPTQ-packed int32 [K/pf, N] (pf = 32/num_bits; field i of a word = row pf*(k/pf)+i),

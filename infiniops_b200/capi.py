@@ -27,6 +27,8 @@ _vp, _i64, _int, _sz, _dbl = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctyp
 PROTOTYPES = {
     "infiniops_b200_last_error": (ctypes.c_char_p, []),
     "infiniops_b200_version": (ctypes.c_char_p, []),
+    "infiniops_b200_swap_device": (_int, [_int, _vp]),
+    "infiniops_b200_thread_scratch": (_vp, [_int, _sz]),
     "infiniops_b200_gptq_marlin_repack": (_int, [_vp, _vp, _i64, _i64, _int, _int, _vp, _vp]),
     "infiniops_b200_awq_marlin_repack": (_int, [_vp, _i64, _i64, _int, _int, _vp, _vp]),
     "infiniops_b200_topk_softmax": (_int, [_vp, _int, _vp, _vp, _int, _vp, _vp, _int, _vp, _i64, _i64, _i64, _vp]),
