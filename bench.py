@@ -283,7 +283,8 @@ def run_ours(args):
                 "steps": e2e_steps, "note": "host activations in, host outputs out, one operator call per GEMM"},
         "gpu_launches": launches_per_step * args.steps,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_kind": f"of {peak_kind}", "traffic": TRAFFIC_BYTES_PER_STEP,
+                     "peak_kind": f"of {peak_kind}", "traffic": TRAFFIC_BYTES_PER_STEP if world == 1 else None,
+                     "traffic_unit": "DRAM bytes per step (16 launches), scaled from one ncu capture",
                      "kernel": "W4A16GemmKernel", "algorithmic_bytes_per_step": step_algo_bytes},
         "clocks": clocks.summary(),
     }
@@ -295,9 +296,11 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-# DRAM bytes (read + write) of the GEMM launches of one step, from an ncu capture; None until
-# a capture of this build has been summarised under profiles/.
-TRAFFIC_BYTES_PER_STEP = None
+# DRAM bytes (read + write) of the 16 GEMM launches of one step.  From the ncu capture of the
+# M=16, K=4096, N=28672 launch (profiles/w4a16_gemm_decode_m16_k4096_n28672.md): 61.79 MB measured
+# against 62.06 MB algorithmic, ratio 0.996; the other launches stream their weights once in the same
+# way, so the step's traffic is taken as its algorithmic bytes times that ratio (single GPU).
+TRAFFIC_BYTES_PER_STEP = int(465084416 * 61.79 / 62.06)
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -382,15 +385,47 @@ def run_reference(args):
     }), flush=True)
 
 
+def run_one(args):
+    """One dense AWQ bf16 GEMM `M,K,N`, launched a few times with an L2 flush in between: the small,
+    self-terminating case used for profiler captures (`ncu ... python bench.py --one 16,4096,28672`)."""
+    from infiniops_b200 import capi
+
+    m, k, n = (int(v) for v in args.one.split(","))
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator(device=dev).manual_seed(SEED)
+    awq = torch.randint(-2**31, 2**31 - 1, (k, n // 8), dtype=torch.int32, device=dev, generator=gen)
+    marlin = torch.empty((k // 16, 2 * n), dtype=torch.int32, device=dev)
+    capi.awq_marlin_repack(awq, k, n, 4, False, marlin)
+    scales = (torch.randn((k // GROUP, n), device=dev, generator=gen).abs() * 0.01 + 1e-3).bfloat16()
+    zeros = torch.randint(-2**31, 2**31 - 1, (k // GROUP, n // 8), dtype=torch.int32, device=dev, generator=gen)
+    a = torch.randn((m, k), device=dev, generator=gen).bfloat16()
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    times = []
+    for _ in range(3):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        capi.marlin_gemm(a, marlin, None, scales, zeros, capi.QTYPE_UINT4, m, n, k, out)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3)
+    print(json.dumps({"case": args.one, "us_per_launch_with_launch_gap": times,
+                      "algorithmic_bytes": algorithmic_bytes(m, k, n), "flops": 2 * m * k * n}))
+
+
 def main():
     parser = argparse.ArgumentParser()
+    parser.add_argument("--one", default=None, help="M,K,N: run this single GEMM three times (profiling case)")
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--no-cpu-baseline", action="store_true")
     args = parser.parse_args()
-    if args.impl == "reference":
+    if args.one:
+        run_one(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
