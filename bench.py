@@ -141,7 +141,7 @@ def make_layer(rank, world, device, copy_index):
 def run_ours(args):
     import torch.distributed as dist
 
-    from infiniops_b200 import capi
+    from infiniops_b200 import capi, parallel
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -177,7 +177,7 @@ def run_ours(args):
                                  w["n"], k, outs[(name, m)], stream=stream, scratch_buf=scratch)
                 launches += 1
                 if world > 1:
-                    dist.all_gather_into_tensor(gathered[(name, m)], outs[(name, m)])
+                    parallel.gather_columns(outs[(name, m)], gathered[(name, m)])
         return launches
 
     # warm-up outside any graph (function attributes, tensor maps, NCCL channels)
@@ -238,7 +238,7 @@ def run_ours(args):
                 capi.marlin_gemm(dev_in[(name, m)], w["marlin"], None, w["scales"], w["zeros"], capi.QTYPE_UINT4, m,
                                  w["n"], k, outs[(name, m)], scratch_buf=scratch)
                 if world > 1:
-                    dist.all_gather_into_tensor(gathered[(name, m)], outs[(name, m)])
+                    parallel.gather_columns(outs[(name, m)], gathered[(name, m)])
                     full = gathered[(name, m)].permute(1, 0, 2).reshape(m, n)
                     host_out[(name, m)].copy_(full, non_blocking=True)
                 else:
@@ -290,7 +290,7 @@ def run_ours(args):
     }
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
-            result["cpu_baseline"] = cpu_baseline(layers[0], sample_ms=(16,), repeats=2)
+            result["cpu_baseline"] = cpu_baseline(layers[0], sample_ms=MS, repeats=12)
         print(json.dumps(result), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -343,7 +343,8 @@ def cpu_baseline(layer, sample_ms, repeats):
         best = min(best, time.perf_counter() - t0)
     nbytes = sum(weight_bytes(k, n) for _, (_, _, _, k, n) in problem.items()) * len(sample_ms)
     return {"value": nbytes / best / 1e9, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"the four linears at M in {list(sample_ms)}, best of {repeats} passes ({best:.2f} s per pass)"}
+            "sample": f"the four linears at M in {list(sample_ms)}, best of {repeats} passes "
+                      f"({best:.2f} s per pass, {best * repeats:.0f} s of CPU work)"}
 
 
 def run_reference(args):
@@ -385,6 +386,97 @@ def run_reference(args):
     }), flush=True)
 
 
+def run_moe(args):
+    """Mixtral-8x7B-shaped MoE layer (BASELINE.json configs[3]): E=8, top-2, hidden 4096, intermediate 14336,
+    GPTQ-symmetric int4 g=128, bf16; router topk_softmax -> moe_align_block_size(64) -> w13 GEMM -> silu_and_mul
+    -> w2 GEMM -> moe_sum.  Metric: tokens/s of the whole layer for `--tokens` tokens (global).  With N > 1 the
+    experts are split over the ranks and the tokens are data-parallel (T/N each) with all-to-all dispatch and
+    combine (strong scaling: the same global batch for every N)."""
+    import torch.distributed as dist
+
+    from infiniops_b200 import capi, moe_layer, parallel
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    experts, top_k, hidden, inter, block = 8, 2, 4096, 14336, 64
+    e_local = experts // world
+    t_local = max(1, args.tokens // world)
+    gen = torch.Generator(device=dev).manual_seed(SEED + 3000 + rank)
+
+    def packed(k, n):
+        out = torch.empty((e_local, k // 16, 2 * n), dtype=torch.int32, device=dev)
+        for e in range(e_local):
+            src = torch.randint(-2**31, 2**31 - 1, (k // 8, n), dtype=torch.int32, device=dev, generator=gen)
+            capi.gptq_marlin_repack(src, None, k, n, 4, False, out[e])
+        scales = (torch.randn((e_local, k // GROUP, n), device=dev, generator=gen).abs() * 0.01 + 1e-3).bfloat16()
+        return out, scales
+
+    w13, s13 = packed(hidden, 2 * inter)
+    w2, s2 = packed(inter, hidden)
+    runner = moe_layer.RoutedExperts(moe_layer.ExpertWeights(w13, s13, None, w2, s2, None, hidden, inter), block)
+    x = torch.randn((t_local, hidden), device=dev, generator=gen).bfloat16()
+    logits = torch.randn((t_local, experts), device=dev, generator=gen)
+    launches = [0]
+
+    def step():
+        weights, ids = moe_layer.route_softmax(logits, top_k)
+        if world == 1:
+            launches[0] = 8   # router, sort, 2 x (gather + GEMM), silu_and_mul, moe_sum
+            return moe_layer.single_gpu_layer(x, weights, ids, runner)
+        launches[0] = 9
+        return parallel.expert_parallel_layer(
+            x, ids, weights, experts, top_k, runner,
+            lambda routed: _moe_sum(capi, routed))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    steps = min(args.steps, 50)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            out = step()
+        e1.record()
+        barrier()
+    ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_per_step = float(ms) / steps
+    assert capi.scratch_status(capi.scratch(dev, 0)) == 0
+    tokens = t_local * world
+    flops = tokens * top_k * (2 * hidden * 2 * inter + 2 * inter * hidden)
+    if rank == 0:
+        print(json.dumps({
+            "metric": "MoE tokens/s", "value": tokens / (ms_per_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"configs[3]: Mixtral-8x7B-shaped MoE layer, E=8 top-2 H=4096 I=14336, T={tokens}",
+                       "parallelism": "single GPU" if world == 1 else f"expert-parallel x{world}, NCCL all-to-all",
+                       "l2": "inputs larger than L2: 705 MB of expert weights per layer pass"},
+            "tflops": flops / (ms_per_step * 1e-3) / 1e12, "gpu_launches": launches[0] * steps,
+            "clocks": clocks.summary()}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def _moe_sum(capi, routed):
+    out = torch.empty((routed.shape[0], routed.shape[2]), dtype=routed.dtype, device=routed.device)
+    capi.moe_sum(routed, out)
+    return out
+
+
 def run_one(args):
     """One dense AWQ bf16 GEMM `M,K,N`, launched a few times with an L2 flush in between: the small,
     self-terminating case used for profiler captures (`ncu ... python bench.py --one 16,4096,28672`)."""
@@ -416,6 +508,9 @@ def run_one(args):
 
 def main():
     parser = argparse.ArgumentParser()
+    parser.add_argument("--workload", default="decode", choices=("decode", "moe"),
+                        help="decode = the headline W4A16 decode step; moe = Mixtral-shaped MoE layer, tokens/s")
+    parser.add_argument("--tokens", type=int, default=1024, help="global tokens of the MoE workload")
     parser.add_argument("--one", default=None, help="M,K,N: run this single GEMM three times (profiling case)")
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=200)
@@ -425,6 +520,8 @@ def main():
     args = parser.parse_args()
     if args.one:
         run_one(args)
+    elif args.workload == "moe" and args.impl == "ours":
+        run_moe(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

@@ -1,0 +1,120 @@
+"""The MoE operator chain as a caller strings it together (the reference ships the operators,
+not this caller): router -> moe_align_block_size -> moe_wna16_marlin_gemm (w13) -> silu_and_mul
+-> moe_wna16_marlin_gemm (w2, x routing weight) -> moe_sum.  Used by the tests, the smoke check
+and the MoE benchmark; every step is a call into the CUDA library through `capi`.
+"""
+
+from __future__ import annotations
+
+import dataclasses
+
+import torch
+
+from . import capi
+
+
+def padded_sizes(numel: int, num_experts: int, block: int) -> tuple[int, int]:
+    size = numel + num_experts * (block - 1)
+    if numel < num_experts:
+        size = min(numel * block, size)
+    return size, (size + block - 1) // block
+
+
+@dataclasses.dataclass
+class ExpertWeights:
+    """Marlin-packed experts of one rank: w13 [E, H/16, 2*2I], w2 [E, I/16, 2H], scales, optional zeros."""
+    w13: torch.Tensor
+    s13: torch.Tensor
+    z13: torch.Tensor | None
+    w2: torch.Tensor
+    s2: torch.Tensor
+    z2: torch.Tensor | None
+    hidden: int
+    inter: int
+
+    @property
+    def num_experts(self) -> int:
+        return self.w13.shape[0]
+
+    @property
+    def qtype(self) -> int:
+        return capi.QTYPE_UINT4 if self.z13 is not None else capi.QTYPE_UINT4B8
+
+
+class RoutedExperts:
+    """Runs a set of experts on rows that each name ONE expert (top-1 form).  A token with k experts
+    appears as k rows; this is also exactly what an expert-parallel rank receives."""
+
+    def __init__(self, weights: ExpertWeights, block: int = 64):
+        self.w, self.block = weights, block
+        self._buffers: dict = {}
+
+    def _buf(self, name, shape, dtype, device):
+        key = (name, tuple(shape), dtype)
+        t = self._buffers.get(key)
+        if t is None:
+            t = torch.empty(shape, dtype=dtype, device=device)
+            self._buffers[key] = t
+        return t
+
+    def __call__(self, rows: torch.Tensor, expert: torch.Tensor, weights: torch.Tensor, stream=None) -> torch.Tensor:
+        w, block, dev = self.w, self.block, rows.device
+        r = rows.shape[0]
+        out = self._buf("y", (r, w.hidden), rows.dtype, dev)
+        if r == 0:
+            return out
+        size, blocks = padded_sizes(r, w.num_experts, block)
+        sorted_ids = self._buf("sorted", (size,), torch.int32, dev)
+        expert_ids = self._buf("eids", (blocks,), torch.int32, dev)
+        npost = self._buf("npost", (1,), torch.int32, dev)
+        capi.moe_align_block_size(expert.view(r, 1), None, w.num_experts, block, sorted_ids, expert_ids, npost,
+                                  stream=stream)
+        g = self._buf("g", (r, 2 * w.inter), rows.dtype, dev)
+        capi.moe_wna16_marlin_gemm(rows, w.w13, None, w.s13, w.z13, sorted_ids, expert_ids, npost, weights, block, 1,
+                                   False, w.qtype, r, 2 * w.inter, w.hidden, g, stream=stream)
+        h = self._buf("h", (r, w.inter), rows.dtype, dev)
+        capi.silu_and_mul(g, h, stream=stream)
+        capi.moe_wna16_marlin_gemm(h, w.w2, None, w.s2, w.z2, sorted_ids, expert_ids, npost, weights, block, 1, True,
+                                   w.qtype, r, w.hidden, w.inter, out, stream=stream)
+        return out
+
+
+def route_softmax(logits: torch.Tensor, top_k: int, renormalize: bool = True, stream=None):
+    t = logits.shape[0]
+    w = torch.empty((t, top_k), dtype=torch.float32, device=logits.device)
+    ids = torch.empty((t, top_k), dtype=torch.int32, device=logits.device)
+    tei = torch.empty((t, top_k), dtype=torch.int32, device=logits.device)
+    capi.topk_softmax(logits, None, None, renormalize, w, ids, tei, stream=stream)
+    return w, ids
+
+
+def route_grouped(scores, bias, groups, topk_group, top_k, scaling, stream=None):
+    t = scores.shape[0]
+    w = torch.empty((t, top_k), dtype=torch.float32, device=scores.device)
+    ids = torch.empty((t, top_k), dtype=torch.int32, device=scores.device)
+    capi.grouped_topk(scores, bias, groups, topk_group, top_k, True, scaling, 1, w, ids, stream=stream)
+    return w, ids
+
+
+def single_gpu_layer(x, topk_weights, topk_ids, experts: RoutedExperts, stream=None) -> torch.Tensor:
+    """The layer on one GPU in the reference's chaining: the sort runs on the [T, k] ids and the first
+    GEMM reads token `route // k` directly (no row duplication)."""
+    w, block, dev = experts.w, experts.block, x.device
+    t, k = topk_ids.shape
+    size, blocks = padded_sizes(t * k, w.num_experts, block)
+    sorted_ids = experts._buf("L_sorted", (size,), torch.int32, dev)
+    expert_ids = experts._buf("L_eids", (blocks,), torch.int32, dev)
+    npost = experts._buf("L_npost", (1,), torch.int32, dev)
+    capi.moe_align_block_size(topk_ids, None, w.num_experts, block, sorted_ids, expert_ids, npost, stream=stream)
+    flat_w = topk_weights.reshape(-1)
+    g = experts._buf("L_g", (t * k, 2 * w.inter), x.dtype, dev)
+    capi.moe_wna16_marlin_gemm(x, w.w13, None, w.s13, w.z13, sorted_ids, expert_ids, npost, flat_w, block, k, False,
+                               w.qtype, t, 2 * w.inter, w.hidden, g, stream=stream)
+    h = experts._buf("L_h", (t * k, w.inter), x.dtype, dev)
+    capi.silu_and_mul(g, h, stream=stream)
+    y = experts._buf("L_y", (t * k, w.hidden), x.dtype, dev)
+    capi.moe_wna16_marlin_gemm(h, w.w2, None, w.s2, w.z2, sorted_ids, expert_ids, npost, flat_w, block, 1, True,
+                               w.qtype, t * k, w.hidden, w.inter, y, stream=stream)
+    out = experts._buf("L_out", (t, w.hidden), x.dtype, dev)
+    capi.moe_sum(y.view(t, k, w.hidden), out, stream=stream)
+    return out

@@ -1,0 +1,133 @@
+"""Host-side plumbing for the two ways this path shards across GPUs (one process per GPU).
+
+The reference has no communication layer at all; both schemes are additions around its operators.
+
+* Dense linears: column-parallel.  Rank r holds output columns [r N/g, (r+1) N/g) of the packed
+  weight, scales and zero points, runs the GEMM on its slice, and the [M, N/g] slices are
+  all-gathered (`gather_columns`).
+* MoE layers: expert-parallel.  Rank r owns experts [r E/g, (r+1) E/g); tokens are data-parallel.
+  Routed rows travel to the owner of their expert with one variable-size all-to-all (`dispatch`),
+  are processed there as a top-1 problem over the local experts, and travel back with a second
+  all-to-all (`combine`); the token owner then sums its k slots.
+
+Everything here is torch.distributed (NCCL on GPUs, gloo in the CPU tests) and index arithmetic;
+the arithmetic kernels are passed in by the caller, so the same code is exercised on CPU with the
+oracle standing in for the CUDA operators.
+"""
+
+from __future__ import annotations
+
+import dataclasses
+
+import torch
+import torch.distributed as dist
+
+
+# ---- dense: column-parallel -------------------------------------------------------------------------
+def column_range(n: int, rank: int, world: int) -> tuple[int, int]:
+    """Output columns of `rank`; every shard must stay a multiple of 64 columns (repack tile)."""
+    if n % world or (n // world) % 64:
+        raise ValueError(f"N={n} cannot be split into {world} shards of a multiple of 64 columns")
+    width = n // world
+    return rank * width, (rank + 1) * width
+
+
+def shard_columns(packed, scales, zeros_packed, n: int, rank: int, world: int, source: str):
+    """Column shard of a GPTQ- ([K/8, N]) or AWQ-packed ([K, N/8]) weight with its scales [G, N] and
+    packed zero points [G, N/8].  Sharding happens BEFORE the Marlin repack, which each rank then
+    runs on its own slice."""
+    lo, hi = column_range(n, rank, world)
+    if source == "gptq":
+        w = packed[:, lo:hi]
+    elif source == "awq":
+        w = packed[:, lo // 8:hi // 8]
+    else:
+        raise ValueError(source)
+    z = None if zeros_packed is None else zeros_packed[:, lo // 8:hi // 8].contiguous()
+    return w.contiguous(), scales[:, lo:hi].contiguous(), z
+
+
+def gather_columns(out_local: torch.Tensor, gathered: torch.Tensor | None = None, group=None) -> torch.Tensor:
+    """All-gathers [M, N/g] slices; returns the [g, M, N/g] buffer (rank-major).  `as_matrix` turns it
+    into [M, N]."""
+    world = dist.get_world_size(group)
+    if gathered is None:
+        gathered = out_local.new_empty((world, *out_local.shape))
+    # flat [g*M, N/g] view: the form every backend accepts
+    dist.all_gather_into_tensor(gathered.view(-1, out_local.shape[-1]), out_local.contiguous(), group=group)
+    return gathered
+
+
+def as_matrix(gathered: torch.Tensor) -> torch.Tensor:
+    g, m, width = gathered.shape
+    return gathered.permute(1, 0, 2).reshape(m, g * width)
+
+
+# ---- MoE: expert-parallel -----------------------------------------------------------------------
+@dataclasses.dataclass
+class DispatchPlan:
+    """Where every routed (token, slot) pair of this rank goes and how to put the answers back."""
+    order: torch.Tensor        # [T*k] routes sorted by destination rank (stable), as flat route ids
+    send_counts: list[int]     # rows sent to each rank
+    recv_counts: list[int]     # rows received from each rank
+    local_expert: torch.Tensor  # [sum(recv)] expert index on this rank of every received row
+    weights: torch.Tensor      # [sum(recv)] routing weight of every received row
+
+
+def experts_per_rank(num_experts: int, world: int) -> int:
+    if num_experts % world:
+        raise ValueError(f"{num_experts} experts cannot be split evenly over {world} ranks")
+    return num_experts // world
+
+
+def plan_dispatch(topk_ids: torch.Tensor, topk_weights: torch.Tensor, num_experts: int, group=None) -> DispatchPlan:
+    """Exchanges per-rank row counts, then expert ids and routing weights of the rows."""
+    world = dist.get_world_size(group)
+    per_rank = experts_per_rank(num_experts, world)
+    flat_ids = topk_ids.reshape(-1).to(torch.int64)
+    dest = torch.div(flat_ids, per_rank, rounding_mode="floor")
+    order = torch.argsort(dest, stable=True)
+    send = torch.bincount(dest, minlength=world).to(torch.int64)
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send, group=group)
+    send_counts, recv_counts = send.tolist(), recv.tolist()   # host sync: the split sizes of the next calls
+    total = sum(recv_counts)
+    local_out = (flat_ids[order] % per_rank).to(torch.int32)
+    local_in = local_out.new_empty(total)
+    dist.all_to_all_single(local_in, local_out, recv_counts, send_counts, group=group)
+    w_out = topk_weights.reshape(-1)[order].to(torch.float32)
+    w_in = w_out.new_empty(total)
+    dist.all_to_all_single(w_in, w_out, recv_counts, send_counts, group=group)
+    return DispatchPlan(order, send_counts, recv_counts, local_in, w_in)
+
+
+def dispatch(x: torch.Tensor, top_k: int, plan: DispatchPlan, group=None) -> torch.Tensor:
+    """Sends row `route // top_k` of x for every route, grouped by destination; returns the rows this
+    rank has to process, [sum(recv), H]."""
+    rows = x[torch.div(plan.order, top_k, rounding_mode="floor")].contiguous()
+    out = x.new_empty((sum(plan.recv_counts), x.shape[1]))
+    dist.all_to_all_single(out, rows, plan.recv_counts, plan.send_counts, group=group)
+    return out
+
+
+def combine(y: torch.Tensor, plan: DispatchPlan, group=None) -> torch.Tensor:
+    """Inverse of `dispatch`: returns [T*k, H] in flat route order (row t*k + slot)."""
+    back = y.new_empty((sum(plan.send_counts), y.shape[1]))
+    dist.all_to_all_single(back, y.contiguous(), plan.send_counts, plan.recv_counts, group=group)
+    out = torch.empty_like(back)
+    out[plan.order] = back
+    return out
+
+
+def expert_parallel_layer(x, topk_ids, topk_weights, num_experts, top_k, local_experts_forward, moe_sum, group=None):
+    """One MoE layer, expert-parallel.
+
+    `local_experts_forward(rows [R, H], local_expert [R] int32, weights [R] f32) -> [R, H]` runs this rank's
+    experts on the received rows (sort, two routed GEMMs with silu_and_mul between, routing weight
+    applied); `moe_sum([T, k, H]) -> [T, H]` adds a token's slots.
+    """
+    plan = plan_dispatch(topk_ids, topk_weights, num_experts, group)
+    rows = dispatch(x, top_k, plan, group)
+    y = local_experts_forward(rows, plan.local_expert, plan.weights)
+    routed = combine(y, plan, group)
+    return moe_sum(routed.view(x.shape[0], top_k, x.shape[1]))
