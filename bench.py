@@ -293,7 +293,7 @@ def run_ours(args):
             result["cpu_baseline"] = cpu_baseline(layers[0], sample_ms=MS, repeats=12)
         print(json.dumps(result), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        _shutdown(dist, graphs)
 
 
 # DRAM bytes (read + write) of the 16 GEMM launches of one step.  From the ncu capture of the
@@ -468,7 +468,22 @@ def run_moe(args):
             "tflops": flops / (ms_per_step * 1e-3) / 1e12, "gpu_launches": launches[0] * steps,
             "clocks": clocks.summary()}), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        _shutdown(dist)
+
+
+def _shutdown(dist, graphs=None):
+    """Releases captured graphs (they hold NCCL kernels) before the process group goes away; a
+    watchdog ends the process if the teardown itself blocks -- the result line is already out."""
+    import gc
+    import threading
+
+    threading.Thread(target=lambda: (time.sleep(20), os._exit(0)), daemon=True).start()
+    if graphs is not None:
+        graphs.clear()
+    gc.collect()
+    torch.cuda.synchronize()
+    dist.barrier()
+    dist.destroy_process_group()
 
 
 def _moe_sum(capi, routed):
