@@ -68,14 +68,15 @@ __host__ __device__ constexpr int StagesFor(int tok) {
 __host__ __device__ constexpr int SetsFor(int tok) { return tok <= 32 ? 3 : tok <= 128 ? 2 : 3; }
 // Tensor-memory stages of dequantised weights (64 columns each).
 __host__ __device__ constexpr int AStagesFor(int tok) { return tok <= 32 ? 6 : tok <= 128 ? 4 : 3; }
-__host__ __device__ constexpr int AccStagesFor(int tok) { return tok <= 128 ? 2 : 1; }
+// accumulator stages (so the epilogue of one segment overlaps the next); limited by the 512 columns
+__host__ __device__ constexpr int AccStagesFor(int tok) { return tok == 32 || tok > 128 ? 1 : 2; }
 // activations (two swizzle atoms of tok x 128 B) | packed weights 8 KB | 2 scale rows | 2 zero rows
 __host__ __device__ constexpr int StageBytes(int tok) { return tok * 256 + 8192 + 1024; }
 // MMA-issuing threads.  One thread cannot keep the tensor pipe busy when a stage is only a few
 // hundred cycles of MMA work (its barrier wait and commits are not overlapped), so small token
-// tiles use two issuers on alternating stages, each with its own accumulator; the epilogue adds
-// the two in a fixed order.
-__host__ __device__ constexpr int IssuersFor(int tok) { return tok <= 64 ? 2 : 1; }
+// tiles use two or three issuers on alternating stages, each with its own accumulator; the epilogue
+// adds them in a fixed order.
+__host__ __device__ constexpr int IssuersFor(int tok) { return tok <= 32 ? 3 : tok <= 64 ? 2 : 1; }
 __host__ __device__ constexpr int TmemColsFor(int tok) {
   const int need = AccStagesFor(tok) * IssuersFor(tok) * tok + AStagesFor(tok) * kAStageCols;
   return need <= 32 ? 32 : need <= 64 ? 64 : need <= 128 ? 128 : need <= 256 ? 256 : 512;
@@ -701,16 +702,17 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
 #pragma unroll
           for (int j = 0; j < 16; ++j) r[j] = 0u;
         }
-        if constexpr (kIssuers == 2) {
-          if (present[1]) {
+        TmemWaitLd();
+#pragma unroll
+        for (int other = 1; other < kIssuers; ++other) {
+          if (present[other]) {
             uint32_t r1[16];
-            TmemLoad16(d_addr + kTok + c, r1);
+            TmemLoad16(d_addr + other * kTok + c, r1);
             TmemWaitLd();
 #pragma unroll
             for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r1[j]));
           }
         }
-        TmemWaitLd();
         if (whole) {
           if (n_ok) {
 #pragma unroll

@@ -6,7 +6,8 @@ The reference has no communication layer at all; both schemes are additions arou
   weight, scales and zero points, runs the GEMM on its slice, and the [M, N/g] slices are
   all-gathered (`gather_columns`).
 * MoE layers: expert-parallel.  Rank r owns experts [r E/g, (r+1) E/g); tokens are data-parallel.
-  Routed rows travel to the owner of their expert with one variable-size all-to-all (`dispatch`),
+  After a count exchange, routed rows travel to the owner of their expert with one variable-size
+  all-to-all that also carries each row's expert index and routing weight (`dispatch`),
   are processed there as a top-1 problem over the local experts, and travel back with a second
   all-to-all (`combine`); the token owner then sums its k slots.
 
@@ -70,8 +71,8 @@ class DispatchPlan:
     order: torch.Tensor        # [T*k] routes sorted by destination rank (stable), as flat route ids
     send_counts: list[int]     # rows sent to each rank
     recv_counts: list[int]     # rows received from each rank
-    local_expert: torch.Tensor  # [sum(recv)] expert index on this rank of every received row
-    weights: torch.Tensor      # [sum(recv)] routing weight of every received row
+    local_expert: torch.Tensor | None = None   # [sum(recv)] expert index on this rank of every received row
+    weights: torch.Tensor | None = None        # [sum(recv)] routing weight of every received row
 
 
 def experts_per_rank(num_experts: int, world: int) -> int:
@@ -80,34 +81,45 @@ def experts_per_rank(num_experts: int, world: int) -> int:
     return num_experts // world
 
 
-def plan_dispatch(topk_ids: torch.Tensor, topk_weights: torch.Tensor, num_experts: int, group=None) -> DispatchPlan:
-    """Exchanges per-rank row counts, then expert ids and routing weights of the rows."""
+def plan_dispatch(topk_ids: torch.Tensor, num_experts: int, group=None) -> DispatchPlan:
+    """Sorts this rank's routes by owner of their expert and exchanges the per-rank row counts (the
+    one place the host has to read device data: the split sizes of the payload exchange)."""
     world = dist.get_world_size(group)
     per_rank = experts_per_rank(num_experts, world)
-    flat_ids = topk_ids.reshape(-1).to(torch.int64)
-    dest = torch.div(flat_ids, per_rank, rounding_mode="floor")
+    dest = torch.div(topk_ids.reshape(-1).to(torch.int64), per_rank, rounding_mode="floor")
     order = torch.argsort(dest, stable=True)
     send = torch.bincount(dest, minlength=world).to(torch.int64)
     recv = torch.empty_like(send)
     dist.all_to_all_single(recv, send, group=group)
-    send_counts, recv_counts = send.tolist(), recv.tolist()   # host sync: the split sizes of the next calls
-    total = sum(recv_counts)
-    local_out = (flat_ids[order] % per_rank).to(torch.int32)
-    local_in = local_out.new_empty(total)
-    dist.all_to_all_single(local_in, local_out, recv_counts, send_counts, group=group)
-    w_out = topk_weights.reshape(-1)[order].to(torch.float32)
-    w_in = w_out.new_empty(total)
-    dist.all_to_all_single(w_in, w_out, recv_counts, send_counts, group=group)
-    return DispatchPlan(order, send_counts, recv_counts, local_in, w_in)
+    counts = torch.stack((send, recv)).tolist()
+    return DispatchPlan(order, counts[0], counts[1])
 
 
-def dispatch(x: torch.Tensor, top_k: int, plan: DispatchPlan, group=None) -> torch.Tensor:
-    """Sends row `route // top_k` of x for every route, grouped by destination; returns the rows this
-    rank has to process, [sum(recv), H]."""
-    rows = x[torch.div(plan.order, top_k, rounding_mode="floor")].contiguous()
-    out = x.new_empty((sum(plan.recv_counts), x.shape[1]))
-    dist.all_to_all_single(out, rows, plan.recv_counts, plan.send_counts, group=group)
-    return out
+def _meta_slots(dtype: torch.dtype) -> int:
+    """Elements of `dtype` that hold one 32-bit word."""
+    return 4 // torch.empty((), dtype=dtype).element_size()
+
+
+def dispatch(x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, num_experts: int,
+             plan: DispatchPlan, group=None) -> torch.Tensor:
+    """One all-to-all carrying, per route, row `route // k` of x followed by two 32-bit words (expert
+    index on the owner, routing weight) packed into spare columns.  Returns the rows this rank has to
+    process, [sum(recv), H], and fills `plan.local_expert` / `plan.weights`."""
+    top_k = topk_ids.shape[1]
+    hidden = x.shape[1]
+    slots = _meta_slots(x.dtype)
+    per_rank = experts_per_rank(num_experts, dist.get_world_size(group))
+    out_buf = x.new_empty((plan.order.numel(), hidden + 2 * slots))
+    out_buf[:, :hidden] = x[torch.div(plan.order, top_k, rounding_mode="floor")]
+    meta = torch.stack(((topk_ids.reshape(-1)[plan.order].to(torch.int32) % per_rank),
+                        topk_weights.reshape(-1)[plan.order].to(torch.float32).view(torch.int32)), dim=1)
+    out_buf[:, hidden:] = meta.view(x.dtype).view(-1, 2 * slots)
+    in_buf = x.new_empty((sum(plan.recv_counts), hidden + 2 * slots))
+    dist.all_to_all_single(in_buf, out_buf, plan.recv_counts, plan.send_counts, group=group)
+    meta_in = in_buf[:, hidden:].contiguous().view(torch.int32)
+    plan.local_expert = meta_in[:, 0].contiguous()
+    plan.weights = meta_in[:, 1].contiguous().view(torch.float32)
+    return in_buf[:, :hidden].contiguous()
 
 
 def combine(y: torch.Tensor, plan: DispatchPlan, group=None) -> torch.Tensor:
@@ -126,8 +138,8 @@ def expert_parallel_layer(x, topk_ids, topk_weights, num_experts, top_k, local_e
     experts on the received rows (sort, two routed GEMMs with silu_and_mul between, routing weight
     applied); `moe_sum([T, k, H]) -> [T, H]` adds a token's slots.
     """
-    plan = plan_dispatch(topk_ids, topk_weights, num_experts, group)
-    rows = dispatch(x, top_k, plan, group)
+    plan = plan_dispatch(topk_ids, num_experts, group)
+    rows = dispatch(x, topk_ids, topk_weights, num_experts, plan, group)
     y = local_experts_forward(rows, plan.local_expert, plan.weights)
     routed = combine(y, plan, group)
     return moe_sum(routed.view(x.shape[0], top_k, x.shape[1]))

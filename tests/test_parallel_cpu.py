@@ -118,10 +118,17 @@ def _all_to_one_rank(rank):
 
     ids = torch.tensor([[0, 1], [1, 2]], dtype=torch.int32)       # experts 0..3 live on rank 0 (E = 8)
     w = torch.full((2, 2), 0.5)
-    x = torch.arange(8, dtype=torch.float32).reshape(2, 4) + 10 * rank
-    plan = parallel.plan_dispatch(ids, w, 8)
-    rows = parallel.dispatch(x, 2, plan)
+    for dtype in (torch.float32, torch.bfloat16):     # 32-bit metadata rides in 1 or 2 spare columns
+        _one_rank_case(parallel, rank, ids, w, dtype)
+
+
+def _one_rank_case(parallel, rank, ids, w, dtype):
+    x = (torch.arange(8, dtype=torch.float32).reshape(2, 4) + 10 * rank).to(dtype)
+    plan = parallel.plan_dispatch(ids, 8)
+    rows = parallel.dispatch(x, ids, w, 8, plan)
     assert rows.shape[0] == (8 if rank == 0 else 0)
+    if rank == 0:
+        assert plan.local_expert.tolist() == [0, 1, 1, 2, 0, 1, 1, 2] and bool((plan.weights == 0.5).all())
     back = parallel.combine(rows * 2, plan)
     torch.testing.assert_close(back, x.repeat_interleave(2, dim=0) * 2)
 
