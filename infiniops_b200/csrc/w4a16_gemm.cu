@@ -76,9 +76,16 @@ __host__ __device__ constexpr int StageBytes(int tok) { return tok * 256 + 8192 
 // hundred cycles of MMA work (its barrier wait and commits are not overlapped), so small token
 // tiles use two or three issuers on alternating stages, each with its own accumulator; the epilogue
 // adds them in a fixed order.
-__host__ __device__ constexpr int IssuersFor(int tok) { return tok <= 32 ? 3 : tok <= 64 ? 2 : 1; }
+__host__ __device__ constexpr int IssuersFor(int tok) { return tok <= 32 ? 3 : tok <= 64 ? 2 : tok <= 128 ? 1 : 2; }
+// With a 256-token tile the two issuers do not alternate stages: both take every stage and each
+// issues the MMAs of one half of the token columns (N = 128 each, same total pipe time), writing
+// disjoint columns of one accumulator.  (For N <= 128 an MMA costs 64 cycles whatever N is, so
+// halving N would only double the pipe time; there the issuers alternate instead.)
+__host__ __device__ constexpr bool SplitTokens(int tok) { return tok > 128; }
+// independent accumulators per accumulator stage
+__host__ __device__ constexpr int AccSetsFor(int tok) { return SplitTokens(tok) ? 1 : IssuersFor(tok); }
 __host__ __device__ constexpr int TmemColsFor(int tok) {
-  const int need = AccStagesFor(tok) * IssuersFor(tok) * tok + AStagesFor(tok) * kAStageCols;
+  const int need = AccStagesFor(tok) * AccSetsFor(tok) * tok + AStagesFor(tok) * kAStageCols;
   return need <= 32 ? 32 : need <= 64 ? 64 : need <= 128 ? 128 : need <= 256 ? 256 : 512;
 }
 
@@ -167,7 +174,7 @@ __device__ __forceinline__ bool MbarWaitWarp(unsigned mask, int leader, uint32_t
       }
       uint32_t spin = 0;
       while (!ok) {
-        __nanosleep(128);
+        __nanosleep(64);
         ok = MbarTryWait(bar, parity);
         if (!ok && ((++spin & 0xff) == 0xff)) {
           if (*abort_flag) {
@@ -356,7 +363,8 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
   constexpr int kAcc = Sh::kAcc;
   constexpr int kAStages = Sh::kAStages;
   static_assert(kStages % kSets == 0 && kAStages % kSets == 0, "a ring slot must always meet the same dequantiser set");
-  static_assert(kStages % IssuersFor(kTok) == 0 && kAStages % IssuersFor(kTok) == 0, "a ring slot must always meet the same issuer");
+  static_assert(SplitTokens(kTok) || (kStages % IssuersFor(kTok) == 0 && kAStages % IssuersFor(kTok) == 0),
+                "a ring slot must always meet the same issuer");
   constexpr int kStage = StageBytes(kTok);
   constexpr int kAtomBytes = kTok * 128;  // one 64-k activation atom
   constexpr int kActBytes = 2 * kAtomBytes;
@@ -366,9 +374,13 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
   constexpr int kTmemCols = TmemColsFor(kTok);
   constexpr int kDequantWarps = 4 * kSets;
   constexpr int kIssuers = IssuersFor(kTok);
+  constexpr bool kSplit = SplitTokens(kTok);
+  constexpr int kAccSets = AccSetsFor(kTok);
+  constexpr int kIssueStride = kSplit ? 1 : kIssuers;  // an issuer takes every kIssueStride-th stage
+  constexpr int kMmaN = kSplit ? kTok / 2 : kTok;
   constexpr int kFirstDq = 1 + kIssuers;  // warp 0 producer, then the issuers, dequantisers, epilogue
   constexpr uint32_t kIdesc = (1u << 4) | (Half2Of<T>::kFormat << 7) | (Half2Of<T>::kFormat << 10) |
-                              (static_cast<uint32_t>(kTok >> 3) << 17) | (static_cast<uint32_t>(kTileN >> 4) << 24);
+                              (static_cast<uint32_t>((SplitTokens(kTok) ? kTok / 2 : kTok) >> 3) << 17) | (static_cast<uint32_t>(kTileN >> 4) << 24);
 
   extern __shared__ unsigned char smem_dyn[];
   __shared__ Sh sh;
@@ -390,8 +402,18 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
   const long long total_units = static_cast<long long>(n_tiles) * m_tiles * k_stages;
   // Never more ranges than units: an empty range between two sharers of a tile would break the
   // arrival count of the tile.  Surplus blocks get nothing to do.
-  const long long grid = total_units < static_cast<long long>(gridDim.x) ? (total_units > 0 ? total_units : 1)
-                                                                          : static_cast<long long>(gridDim.x);
+  long long grid = total_units < static_cast<long long>(gridDim.x) ? (total_units > 0 ? total_units : 1)
+                                                                    : static_cast<long long>(gridDim.x);
+  // Few tiles: use a multiple of the tile count.  Then every range lies inside one tile (plain
+  // split-K), so a block has a single segment and a single hand-over instead of two ragged ones --
+  // worth more than the last few SMs when the whole GEMM is only a handful of stages per block.
+  {
+    const long long tiles = static_cast<long long>(n_tiles) * m_tiles;
+    if (tiles > 0 && tiles <= grid) {
+      const long long splits = grid / tiles < k_stages ? grid / tiles : k_stages;
+      if (tiles * splits * 5 >= grid * 4) grid = tiles * splits;
+    }
+  }
   const bool idle = static_cast<long long>(blockIdx.x) >= grid || total_units == 0;
   const long long u_begin = idle ? 0 : RangeStart(blockIdx.x, total_units, grid);
   const long long u_end = idle ? 0 : RangeStart(blockIdx.x + 1, total_units, grid);
@@ -399,11 +421,11 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
       MbarInit(SmemAddr(&sh.full[i]), 1);
-      MbarInit(SmemAddr(&sh.empty[i]), 5);
+      MbarInit(SmemAddr(&sh.empty[i]), 4 + (kSplit ? kIssuers : 1));
     }
     for (int i = 0; i < kAStages; ++i) {
       MbarInit(SmemAddr(&sh.a_full[i]), 4);
-      MbarInit(SmemAddr(&sh.a_empty[i]), 1);
+      MbarInit(SmemAddr(&sh.a_empty[i]), kSplit ? kIssuers : 1);
     }
     for (int i = 0; i < kAcc; ++i) {
       MbarInit(SmemAddr(&sh.d_full[i]), kIssuers);
@@ -427,7 +449,7 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
   TcFenceAfter();
   const uint32_t tmem_base = sh.tmem_base;
   const uint32_t tmem_d = tmem_base;  // accumulators: kAcc stages x kIssuers x kTok columns
-  const uint32_t tmem_a = tmem_base + kAcc * kIssuers * kTok;  // weights: kAStages x 64 columns
+  const uint32_t tmem_a = tmem_base + kAcc * kAccSets * kTok;  // weights: kAStages x 64 columns
 
   if (warp == 0) {
     // ================= producer =================
@@ -509,10 +531,10 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
           break;
         }
         TcFenceAfter();
-        const uint32_t d_addr = tmem_d + (acc * kIssuers + me) * kTok;
+        const uint32_t d_addr = kSplit ? tmem_d + acc * kTok + me * kMmaN : tmem_d + (acc * kIssuers + me) * kTok;
         bool issued = false;
         for (int ks = seg.k_begin; ks < seg.k_end; ++ks, ++it) {
-          if (static_cast<int>(it % kIssuers) != me) continue;
+          if (!kSplit && static_cast<int>(it % kIssuers) != me) continue;
           last_it = static_cast<int>(it);
           if (first_it < 0) first_it = last_it;
           const int s = it % kStages, a = it % kAStages;
@@ -525,7 +547,9 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
           }
           TcFenceAfter();
           const uint32_t act = stages_addr + s * kStage;
-          const uint64_t desc0 = static_cast<uint64_t>((act >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) |
+          // in split mode issuer `me` reads token rows [me * kMmaN, ...) of each activation atom
+          const uint32_t rows_at = act + (kSplit ? me * kMmaN * 128 : 0);
+          const uint64_t desc0 = static_cast<uint64_t>((rows_at >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) |
                                  (1ull << 46) | (2ull << 61);
 #pragma unroll
           for (int j = 0; j < kBlockK / 16; ++j) {
@@ -550,13 +574,13 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
       // asynchronous; if the block exited with one still on its way, it could land in the
       // barriers of the next block that gets this shared memory.  So see them arrive first.
       if (alive && last_it >= 0) {
-        for (int d = 0; d * kIssuers < kStages; ++d) {  // only stages not reused since
-          const int step = last_it - d * kIssuers;
+        for (int d = 0; d * kIssueStride < kStages; ++d) {  // only stages not reused since
+          const int step = last_it - d * kIssueStride;
           if (step < first_it) break;
           if (!MbarWait(SmemAddr(&sh.empty[step % kStages]), (step / kStages) & 1, abort_flag, p.status, kErrEmpty, step)) {
             break;
           }
-          if (d * kIssuers < kAStages &&
+          if (d * kIssueStride < kAStages &&
               !MbarWait(SmemAddr(&sh.a_empty[step % kAStages]), (step / kAStages) & 1, abort_flag, p.status, kErrAEmpty,
                         step)) {
             break;
@@ -662,13 +686,13 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
       const int row0 = kMoe ? seg.m_tile * p.block_size : seg.m_tile * kTok;
       const int m_valid = kMoe ? p.block_size : min(kTok, p.m - row0);
       const bool whole = seg.k_begin == 0 && seg.k_end == k_stages;
-      const uint32_t d_addr = tmem_d + acc * kIssuers * kTok + (static_cast<uint32_t>(32 * q) << 16);
+      const uint32_t d_addr = tmem_d + acc * kAccSets * kTok + (static_cast<uint32_t>(32 * q) << 16);
       // which issuers contributed to this segment (they alternate stages, counted by `it`)
       const int n_steps = seg.k_end - seg.k_begin;
-      bool present[kIssuers];
+      bool present[kAccSets];
 #pragma unroll
-      for (int j = 0; j < kIssuers; ++j) {
-        present[j] = n_steps >= kIssuers || static_cast<int>((j + kIssuers - it % kIssuers) % kIssuers) < n_steps;
+      for (int j = 0; j < kAccSets; ++j) {
+        present[j] = n_steps >= kAccSets || static_cast<int>((j + kAccSets - it % kAccSets) % kAccSets) < n_steps;
       }
       it += n_steps;
       float bias_v = 0.0f;
@@ -704,7 +728,7 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
         }
         TmemWaitLd();
 #pragma unroll
-        for (int other = 1; other < kIssuers; ++other) {
+        for (int other = 1; other < kAccSets; ++other) {
           if (present[other]) {
             uint32_t r1[16];
             TmemLoad16(d_addr + other * kTok + c, r1);
@@ -742,13 +766,16 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
         const int last_block = OwnerOf(tile_u0 + k_stages - 1, total_units, grid);
         // A split tile is identified by the first block working on it: no two split tiles share one.
         int* counter = p.counters + 4 * first_block + q;
-        __threadfence();
+        // Publish the partial and take a ticket in one acquire-release atomic: the warp barrier
+        // orders every lane's stores before lane 0's release, and the shuffle orders the other lanes'
+        // loads after its acquire.
         __syncwarp();
         int ticket = 0;
-        if (lane == 0) ticket = atomicAdd(counter, 1);
+        if (lane == 0) {
+          asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(ticket) : "l"(counter) : "memory");
+        }
         ticket = __shfl_sync(0xffffffffu, ticket, 0);
         if (ticket == last_block - first_block) {
-          __threadfence();
           if (n_ok) {
             // a block's first segment uses slot 2b, any later one slot 2b + 1
             auto slot_of = [&](int b) -> const float* {
