@@ -71,7 +71,7 @@ __host__ __device__ constexpr int AStagesFor(int tok) { return tok <= 32 ? 6 : t
 // accumulator stages (so the epilogue of one segment overlaps the next); limited by the 512 columns
 __host__ __device__ constexpr int AccStagesFor(int tok) { return tok == 32 || tok > 128 ? 1 : 2; }
 // activations (two swizzle atoms of tok x 128 B) | packed weights 8 KB | 2 scale rows | 2 zero rows
-__host__ __device__ constexpr int StageBytes(int tok) { return tok * 256 + 8192 + 1024; }
+__host__ __device__ constexpr int StageBytes(int tok) { return tok * 256 + 8192; }
 // MMA-issuing threads.  One thread cannot keep the tensor pipe busy when a stage is only a few
 // hundred cycles of MMA work (its barrier wait and commits are not overlapped), so small token
 // tiles use two or three issuers on alternating stages, each with its own accumulator; the epilogue
@@ -99,6 +99,7 @@ struct GemmParams {
   int* counters;           // [kMaxGrid][4]: one per (first block of a split tile, lane quarter)
   int* status;
   int m, n, k, groups, group_size;
+  int g_mul, g_shift;  // scale row of k-stage ks = (ks * g_mul) >> g_shift; g_shift < 0: divide instead
   // routed form only
   const int32_t* sorted_ids;
   const int32_t* expert_ids;
@@ -106,6 +107,11 @@ struct GemmParams {
   const float* topk_weights;
   int top_k, block_size, mul_weights, out_rows;
 };
+
+// Scale / zero-point row that the first k of stage `ks` falls in.
+__device__ __forceinline__ int GroupOf(const GemmParams& p, int ks) {
+  return p.g_shift >= 0 ? (ks * p.g_mul) >> p.g_shift : ks * kBlockK / p.group_size;
+}
 
 // ---- PTX wrappers ------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t SmemAddr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -127,6 +133,34 @@ __device__ __forceinline__ bool MbarTryWait(uint32_t bar, uint32_t parity) {
       : "r"(bar), "r"(parity)
       : "memory");
   return ok != 0;
+}
+// Non-blocking test of a phase (try_wait may suspend the thread for a while when it fails).
+__device__ __forceinline__ bool MbarTestWait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Two phase tests (by the lanes with `tester` set) issued ahead of the warp-wide wait for this
+// thread's tensor-memory stores, so the round trips overlap.  Bit 0: first barrier's phase is
+// complete, bit 1: second's.  Lanes that do not test get 0.
+__device__ __forceinline__ uint32_t TestTwoAndWaitSt(bool tester, uint32_t bar0, uint32_t parity0, uint32_t bar1,
+                                                     uint32_t parity1) {
+  uint32_t bits;
+  asm volatile(
+      "{\n .reg .pred t, p, q;\n .reg .u32 hi;\n"
+      " setp.ne.u32 t, %1, 0;\n setp.ne.u32 p, 0, 0;\n setp.ne.u32 q, 0, 0;\n"
+      " @t mbarrier.test_wait.parity.shared::cta.b64 p, [%2], %3;\n"
+      " @t mbarrier.test_wait.parity.shared::cta.b64 q, [%4], %5;\n"
+      " tcgen05.wait::st.sync.aligned;\n"
+      " selp.u32 %0, 1, 0, p;\n selp.u32 hi, 2, 0, q;\n or.b32 %0, %0, hi;\n}"
+      : "=r"(bits)
+      : "r"(static_cast<uint32_t>(tester)), "r"(bar0), "r"(parity0), "r"(bar1), "r"(parity1)
+      : "memory");
+  return bits;
 }
 // Post-mortem aid: when a block gives up, every warp of that block that was blocked in a wait
 // leaves (wait code, detail) in the scratch header at ints [8 + 2 * warp, 9 + 2 * warp].
@@ -210,6 +244,16 @@ __device__ __forceinline__ void TmaLoad2D(uint32_t dst, const CUtensorMap* map, 
           dst),
       "l"(map), "r"(x), "r"(y), "r"(bar)
       : "memory");
+}
+__device__ __forceinline__ void TmaLoad3D(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+          dst),
+      "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void PrefetchL2(const void* ptr) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr) : "memory");
 }
 __device__ __forceinline__ void TcFenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void TcFenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -328,6 +372,30 @@ struct Walker {
     return true;
   }
 };
+// Position of one warp (or lane) in the block's sequence of k-stages.  `it` counts the stages the
+// block really processes (segments of expert-less blocks are skipped and not counted); Locate moves
+// the walker forward until its segment holds stage `it`.
+struct Cursor {
+  Walker walk;
+  Segment seg;
+  uint32_t it, seg_it;
+  int seg_len, expert;
+  __device__ __forceinline__ int Ks() const { return seg.k_begin + static_cast<int>(it - seg_it); }
+};
+template <bool kMoe>
+__device__ __forceinline__ bool Locate(Cursor& c, const int32_t* expert_ids) {
+  while (c.it >= c.seg_it + c.seg_len) {
+    c.seg_it += c.seg_len;
+    c.seg_len = 0;
+    if (!c.walk.Next(c.seg)) return false;
+    if constexpr (kMoe) {
+      c.expert = expert_ids[c.seg.m_tile];
+      if (c.expert < 0) continue;
+    }
+    c.seg_len = c.seg.k_end - c.seg.k_begin;
+  }
+  return true;
+}
 // First unit of a block's range: floor(block * total / grid).  Written with the quotient and
 // remainder of total / grid so that no 64-bit division is needed (block, grid <= 1024).
 __device__ __forceinline__ long long RangeStart(long long block, long long total, long long grid) {
@@ -370,7 +438,7 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
   constexpr int kActBytes = 2 * kAtomBytes;
   // The lanes of a pass wait for each other, so a pass must stay well below the ring size or the
   // ring would drain between passes.
-  constexpr int kProdLanes = kStages >= 12 ? 4 : kStages >= 5 ? 2 : 1;
+  constexpr int kProdLanes = kStages >= 8 ? 4 : kStages >= 4 ? 2 : 1;
   constexpr int kTmemCols = TmemColsFor(kTok);
   constexpr int kDequantWarps = 4 * kSets;
   constexpr int kIssuers = IssuersFor(kTok);
@@ -421,7 +489,7 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
       MbarInit(SmemAddr(&sh.full[i]), 1);
-      MbarInit(SmemAddr(&sh.empty[i]), 4 + (kSplit ? kIssuers : 1));
+      MbarInit(SmemAddr(&sh.empty[i]), kSplit ? kIssuers : 1);
     }
     for (int i = 0; i < kAStages; ++i) {
       MbarInit(SmemAddr(&sh.a_full[i]), 4);
@@ -453,62 +521,67 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
 
   if (warp == 0) {
     // ================= producer =================
-    // SIMT over stages: lane j issues every copy of k-step (base + j), so up to kProdLanes stages
-    // are requested per pass of the loop instead of one (each mbarrier / TMA instruction costs a
-    // shared-memory round trip, which one thread alone cannot hide).
+    // SIMT over stages: lane j requests the stages with it % kProdLanes == j (each mbarrier / TMA
+    // instruction costs a shared-memory round trip, which one thread alone cannot hide).  A lane
+    // never blocks: every pass each lane tests its own slot once and issues if the slot is free,
+    // so one slow slot does not hold back the requests for the others.
     if (lane < kProdLanes) {
       constexpr unsigned kMask = (1u << kProdLanes) - 1u;
-      Walker walk{u_begin, u_end, k_stages, m_tiles};
-      Segment seg;
-      uint32_t it = 0;
-      bool alive = true;
-      const int rows = p.group_size == 64 ? 2 : 1;  // scale / zero rows a stage needs
-      while (alive && walk.Next(seg)) {
-        int expert = 0;
-        if constexpr (kMoe) {
-          expert = p.expert_ids[seg.m_tile];
-          if (expert < 0) continue;
-        }
-        const int n0 = seg.n_tile * kTileN;
-        const int n_valid = min(kTileN, p.n - n0);
-        const int row0 = kMoe ? seg.m_tile * p.block_size : seg.m_tile * kTok;
-        const int w_row0 = expert * (p.k / 16);
-        const T* scales = static_cast<const T*>(p.scales) + static_cast<size_t>(expert) * p.groups * p.n + n0;
-        const uint32_t* zeros =
-            kZeros ? p.zeros + static_cast<size_t>(expert) * p.groups * (p.n / 8) + n0 / 8 : nullptr;
-        // the weight box is always counted in full (columns past N arrive as zeros)
-        const uint32_t tx = kActBytes + 8192 + rows * (n_valid * 2 + (kZeros ? n_valid / 2 : 0));
-        for (int ks0 = seg.k_begin; ks0 < seg.k_end; ks0 += kProdLanes) {
-          const int ks = ks0 + lane;
-          const uint32_t my_it = it + lane;
-          int ok = 1;
-          if (ks < seg.k_end) {
-            const int s = my_it % kStages;
+      Cursor c{Walker{u_begin, u_end, k_stages, m_tiles}, Segment{}, static_cast<uint32_t>(lane), 0u, 0, 0};
+      bool active = Locate<kMoe>(c, p.expert_ids);
+      const int grp_rows = p.group_size == 64 ? 2 : 1;
+      uint32_t idle = 0;
+      while (__any_sync(kMask, active)) {
+        bool progressed = false;
+        if (active) {
+          const int s = c.it % kStages;
+          if (MbarTestWait(SmemAddr(&sh.empty[s]), ((c.it / kStages) & 1) ^ 1)) {
+            const int ks = c.Ks();
+            const int row0 = kMoe ? c.seg.m_tile * p.block_size : c.seg.m_tile * kTok;
             const uint32_t full = SmemAddr(&sh.full[s]);
-            ok = MbarWait(SmemAddr(&sh.empty[s]), ((my_it / kStages) & 1) ^ 1, abort_flag, p.status, kErrEmpty,
-                          static_cast<int>(my_it));
-            if (ok) {
-              const uint32_t base = stages_addr + s * kStage;
-              const int g = ks * kBlockK / p.group_size;
-              MbarExpectTx(full, tx);
-              TmaLoad2D(base, &a_map, ks * kBlockK, row0, full);
-              TmaLoad2D(base + kAtomBytes, &a_map, ks * kBlockK + 64, row0, full);
-              TmaLoad2D(base + kActBytes, &w_map, 2 * n0, w_row0 + ks * 8, full);
-              for (int r = 0; r < rows; ++r) {
-                BulkLoad(base + kActBytes + 8192 + r * 256, scales + static_cast<size_t>(g + r) * p.n, n_valid * 2,
-                         full);
-                if constexpr (kZeros) {
-                  BulkLoad(base + kActBytes + 8192 + 512 + r * 64, zeros + static_cast<size_t>(g + r) * (p.n / 8),
-                           n_valid / 2, full);
-                }
+            const uint32_t base = stages_addr + s * kStage;
+            // both boxes are always counted in full (rows past M and columns past N arrive as zeros)
+            MbarExpectTx(full, kActBytes + 8192);
+            TmaLoad2D(base + kActBytes, &w_map, 2 * c.seg.n_tile * kTileN, c.expert * (p.k / 16) + ks * 8, full);
+            TmaLoad3D(base, &a_map, 0, row0, 2 * ks, full);  // two 64-k atoms, one after the other
+            // The dequantisers read this stage's scales and zero points with plain loads one stage
+            // ahead; pull the lines into L2 now, a whole ring ahead.
+            {
+              const int n0 = c.seg.n_tile * kTileN;
+              const size_t grow = static_cast<size_t>(c.expert) * p.groups + GroupOf(p, ks);
+              const char* sc = reinterpret_cast<const char*>(static_cast<const T*>(p.scales) + grow * p.n + n0);
+              const bool wide = n0 + 64 < p.n;  // second 128-byte line of the tile's 256 bytes of scales
+              for (int r = 0; r < grp_rows; ++r) {
+                PrefetchL2(sc + static_cast<size_t>(r) * p.n * 2);
+                if (wide) PrefetchL2(sc + static_cast<size_t>(r) * p.n * 2 + 128);
+                if constexpr (kZeros) PrefetchL2(p.zeros + (grow + r) * (p.n / 8) + n0 / 8);
               }
             }
+            c.it += kProdLanes;
+            active = Locate<kMoe>(c, p.expert_ids);
+            progressed = true;
+            idle = 0;
           }
-          if (!__all_sync(kMask, ok)) {
-            alive = false;
-            break;
+        }
+        if (!__any_sync(kMask, progressed)) {
+          // nothing was free: back off briefly; give up when the block does or after a bounded wait
+          __nanosleep(32);
+          if ((++idle & 0xff) == 0xff) {
+            if (*abort_flag) {
+              if (active) NoteBlockedWarp(p.status, kErrEmpty, static_cast<int>(c.it));
+              break;
+            }
+            if (idle > kSpinLimit) {
+              if (active && atomicCAS(p.status, 0, kErrEmpty) == 0) {
+                p.status[1] = static_cast<int>(blockIdx.x);
+                p.status[2] = static_cast<int>(threadIdx.x);
+                p.status[3] = static_cast<int>(c.it);
+                __threadfence();
+              }
+              *abort_flag = 1;
+              break;
+            }
           }
-          it += min(kProdLanes, seg.k_end - ks0);
         }
       }
     }
@@ -592,74 +665,130 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
     // ================= dequantisers =================
     const int set = (warp - kFirstDq) / 4;
     const int q = warp & 3;  // tensor-memory lane quarter this warp may touch
-    Walker walk{u_begin, u_end, k_stages, m_tiles};
-    Segment seg;
-    uint32_t it = 0;
-    bool alive = true;
     // symmetric types: implicit zero point 8
     const uint32_t zero_sym = Half2Of<T>::kMagic | 0x00080008u;
-    while (alive && walk.Next(seg)) {
-      if constexpr (kMoe) {
-        if (p.expert_ids[seg.m_tile] < 0) continue;
+    const int rows = p.group_size == 64 ? 2 : 1;  // scale / zero rows a 128-k stage spans
+    // Scales and zero points come straight from global memory (they are tiny and mostly L2 hits),
+    // one stage ahead of their use, so the producer has only the two big copies to request.
+    // This thread owns tile columns c0 = 16 (2q + h) + lane / 4 and c0 + 8 for h = 0, 1; `sc`
+    // packs their two 16-bit scales per (row, h), `zp` holds the four zero-point words of the
+    // warp's 32 columns per row.
+    struct GroupRegs {
+      uint32_t sc[2][2];
+      uint4 zp[2];
+    };
+    // Per-segment bases (tile and expert are fixed inside a segment); columns past N (a 64-wide
+    // last tile) are redirected to valid ones: their results are never written out.
+    uint32_t based_on = 0xffffffffu;
+    const unsigned short* sbase = nullptr;
+    const uint4* zbase = nullptr;
+    int col = 0;
+    auto fetch_groups = [&](const Cursor& c) {
+      if (c.seg_it != based_on) {
+        based_on = c.seg_it;
+        const int n0 = c.seg.n_tile * kTileN;
+        const size_t g0 = static_cast<size_t>(c.expert) * p.groups;
+        const bool inside = n0 + 32 * q < p.n;
+        col = 32 * q + (lane >> 2) - (inside ? 0 : 64);
+        sbase = reinterpret_cast<const unsigned short*>(p.scales) + g0 * p.n + n0;
+        if constexpr (kZeros) zbase = reinterpret_cast<const uint4*>(p.zeros + g0 * (p.n / 8) + n0 / 8) + (inside ? q : q - 2);
       }
-      for (int ks = seg.k_begin; ks < seg.k_end; ++ks, ++it) {
-        if (static_cast<int>(it % kSets) != set) continue;
-        const int s = it % kStages, a = it % kAStages;
-        if (!MbarWaitWarp(0xffffffffu, 0, SmemAddr(&sh.full[s]), (it / kStages) & 1, abort_flag, p.status, kErrFull,
-                          false, static_cast<int>(it)) ||
-            !MbarWaitWarp(0xffffffffu, 0, SmemAddr(&sh.a_empty[a]), ((it / kAStages) & 1) ^ 1, abort_flag, p.status,
-                          kErrAEmpty, false, static_cast<int>(it))) {
-          alive = false;
-          break;
-        }
-        TcFenceAfter();
-        // Explicit shared-space loads (32-bit addresses) keep these off the generic-address path.
-        const uint32_t wbase = stages_addr + s * kStage + kActBytes;
-        const uint32_t sbase = wbase + 8192, zbase = wbase + 8192 + 512;
-        // The thread's words for sub-blocks 2q and 2q + 1 of a 16-k slab are adjacent: one 8-byte load.
-        const uint32_t waddr = wbase + ((q >> 1) * 128 + lane * 4 + 2 * (q & 1)) * 4;
-        const int row_step = p.group_size == 64 ? 1 : 0;  // second 64 k use the next scale row
+      GroupRegs g;
+      const uint32_t grp = static_cast<uint32_t>(GroupOf(p, c.Ks()));
+      const unsigned short* sp = sbase + static_cast<size_t>(grp) * static_cast<uint32_t>(p.n) + col;
+      g.sc[0][0] = static_cast<uint32_t>(__ldg(sp)) | (static_cast<uint32_t>(__ldg(sp + 8)) << 16);
+      g.sc[0][1] = static_cast<uint32_t>(__ldg(sp + 16)) | (static_cast<uint32_t>(__ldg(sp + 24)) << 16);
+      g.sc[1][0] = g.sc[1][1] = 0;
+      g.zp[0] = g.zp[1] = make_uint4(0, 0, 0, 0);
+      if constexpr (kZeros) g.zp[0] = __ldg(zbase + static_cast<size_t>(grp) * static_cast<uint32_t>(p.n / 32));
+      if (rows == 2) {
+        sp += p.n;
+        g.sc[1][0] = static_cast<uint32_t>(__ldg(sp)) | (static_cast<uint32_t>(__ldg(sp + 8)) << 16);
+        g.sc[1][1] = static_cast<uint32_t>(__ldg(sp + 16)) | (static_cast<uint32_t>(__ldg(sp + 24)) << 16);
+        if constexpr (kZeros) g.zp[1] = __ldg(zbase + static_cast<size_t>(grp + 1) * static_cast<uint32_t>(p.n / 32));
+      }
+      return g;
+    };
+    Cursor nx{Walker{u_begin, u_end, k_stages, m_tiles}, Segment{}, static_cast<uint32_t>(set), 0u, 0, 0};
+    bool more = Locate<kMoe>(nx, p.expert_ids);
+    GroupRegs coming{};
+    if (more) coming = fetch_groups(nx);
+    uint32_t early = 0;  // lane 0: early barrier tests for the coming stage
+    while (more) {
+      const uint32_t it = nx.it;
+      const GroupRegs gr = coming;
+      nx.it += kSets;
+      more = Locate<kMoe>(nx, p.expert_ids);
+      if (more) coming = fetch_groups(nx);
+      const int s = it % kStages, a = it % kAStages;
+      // `early` holds lane 0's tests of this stage's two barriers, made while the previous stage
+      // was still being converted (bit 0: copies landed, bit 1: tensor-memory stage free), so
+      // that the round trip of a barrier test is off the critical path whenever the pipeline
+      // runs ahead of this warp.  The shuffle hands the outcome to the warp and orders the other
+      // lanes' reads behind lane 0's acquire.
+      const uint32_t seen = __shfl_sync(0xffffffffu, early, 0);
+      if (!(seen & 1u) && !MbarWaitWarp(0xffffffffu, 0, SmemAddr(&sh.full[s]), (it / kStages) & 1, abort_flag, p.status,
+                                        kErrFull, false, static_cast<int>(it))) {
+        break;
+      }
+      // Explicit shared-space loads (32-bit addresses) keep these off the generic-address path.
+      const uint32_t wbase = stages_addr + s * kStage + kActBytes;
+      // The thread's words for sub-blocks 2q and 2q + 1 of a 16-k slab are adjacent: one 8-byte load.
+      const uint32_t waddr = wbase + ((q >> 1) * 128 + lane * 4 + 2 * (q & 1)) * 4;
+      const int row_step = rows - 1;  // second 64 k use the next scale row
+      bool alive = true;
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t w[4][2];
+      for (int half = 0; half < 2; ++half) {
+        uint32_t w[4][2];
 #pragma unroll
-          for (int kt = 0; kt < 4; ++kt) LdShared64(waddr + (half * 4 + kt) * 1024, w[kt][0], w[kt][1]);
-          const int row = half * row_step;
+        for (int kt = 0; kt < 4; ++kt) LdShared64(waddr + (half * 4 + kt) * 1024, w[kt][0], w[kt][1]);
+        const int row = half * row_step;
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            // sub-block sb = 2q + h covers tile columns [16 sb, 16 sb + 16); this thread owns
-            // columns c0 = 16 sb + lane / 4 and c0 + 8.
-            const int sb = 2 * q + h;
-            const int c0 = 16 * sb + (lane >> 2);
-            const uint32_t s_lo = LdSharedU16(sbase + row * 256 + 2 * c0) * 0x10001u;
-            const uint32_t s_hi = LdSharedU16(sbase + row * 256 + 2 * (c0 + 8)) * 0x10001u;
-            // magic | z is the 16-bit float (base + z) for z < 16, the same trick as for the weights
-            uint32_t z_lo = zero_sym, z_hi = zero_sym;
-            if constexpr (kZeros) {
-              const uint32_t shift = 4 * (lane >> 2);
-              z_lo = Half2Of<T>::kMagic | (((LdShared32(zbase + row * 64 + 8 * sb) >> shift) & 0xFu) * 0x10001u);
-              z_hi = Half2Of<T>::kMagic | (((LdShared32(zbase + row * 64 + 8 * sb + 4) >> shift) & 0xFu) * 0x10001u);
+        for (int h = 0; h < 2; ++h) {
+          const uint32_t pair = row ? gr.sc[1][h] : gr.sc[0][h];
+          const uint32_t s_lo = __byte_perm(pair, 0, 0x1010), s_hi = __byte_perm(pair, 0, 0x3232);
+          // magic | z is the 16-bit float (base + z) for z < 16, the same trick as for the weights
+          uint32_t z_lo = zero_sym, z_hi = zero_sym;
+          if constexpr (kZeros) {
+            const uint4 zw = row ? gr.zp[1] : gr.zp[0];
+            const uint32_t shift = 4 * (lane >> 2);
+            z_lo = Half2Of<T>::kMagic | ((((h ? zw.z : zw.x) >> shift) & 0xFu) * 0x10001u);
+            z_hi = Half2Of<T>::kMagic | ((((h ? zw.w : zw.y) >> shift) & 0xFu) * 0x10001u);
+          }
+          uint32_t regs[16];
+#pragma unroll
+          for (int kt = 0; kt < 4; ++kt) {
+            const uint32_t word = w[kt][h];
+            regs[4 * kt + 0] = Dequant2<T>(word, z_lo, s_lo);        // column c0,     k pair lane % 4
+            regs[4 * kt + 1] = Dequant2<T>(word >> 8, z_hi, s_hi);   // column c0 + 8, k pair lane % 4
+            regs[4 * kt + 2] = Dequant2<T>(word >> 4, z_lo, s_lo);   // column c0,     k pair lane % 4 + 4
+            regs[4 * kt + 3] = Dequant2<T>(word >> 12, z_hi, s_hi);  // column c0 + 8, k pair lane % 4 + 4
+          }
+          if (half == 0 && h == 0) {
+            // first store of the stage: this tensor-memory stage must have been read out by the
+            // MMAs that used it last
+            if (!(seen & 2u) && !MbarWaitWarp(0xffffffffu, 0, SmemAddr(&sh.a_empty[a]), ((it / kAStages) & 1) ^ 1,
+                                              abort_flag, p.status, kErrAEmpty, false, static_cast<int>(it))) {
+              alive = false;
             }
-            uint32_t regs[16];
-#pragma unroll
-            for (int kt = 0; kt < 4; ++kt) {
-              const uint32_t word = w[kt][h];
-              regs[4 * kt + 0] = Dequant2<T>(word, z_lo, s_lo);        // column c0,     k pair lane % 4
-              regs[4 * kt + 1] = Dequant2<T>(word >> 8, z_hi, s_hi);   // column c0 + 8, k pair lane % 4
-              regs[4 * kt + 2] = Dequant2<T>(word >> 4, z_lo, s_lo);   // column c0,     k pair lane % 4 + 4
-              regs[4 * kt + 3] = Dequant2<T>(word >> 12, z_hi, s_hi);  // column c0 + 8, k pair lane % 4 + 4
-            }
+            TcFenceAfter();
+          }
+          if (alive) {
             TmemStore16(tmem_a + (static_cast<uint32_t>(32 * q + 16 * h) << 16) + a * kAStageCols + half * 32, regs);
           }
         }
-        TmemWaitSt();
-        TcFenceBefore();
-        __syncwarp();
-        if (lane == 0) {
-          MbarArrive(SmemAddr(&sh.a_full[a]));
-          MbarArrive(SmemAddr(&sh.empty[s]));
-        }
       }
+      if (!alive) break;
+      // Lane 0 tests the two barriers of this warp's next stage while the warp waits for its
+      // tensor-memory stores, so the two latencies overlap; the answer is used on the next pass.
+      {
+        const uint32_t nxt = it + kSets;
+        early = TestTwoAndWaitSt(lane == 0, SmemAddr(&sh.full[nxt % kStages]), (nxt / kStages) & 1,
+                                 SmemAddr(&sh.a_empty[nxt % kAStages]), ((nxt / kAStages) & 1) ^ 1);
+      }
+      TcFenceBefore();
+      __syncwarp();
+      if (lane == 0) MbarArrive(SmemAddr(&sh.a_full[a]));
     }
   } else {
     // ================= epilogue =================
@@ -923,13 +1052,55 @@ int TensorMap2D(const void* ptr, int64_t rows, int64_t cols, int box_rows, int b
   return IOB_OK;
 }
 
+// Activations [rows, cols] of a 16-bit type seen as [cols / 64][rows][64]: one copy of a
+// (2, box_rows, 64) box fetches the two 64-k atoms of a 128-k stage, each [box_rows][128 bytes]
+// with the 128-byte swizzle, one after the other in shared memory.
 int ActivationMap(const void* ptr, int64_t rows, int64_t cols, int box_rows, int dtype, CUtensorMap* out) {
-  return TensorMap2D(ptr, rows, cols, box_rows, 64, dtype == IOB_BF16 ? kMapBf16 : kMapF16, out);
+  static thread_local std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  const MapKey key{ptr, rows, cols, box_rows, 64, dtype == IOB_BF16 ? kMapBf16 : kMapF16};
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return IOB_OK;
+  }
+  EncodeFn encode = GetEncode();
+  if (encode == nullptr) return Fail(IOB_CUDA_ERROR, "W4A16 GEMM: cuTensorMapEncodeTiled is not available");
+  const cuuint64_t dims[3] = {64, static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(cols / 64)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(cols) * 2, 128};
+  const cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 2};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  const CUresult rc = encode(out, dtype == IOB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                             3, const_cast<void*>(ptr), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) return Fail(IOB_CUDA_ERROR, "W4A16 GEMM: tensor map encode failed (%d)", static_cast<int>(rc));
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *out);
+  return IOB_OK;
 }
 
 // Packed weights [E * K/16, 2N] words, box = 8 rows (128 k) x 256 words (128 columns).
 int WeightMap(const void* ptr, int64_t experts, int64_t k, int64_t n, CUtensorMap* out) {
   return TensorMap2D(ptr, experts * (k / 16), 2 * n, 8, 256, kMapWords, out);
+}
+
+// Shift/multiply form of `ks * 128 / group_size` for the usual group sizes.
+void SetGroupMap(GemmParams& p) {
+  p.g_mul = 1;
+  p.g_shift = -1;
+  if (p.groups == 1) {
+    p.g_mul = 0;
+    p.g_shift = 0;
+  } else if (p.group_size == 64) {
+    p.g_mul = 2;
+    p.g_shift = 0;
+  } else {
+    const int per = p.group_size / kBlockK;  // stages per group
+    if (per > 0 && (per & (per - 1)) == 0) {
+      p.g_shift = 0;
+      while ((1 << p.g_shift) < per) ++p.g_shift;
+    }
+  }
 }
 
 int TokenTile(int64_t m) { return m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : m <= 128 ? 128 : 256; }
@@ -1072,6 +1243,7 @@ extern "C" int infiniops_b200_marlin_gemm(const void* a, int a_dtype, const int3
   p.k = static_cast<int>(size_k);
   p.groups = static_cast<int>(num_groups);
   p.group_size = static_cast<int>(size_k / num_groups);
+  SetGroupMap(p);
   const int64_t units = n_tiles * m_tiles * (size_k / kBlockK);
   const int grid = static_cast<int>(units < NumSms() ? units : NumSms());
   return Dispatch<false>(a_dtype, b_zeros != nullptr, tok, map, w_map, p, grid, static_cast<cudaStream_t>(stream));
@@ -1152,6 +1324,7 @@ extern "C" int infiniops_b200_moe_wna16_marlin_gemm(
   p.k = static_cast<int>(size_k);
   p.groups = static_cast<int>(num_groups);
   p.group_size = static_cast<int>(size_k / num_groups);
+  SetGroupMap(p);
   p.sorted_ids = sorted_token_ids;
   p.expert_ids = expert_ids;
   p.num_post_pad = num_tokens_past_padded;
