@@ -162,6 +162,21 @@ __device__ __forceinline__ uint32_t TestTwoAndWaitSt(bool tester, uint32_t bar0,
       : "memory");
   return bits;
 }
+// One phase test (by the lanes with `tester` set) issued ahead of the warp-wide wait for this
+// thread's tensor-memory loads.  1: the phase is complete.  Lanes that do not test get 0.
+__device__ __forceinline__ uint32_t TestAndWaitLd(bool tester, uint32_t bar, uint32_t parity) {
+  uint32_t bit;
+  asm volatile(
+      "{\n .reg .pred t, p;\n"
+      " setp.ne.u32 t, %1, 0;\n setp.ne.u32 p, 0, 0;\n"
+      " @t mbarrier.test_wait.parity.shared::cta.b64 p, [%2], %3;\n"
+      " tcgen05.wait::ld.sync.aligned;\n"
+      " selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(bit)
+      : "r"(static_cast<uint32_t>(tester)), "r"(bar), "r"(parity)
+      : "memory");
+  return bit;
+}
 // Post-mortem aid: when a block gives up, every warp of that block that was blocked in a wait
 // leaves (wait code, detail) in the scratch header at ints [8 + 2 * warp, 9 + 2 * warp].
 __device__ __forceinline__ void NoteBlockedWarp(int* status, int code, int detail) {
@@ -252,6 +267,21 @@ __device__ __forceinline__ void TmaLoad3D(uint32_t dst, const CUtensorMap* map, 
       "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
       : "memory");
 }
+// Loads that must be issued where they are written (a look-ahead fetch whose value is used a
+// whole stage later): the compiler is free to sink an ordinary read-only load to its first use.
+__device__ __forceinline__ uint32_t LdGlobalU16Here(const void* ptr) {
+  uint32_t v;
+  asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(v) : "l"(ptr));
+  return v;
+}
+__device__ __forceinline__ uint4 LdGlobalV4Here(const void* ptr) {
+  uint4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr));
+  return v;
+}
+// Waits until the kernels this launch depends on have completed and their writes are visible
+// (a no-op for a launch without a programmatic dependency).
+__device__ __forceinline__ void GridDependencyWait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void PrefetchL2(const void* ptr) {
   asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr) : "memory");
 }
@@ -353,6 +383,24 @@ __device__ __forceinline__ uint32_t Dequant2(uint32_t shifted_word, uint32_t zer
   return *reinterpret_cast<const uint32_t*>(&scaled);
 }
 
+// (magic | nibbles) - zero_magic: the exact integer q - zero in both halves.
+template <typename T>
+__device__ __forceinline__ uint32_t Centre2(uint32_t shifted_word, uint32_t zero_magic) {
+  using H2 = typename Half2Of<T>::type;
+  const uint32_t biased = Lop3AndOr(shifted_word, 0x000F000Fu, Half2Of<T>::kMagic);
+  const H2 centred = __hsub2(*reinterpret_cast<const H2*>(&biased), *reinterpret_cast<const H2*>(&zero_magic));
+  return *reinterpret_cast<const uint32_t*>(&centred);
+}
+// float16 only: the nibbles at bits 4..7 of each half read in place, 1024 + 16 q, and brought to
+// q - zero with one exact fused multiply-add: (1024 + 16 q) / 16 - (64 + zero).  Saves the shift.
+__device__ __forceinline__ uint32_t CentreHigh2(uint32_t word, uint32_t minus_64_zero) {
+  const uint32_t biased = Lop3AndOr(word, 0x00F000F0u, 0x64006400u);
+  const uint32_t sixteenth = 0x2C002C00u;
+  const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&biased), *reinterpret_cast<const __half2*>(&sixteenth),
+                            *reinterpret_cast<const __half2*>(&minus_64_zero));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+
 // ---- work walker ------------------------------------------------------------------------------
 struct Segment {
   int tile, n_tile, m_tile, k_begin, k_end;
@@ -417,12 +465,17 @@ struct Shared {
   uint64_t full[kStages], empty[kStages];
   static constexpr int kAStages = AStagesFor(kTok);
   uint64_t a_full[kAStages], a_empty[kAStages];
-  uint64_t d_full[kAcc], d_empty[kAcc];
+  static constexpr int kDBars = kAcc * AccSetsFor(kTok);  // per-segment use needs kAcc of them, per-stage use all
+  uint64_t d_full[kDBars], d_empty[kDBars];
   uint32_t tmem_base;
   int abort_flag;
 };
 
-template <typename T, int kTok, bool kZeros, bool kMoe, int kSets>
+// kLate (token tiles <= 32, groups of 128 k or more): the dequantisers write the exact integers
+// (q - zero) and every k-stage gets an accumulator of its own; the epilogue warps, idle otherwise,
+// read it out stage by stage and apply the group's scale in fp32.  That takes the multiply off the
+// dequantisers, whose instruction issue is what bounds small-M problems.
+template <typename T, int kTok, bool kZeros, bool kMoe, int kSets, bool kLate>
 __global__ void __launch_bounds__((5 + IssuersFor(kTok) + 4 * kSets) * 32, 1)
 W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap w_map,
                 const GemmParams p) {
@@ -447,6 +500,8 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
   constexpr int kIssueStride = kSplit ? 1 : kIssuers;  // an issuer takes every kIssueStride-th stage
   constexpr int kMmaN = kSplit ? kTok / 2 : kTok;
   constexpr int kFirstDq = 1 + kIssuers;  // warp 0 producer, then the issuers, dequantisers, epilogue
+  constexpr int kSlots = kAcc * kAccSets;  // kLate: accumulators, one per stage in flight
+  static_assert(!kLate || (!kSplit && kSlots % kIssuers == 0 && kTok <= 32), "per-stage accumulators: small tiles only");
   constexpr uint32_t kIdesc = (1u << 4) | (Half2Of<T>::kFormat << 7) | (Half2Of<T>::kFormat << 10) |
                               (static_cast<uint32_t>((SplitTokens(kTok) ? kTok / 2 : kTok) >> 3) << 17) | (static_cast<uint32_t>(kTileN >> 4) << 24);
 
@@ -459,10 +514,16 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort_flag = &sh.abort_flag;
 
+  // Programmatic dependent launch: a following kernel launched with the matching attribute may
+  // be scheduled once every block here has passed this point, so that its launch and set-up
+  // overlap this kernel's tail.  Nothing of this kernel is published by it: the follower still
+  // has to wait (GridDependencyWait) before it touches global memory.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int k_stages = p.k / kBlockK;
   const int n_tiles = (p.n + kTileN - 1) / kTileN;
   int m_tiles;
   if constexpr (kMoe) {
+    GridDependencyWait();  // the block count itself is a predecessor's output
     m_tiles = *p.num_post_pad / p.block_size;
   } else {
     m_tiles = (p.m + kTok - 1) / kTok;
@@ -495,8 +556,8 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
       MbarInit(SmemAddr(&sh.a_full[i]), 4);
       MbarInit(SmemAddr(&sh.a_empty[i]), kSplit ? kIssuers : 1);
     }
-    for (int i = 0; i < kAcc; ++i) {
-      MbarInit(SmemAddr(&sh.d_full[i]), kIssuers);
+    for (int i = 0; i < (kLate ? kSlots : kAcc); ++i) {
+      MbarInit(SmemAddr(&sh.d_full[i]), kLate ? 1 : kIssuers);
       MbarInit(SmemAddr(&sh.d_empty[i]), 4);
     }
     sh.abort_flag = 0;
@@ -512,10 +573,21 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
-  TcFenceBefore();
-  __syncthreads();
-  TcFenceAfter();
-  const uint32_t tmem_base = sh.tmem_base;
+  // Set-up rendezvous.  The producer warp, which initialised the barriers, only announces that
+  // (it needs no tensor memory) and goes straight to requesting copies; everyone else waits for
+  // the barriers and the tensor-memory address.
+  constexpr int kThreads = (5 + IssuersFor(kTok) + 4 * kSets) * 32;
+  if (warp == 0) {
+    __threadfence_block();
+    asm volatile("bar.arrive 1, %0;" ::"n"(kThreads) : "memory");
+  } else {
+    TcFenceBefore();
+    asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
+    TcFenceAfter();
+  }
+  // From here on global memory is read and written: everything before was on-chip set-up.
+  if constexpr (!kMoe) GridDependencyWait();
+  const uint32_t tmem_base = warp == 0 ? 0u : sh.tmem_base;
   const uint32_t tmem_d = tmem_base;  // accumulators: kAcc stages x kIssuers x kTok columns
   const uint32_t tmem_a = tmem_base + kAcc * kAccSets * kTok;  // weights: kAStages x 64 columns
 
@@ -598,19 +670,33 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
         if constexpr (kMoe) {
           if (p.expert_ids[seg.m_tile] < 0) continue;
         }
-        const int acc = seg_idx % kAcc;
-        if (!MbarWait(SmemAddr(&sh.d_empty[acc]), ((seg_idx / kAcc) & 1) ^ 1, abort_flag, p.status, kErrDEmpty,
-                      static_cast<int>(seg_idx))) {
-          break;
+        int acc = 0;
+        uint32_t d_addr = tmem_d;
+        if constexpr (!kLate) {
+          acc = seg_idx % kAcc;
+          if (!MbarWait(SmemAddr(&sh.d_empty[acc]), ((seg_idx / kAcc) & 1) ^ 1, abort_flag, p.status, kErrDEmpty,
+                        static_cast<int>(seg_idx))) {
+            break;
+          }
+          TcFenceAfter();
+          d_addr = kSplit ? tmem_d + acc * kTok + me * kMmaN : tmem_d + (acc * kIssuers + me) * kTok;
         }
-        TcFenceAfter();
-        const uint32_t d_addr = kSplit ? tmem_d + acc * kTok + me * kMmaN : tmem_d + (acc * kIssuers + me) * kTok;
         bool issued = false;
         for (int ks = seg.k_begin; ks < seg.k_end; ++ks, ++it) {
           if (!kSplit && static_cast<int>(it % kIssuers) != me) continue;
           last_it = static_cast<int>(it);
           if (first_it < 0) first_it = last_it;
           const int s = it % kStages, a = it % kAStages;
+          if constexpr (kLate) {
+            // this stage's own accumulator must have been read out by the epilogue
+            acc = it % kSlots;
+            if (!MbarWait(SmemAddr(&sh.d_empty[acc]), ((it / kSlots) & 1) ^ 1, abort_flag, p.status, kErrDEmpty,
+                          static_cast<int>(it))) {
+              alive = false;
+              break;
+            }
+            d_addr = tmem_d + acc * kTok;
+          }
           // `a_full` is raised by warps that waited for this stage's copies themselves, so it
           // also covers the activation tile.
           if (!MbarWait(SmemAddr(&sh.a_full[a]), (it / kAStages) & 1, abort_flag, p.status, kErrAFull,
@@ -628,18 +714,21 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
           for (int j = 0; j < kBlockK / 16; ++j) {
             // 16-k slab j: atom j / 4, 32 bytes per slab inside the 128-byte swizzled row
             const uint64_t desc = desc0 + static_cast<uint64_t>((j >> 2) * (kAtomBytes >> 4) + 2 * (j & 3));
-            MmaTs(d_addr, tmem_a + a * kAStageCols + 8 * j, desc, kIdesc, (issued || j > 0) ? 1u : 0u);
+            MmaTs(d_addr, tmem_a + a * kAStageCols + 8 * j, desc, kIdesc, ((issued && !kLate) || j > 0) ? 1u : 0u);
           }
           issued = true;
           TcCommit(SmemAddr(&sh.empty[s]));
           TcCommit(SmemAddr(&sh.a_empty[a]));
+          if constexpr (kLate) TcCommit(SmemAddr(&sh.d_full[acc]));
         }
         if (!alive) break;
-        // an issuer without a stage in this segment still has to count as arrived
-        if (issued) {
-          TcCommit(SmemAddr(&sh.d_full[acc]));
-        } else {
-          MbarArrive(SmemAddr(&sh.d_full[acc]));
+        if constexpr (!kLate) {
+          // an issuer without a stage in this segment still has to count as arrived
+          if (issued) {
+            TcCommit(SmemAddr(&sh.d_full[acc]));
+          } else {
+            MbarArrive(SmemAddr(&sh.d_full[acc]));
+          }
         }
         ++seg_idx;
       }
@@ -696,16 +785,18 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
       GroupRegs g;
       const uint32_t grp = static_cast<uint32_t>(GroupOf(p, c.Ks()));
       const unsigned short* sp = sbase + static_cast<size_t>(grp) * static_cast<uint32_t>(p.n) + col;
-      g.sc[0][0] = static_cast<uint32_t>(__ldg(sp)) | (static_cast<uint32_t>(__ldg(sp + 8)) << 16);
-      g.sc[0][1] = static_cast<uint32_t>(__ldg(sp + 16)) | (static_cast<uint32_t>(__ldg(sp + 24)) << 16);
-      g.sc[1][0] = g.sc[1][1] = 0;
+      g.sc[0][0] = g.sc[0][1] = g.sc[1][0] = g.sc[1][1] = 0;
+      if constexpr (!kLate) {
+        g.sc[0][0] = LdGlobalU16Here(sp) | (LdGlobalU16Here(sp + 8) << 16);
+        g.sc[0][1] = LdGlobalU16Here(sp + 16) | (LdGlobalU16Here(sp + 24) << 16);
+      }
       g.zp[0] = g.zp[1] = make_uint4(0, 0, 0, 0);
-      if constexpr (kZeros) g.zp[0] = __ldg(zbase + static_cast<size_t>(grp) * static_cast<uint32_t>(p.n / 32));
-      if (rows == 2) {
+      if constexpr (kZeros) g.zp[0] = LdGlobalV4Here(zbase + static_cast<size_t>(grp) * static_cast<uint32_t>(p.n / 32));
+      if (!kLate && rows == 2) {
         sp += p.n;
-        g.sc[1][0] = static_cast<uint32_t>(__ldg(sp)) | (static_cast<uint32_t>(__ldg(sp + 8)) << 16);
-        g.sc[1][1] = static_cast<uint32_t>(__ldg(sp + 16)) | (static_cast<uint32_t>(__ldg(sp + 24)) << 16);
-        if constexpr (kZeros) g.zp[1] = __ldg(zbase + static_cast<size_t>(grp + 1) * static_cast<uint32_t>(p.n / 32));
+        g.sc[1][0] = LdGlobalU16Here(sp) | (LdGlobalU16Here(sp + 8) << 16);
+        g.sc[1][1] = LdGlobalU16Here(sp + 16) | (LdGlobalU16Here(sp + 24) << 16);
+        if constexpr (kZeros) g.zp[1] = LdGlobalV4Here(zbase + static_cast<size_t>(grp + 1) * static_cast<uint32_t>(p.n / 32));
       }
       return g;
     };
@@ -714,21 +805,24 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
     GroupRegs coming{};
     if (more) coming = fetch_groups(nx);
     uint32_t early = 0;  // lane 0: early barrier tests for the coming stage
+    // ring positions of the stage in hand and their phase bits, advanced by kSets per stage
+    // (both rings are multiples of kSets, so no division is needed)
+    int s = set % kStages, a = set % kAStages;
+    uint32_t s_phase = 0, a_phase = 0;
     while (more) {
       const uint32_t it = nx.it;
       const GroupRegs gr = coming;
       nx.it += kSets;
       more = Locate<kMoe>(nx, p.expert_ids);
       if (more) coming = fetch_groups(nx);
-      const int s = it % kStages, a = it % kAStages;
       // `early` holds lane 0's tests of this stage's two barriers, made while the previous stage
       // was still being converted (bit 0: copies landed, bit 1: tensor-memory stage free), so
       // that the round trip of a barrier test is off the critical path whenever the pipeline
       // runs ahead of this warp.  The shuffle hands the outcome to the warp and orders the other
       // lanes' reads behind lane 0's acquire.
       const uint32_t seen = __shfl_sync(0xffffffffu, early, 0);
-      if (!(seen & 1u) && !MbarWaitWarp(0xffffffffu, 0, SmemAddr(&sh.full[s]), (it / kStages) & 1, abort_flag, p.status,
-                                        kErrFull, false, static_cast<int>(it))) {
+      if (!(seen & 1u) && !MbarWaitWarp(0xffffffffu, 0, SmemAddr(&sh.full[s]), s_phase, abort_flag, p.status, kErrFull,
+                                        false, static_cast<int>(it))) {
         break;
       }
       // Explicit shared-space loads (32-bit addresses) keep these off the generic-address path.
@@ -737,58 +831,114 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
       const uint32_t waddr = wbase + ((q >> 1) * 128 + lane * 4 + 2 * (q & 1)) * 4;
       const int row_step = rows - 1;  // second 64 k use the next scale row
       bool alive = true;
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t w[4][2];
-#pragma unroll
-        for (int kt = 0; kt < 4; ++kt) LdShared64(waddr + (half * 4 + kt) * 1024, w[kt][0], w[kt][1]);
-        const int row = half * row_step;
+      // first store of the stage: this tensor-memory stage must have been read out by the MMAs
+      // that used it last
+      auto before_first_store = [&]() {
+        if (!(seen & 2u) && !MbarWaitWarp(0xffffffffu, 0, SmemAddr(&sh.a_empty[a]), a_phase ^ 1, abort_flag, p.status,
+                                          kErrAEmpty, false, static_cast<int>(it))) {
+          alive = false;
+        }
+        TcFenceAfter();
+      };
+      if constexpr (kLate) {
+        // Integers only: (q - zero) for the thread's four columns; the scale is applied to the
+        // stage's accumulator by the epilogue warps.
+        constexpr bool kHalf = Half2Of<T>::kFormat == 0;
+        uint32_t zm[2][2], zh[2][2];  // [h][column c0 / c0 + 8]: magic + zero, and -(64 + zero) for float16
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          const uint32_t pair = row ? gr.sc[1][h] : gr.sc[0][h];
-          const uint32_t s_lo = __byte_perm(pair, 0, 0x1010), s_hi = __byte_perm(pair, 0, 0x3232);
-          // magic | z is the 16-bit float (base + z) for z < 16, the same trick as for the weights
-          uint32_t z_lo = zero_sym, z_hi = zero_sym;
-          if constexpr (kZeros) {
-            const uint4 zw = row ? gr.zp[1] : gr.zp[0];
-            const uint32_t shift = 4 * (lane >> 2);
-            z_lo = Half2Of<T>::kMagic | ((((h ? zw.z : zw.x) >> shift) & 0xFu) * 0x10001u);
-            z_hi = Half2Of<T>::kMagic | ((((h ? zw.w : zw.y) >> shift) & 0xFu) * 0x10001u);
-          }
-          uint32_t regs[16];
 #pragma unroll
-          for (int kt = 0; kt < 4; ++kt) {
-            const uint32_t word = w[kt][h];
-            regs[4 * kt + 0] = Dequant2<T>(word, z_lo, s_lo);        // column c0,     k pair lane % 4
-            regs[4 * kt + 1] = Dequant2<T>(word >> 8, z_hi, s_hi);   // column c0 + 8, k pair lane % 4
-            regs[4 * kt + 2] = Dequant2<T>(word >> 4, z_lo, s_lo);   // column c0,     k pair lane % 4 + 4
-            regs[4 * kt + 3] = Dequant2<T>(word >> 12, z_hi, s_hi);  // column c0 + 8, k pair lane % 4 + 4
-          }
-          if (half == 0 && h == 0) {
-            // first store of the stage: this tensor-memory stage must have been read out by the
-            // MMAs that used it last
-            if (!(seen & 2u) && !MbarWaitWarp(0xffffffffu, 0, SmemAddr(&sh.a_empty[a]), ((it / kAStages) & 1) ^ 1,
-                                              abort_flag, p.status, kErrAEmpty, false, static_cast<int>(it))) {
-              alive = false;
+          for (int c2 = 0; c2 < 2; ++c2) {
+            uint32_t zz = 0x00080008u;
+            if constexpr (kZeros) {
+              const uint32_t zw = h ? (c2 ? gr.zp[0].w : gr.zp[0].z) : (c2 ? gr.zp[0].y : gr.zp[0].x);
+              zz = ((zw >> (4 * (lane >> 2))) & 0xFu) * 0x10001u;
             }
-            TcFenceAfter();
+            zm[h][c2] = Half2Of<T>::kMagic | zz;
+            zh[h][c2] = 0xD400D400u | (zz << 4);
           }
-          if (alive) {
-            TmemStore16(tmem_a + (static_cast<uint32_t>(32 * q + 16 * h) << 16) + a * kAStageCols + half * 32, regs);
+        }
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t w[4][2];
+#pragma unroll
+          for (int kt = 0; kt < 4; ++kt) LdShared64(waddr + (half * 4 + kt) * 1024, w[kt][0], w[kt][1]);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t regs[16];
+#pragma unroll
+            for (int kt = 0; kt < 4; ++kt) {
+              const uint32_t word = w[kt][h];
+              const uint32_t word8 = word >> 8;
+              regs[4 * kt + 0] = Centre2<T>(word, zm[h][0]);   // column c0,     k pair lane % 4
+              regs[4 * kt + 1] = Centre2<T>(word8, zm[h][1]);  // column c0 + 8, k pair lane % 4
+              if constexpr (kHalf) {
+                regs[4 * kt + 2] = CentreHigh2(word, zh[h][0]);   // column c0,     k pair lane % 4 + 4
+                regs[4 * kt + 3] = CentreHigh2(word8, zh[h][1]);  // column c0 + 8, k pair lane % 4 + 4
+              } else {
+                regs[4 * kt + 2] = Centre2<T>(word >> 4, zm[h][0]);
+                regs[4 * kt + 3] = Centre2<T>(word >> 12, zm[h][1]);
+              }
+            }
+            if (half == 0 && h == 0) before_first_store();
+            if (alive) {
+              TmemStore16(tmem_a + (static_cast<uint32_t>(32 * q + 16 * h) << 16) + a * kAStageCols + half * 32, regs);
+            }
+          }
+        }
+      } else {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t w[4][2];
+  #pragma unroll
+          for (int kt = 0; kt < 4; ++kt) LdShared64(waddr + (half * 4 + kt) * 1024, w[kt][0], w[kt][1]);
+          const int row = half * row_step;
+  #pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint32_t pair = row ? gr.sc[1][h] : gr.sc[0][h];
+            const uint32_t s_lo = __byte_perm(pair, 0, 0x1010), s_hi = __byte_perm(pair, 0, 0x3232);
+            // magic | z is the 16-bit float (base + z) for z < 16, the same trick as for the weights
+            uint32_t z_lo = zero_sym, z_hi = zero_sym;
+            if constexpr (kZeros) {
+              const uint4 zw = row ? gr.zp[1] : gr.zp[0];
+              const uint32_t shift = 4 * (lane >> 2);
+              z_lo = Half2Of<T>::kMagic | ((((h ? zw.z : zw.x) >> shift) & 0xFu) * 0x10001u);
+              z_hi = Half2Of<T>::kMagic | ((((h ? zw.w : zw.y) >> shift) & 0xFu) * 0x10001u);
+            }
+            uint32_t regs[16];
+  #pragma unroll
+            for (int kt = 0; kt < 4; ++kt) {
+              const uint32_t word = w[kt][h];
+              regs[4 * kt + 0] = Dequant2<T>(word, z_lo, s_lo);        // column c0,     k pair lane % 4
+              regs[4 * kt + 1] = Dequant2<T>(word >> 8, z_hi, s_hi);   // column c0 + 8, k pair lane % 4
+              regs[4 * kt + 2] = Dequant2<T>(word >> 4, z_lo, s_lo);   // column c0,     k pair lane % 4 + 4
+              regs[4 * kt + 3] = Dequant2<T>(word >> 12, z_hi, s_hi);  // column c0 + 8, k pair lane % 4 + 4
+            }
+            if (half == 0 && h == 0) before_first_store();
+            if (alive) {
+              TmemStore16(tmem_a + (static_cast<uint32_t>(32 * q + 16 * h) << 16) + a * kAStageCols + half * 32, regs);
+            }
           }
         }
       }
       if (!alive) break;
       // Lane 0 tests the two barriers of this warp's next stage while the warp waits for its
       // tensor-memory stores, so the two latencies overlap; the answer is used on the next pass.
-      {
-        const uint32_t nxt = it + kSets;
-        early = TestTwoAndWaitSt(lane == 0, SmemAddr(&sh.full[nxt % kStages]), (nxt / kStages) & 1,
-                                 SmemAddr(&sh.a_empty[nxt % kAStages]), ((nxt / kAStages) & 1) ^ 1);
+      const int a_done = a;
+      s += kSets;
+      if (s >= kStages) {
+        s -= kStages;
+        s_phase ^= 1;
       }
+      a += kSets;
+      if (a >= kAStages) {
+        a -= kAStages;
+        a_phase ^= 1;
+      }
+      early = TestTwoAndWaitSt(lane == 0, SmemAddr(&sh.full[s]), s_phase, SmemAddr(&sh.a_empty[a]), a_phase ^ 1);
       TcFenceBefore();
       __syncwarp();
-      if (lane == 0) MbarArrive(SmemAddr(&sh.a_full[a]));
+      if (lane == 0) MbarArrive(SmemAddr(&sh.a_full[a_done]));
     }
   } else {
     // ================= epilogue =================
@@ -796,6 +946,7 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
     Walker walk{u_begin, u_end, k_stages, m_tiles};
     Segment seg;
     uint32_t seg_idx = 0, it = 0;
+    uint32_t early = 0;  // kLate, lane 0: early test of the coming stage's accumulator barrier
     T* out = static_cast<T*>(p.out);
     while (walk.Next(seg)) {
       int expert = 0;
@@ -803,27 +954,13 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
         expert = p.expert_ids[seg.m_tile];
         if (expert < 0) continue;
       }
-      const int acc = seg_idx % kAcc;
-      if (!MbarWaitWarp(0xffffffffu, 0, SmemAddr(&sh.d_full[acc]), (seg_idx / kAcc) & 1, abort_flag, p.status,
-                        kErrDFull, /*relaxed=*/true, static_cast<int>(seg_idx))) {
-        break;
-      }
-      TcFenceAfter();
       const int n_local = 32 * q + lane;
       const int n = seg.n_tile * kTileN + n_local;
       const bool n_ok = n < p.n;
       const int row0 = kMoe ? seg.m_tile * p.block_size : seg.m_tile * kTok;
       const int m_valid = kMoe ? p.block_size : min(kTok, p.m - row0);
       const bool whole = seg.k_begin == 0 && seg.k_end == k_stages;
-      const uint32_t d_addr = tmem_d + acc * kAccSets * kTok + (static_cast<uint32_t>(32 * q) << 16);
-      // which issuers contributed to this segment (they alternate stages, counted by `it`)
       const int n_steps = seg.k_end - seg.k_begin;
-      bool present[kAccSets];
-#pragma unroll
-      for (int j = 0; j < kAccSets; ++j) {
-        present[j] = n_steps >= kAccSets || static_cast<int>((j + kAccSets - it % kAccSets) % kAccSets) < n_steps;
-      }
-      it += n_steps;
       float bias_v = 0.0f;
       if (p.bias != nullptr && n_ok) bias_v = ToFloat<T>(static_cast<const T*>(p.bias)[static_cast<size_t>(expert) * p.n + n]);
 
@@ -845,27 +982,9 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
       // partial slot layout: [128 tile columns][kTok tokens], so a thread's tokens are contiguous
       float* my_partial =
           p.partial + (static_cast<size_t>(2 * blockIdx.x + (first_of_block ? 0 : 1)) * kTileN + n_local) * kTok;
-#pragma unroll 1
-      for (int c = 0; c < kTok; c += 16) {
-        if (c >= m_valid) break;
-        uint32_t r[16];
-        if (present[0]) {
-          TmemLoad16(d_addr + c, r);
-        } else {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) r[j] = 0u;
-        }
-        TmemWaitLd();
-#pragma unroll
-        for (int other = 1; other < kAccSets; ++other) {
-          if (present[other]) {
-            uint32_t r1[16];
-            TmemLoad16(d_addr + other * kTok + c, r1);
-            TmemWaitLd();
-#pragma unroll
-            for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r1[j]));
-          }
-        }
+      // 16 token columns of this thread's output row, summed over the segment: final values of a
+      // whole tile, else this block's partial
+      auto finish_chunk = [&](int c, const uint32_t (&r)[16]) {
         if (whole) {
           if (n_ok) {
 #pragma unroll
@@ -879,12 +998,98 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
             *reinterpret_cast<uint4*>(my_partial + c + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
           }
         }
+      };
+
+      if constexpr (kLate) {
+        // Every stage has its own accumulator: read it, hand it back, add scale * value.  The
+        // scale of the thread's row comes from global memory one stage ahead of its use.
+        float sum[kTok];
+#pragma unroll
+        for (int j = 0; j < kTok; ++j) sum[j] = 0.0f;
+        const T* srow = static_cast<const T*>(p.scales) + static_cast<size_t>(expert) * p.groups * p.n +
+                        (n_ok ? n : n - 64);  // a column past N borrows a valid one; it is never written
+        uint32_t coming = LdGlobalU16Here(srow + static_cast<size_t>(GroupOf(p, seg.k_begin)) * p.n);
+        bool alive = true;
+        for (int ks = seg.k_begin; ks < seg.k_end; ++ks, ++it) {
+          const unsigned short raw = static_cast<unsigned short>(coming);
+          const float scale = ToFloat<T>(*reinterpret_cast<const T*>(&raw));
+          if (ks + 1 < seg.k_end) coming = LdGlobalU16Here(srow + static_cast<size_t>(GroupOf(p, ks + 1)) * p.n);
+          const int slot = it % kSlots;
+          const uint32_t seen = __shfl_sync(0xffffffffu, early, 0);
+          if (!(seen & 1u) && !MbarWaitWarp(0xffffffffu, 0, SmemAddr(&sh.d_full[slot]), (it / kSlots) & 1, abort_flag,
+                                            p.status, kErrDFull, /*relaxed=*/false, static_cast<int>(it))) {
+            alive = false;
+            break;
+          }
+          TcFenceAfter();
+          uint32_t r[kTok];
+#pragma unroll
+          for (int c = 0; c < kTok; c += 16) {
+            TmemLoad16(tmem_d + slot * kTok + (static_cast<uint32_t>(32 * q) << 16) + c, &r[c]);
+          }
+          // the next stage's barrier is tested while the loads are in flight
+          early = TestAndWaitLd(lane == 0, SmemAddr(&sh.d_full[(it + 1) % kSlots]), ((it + 1) / kSlots) & 1);
+          TcFenceBefore();
+          __syncwarp();
+          if (lane == 0) MbarArrive(SmemAddr(&sh.d_empty[slot]));
+#pragma unroll
+          for (int j = 0; j < kTok; ++j) sum[j] = fmaf(scale, __uint_as_float(r[j]), sum[j]);
+        }
+        if (!alive) break;
+#pragma unroll
+        for (int c = 0; c < kTok; c += 16) {
+          if (c < m_valid) {
+            uint32_t r[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(sum[c + j]);
+            finish_chunk(c, r);
+          }
+        }
+        ++seg_idx;
+      } else {
+        const int acc = seg_idx % kAcc;
+        if (!MbarWaitWarp(0xffffffffu, 0, SmemAddr(&sh.d_full[acc]), (seg_idx / kAcc) & 1, abort_flag, p.status,
+                          kErrDFull, /*relaxed=*/true, static_cast<int>(seg_idx))) {
+          break;
+        }
+        TcFenceAfter();
+        const uint32_t d_addr = tmem_d + acc * kAccSets * kTok + (static_cast<uint32_t>(32 * q) << 16);
+        // which issuers contributed to this segment (they alternate stages, counted by `it`)
+        bool present[kAccSets];
+#pragma unroll
+        for (int j = 0; j < kAccSets; ++j) {
+          present[j] = n_steps >= kAccSets || static_cast<int>((j + kAccSets - it % kAccSets) % kAccSets) < n_steps;
+        }
+        it += n_steps;
+#pragma unroll 1
+        for (int c = 0; c < kTok; c += 16) {
+          if (c >= m_valid) break;
+          uint32_t r[16];
+          if (present[0]) {
+            TmemLoad16(d_addr + c, r);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) r[j] = 0u;
+          }
+          TmemWaitLd();
+#pragma unroll
+          for (int other = 1; other < kAccSets; ++other) {
+            if (present[other]) {
+              uint32_t r1[16];
+              TmemLoad16(d_addr + other * kTok + c, r1);
+              TmemWaitLd();
+#pragma unroll
+              for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r1[j]));
+            }
+          }
+          finish_chunk(c, r);
+        }
+        // The accumulator is in registers / memory now: hand it back to the MMA warp.
+        TcFenceBefore();
+        __syncwarp();
+        if (lane == 0) MbarArrive(SmemAddr(&sh.d_empty[acc]));
+        ++seg_idx;
       }
-      // The accumulator is in registers / memory now: hand it back to the MMA warp.
-      TcFenceBefore();
-      __syncwarp();
-      if (lane == 0) MbarArrive(SmemAddr(&sh.d_empty[acc]));
-      ++seg_idx;
 
       if (!whole) {
         // Each lane quarter of the tile has its own arrival counter, so the four epilogue
@@ -1122,11 +1327,11 @@ ScratchPlan PlanScratch(int64_t tiles, int tok, int64_t gathered_bytes) {
   return plan;
 }
 
-template <typename T, int kTok, bool kZeros, bool kMoe>
-int LaunchKernel(const CUtensorMap& map, const CUtensorMap& w_map, const GemmParams& p, int grid,
-                 cudaStream_t stream) {
+template <typename T, int kTok, bool kZeros, bool kMoe, bool kLate>
+int LaunchVariant(const CUtensorMap& map, const CUtensorMap& w_map, const GemmParams& p, int grid,
+                  cudaStream_t stream) {
   constexpr int kSets = SetsFor(kTok);
-  auto kernel = W4A16GemmKernel<T, kTok, kZeros, kMoe, kSets>;
+  auto kernel = W4A16GemmKernel<T, kTok, kZeros, kMoe, kSets, kLate>;
   constexpr int smem = StagesFor(kTok) * StageBytes(kTok) + 1024;
   static thread_local bool configured[64] = {};
   int device = 0;
@@ -1136,8 +1341,32 @@ int LaunchKernel(const CUtensorMap& map, const CUtensorMap& w_map, const GemmPar
     if (err != cudaSuccess) return Fail(IOB_CUDA_ERROR, "W4A16 GEMM: %s", cudaGetErrorString(err));
     if (device >= 0 && device < 64) configured[device] = true;
   }
-  kernel<<<grid, (5 + IssuersFor(kTok) + 4 * kSets) * 32, smem, stream>>>(map, w_map, p);
+  // Launched as a programmatic dependent of whatever precedes it in the stream: the kernel does
+  // its on-chip set-up at once and waits for its predecessors before the first global access.
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(grid);
+  config.blockDim = dim3((5 + IssuersFor(kTok) + 4 * kSets) * 32);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = 1;
+  const cudaError_t err = cudaLaunchKernelEx(&config, kernel, map, w_map, p);
+  if (err != cudaSuccess) return Fail(IOB_CUDA_ERROR, "W4A16 GEMM launch: %s", cudaGetErrorString(err));
   return CheckLaunch("W4A16 GEMM launch");
+}
+
+// Token tiles up to 32 with groups of at least one k-stage take the variant that scales the
+// accumulators instead of the weights.
+template <typename T, int kTok, bool kZeros, bool kMoe>
+int LaunchKernel(const CUtensorMap& map, const CUtensorMap& w_map, const GemmParams& p, int grid,
+                 cudaStream_t stream) {
+  if constexpr (kTok <= 32) {
+    if (p.group_size >= kBlockK) return LaunchVariant<T, kTok, kZeros, kMoe, true>(map, w_map, p, grid, stream);
+  }
+  return LaunchVariant<T, kTok, kZeros, kMoe, false>(map, w_map, p, grid, stream);
 }
 
 template <typename T, bool kZeros, bool kMoe>
