@@ -99,6 +99,7 @@ struct GemmParams {
   int* counters;           // [kMaxGrid][4]: one per (first block of a split tile, lane quarter)
   int* status;
   int m, n, k, groups, group_size;
+  int pair;            // dense 256-token tiles: blocks work in pairs (the activation map's box is 128 rows then)
   int g_mul, g_shift;  // scale row of k-stage ks = (ks * g_mul) >> g_shift; g_shift < 0: divide instead
   // routed form only
   const int32_t* sorted_ids;
@@ -129,6 +130,16 @@ __device__ __forceinline__ bool MbarTryWait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// try_wait that also acquires what the other block of the cluster released with its arrival.
+__device__ __forceinline__ bool MbarTryWaitCluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
       : "memory");
@@ -186,10 +197,11 @@ __device__ __forceinline__ void NoteBlockedWarp(int* status, int code, int detai
   }
 }
 // Bounded wait.  Returns false when the block is giving up (this wait expired, or another did).
+template <bool kClusterScope = false>
 __device__ __forceinline__ bool MbarWait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
                                          int code, int detail = 0) {
   for (uint32_t spin = 0;; ++spin) {
-    if (MbarTryWait(bar, parity)) return true;
+    if (kClusterScope ? MbarTryWaitCluster(bar, parity) : MbarTryWait(bar, parity)) return true;
     if ((spin & 0xff) == 0xff) {
       if (*abort_flag) {
         NoteBlockedWarp(status, code, detail);
@@ -278,6 +290,34 @@ __device__ __forceinline__ uint4 LdGlobalV4Here(const void* ptr) {
   uint4 v;
   asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr));
   return v;
+}
+// Both blocks of a cluster meet (all threads), with release / acquire ordering across the cluster.
+__device__ __forceinline__ void ClusterSync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address, valid from any block of the cluster, of a shared-memory location of block `target`.
+__device__ __forceinline__ uint32_t MapToBlock(uint32_t smem_addr, uint32_t target) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(target));
+  return r;
+}
+// Arrival on a barrier that may live in the other block of the cluster.
+__device__ __forceinline__ void MbarArriveCluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// `cta_group::2` forms: the MMA spans both blocks of the pair; the commit counts the MMAs of both
+// and its barrier address may point into either block.
+__device__ __forceinline__ void MmaTsPair(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n}" ::"r"(
+          d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void TcCommitPair(uint32_t cluster_bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
 }
 // Waits until the kernels this launch depends on have completed and their writes are visible
 // (a no-op for a launch without a programmatic dependency).
@@ -458,15 +498,24 @@ __device__ __forceinline__ int OwnerOf(long long u, long long total, long long g
   return static_cast<int>(num / static_cast<unsigned long long>(total));
 }
 
-template <int kTok, int kSets>
+// Paired blocks (40 KB stages) run two dequantiser sets over four shared-memory and four
+// tensor-memory stages: the depth of the shared-memory ring is what bounds the prefill kernel.
+// Their activations (32 KB a stage) travel in a ring of their own, freed by the MMAs alone, so a
+// slot is not held while its weights are being converted; the 8 KB weight stages are freed by
+// the dequantisers.
+constexpr int kPairStages = 6, kPairAStages = 4, kPairSets = 2, kPairActStages = 5;
+template <int kTok, int kSets, bool kPair = false>
 struct Shared {
-  static constexpr int kStages = StagesFor(kTok);
+  static constexpr int kStages = kPair ? kPairStages : StagesFor(kTok);
   static constexpr int kAcc = AccStagesFor(kTok);
   uint64_t full[kStages], empty[kStages];
-  static constexpr int kAStages = AStagesFor(kTok);
+  static constexpr int kAStages = kPair ? kPairAStages : AStagesFor(kTok);
   uint64_t a_full[kAStages], a_empty[kAStages];
   static constexpr int kDBars = kAcc * AccSetsFor(kTok);  // per-segment use needs kAcc of them, per-stage use all
   uint64_t d_full[kDBars], d_empty[kDBars];
+  static constexpr int kActStages = kPair ? kPairActStages : 1;
+  uint64_t act_full[kActStages], act_empty[kActStages];  // kPair: activation ring
+  uint64_t peer_act[kActStages];                         // kPair, even block: the odd block's activations have landed
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -475,41 +524,57 @@ struct Shared {
 // (q - zero) and every k-stage gets an accumulator of its own; the epilogue warps, idle otherwise,
 // read it out stage by stage and apply the group's scale in fp32.  That takes the multiply off the
 // dequantisers, whose instruction issue is what bounds small-M problems.
-template <typename T, int kTok, bool kZeros, bool kMoe, int kSets, bool kLate>
+//
+// kPair (256-token tiles, dense, N a multiple of 256): two blocks of a cluster work as one.  Each
+// dequantises its own 128 output columns into its own tensor memory and loads only half of the
+// 256 activation rows; one thread of the even block issues `cta_group::2` MMAs (M = 256, N = 256)
+// that run on both SMs and read the two activation halves from the two shared memories.  Per
+// block and stage that is 40 KB of copies for the arithmetic that costs 72 KB alone -- the
+// single-block prefill kernel is bound by how fast an SM can pull operands out of L2.
+template <typename T, int kTok, bool kZeros, bool kMoe, int kSets, bool kLate, bool kPair = false>
 __global__ void __launch_bounds__((5 + IssuersFor(kTok) + 4 * kSets) * 32, 1)
 W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap w_map,
                 const GemmParams p) {
-  using Sh = Shared<kTok, kSets>;
+  using Sh = Shared<kTok, kSets, kPair>;
   constexpr int kStages = Sh::kStages;
   constexpr int kAcc = Sh::kAcc;
   constexpr int kAStages = Sh::kAStages;
   static_assert(kStages % kSets == 0 && kAStages % kSets == 0, "a ring slot must always meet the same dequantiser set");
-  static_assert(SplitTokens(kTok) || (kStages % IssuersFor(kTok) == 0 && kAStages % IssuersFor(kTok) == 0),
+  static_assert(kPair || SplitTokens(kTok) || (kStages % IssuersFor(kTok) == 0 && kAStages % IssuersFor(kTok) == 0),
                 "a ring slot must always meet the same issuer");
-  constexpr int kStage = StageBytes(kTok);
-  constexpr int kAtomBytes = kTok * 128;  // one 64-k activation atom
+  static_assert(!kPair || (kTok == 256 && !kMoe && !kLate), "paired blocks: dense 256-token tiles only");
+  constexpr int kActRows = kPair ? kTok / 2 : kTok;  // activation rows this block loads per stage
+  constexpr int kAtomBytes = kActRows * 128;          // one 64-k activation atom
   constexpr int kActBytes = 2 * kAtomBytes;
+  constexpr int kStage = kPair ? 8192 : kActBytes + 8192;  // bytes of a ring slot (kPair: weights only)
+  constexpr int kWeightsAt = kPair ? 0 : kActBytes;         // where the packed weights sit in a slot
+  constexpr int kActStages = Sh::kActStages;
+  static_assert(kStage <= StageBytes(kTok), "stage layout");
   // The lanes of a pass wait for each other, so a pass must stay well below the ring size or the
   // ring would drain between passes.
   constexpr int kProdLanes = kStages >= 8 ? 4 : kStages >= 4 ? 2 : 1;
-  constexpr int kTmemCols = TmemColsFor(kTok);
+  constexpr int kTmemCols = kPair ? 512 : TmemColsFor(kTok);
   constexpr int kDequantWarps = 4 * kSets;
-  constexpr int kIssuers = IssuersFor(kTok);
-  constexpr bool kSplit = SplitTokens(kTok);
-  constexpr int kAccSets = AccSetsFor(kTok);
+  constexpr int kIssuerWarps = IssuersFor(kTok);        // warps reserved for issuing
+  constexpr int kIssuers = kPair ? 1 : kIssuerWarps;    // threads that really issue MMAs
+  constexpr bool kSplit = !kPair && SplitTokens(kTok);
+  constexpr int kAccSets = kPair ? 1 : AccSetsFor(kTok);
   constexpr int kIssueStride = kSplit ? 1 : kIssuers;  // an issuer takes every kIssueStride-th stage
   constexpr int kMmaN = kSplit ? kTok / 2 : kTok;
-  constexpr int kFirstDq = 1 + kIssuers;  // warp 0 producer, then the issuers, dequantisers, epilogue
+  constexpr int kFirstDq = 1 + kIssuerWarps;  // warp 0 producer, then the issuers, dequantisers, epilogue
   constexpr int kSlots = kAcc * kAccSets;  // kLate: accumulators, one per stage in flight
   static_assert(!kLate || (!kSplit && kSlots % kIssuers == 0 && kTok <= 32), "per-stage accumulators: small tiles only");
+  constexpr int kPeers = kPair ? 2 : 1;  // blocks whose warps arrive on the issuing block's barriers
   constexpr uint32_t kIdesc = (1u << 4) | (Half2Of<T>::kFormat << 7) | (Half2Of<T>::kFormat << 10) |
-                              (static_cast<uint32_t>((SplitTokens(kTok) ? kTok / 2 : kTok) >> 3) << 17) | (static_cast<uint32_t>(kTileN >> 4) << 24);
+                              (static_cast<uint32_t>(kMmaN >> 3) << 17) |
+                              (static_cast<uint32_t>((kPair ? 2 * kTileN : kTileN) >> 4) << 24);
 
   extern __shared__ unsigned char smem_dyn[];
   __shared__ Sh sh;
   unsigned char* stages =
       reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   const uint32_t stages_addr = SmemAddr(stages);
+  [[maybe_unused]] const uint32_t acts_addr = stages_addr + Sh::kStages * 8192;  // kPair: activation ring behind the weight ring
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort_flag = &sh.abort_flag;
@@ -520,7 +585,13 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
   // has to wait (GridDependencyWait) before it touches global memory.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int k_stages = p.k / kBlockK;
-  const int n_tiles = (p.n + kTileN - 1) / kTileN;
+  // kPair: the two blocks of a cluster walk the same sequence of (tile pair, k-stage) units; block
+  // `rank` owns output tile 2 * pair + rank.  `my_block` / `grid` below count clusters then.
+  uint32_t rank = 0;
+  if constexpr (kPair) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  const int my_block = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int blocks_launched = kPair ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  const int n_tiles = kPair ? p.n / (2 * kTileN) : (p.n + kTileN - 1) / kTileN;
   int m_tiles;
   if constexpr (kMoe) {
     GridDependencyWait();  // the block count itself is a predecessor's output
@@ -531,8 +602,8 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
   const long long total_units = static_cast<long long>(n_tiles) * m_tiles * k_stages;
   // Never more ranges than units: an empty range between two sharers of a tile would break the
   // arrival count of the tile.  Surplus blocks get nothing to do.
-  long long grid = total_units < static_cast<long long>(gridDim.x) ? (total_units > 0 ? total_units : 1)
-                                                                    : static_cast<long long>(gridDim.x);
+  long long grid = total_units < static_cast<long long>(blocks_launched) ? (total_units > 0 ? total_units : 1)
+                                                                          : static_cast<long long>(blocks_launched);
   // Few tiles: use a multiple of the tile count.  Then every range lies inside one tile (plain
   // split-K), so a block has a single segment and a single hand-over instead of two ragged ones --
   // worth more than the last few SMs when the whole GEMM is only a handful of stages per block.
@@ -543,22 +614,32 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
       if (tiles * splits * 5 >= grid * 4) grid = tiles * splits;
     }
   }
-  const bool idle = static_cast<long long>(blockIdx.x) >= grid || total_units == 0;
-  const long long u_begin = idle ? 0 : RangeStart(blockIdx.x, total_units, grid);
-  const long long u_end = idle ? 0 : RangeStart(blockIdx.x + 1, total_units, grid);
+  const bool idle = static_cast<long long>(my_block) >= grid || total_units == 0;
+  const long long u_begin = idle ? 0 : RangeStart(my_block, total_units, grid);
+  const long long u_end = idle ? 0 : RangeStart(my_block + 1, total_units, grid);
+  // output tile of a walker segment, and the block (as launched) behind a walker block number
+  auto tile_of = [&](int seg_n_tile) { return kPair ? 2 * seg_n_tile + static_cast<int>(rank) : seg_n_tile; };
+  auto launched_block = [&](int b) { return kPair ? 2 * b + static_cast<int>(rank) : b; };
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
       MbarInit(SmemAddr(&sh.full[i]), 1);
-      MbarInit(SmemAddr(&sh.empty[i]), kSplit ? kIssuers : 1);
+      MbarInit(SmemAddr(&sh.empty[i]), kPair ? 4 : kSplit ? kIssuers : 1);  // kPair: freed by the four dequantiser warps
     }
     for (int i = 0; i < kAStages; ++i) {
-      MbarInit(SmemAddr(&sh.a_full[i]), 4);
+      MbarInit(SmemAddr(&sh.a_full[i]), 4 * kPeers);
       MbarInit(SmemAddr(&sh.a_empty[i]), kSplit ? kIssuers : 1);
     }
     for (int i = 0; i < (kLate ? kSlots : kAcc); ++i) {
       MbarInit(SmemAddr(&sh.d_full[i]), kLate ? 1 : kIssuers);
-      MbarInit(SmemAddr(&sh.d_empty[i]), 4);
+      MbarInit(SmemAddr(&sh.d_empty[i]), 4 * kPeers);
+    }
+    if constexpr (kPair) {
+      for (int i = 0; i < kActStages; ++i) {
+        MbarInit(SmemAddr(&sh.act_full[i]), 1);
+        MbarInit(SmemAddr(&sh.act_empty[i]), 1);
+        MbarInit(SmemAddr(&sh.peer_act[i]), 1);
+      }
     }
     sh.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -568,10 +649,18 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
     asm volatile("prefetch.tensormap [%0];" ::"l"(&w_map) : "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(SmemAddr(&sh.tmem_base)),
-                 "r"(kTmemCols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    // paired blocks allocate together: the same warp of each block, the same columns in both
+    if constexpr (kPair) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(SmemAddr(&sh.tmem_base)),
+                   "r"(kTmemCols)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(SmemAddr(&sh.tmem_base)),
+                   "r"(kTmemCols)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   // Set-up rendezvous.  The producer warp, which initialised the barriers, only announces that
   // (it needs no tensor memory) and goes straight to requesting copies; everyone else waits for
@@ -585,6 +674,8 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
     asm volatile("bar.sync 1, %0;" ::"n"(kThreads) : "memory");
     TcFenceAfter();
   }
+  // Paired blocks signal each other's barriers: nobody may start before both have initialised theirs.
+  if constexpr (kPair) ClusterSync();
   // From here on global memory is read and written: everything before was on-chip set-up.
   if constexpr (!kMoe) GridDependencyWait();
   const uint32_t tmem_base = warp == 0 ? 0u : sh.tmem_base;
@@ -609,17 +700,18 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
           const int s = c.it % kStages;
           if (MbarTestWait(SmemAddr(&sh.empty[s]), ((c.it / kStages) & 1) ^ 1)) {
             const int ks = c.Ks();
-            const int row0 = kMoe ? c.seg.m_tile * p.block_size : c.seg.m_tile * kTok;
+            // a paired block loads its own half of the tile's token rows
+            const int row0 = (kMoe ? c.seg.m_tile * p.block_size : c.seg.m_tile * kTok) + static_cast<int>(rank) * kActRows;
             const uint32_t full = SmemAddr(&sh.full[s]);
             const uint32_t base = stages_addr + s * kStage;
             // both boxes are always counted in full (rows past M and columns past N arrive as zeros)
-            MbarExpectTx(full, kActBytes + 8192);
-            TmaLoad2D(base + kActBytes, &w_map, 2 * c.seg.n_tile * kTileN, c.expert * (p.k / 16) + ks * 8, full);
-            TmaLoad3D(base, &a_map, 0, row0, 2 * ks, full);  // two 64-k atoms, one after the other
+            MbarExpectTx(full, (kPair ? 0 : kActBytes) + 8192);
+            TmaLoad2D(base + kWeightsAt, &w_map, 2 * tile_of(c.seg.n_tile) * kTileN, c.expert * (p.k / 16) + ks * 8, full);
+            if constexpr (!kPair) TmaLoad3D(base, &a_map, 0, row0, 2 * ks, full);  // two 64-k atoms, one after the other
             // The dequantisers read this stage's scales and zero points with plain loads one stage
             // ahead; pull the lines into L2 now, a whole ring ahead.
             {
-              const int n0 = c.seg.n_tile * kTileN;
+              const int n0 = tile_of(c.seg.n_tile) * kTileN;
               const size_t grow = static_cast<size_t>(c.expert) * p.groups + GroupOf(p, ks);
               const char* sc = reinterpret_cast<const char*>(static_cast<const T*>(p.scales) + grow * p.n + n0);
               const bool wide = n0 + 64 < p.n;  // second 128-byte line of the tile's 256 bytes of scales
@@ -657,10 +749,22 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
         }
       }
     }
-  } else if (warp <= kIssuers) {
+  } else if (warp <= kIssuerWarps) {
     // ================= MMA issuers =================
-    if (lane == 0) {
+    if (lane == 0 && warp - 1 < kIssuers) {
       const int me = warp - 1;  // takes the stages with it % kIssuers == me
+      // Paired blocks: the even block issues for both.  The odd block's thread only follows the
+      // sequence, to know which of its own barriers the last commits will still arrive on.
+      const bool issuing = !kPair || rank == 0;
+      // barrier of this block and the same barrier of the other block of the pair
+      auto commit = [&](uint64_t* bar) {
+        if constexpr (kPair) {
+          TcCommitPair(SmemAddr(bar));
+          TcCommitPair(MapToBlock(SmemAddr(bar), 1));
+        } else {
+          TcCommit(SmemAddr(bar));
+        }
+      };
       int first_it = -1, last_it = -1;
       Walker walk{u_begin, u_end, k_stages, m_tiles};
       Segment seg;
@@ -674,11 +778,14 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
         uint32_t d_addr = tmem_d;
         if constexpr (!kLate) {
           acc = seg_idx % kAcc;
-          if (!MbarWait(SmemAddr(&sh.d_empty[acc]), ((seg_idx / kAcc) & 1) ^ 1, abort_flag, p.status, kErrDEmpty,
-                        static_cast<int>(seg_idx))) {
-            break;
+          if (issuing) {
+            // (paired blocks: arrivals come from both blocks, hence the cluster-scope acquire)
+            if (!MbarWait<kPair>(SmemAddr(&sh.d_empty[acc]), ((seg_idx / kAcc) & 1) ^ 1, abort_flag, p.status, kErrDEmpty,
+                                 static_cast<int>(seg_idx))) {
+              break;
+            }
+            TcFenceAfter();
           }
-          TcFenceAfter();
           d_addr = kSplit ? tmem_d + acc * kTok + me * kMmaN : tmem_d + (acc * kIssuers + me) * kTok;
         }
         bool issued = false;
@@ -686,6 +793,20 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
           if (!kSplit && static_cast<int>(it % kIssuers) != me) continue;
           last_it = static_cast<int>(it);
           if (first_it < 0) first_it = last_it;
+          [[maybe_unused]] const int sa = it % kActStages;
+          [[maybe_unused]] const uint32_t sa_phase = (it / kActStages) & 1;
+          if (!issuing) {
+            // odd block of a pair: tell the issuing block when this block's half of the activation
+            // tile has landed
+            if constexpr (kPair) {
+              if (!MbarWait(SmemAddr(&sh.act_full[sa]), sa_phase, abort_flag, p.status, kErrFull, static_cast<int>(it))) {
+                alive = false;
+                break;
+              }
+              MbarArriveCluster(MapToBlock(SmemAddr(&sh.peer_act[sa]), 0));
+            }
+            continue;
+          }
           const int s = it % kStages, a = it % kAStages;
           if constexpr (kLate) {
             // this stage's own accumulator must have been read out by the epilogue
@@ -698,14 +819,22 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
             d_addr = tmem_d + acc * kTok;
           }
           // `a_full` is raised by warps that waited for this stage's copies themselves, so it
-          // also covers the activation tile.
-          if (!MbarWait(SmemAddr(&sh.a_full[a]), (it / kAStages) & 1, abort_flag, p.status, kErrAFull,
-                        static_cast<int>(it))) {
+          // also covers the activation tile (in both blocks of a pair).
+          if (!MbarWait<kPair>(SmemAddr(&sh.a_full[a]), (it / kAStages) & 1, abort_flag, p.status, kErrAFull,
+                               static_cast<int>(it))) {
             alive = false;
             break;
           }
+          if constexpr (kPair) {
+            // both halves of the activation tile: this block's copy and the other block's word
+            if (!MbarWait(SmemAddr(&sh.act_full[sa]), sa_phase, abort_flag, p.status, kErrFull, static_cast<int>(it)) ||
+                !MbarWait<true>(SmemAddr(&sh.peer_act[sa]), sa_phase, abort_flag, p.status, kErrFull, static_cast<int>(it))) {
+              alive = false;
+              break;
+            }
+          }
           TcFenceAfter();
-          const uint32_t act = stages_addr + s * kStage;
+          const uint32_t act = kPair ? acts_addr + sa * kActBytes : stages_addr + s * kStage;
           // in split mode issuer `me` reads token rows [me * kMmaN, ...) of each activation atom
           const uint32_t rows_at = act + (kSplit ? me * kMmaN * 128 : 0);
           const uint64_t desc0 = static_cast<uint64_t>((rows_at >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) |
@@ -714,20 +843,31 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
           for (int j = 0; j < kBlockK / 16; ++j) {
             // 16-k slab j: atom j / 4, 32 bytes per slab inside the 128-byte swizzled row
             const uint64_t desc = desc0 + static_cast<uint64_t>((j >> 2) * (kAtomBytes >> 4) + 2 * (j & 3));
-            MmaTs(d_addr, tmem_a + a * kAStageCols + 8 * j, desc, kIdesc, ((issued && !kLate) || j > 0) ? 1u : 0u);
+            const uint32_t accumulate = ((issued && !kLate) || j > 0) ? 1u : 0u;
+            if constexpr (kPair) {
+              MmaTsPair(d_addr, tmem_a + a * kAStageCols + 8 * j, desc, kIdesc, accumulate);
+            } else {
+              MmaTs(d_addr, tmem_a + a * kAStageCols + 8 * j, desc, kIdesc, accumulate);
+            }
           }
           issued = true;
-          TcCommit(SmemAddr(&sh.empty[s]));
-          TcCommit(SmemAddr(&sh.a_empty[a]));
-          if constexpr (kLate) TcCommit(SmemAddr(&sh.d_full[acc]));
+          if constexpr (kPair) {
+            commit(&sh.act_empty[sa]);
+          } else {
+            commit(&sh.empty[s]);
+          }
+          commit(&sh.a_empty[a]);
+          if constexpr (kLate) commit(&sh.d_full[acc]);
         }
         if (!alive) break;
         if constexpr (!kLate) {
-          // an issuer without a stage in this segment still has to count as arrived
-          if (issued) {
-            TcCommit(SmemAddr(&sh.d_full[acc]));
-          } else {
-            MbarArrive(SmemAddr(&sh.d_full[acc]));
+          if (issuing) {
+            // an issuer without a stage in this segment still has to count as arrived
+            if (issued) {
+              commit(&sh.d_full[acc]);
+            } else {
+              MbarArrive(SmemAddr(&sh.d_full[acc]));
+            }
           }
         }
         ++seg_idx;
@@ -736,10 +876,17 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
       // asynchronous; if the block exited with one still on its way, it could land in the
       // barriers of the next block that gets this shared memory.  So see them arrive first.
       if (alive && last_it >= 0) {
-        for (int d = 0; d * kIssueStride < kStages; ++d) {  // only stages not reused since
+        constexpr int kDrain = kPair ? (kActStages > kAStages ? kActStages : kAStages) : kStages;
+        for (int d = 0; d * kIssueStride < kDrain; ++d) {  // only stages not reused since
           const int step = last_it - d * kIssueStride;
           if (step < first_it) break;
-          if (!MbarWait(SmemAddr(&sh.empty[step % kStages]), (step / kStages) & 1, abort_flag, p.status, kErrEmpty, step)) {
+          if constexpr (kPair) {
+            if (d < kActStages && !MbarWait(SmemAddr(&sh.act_empty[step % kActStages]), (step / kActStages) & 1, abort_flag,
+                                            p.status, kErrEmpty, step)) {
+              break;
+            }
+          } else if (!MbarWait(SmemAddr(&sh.empty[step % kStages]), (step / kStages) & 1, abort_flag, p.status, kErrEmpty,
+                               step)) {
             break;
           }
           if (d * kIssueStride < kAStages &&
@@ -747,6 +894,25 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
                         step)) {
             break;
           }
+        }
+      }
+    }
+    if constexpr (kPair) {
+      if (lane == 0 && warp == 2) {
+        // ================= activation producer (paired blocks) =================
+        // this block's 128 token rows of every stage, into the activation ring
+        Cursor c{Walker{u_begin, u_end, k_stages, m_tiles}, Segment{}, 0u, 0u, 0, 0};
+        while (Locate<kMoe>(c, p.expert_ids)) {
+          const int sa = c.it % kActStages;
+          if (!MbarWait(SmemAddr(&sh.act_empty[sa]), ((c.it / kActStages) & 1) ^ 1, abort_flag, p.status, kErrEmpty,
+                        static_cast<int>(c.it))) {
+            break;
+          }
+          const uint32_t full = SmemAddr(&sh.act_full[sa]);
+          MbarExpectTx(full, kActBytes);
+          TmaLoad3D(acts_addr + sa * kActBytes, &a_map, 0, c.seg.m_tile * kTok + static_cast<int>(rank) * kActRows, 2 * c.Ks(),
+                    full);
+          ++c.it;
         }
       }
     }
@@ -775,7 +941,7 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
     auto fetch_groups = [&](const Cursor& c) {
       if (c.seg_it != based_on) {
         based_on = c.seg_it;
-        const int n0 = c.seg.n_tile * kTileN;
+        const int n0 = tile_of(c.seg.n_tile) * kTileN;
         const size_t g0 = static_cast<size_t>(c.expert) * p.groups;
         const bool inside = n0 + 32 * q < p.n;
         col = 32 * q + (lane >> 2) - (inside ? 0 : 64);
@@ -826,7 +992,7 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
         break;
       }
       // Explicit shared-space loads (32-bit addresses) keep these off the generic-address path.
-      const uint32_t wbase = stages_addr + s * kStage + kActBytes;
+      const uint32_t wbase = stages_addr + s * kStage + kWeightsAt;
       // The thread's words for sub-blocks 2q and 2q + 1 of a 16-k slab are adjacent: one 8-byte load.
       const uint32_t waddr = wbase + ((q >> 1) * 128 + lane * 4 + 2 * (q & 1)) * 4;
       const int row_step = rows - 1;  // second 64 k use the next scale row
@@ -922,6 +1088,11 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
         }
       }
       if (!alive) break;
+      if constexpr (kPair) {
+        // every word of the stage is in registers: the weight slot can be refilled
+        __syncwarp();
+        if (lane == 0) MbarArrive(SmemAddr(&sh.empty[s]));
+      }
       // Lane 0 tests the two barriers of this warp's next stage while the warp waits for its
       // tensor-memory stores, so the two latencies overlap; the answer is used on the next pass.
       const int a_done = a;
@@ -938,7 +1109,14 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
       early = TestTwoAndWaitSt(lane == 0, SmemAddr(&sh.full[s]), s_phase, SmemAddr(&sh.a_empty[a]), a_phase ^ 1);
       TcFenceBefore();
       __syncwarp();
-      if (lane == 0) MbarArrive(SmemAddr(&sh.a_full[a_done]));
+      if (lane == 0) {
+        if constexpr (kPair) {
+          // the issuing thread lives in the even block and counts the warps of both
+          MbarArriveCluster(MapToBlock(SmemAddr(&sh.a_full[a_done]), 0));
+        } else {
+          MbarArrive(SmemAddr(&sh.a_full[a_done]));
+        }
+      }
     }
   } else {
     // ================= epilogue =================
@@ -955,7 +1133,7 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
         if (expert < 0) continue;
       }
       const int n_local = 32 * q + lane;
-      const int n = seg.n_tile * kTileN + n_local;
+      const int n = tile_of(seg.n_tile) * kTileN + n_local;
       const bool n_ok = n < p.n;
       const int row0 = kMoe ? seg.m_tile * p.block_size : seg.m_tile * kTok;
       const int m_valid = kMoe ? p.block_size : min(kTok, p.m - row0);
@@ -1061,6 +1239,25 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
           present[j] = n_steps >= kAccSets || static_cast<int>((j + kAccSets - it % kAccSets) % kAccSets) < n_steps;
         }
         it += n_steps;
+        if constexpr (kAccSets == 1 && kTok >= 64) {
+          // One accumulator, many columns: the load of the next 16 columns is in flight while
+          // the current 16 are converted and stored (the tile's MMAs cannot restart before the
+          // accumulator is drained, so this latency is on the critical path of every tile).
+          const int c_end = min(kTok, (m_valid + 15) & ~15);
+          uint32_t b0[16], b1[16];
+          TmemLoad16(d_addr, b0);
+#pragma unroll 1
+          for (int c = 0; c < c_end; c += 32) {
+            TmemWaitLd();
+            if (c + 16 < c_end) TmemLoad16(d_addr + c + 16, b1);
+            finish_chunk(c, b0);
+            if (c + 16 < c_end) {
+              TmemWaitLd();
+              if (c + 32 < c_end) TmemLoad16(d_addr + c + 32, b0);
+              finish_chunk(c + 16, b1);
+            }
+          }
+        } else
 #pragma unroll 1
         for (int c = 0; c < kTok; c += 16) {
           if (c >= m_valid) break;
@@ -1087,7 +1284,13 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
         // The accumulator is in registers / memory now: hand it back to the MMA warp.
         TcFenceBefore();
         __syncwarp();
-        if (lane == 0) MbarArrive(SmemAddr(&sh.d_empty[acc]));
+        if (lane == 0) {
+          if constexpr (kPair) {
+            MbarArriveCluster(MapToBlock(SmemAddr(&sh.d_empty[acc]), 0));
+          } else {
+            MbarArrive(SmemAddr(&sh.d_empty[acc]));
+          }
+        }
         ++seg_idx;
       }
 
@@ -1099,7 +1302,7 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
         const int first_block = OwnerOf(tile_u0, total_units, grid);
         const int last_block = OwnerOf(tile_u0 + k_stages - 1, total_units, grid);
         // A split tile is identified by the first block working on it: no two split tiles share one.
-        int* counter = p.counters + 4 * first_block + q;
+        int* counter = p.counters + 4 * launched_block(first_block) + q;
         // Publish the partial and take a ticket in one acquire-release atomic: the warp barrier
         // orders every lane's stores before lane 0's release, and the shuffle orders the other lanes'
         // loads after its acquire.
@@ -1114,7 +1317,7 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
             // a block's first segment uses slot 2b, any later one slot 2b + 1
             auto slot_of = [&](int b) -> const float* {
               const bool is_first = RangeStart(b, total_units, grid) >= tile_u0;
-              return p.partial + (static_cast<size_t>(2 * b + (is_first ? 0 : 1)) * kTileN + n_local) * kTok;
+              return p.partial + (static_cast<size_t>(2 * launched_block(b) + (is_first ? 0 : 1)) * kTileN + n_local) * kTok;
             };
             for (int c = 0; c < m_valid; c += 16) {
               float sum[16];
@@ -1161,7 +1364,13 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
   }
   TcFenceBefore();
   __syncthreads();
-  if (warp == 1) {
+  if constexpr (kPair) {
+    // neither block may free tensor memory, or leave, while the other could still signal it
+    ClusterSync();
+    if (warp == 1) {
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+  } else if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
 }
@@ -1327,12 +1536,12 @@ ScratchPlan PlanScratch(int64_t tiles, int tok, int64_t gathered_bytes) {
   return plan;
 }
 
-template <typename T, int kTok, bool kZeros, bool kMoe, bool kLate>
+template <typename T, int kTok, bool kZeros, bool kMoe, bool kLate, bool kPair = false>
 int LaunchVariant(const CUtensorMap& map, const CUtensorMap& w_map, const GemmParams& p, int grid,
                   cudaStream_t stream) {
-  constexpr int kSets = SetsFor(kTok);
-  auto kernel = W4A16GemmKernel<T, kTok, kZeros, kMoe, kSets, kLate>;
-  constexpr int smem = StagesFor(kTok) * StageBytes(kTok) + 1024;
+  constexpr int kSets = kPair ? kPairSets : SetsFor(kTok);
+  auto kernel = W4A16GemmKernel<T, kTok, kZeros, kMoe, kSets, kLate, kPair>;
+  constexpr int smem = (kPair ? kPairStages * 8192 + kPairActStages * kTok * 128 : StagesFor(kTok) * StageBytes(kTok)) + 1024;
   static thread_local bool configured[64] = {};
   int device = 0;
   cudaGetDevice(&device);
@@ -1348,11 +1557,20 @@ int LaunchVariant(const CUtensorMap& map, const CUtensorMap& w_map, const GemmPa
   config.blockDim = dim3((5 + IssuersFor(kTok) + 4 * kSets) * 32);
   config.dynamicSmemBytes = smem;
   config.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attr;
   config.numAttrs = 1;
+  if constexpr (kPair) {
+    // clusters of two blocks; the grid is a whole number of them
+    config.gridDim = dim3(grid & ~1);
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = 2;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    config.numAttrs = 2;
+  }
   const cudaError_t err = cudaLaunchKernelEx(&config, kernel, map, w_map, p);
   if (err != cudaSuccess) return Fail(IOB_CUDA_ERROR, "W4A16 GEMM launch: %s", cudaGetErrorString(err));
   return CheckLaunch("W4A16 GEMM launch");
@@ -1365,6 +1583,9 @@ int LaunchKernel(const CUtensorMap& map, const CUtensorMap& w_map, const GemmPar
                  cudaStream_t stream) {
   if constexpr (kTok <= 32) {
     if (p.group_size >= kBlockK) return LaunchVariant<T, kTok, kZeros, kMoe, true>(map, w_map, p, grid, stream);
+  }
+  if constexpr (kTok == 256 && !kMoe) {
+    if (p.pair) return LaunchVariant<T, kTok, kZeros, kMoe, false, true>(map, w_map, p, grid, stream);
   }
   return LaunchVariant<T, kTok, kZeros, kMoe, false>(map, w_map, p, grid, stream);
 }
@@ -1453,12 +1674,15 @@ extern "C" int infiniops_b200_marlin_gemm(const void* a, int a_dtype, const int3
   if (scratch == nullptr || scratch_bytes < plan.total) {
     return Fail(IOB_SCRATCH_TOO_SMALL, "marlin_gemm: needs %zu bytes of scratch, got %zu", plan.total, scratch_bytes);
   }
+  // Prefill-sized problems whose columns pair up run two blocks per 256 x 256 output tile.
+  const bool pair = tok == 256 && size_n % (2 * kTileN) == 0 && NumSms() >= 2;
   CUtensorMap map;
-  if (const int rc = ActivationMap(a, size_m, size_k, tok, a_dtype, &map)) return rc;
+  if (const int rc = ActivationMap(a, size_m, size_k, pair ? tok / 2 : tok, a_dtype, &map)) return rc;
   CUtensorMap w_map;
   if (const int rc = WeightMap(b_q_weight, 1, size_k, size_n, &w_map)) return rc;
   auto* base = static_cast<unsigned char*>(scratch);
   GemmParams p{};
+  p.pair = pair ? 1 : 0;
   p.wq = reinterpret_cast<const uint32_t*>(b_q_weight);
   p.scales = b_scales;
   p.zeros = reinterpret_cast<const uint32_t*>(b_zeros);
@@ -1474,7 +1698,7 @@ extern "C" int infiniops_b200_marlin_gemm(const void* a, int a_dtype, const int3
   p.group_size = static_cast<int>(size_k / num_groups);
   SetGroupMap(p);
   const int64_t units = n_tiles * m_tiles * (size_k / kBlockK);
-  const int grid = static_cast<int>(units < NumSms() ? units : NumSms());
+  const int grid = pair ? NumSms() : static_cast<int>(units < NumSms() ? units : NumSms());
   return Dispatch<false>(a_dtype, b_zeros != nullptr, tok, map, w_map, p, grid, static_cast<cudaStream_t>(stream));
 }
 

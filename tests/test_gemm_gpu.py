@@ -64,6 +64,8 @@ def test_config2_gate_up_shape():
     (100, 256, 320, 64, torch.float16, True),   # token tile 128, group size 64
     (130, 512, 128, -1, torch.bfloat16, False), # per-channel scales, token tile 256, ragged rows
     (300, 1024, 256, 128, torch.bfloat16, True),  # two token tiles
+    (513, 640, 768, 128, torch.float16, True),   # three 256-column tile pairs, ragged rows in the last token tile
+    (257, 256, 384, 128, torch.bfloat16, False), # 256-token tiles whose columns do not pair up
     (64, 8192, 64, 128, torch.float16, False),  # one tile shared by many blocks along k
 ))
 def test_edge_shapes(m, k, n, group, dtype, zeros):
