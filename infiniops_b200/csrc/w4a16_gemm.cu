@@ -325,6 +325,20 @@ __device__ __forceinline__ void GridDependencyWait() { asm volatile("griddepcont
 __device__ __forceinline__ void PrefetchL2(const void* ptr) {
   asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr) : "memory");
 }
+// Tile store (shared memory -> global, clipped at the tensor's edges) as a bulk-async group.
+__device__ __forceinline__ void TmaStore2D(const CUtensorMap* map, uint32_t src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(map), "r"(x), "r"(y),
+               "r"(src)
+               : "memory");
+}
+__device__ __forceinline__ void BulkCommitGroup() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Until at most one (resp. none) of this thread's store groups still has to read its source.
+__device__ __forceinline__ void BulkWaitRead1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
+__device__ __forceinline__ void BulkWaitAll() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void FenceProxyAsyncShared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void StShared16(uint32_t addr, unsigned short v) {
+  asm volatile("st.shared.b16 [%0], %1;" ::"r"(addr), "h"(v) : "memory");
+}
 __device__ __forceinline__ void TcFenceBefore() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void TcFenceAfter() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void TcCommit(uint32_t bar) {
@@ -534,7 +548,7 @@ struct Shared {
 template <typename T, int kTok, bool kZeros, bool kMoe, int kSets, bool kLate, bool kPair = false>
 __global__ void __launch_bounds__((5 + IssuersFor(kTok) + 4 * kSets) * 32, 1)
 W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap w_map,
-                const GemmParams p) {
+                const __grid_constant__ CUtensorMap c_map, const GemmParams p) {
   using Sh = Shared<kTok, kSets, kPair>;
   constexpr int kStages = Sh::kStages;
   constexpr int kAcc = Sh::kAcc;
@@ -575,6 +589,9 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
       reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   const uint32_t stages_addr = SmemAddr(stages);
   [[maybe_unused]] const uint32_t acts_addr = stages_addr + Sh::kStages * 8192;  // kPair: activation ring behind the weight ring
+  // behind the rings: two 16-row x 32-column output staging tiles per epilogue warp (8 KB in all)
+  [[maybe_unused]] const uint32_t out_stage_addr =
+      stages_addr + (kPair ? Sh::kStages * 8192 + Sh::kActStages * (kTok * 128) : Sh::kStages * StageBytes(kTok));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort_flag = &sh.abort_flag;
@@ -1125,6 +1142,7 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
     Segment seg;
     uint32_t seg_idx = 0, it = 0;
     uint32_t early = 0;  // kLate, lane 0: early test of the coming stage's accumulator barrier
+    uint32_t staged = 0;  // output chunks this warp has sent through its staging buffers
     T* out = static_cast<T*>(p.out);
     while (walk.Next(seg)) {
       int expert = 0;
@@ -1164,7 +1182,29 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
       // whole tile, else this block's partial
       auto finish_chunk = [&](int c, const uint32_t (&r)[16]) {
         if (whole) {
-          if (n_ok) {
+          if constexpr (!kMoe) {
+            // Dense output: the warp's 16 rows x 32 columns are transposed through shared memory
+            // and leave as one asynchronous tile store (clipped at M and N by the tensor map), so
+            // the warp is not held up by 16 strided 64-byte store instructions per chunk and the
+            // accumulator is handed back as soon as it has been read.
+            if (n_ok) {
+              const uint32_t buf = out_stage_addr + q * 2048 + (staged & 1) * 1024;
+              if (lane == 0) BulkWaitRead1();  // the store that used this buffer two chunks ago has read it
+              __syncwarp();
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const T v = FromFloat<T>(__uint_as_float(r[j]) + bias_v);
+                StShared16(buf + j * 64 + lane * 2, *reinterpret_cast<const unsigned short*>(&v));
+              }
+              FenceProxyAsyncShared();
+              __syncwarp();
+              if (lane == 0) {
+                TmaStore2D(&c_map, buf, n - lane, row0 + c);
+                BulkCommitGroup();
+              }
+              ++staged;
+            }
+          } else if (n_ok) {
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               if (c + j < m_valid) emit(c + j, __uint_as_float(r[j]));
@@ -1355,6 +1395,8 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
         }
       }
     }
+    // the staged tile stores of this warp must have left shared memory (and landed) before the block ends
+    if (lane == 0) BulkWaitAll();
   }
 
   // ---- teardown -----------------------------------------------------------------------------
@@ -1493,6 +1535,31 @@ int ActivationMap(const void* ptr, int64_t rows, int64_t cols, int box_rows, int
   return IOB_OK;
 }
 
+// Output [rows, cols] of a 16-bit type, box = 16 rows x 32 columns: the tile one epilogue warp
+// stages and stores at a time.
+int OutputMap(const void* ptr, int64_t rows, int64_t cols, int dtype, CUtensorMap* out) {
+  static thread_local std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  const MapKey key{ptr, rows, cols, 16, 32, dtype == IOB_BF16 ? kMapBf16 : kMapF16};
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return IOB_OK;
+  }
+  EncodeFn encode = GetEncode();
+  if (encode == nullptr) return Fail(IOB_CUDA_ERROR, "W4A16 GEMM: cuTensorMapEncodeTiled is not available");
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+  const cuuint32_t box[2] = {32, 16};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult rc = encode(out, dtype == IOB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                             2, const_cast<void*>(ptr), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) return Fail(IOB_CUDA_ERROR, "W4A16 GEMM: tensor map encode failed (%d)", static_cast<int>(rc));
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *out);
+  return IOB_OK;
+}
+
 // Packed weights [E * K/16, 2N] words, box = 8 rows (128 k) x 256 words (128 columns).
 int WeightMap(const void* ptr, int64_t experts, int64_t k, int64_t n, CUtensorMap* out) {
   return TensorMap2D(ptr, experts * (k / 16), 2 * n, 8, 256, kMapWords, out);
@@ -1537,11 +1604,14 @@ ScratchPlan PlanScratch(int64_t tiles, int tok, int64_t gathered_bytes) {
 }
 
 template <typename T, int kTok, bool kZeros, bool kMoe, bool kLate, bool kPair = false>
-int LaunchVariant(const CUtensorMap& map, const CUtensorMap& w_map, const GemmParams& p, int grid,
-                  cudaStream_t stream) {
+int LaunchVariant(const CUtensorMap& map, const CUtensorMap& w_map, const CUtensorMap& c_map, const GemmParams& p,
+                  int grid, cudaStream_t stream) {
   constexpr int kSets = kPair ? kPairSets : SetsFor(kTok);
   auto kernel = W4A16GemmKernel<T, kTok, kZeros, kMoe, kSets, kLate, kPair>;
-  constexpr int smem = (kPair ? kPairStages * 8192 + kPairActStages * kTok * 128 : StagesFor(kTok) * StageBytes(kTok)) + 1024;
+  // rings + 8 KB of output staging + slack for the 1024-byte alignment
+  constexpr int smem =
+      (kPair ? kPairStages * 8192 + kPairActStages * kTok * 128 : StagesFor(kTok) * StageBytes(kTok)) + 8192 + 1024;
+  static_assert(smem <= 232448, "shared memory budget");
   static thread_local bool configured[64] = {};
   int device = 0;
   cudaGetDevice(&device);
@@ -1571,7 +1641,7 @@ int LaunchVariant(const CUtensorMap& map, const CUtensorMap& w_map, const GemmPa
     attr[1].val.clusterDim.z = 1;
     config.numAttrs = 2;
   }
-  const cudaError_t err = cudaLaunchKernelEx(&config, kernel, map, w_map, p);
+  const cudaError_t err = cudaLaunchKernelEx(&config, kernel, map, w_map, c_map, p);
   if (err != cudaSuccess) return Fail(IOB_CUDA_ERROR, "W4A16 GEMM launch: %s", cudaGetErrorString(err));
   return CheckLaunch("W4A16 GEMM launch");
 }
@@ -1579,42 +1649,42 @@ int LaunchVariant(const CUtensorMap& map, const CUtensorMap& w_map, const GemmPa
 // Token tiles up to 32 with groups of at least one k-stage take the variant that scales the
 // accumulators instead of the weights.
 template <typename T, int kTok, bool kZeros, bool kMoe>
-int LaunchKernel(const CUtensorMap& map, const CUtensorMap& w_map, const GemmParams& p, int grid,
+int LaunchKernel(const CUtensorMap& map, const CUtensorMap& w_map, const CUtensorMap& c_map, const GemmParams& p, int grid,
                  cudaStream_t stream) {
   if constexpr (kTok <= 32) {
-    if (p.group_size >= kBlockK) return LaunchVariant<T, kTok, kZeros, kMoe, true>(map, w_map, p, grid, stream);
+    if (p.group_size >= kBlockK) return LaunchVariant<T, kTok, kZeros, kMoe, true>(map, w_map, c_map, p, grid, stream);
   }
   if constexpr (kTok == 256 && !kMoe) {
-    if (p.pair) return LaunchVariant<T, kTok, kZeros, kMoe, false, true>(map, w_map, p, grid, stream);
+    if (p.pair) return LaunchVariant<T, kTok, kZeros, kMoe, false, true>(map, w_map, c_map, p, grid, stream);
   }
-  return LaunchVariant<T, kTok, kZeros, kMoe, false>(map, w_map, p, grid, stream);
+  return LaunchVariant<T, kTok, kZeros, kMoe, false>(map, w_map, c_map, p, grid, stream);
 }
 
 template <typename T, bool kZeros, bool kMoe>
-int DispatchTok(int tok, const CUtensorMap& map, const CUtensorMap& w_map, const GemmParams& p, int grid,
+int DispatchTok(int tok, const CUtensorMap& map, const CUtensorMap& w_map, const CUtensorMap& c_map, const GemmParams& p, int grid,
                 cudaStream_t stream) {
   switch (tok) {
-    case 16: return LaunchKernel<T, 16, kZeros, kMoe>(map, w_map, p, grid, stream);
-    case 32: return LaunchKernel<T, 32, kZeros, kMoe>(map, w_map, p, grid, stream);
-    case 64: return LaunchKernel<T, 64, kZeros, kMoe>(map, w_map, p, grid, stream);
+    case 16: return LaunchKernel<T, 16, kZeros, kMoe>(map, w_map, c_map, p, grid, stream);
+    case 32: return LaunchKernel<T, 32, kZeros, kMoe>(map, w_map, c_map, p, grid, stream);
+    case 64: return LaunchKernel<T, 64, kZeros, kMoe>(map, w_map, c_map, p, grid, stream);
     default: break;
   }
   if constexpr (!kMoe) {
-    if (tok == 128) return LaunchKernel<T, 128, kZeros, kMoe>(map, w_map, p, grid, stream);
-    if (tok == 256) return LaunchKernel<T, 256, kZeros, kMoe>(map, w_map, p, grid, stream);
+    if (tok == 128) return LaunchKernel<T, 128, kZeros, kMoe>(map, w_map, c_map, p, grid, stream);
+    if (tok == 256) return LaunchKernel<T, 256, kZeros, kMoe>(map, w_map, c_map, p, grid, stream);
   }
   return Fail(IOB_UNSUPPORTED, "W4A16 GEMM: no kernel for a token tile of %d", tok);
 }
 
 template <bool kMoe>
 int Dispatch(int a_dtype, bool zeros, int tok, const CUtensorMap& map, const CUtensorMap& w_map,
-             const GemmParams& p, int grid, cudaStream_t stream) {
+             const CUtensorMap& c_map, const GemmParams& p, int grid, cudaStream_t stream) {
   if (a_dtype == IOB_BF16) {
-    return zeros ? DispatchTok<__nv_bfloat16, true, kMoe>(tok, map, w_map, p, grid, stream)
-                 : DispatchTok<__nv_bfloat16, false, kMoe>(tok, map, w_map, p, grid, stream);
+    return zeros ? DispatchTok<__nv_bfloat16, true, kMoe>(tok, map, w_map, c_map, p, grid, stream)
+                 : DispatchTok<__nv_bfloat16, false, kMoe>(tok, map, w_map, c_map, p, grid, stream);
   }
-  return zeros ? DispatchTok<__half, true, kMoe>(tok, map, w_map, p, grid, stream)
-               : DispatchTok<__half, false, kMoe>(tok, map, w_map, p, grid, stream);
+  return zeros ? DispatchTok<__half, true, kMoe>(tok, map, w_map, c_map, p, grid, stream)
+               : DispatchTok<__half, false, kMoe>(tok, map, w_map, c_map, p, grid, stream);
 }
 
 int CheckProblem(const char* op, const void* a, int a_dtype, const void* wq, const void* scales, const void* zeros,
@@ -1633,7 +1703,8 @@ int CheckProblem(const char* op, const void* a, int a_dtype, const void* wq, con
     return Fail(IOB_UNSUPPORTED, "%s: needs `size_k` to be a multiple of 128 and the group size 64 or a multiple of 128", op);
   }
   IOB_REQUIRE(reinterpret_cast<uintptr_t>(a) % 16 == 0 && reinterpret_cast<uintptr_t>(wq) % 16 == 0 &&
-                  reinterpret_cast<uintptr_t>(scales) % 16 == 0 && reinterpret_cast<uintptr_t>(zeros) % 16 == 0,
+                  reinterpret_cast<uintptr_t>(scales) % 16 == 0 && reinterpret_cast<uintptr_t>(zeros) % 16 == 0 &&
+                  reinterpret_cast<uintptr_t>(out) % 16 == 0,
               "%s: tensors must be 16-byte aligned", op);
   return IOB_OK;
 }
@@ -1680,6 +1751,8 @@ extern "C" int infiniops_b200_marlin_gemm(const void* a, int a_dtype, const int3
   if (const int rc = ActivationMap(a, size_m, size_k, pair ? tok / 2 : tok, a_dtype, &map)) return rc;
   CUtensorMap w_map;
   if (const int rc = WeightMap(b_q_weight, 1, size_k, size_n, &w_map)) return rc;
+  CUtensorMap c_map;
+  if (const int rc = OutputMap(out, size_m, size_n, a_dtype, &c_map)) return rc;
   auto* base = static_cast<unsigned char*>(scratch);
   GemmParams p{};
   p.pair = pair ? 1 : 0;
@@ -1699,7 +1772,7 @@ extern "C" int infiniops_b200_marlin_gemm(const void* a, int a_dtype, const int3
   SetGroupMap(p);
   const int64_t units = n_tiles * m_tiles * (size_k / kBlockK);
   const int grid = pair ? NumSms() : static_cast<int>(units < NumSms() ? units : NumSms());
-  return Dispatch<false>(a_dtype, b_zeros != nullptr, tok, map, w_map, p, grid, static_cast<cudaStream_t>(stream));
+  return Dispatch<false>(a_dtype, b_zeros != nullptr, tok, map, w_map, c_map, p, grid, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" size_t infiniops_b200_moe_wna16_marlin_gemm_scratch_bytes(int64_t size_m, int64_t top_k, int64_t size_n,
@@ -1786,7 +1859,7 @@ extern "C" int infiniops_b200_moe_wna16_marlin_gemm(
   p.block_size = static_cast<int>(moe_block_size);
   p.mul_weights = mul_topk_weights;
   p.out_rows = out_rows;
-  return Dispatch<true>(a_dtype, b_zeros != nullptr, tok, map, w_map, p, NumSms(), s);
+  return Dispatch<true>(a_dtype, b_zeros != nullptr, tok, map, w_map, /*c_map (unused: rows are scattered)=*/w_map, p, NumSms(), s);
 }
 
 // ---- dense GEMM for callers that may not allocate device memory ---------------------------------
