@@ -132,6 +132,8 @@ def _moe_gemm(a, packed, scales, zp, sorted_ids, expert_ids, npost, tw, block, t
     (300, 8, 2, 256, 256, 16, False),
     (16, 32, 8, 512, 128, 64, True),     # DeepSeek-shaped routing (grouped, AWQ zeros), fewer experts
     (200, 32, 8, 256, 128, 32, True),
+    (1000, 8, 2, 256, 256, 64, False),   # enough rows per expert for merged 256-row tiles
+    (900, 8, 2, 384, 512, 64, False),    # merged tiles, ragged runs of blocks
 ))
 def test_moe_layer_against_oracle(tokens, experts, topk, hidden, inter, block, zeros):
     """router -> sort -> w13 GEMM -> silu_and_mul -> w2 GEMM (x routing weight) -> moe_sum, every stage
