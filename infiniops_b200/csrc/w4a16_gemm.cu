@@ -145,6 +145,15 @@ __device__ __forceinline__ bool MbarTryWaitCluster(uint32_t bar, uint32_t parity
       : "memory");
   return ok != 0;
 }
+__device__ __forceinline__ bool MbarTestWaitCluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // Non-blocking test of a phase (try_wait may suspend the thread for a while when it fails).
 __device__ __forceinline__ bool MbarTestWait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -197,17 +206,25 @@ __device__ __forceinline__ void NoteBlockedWarp(int* status, int code, int detai
   }
 }
 // Bounded wait.  Returns false when the block is giving up (this wait expired, or another did).
-template <bool kClusterScope = false>
+// kHot: poll with the non-suspending test instead of try_wait.  A thread suspended in try_wait is
+// woken with some delay; on a chain of hand-overs that is on the critical path (paired blocks:
+// commit -> activation producer -> copy -> relay -> issuer) those delays add up to more than the
+// MMAs they gate.  Only single threads wait this way, so the polling costs next to nothing.
+template <bool kClusterScope = false, bool kHot = false>
 __device__ __forceinline__ bool MbarWait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
                                          int code, int detail = 0) {
+  constexpr uint32_t kLimit = kHot ? (kSpinLimit << 6) : kSpinLimit;
   for (uint32_t spin = 0;; ++spin) {
-    if (kClusterScope ? MbarTryWaitCluster(bar, parity) : MbarTryWait(bar, parity)) return true;
+    if (kHot ? (kClusterScope ? MbarTestWaitCluster(bar, parity) : MbarTestWait(bar, parity))
+             : (kClusterScope ? MbarTryWaitCluster(bar, parity) : MbarTryWait(bar, parity))) {
+      return true;
+    }
     if ((spin & 0xff) == 0xff) {
       if (*abort_flag) {
         NoteBlockedWarp(status, code, detail);
         return false;
       }
-      if (spin > kSpinLimit) {
+      if (spin > kLimit) {
         // first expiry wins: code, then who and where (block, thread, caller's detail word)
         if (atomicCAS(status, 0, code) == 0) {
           status[1] = static_cast<int>(blockIdx.x);
@@ -816,7 +833,8 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
             // odd block of a pair: tell the issuing block when this block's half of the activation
             // tile has landed
             if constexpr (kPair) {
-              if (!MbarWait(SmemAddr(&sh.act_full[sa]), sa_phase, abort_flag, p.status, kErrFull, static_cast<int>(it))) {
+              if (!MbarWait<false, true>(SmemAddr(&sh.act_full[sa]), sa_phase, abort_flag, p.status, kErrFull,
+                                         static_cast<int>(it))) {
                 alive = false;
                 break;
               }
@@ -837,15 +855,17 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
           }
           // `a_full` is raised by warps that waited for this stage's copies themselves, so it
           // also covers the activation tile (in both blocks of a pair).
-          if (!MbarWait<kPair>(SmemAddr(&sh.a_full[a]), (it / kAStages) & 1, abort_flag, p.status, kErrAFull,
-                               static_cast<int>(it))) {
+          if (!MbarWait<kPair, kPair>(SmemAddr(&sh.a_full[a]), (it / kAStages) & 1, abort_flag, p.status, kErrAFull,
+                                      static_cast<int>(it))) {
             alive = false;
             break;
           }
           if constexpr (kPair) {
             // both halves of the activation tile: this block's copy and the other block's word
-            if (!MbarWait(SmemAddr(&sh.act_full[sa]), sa_phase, abort_flag, p.status, kErrFull, static_cast<int>(it)) ||
-                !MbarWait<true>(SmemAddr(&sh.peer_act[sa]), sa_phase, abort_flag, p.status, kErrFull, static_cast<int>(it))) {
+            if (!MbarWait<false, true>(SmemAddr(&sh.act_full[sa]), sa_phase, abort_flag, p.status, kErrFull,
+                                       static_cast<int>(it)) ||
+                !MbarWait<true, true>(SmemAddr(&sh.peer_act[sa]), sa_phase, abort_flag, p.status, kErrFull,
+                                      static_cast<int>(it))) {
               alive = false;
               break;
             }
@@ -921,8 +941,8 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
         Cursor c{Walker{u_begin, u_end, k_stages, m_tiles}, Segment{}, 0u, 0u, 0, 0};
         while (Locate<kMoe>(c, p.expert_ids)) {
           const int sa = c.it % kActStages;
-          if (!MbarWait(SmemAddr(&sh.act_empty[sa]), ((c.it / kActStages) & 1) ^ 1, abort_flag, p.status, kErrEmpty,
-                        static_cast<int>(c.it))) {
+          if (!MbarWait<false, true>(SmemAddr(&sh.act_empty[sa]), ((c.it / kActStages) & 1) ^ 1, abort_flag, p.status,
+                                     kErrEmpty, static_cast<int>(c.it))) {
             break;
           }
           const uint32_t full = SmemAddr(&sh.act_full[sa]);
@@ -1584,7 +1604,17 @@ void SetGroupMap(GemmParams& p) {
   }
 }
 
+// Token tile of the dense GEMM.  33..64 rows run as two 32-row tiles when the group size allows the
+// late-scale variant and both row tiles of every column tile find an SM of their own: converting the
+// weights twice that way is then cheaper than once through the 64-row kernel, whose dequantisers
+// also multiply by the scales (measured: 16 vs 20 us at 4096 x 4096, but 54 vs 46 us at 4096 x 28672).
+int DenseTokenTile(int64_t m, int64_t n, int64_t group_size);
 int TokenTile(int64_t m) { return m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : m <= 128 ? 128 : 256; }
+
+int DenseTokenTile(int64_t m, int64_t n, int64_t group_size) {
+  if (m > 32 && m <= 64 && group_size >= kBlockK && 2 * ((n + kTileN - 1) / kTileN) <= NumSms()) return 32;
+  return TokenTile(m);
+}
 
 size_t Align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
 
@@ -1739,8 +1769,9 @@ extern "C" int infiniops_b200_marlin_gemm(const void* a, int a_dtype, const int3
                                   size_k, num_groups, out)) {
     return rc;
   }
-  const int tok = TokenTile(size_m);
+  const int tok = DenseTokenTile(size_m, size_n, size_k / (num_groups > 0 ? num_groups : 1));
   const int64_t n_tiles = (size_n + kTileN - 1) / kTileN, m_tiles = (size_m + tok - 1) / tok;
+  // (the scratch query does not know the group size and answers for the larger plan)
   const ScratchPlan plan = PlanScratch(n_tiles * m_tiles, tok, 0);
   if (scratch == nullptr || scratch_bytes < plan.total) {
     return Fail(IOB_SCRATCH_TOO_SMALL, "marlin_gemm: needs %zu bytes of scratch, got %zu", plan.total, scratch_bytes);
