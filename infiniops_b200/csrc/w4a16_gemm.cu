@@ -594,7 +594,7 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
   constexpr int kMmaN = kSplit ? kTok / 2 : kTok;
   constexpr int kFirstDq = 1 + kIssuerWarps;  // warp 0 producer, then the issuers, dequantisers, epilogue
   constexpr int kSlots = kAcc * kAccSets;  // kLate: accumulators, one per stage in flight
-  static_assert(!kLate || (!kSplit && kSlots % kIssuers == 0 && kTok <= 32), "per-stage accumulators: small tiles only");
+  static_assert(!kLate || (!kSplit && kSlots % kIssuers == 0 && kTok <= 64), "per-stage accumulators: small tiles only");
   constexpr int kPeers = kPair ? 2 : 1;  // blocks whose warps arrive on the issuing block's barriers
   constexpr uint32_t kIdesc = (1u << 4) | (Half2Of<T>::kFormat << 7) | (Half2Of<T>::kFormat << 10) |
                               (static_cast<uint32_t>(kMmaN >> 3) << 17) |
@@ -1260,18 +1260,28 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
             break;
           }
           TcFenceAfter();
-          uint32_t r[kTok];
+          // at most 32 columns in registers at a time (64-token tiles take two rounds)
+          constexpr int kRound = kTok < 32 ? kTok : 32;
 #pragma unroll
-          for (int c = 0; c < kTok; c += 16) {
-            TmemLoad16(tmem_d + slot * kTok + (static_cast<uint32_t>(32 * q) << 16) + c, &r[c]);
+          for (int c0 = 0; c0 < kTok; c0 += kRound) {
+            uint32_t r[kRound];
+#pragma unroll
+            for (int c = 0; c < kRound; c += 16) {
+              TmemLoad16(tmem_d + slot * kTok + (static_cast<uint32_t>(32 * q) << 16) + c0 + c, &r[c]);
+            }
+            if (c0 + kRound >= kTok) {
+              // last round: the next stage's barrier is tested while the loads are in flight,
+              // then the accumulator goes back to the issuers
+              early = TestAndWaitLd(lane == 0, SmemAddr(&sh.d_full[(it + 1) % kSlots]), ((it + 1) / kSlots) & 1);
+              TcFenceBefore();
+              __syncwarp();
+              if (lane == 0) MbarArrive(SmemAddr(&sh.d_empty[slot]));
+            } else {
+              TmemWaitLd();
+            }
+#pragma unroll
+            for (int j = 0; j < kRound; ++j) sum[c0 + j] = fmaf(scale, __uint_as_float(r[j]), sum[c0 + j]);
           }
-          // the next stage's barrier is tested while the loads are in flight
-          early = TestAndWaitLd(lane == 0, SmemAddr(&sh.d_full[(it + 1) % kSlots]), ((it + 1) / kSlots) & 1);
-          TcFenceBefore();
-          __syncwarp();
-          if (lane == 0) MbarArrive(SmemAddr(&sh.d_empty[slot]));
-#pragma unroll
-          for (int j = 0; j < kTok; ++j) sum[j] = fmaf(scale, __uint_as_float(r[j]), sum[j]);
         }
         if (!alive) break;
 #pragma unroll
@@ -1681,7 +1691,9 @@ int LaunchVariant(const CUtensorMap& map, const CUtensorMap& w_map, const CUtens
 template <typename T, int kTok, bool kZeros, bool kMoe>
 int LaunchKernel(const CUtensorMap& map, const CUtensorMap& w_map, const CUtensorMap& c_map, const GemmParams& p, int grid,
                  cudaStream_t stream) {
-  if constexpr (kTok <= 32) {
+  // (64-row tiles: dense only -- the routed form, with its many whole tiles per block and its
+  // scattered tile-end stores, measured 40 % slower that way than with scaled weights)
+  if constexpr (kTok <= 32 || (kTok == 64 && !kMoe)) {
     if (p.group_size >= kBlockK) return LaunchVariant<T, kTok, kZeros, kMoe, true>(map, w_map, c_map, p, grid, stream);
   }
   if constexpr (kTok == 256 && !kMoe) {
