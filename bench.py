@@ -307,10 +307,10 @@ def run_ours(args):
 
 
 # DRAM bytes (read + write) of the 16 GEMM launches of one step.  From the ncu capture of the
-# M=16, K=4096, N=28672 launch (profiles/w4a16_gemm_decode_m16_k4096_n28672.md): 61.79 MB measured
+# M=16, K=4096, N=28672 launch (profiles/w4a16_gemm_decode_m16_k4096_n28672.md): 61.84 MB measured
 # against 62.06 MB algorithmic, ratio 0.996; the other launches stream their weights once in the same
 # way, so the step's traffic is taken as its algorithmic bytes times that ratio (single GPU).
-TRAFFIC_BYTES_PER_STEP = int(465084416 * 61.79 / 62.06)
+TRAFFIC_BYTES_PER_STEP = int(465084416 * 61.84 / 62.06)
 
 
 # ---------------------------------------------------------------------------------------------------
