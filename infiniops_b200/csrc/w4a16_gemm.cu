@@ -339,6 +339,15 @@ __device__ __forceinline__ void TcCommitPair(uint32_t cluster_bar) {
 // Waits until the kernels this launch depends on have completed and their writes are visible
 // (a no-op for a launch without a programmatic dependency).
 __device__ __forceinline__ void GridDependencyWait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Tensor copy of a paired block: the data lands in this block's shared memory, the bytes are
+// counted on a barrier that may belong to the other block of the pair (`bar` is a cluster address).
+__device__ __forceinline__ void TmaLoad3DPair(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+          dst),
+      "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+      : "memory");
+}
 __device__ __forceinline__ void PrefetchL2(const void* ptr) {
   asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr) : "memory");
 }
@@ -546,7 +555,6 @@ struct Shared {
   uint64_t d_full[kDBars], d_empty[kDBars];
   static constexpr int kActStages = kPair ? kPairActStages : 1;
   uint64_t act_full[kActStages], act_empty[kActStages];  // kPair: activation ring
-  uint64_t peer_act[kActStages];                         // kPair, even block: the odd block's activations have landed
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -672,7 +680,6 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
       for (int i = 0; i < kActStages; ++i) {
         MbarInit(SmemAddr(&sh.act_full[i]), 1);
         MbarInit(SmemAddr(&sh.act_empty[i]), 1);
-        MbarInit(SmemAddr(&sh.peer_act[i]), 1);
       }
     }
     sh.abort_flag = 0;
@@ -829,19 +836,7 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
           if (first_it < 0) first_it = last_it;
           [[maybe_unused]] const int sa = it % kActStages;
           [[maybe_unused]] const uint32_t sa_phase = (it / kActStages) & 1;
-          if (!issuing) {
-            // odd block of a pair: tell the issuing block when this block's half of the activation
-            // tile has landed
-            if constexpr (kPair) {
-              if (!MbarWait<false, true>(SmemAddr(&sh.act_full[sa]), sa_phase, abort_flag, p.status, kErrFull,
-                                         static_cast<int>(it))) {
-                alive = false;
-                break;
-              }
-              MbarArriveCluster(MapToBlock(SmemAddr(&sh.peer_act[sa]), 0));
-            }
-            continue;
-          }
+          if (!issuing) continue;
           const int s = it % kStages, a = it % kAStages;
           if constexpr (kLate) {
             // this stage's own accumulator must have been read out by the epilogue
@@ -861,10 +856,8 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
             break;
           }
           if constexpr (kPair) {
-            // both halves of the activation tile: this block's copy and the other block's word
-            if (!MbarWait<false, true>(SmemAddr(&sh.act_full[sa]), sa_phase, abort_flag, p.status, kErrFull,
-                                       static_cast<int>(it)) ||
-                !MbarWait<true, true>(SmemAddr(&sh.peer_act[sa]), sa_phase, abort_flag, p.status, kErrFull,
+            // both halves of the activation tile (the other block's copy counts on this barrier too)
+            if (!MbarWait<true, true>(SmemAddr(&sh.act_full[sa]), sa_phase, abort_flag, p.status, kErrFull,
                                       static_cast<int>(it))) {
               alive = false;
               break;
@@ -945,10 +938,11 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
                                      kErrEmpty, static_cast<int>(c.it))) {
             break;
           }
-          const uint32_t full = SmemAddr(&sh.act_full[sa]);
-          MbarExpectTx(full, kActBytes);
-          TmaLoad3D(acts_addr + sa * kActBytes, &a_map, 0, c.seg.m_tile * kTok + static_cast<int>(rank) * kActRows, 2 * c.Ks(),
-                    full);
+          // Both halves of the tile are counted on the even block's barrier, which that block arms
+          // for the two of them; the odd block's copy reports there directly.
+          if (rank == 0) MbarExpectTx(SmemAddr(&sh.act_full[sa]), 2 * kActBytes);
+          TmaLoad3DPair(acts_addr + sa * kActBytes, &a_map, 0, c.seg.m_tile * kTok + static_cast<int>(rank) * kActRows,
+                        2 * c.Ks(), MapToBlock(SmemAddr(&sh.act_full[sa]), 0));
           ++c.it;
         }
       }

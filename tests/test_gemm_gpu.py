@@ -66,6 +66,10 @@ def test_config2_gate_up_shape():
     (300, 1024, 256, 128, torch.bfloat16, True),  # two token tiles
     (513, 640, 768, 128, torch.float16, True),   # three 256-column tile pairs, ragged rows in the last token tile
     (257, 256, 384, 128, torch.bfloat16, False), # 256-token tiles whose columns do not pair up
+    (48, 256, 9728, 128, torch.float16, True),   # 64-row late-scale tiles (too many column tiles for two 32-row ones), float16
+    (40, 384, 192, 128, torch.bfloat16, True),   # 33..64 rows as two 32-row tiles
+    (64, 256, 9728, 64, torch.bfloat16, True),   # 64-row tiles, group 64: scaled-weight path
+    (700, 384, 512, 64, torch.float16, False),   # paired blocks, group 64, three token tiles (last ragged)
     (64, 8192, 64, 128, torch.float16, False),  # one tile shared by many blocks along k
 ))
 def test_edge_shapes(m, k, n, group, dtype, zeros):
