@@ -168,7 +168,11 @@ def run_ours(args):
 
     phases = copies // len(MS)
 
-    comm = torch.cuda.Stream() if world > 1 else None
+    if args.gather == "auto":
+        args.gather = "overlap" if world <= 2 else "serial"
+    comm = None
+    if world > 1 and args.gather != "serial":
+        comm = torch.cuda.Stream(priority=-1) if args.gather == "overlap-prio" else torch.cuda.Stream()
 
     def step(phase, stream=None):
         """The 16 GEMMs back to back on the compute stream; with N > 1 every all-gather runs on a second
@@ -182,10 +186,13 @@ def run_ours(args):
                                  w["n"], k, outs[(name, m)], stream=stream, scratch_buf=scratch)
                 launches += 1
                 if world > 1:
-                    comm.wait_stream(main)
-                    with torch.cuda.stream(comm):
+                    if comm is None:
                         parallel.gather_columns(outs[(name, m)], gathered[(name, m)])
-        if world > 1:
+                    else:
+                        comm.wait_stream(main)
+                        with torch.cuda.stream(comm):
+                            parallel.gather_columns(outs[(name, m)], gathered[(name, m)])
+        if comm is not None:
             main.wait_stream(comm)
         return launches
 
@@ -285,7 +292,7 @@ def run_ours(args):
         "config": {"workload": "configs[1]: Llama-3-8B-shaped AWQ W4A16 linears (qkv, o, gate_up, down), g=128, "
                                "M in {1,4,16,64}; one step = these 16 GEMMs",
                    "parallelism": "single GPU" if world == 1 else
-                   f"column-parallel N-shard x{world} + NCCL all-gather on a second stream (overlaps the next GEMM)",
+                   f"column-parallel N-shard x{world} + NCCL all-gather per linear ({args.gather})",
                    "l2": f"inputs larger than L2: {copies} full weight copies "
                          f"({copies * layer_bytes / 1e6:.0f} MB per GPU) used in rotation",
                    "launch": "CUDA graph replay of the step"},
@@ -537,6 +544,11 @@ def main():
                         help="decode = the headline W4A16 decode step; moe = Mixtral-shaped MoE layer, tokens/s")
     parser.add_argument("--tokens", type=int, default=1024, help="global tokens of the MoE workload")
     parser.add_argument("--one", default=None, help="M,K,N: run this single GEMM three times (profiling case)")
+    parser.add_argument("--gather", default="auto", choices=("auto", "overlap", "overlap-prio", "serial"),
+                        help="N > 1, decode: all-gather on a second stream / a high-priority second stream / the compute "
+                             "stream; auto = overlap for 2 GPUs, serial beyond (with 8 ranks the overlapped form measured "
+                             "3.1 ms per step: collective kernels of ranks that run ahead hold SMs while they wait for "
+                             "the slowest rank, behind persistent GEMMs that fill every SM)")
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=5)
