@@ -159,8 +159,16 @@ def run_ours(args):
     layers = [make_layer(rank, world, device, c) for c in range(copies)]
     acts = {(name, m): torch.randn((m, k), device=device, generator=torch.Generator(device=device).manual_seed(
         SEED + 7 * m + i)).bfloat16() for i, (name, k, _) in enumerate(SHAPES) for m in MS}
-    outs = {(name, m): torch.empty((m, n // world), dtype=torch.bfloat16, device=device) for name, _, n in SHAPES
-            for m in MS}
+    # The 16 output slices live in one arena, so that the slices of a whole step can also be exchanged
+    # with a single all-gather (--gather step); each slice starts on a 16-byte boundary.
+    arena_elems = sum(-(-(m * (n // world)) // 8) * 8 for _, _, n in SHAPES for m in MS)
+    arena = torch.empty(arena_elems, dtype=torch.bfloat16, device=device)
+    arena_all = torch.empty((world, arena_elems), dtype=torch.bfloat16, device=device) if world > 1 else None
+    outs, off = {}, 0
+    for name, _, n in SHAPES:
+        for m in MS:
+            outs[(name, m)] = arena[off:off + m * (n // world)].view(m, n // world)
+            off += -(-(m * (n // world)) // 8) * 8
     gathered = {(name, m): torch.empty((world, m, n // world), dtype=torch.bfloat16, device=device)
                 for name, _, n in SHAPES for m in MS} if world > 1 else None
     need = max(capi.lib().infiniops_b200_marlin_gemm_scratch_bytes(m, n // world, k) for _, k, n in SHAPES for m in MS)
@@ -169,9 +177,9 @@ def run_ours(args):
     phases = copies // len(MS)
 
     if args.gather == "auto":
-        args.gather = "overlap" if world <= 2 else "serial"
+        args.gather = "overlap" if world <= 2 else "step"
     comm = None
-    if world > 1 and args.gather != "serial":
+    if world > 1 and args.gather not in ("serial", "step"):
         comm = torch.cuda.Stream(priority=-1) if args.gather == "overlap-prio" else torch.cuda.Stream()
 
     def step(phase, stream=None):
@@ -185,7 +193,7 @@ def run_ours(args):
                 capi.marlin_gemm(acts[(name, m)], w["marlin"], None, w["scales"], w["zeros"], capi.QTYPE_UINT4, m,
                                  w["n"], k, outs[(name, m)], stream=stream, scratch_buf=scratch)
                 launches += 1
-                if world > 1:
+                if world > 1 and args.gather != "step":
                     if comm is None:
                         parallel.gather_columns(outs[(name, m)], gathered[(name, m)])
                     else:
@@ -194,6 +202,8 @@ def run_ours(args):
                             parallel.gather_columns(outs[(name, m)], gathered[(name, m)])
         if comm is not None:
             main.wait_stream(comm)
+        if world > 1 and args.gather == "step":
+            dist.all_gather_into_tensor(arena_all.view(-1), arena)  # [g, arena]: rank-major copies of every slice
         return launches
 
     # warm-up outside any graph (function attributes, tensor maps, NCCL channels)
@@ -292,7 +302,9 @@ def run_ours(args):
         "config": {"workload": "configs[1]: Llama-3-8B-shaped AWQ W4A16 linears (qkv, o, gate_up, down), g=128, "
                                "M in {1,4,16,64}; one step = these 16 GEMMs",
                    "parallelism": "single GPU" if world == 1 else
-                   f"column-parallel N-shard x{world} + NCCL all-gather per linear ({args.gather})",
+                   f"column-parallel N-shard x{world} + " + ("one NCCL all-gather per step over the 16 output slices"
+                                                               if args.gather == "step" else
+                                                               f"NCCL all-gather per linear ({args.gather})"),
                    "l2": f"inputs larger than L2: {copies} full weight copies "
                          f"({copies * layer_bytes / 1e6:.0f} MB per GPU) used in rotation",
                    "launch": "CUDA graph replay of the step"},
@@ -544,11 +556,11 @@ def main():
                         help="decode = the headline W4A16 decode step; moe = Mixtral-shaped MoE layer, tokens/s")
     parser.add_argument("--tokens", type=int, default=1024, help="global tokens of the MoE workload")
     parser.add_argument("--one", default=None, help="M,K,N: run this single GEMM three times (profiling case)")
-    parser.add_argument("--gather", default="auto", choices=("auto", "overlap", "overlap-prio", "serial"),
-                        help="N > 1, decode: all-gather on a second stream / a high-priority second stream / the compute "
-                             "stream; auto = overlap for 2 GPUs, serial beyond (with 8 ranks the overlapped form measured "
-                             "3.1 ms per step: collective kernels of ranks that run ahead hold SMs while they wait for "
-                             "the slowest rank, behind persistent GEMMs that fill every SM)")
+    parser.add_argument("--gather", default="auto", choices=("auto", "overlap", "overlap-prio", "serial", "step"),
+                        help="N > 1, decode: one all-gather per linear on a second stream / a high-priority second "
+                             "stream / the compute stream, or one all-gather per step over all 16 output slices; "
+                             "auto = overlap for 2 GPUs, step beyond (at 8 ranks a captured all-gather of a few KB "
+                             "costs ~120 us on this pool, 2.1 ms per step for sixteen of them)")
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=5)
