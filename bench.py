@@ -177,7 +177,7 @@ def run_ours(args):
     phases = copies // len(MS)
 
     if args.gather == "auto":
-        args.gather = "overlap" if world <= 2 else "step"
+        args.gather = "step"
     comm = None
     if world > 1 and args.gather not in ("serial", "step"):
         comm = torch.cuda.Stream(priority=-1) if args.gather == "overlap-prio" else torch.cuda.Stream()
@@ -559,8 +559,8 @@ def main():
     parser.add_argument("--gather", default="auto", choices=("auto", "overlap", "overlap-prio", "serial", "step"),
                         help="N > 1, decode: one all-gather per linear on a second stream / a high-priority second "
                              "stream / the compute stream, or one all-gather per step over all 16 output slices; "
-                             "auto = overlap for 2 GPUs, step beyond (at 8 ranks a captured all-gather of a few KB "
-                             "costs ~120 us on this pool, 2.1 ms per step for sixteen of them)")
+                             "auto = step (at 8 ranks a captured all-gather of a few KB costs ~120 us on this pool, "
+                             "2.1 ms per step for sixteen of them against 0.33 ms of GEMMs)")
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=5)
