@@ -60,13 +60,15 @@ const char* infiniops_b200_version(void);
 int infiniops_b200_swap_device(int device, int* previous);
 
 /* A zero-initialised scratch buffer of at least `bytes` on the current device, owned by the
- * library, one per (calling thread, device, purpose); purpose 0 = GEMM, 1 = token sort.  It only
- * grows; growing ALLOCATES (cudaMalloc + cudaMemset, frees the old buffer) and therefore must not
- * happen during stream capture -- size it once up front.  Returns NULL on failure.  This is what the
- * C++ / Python operators fall back to when the Handle carries no workspace; the kernel entry points
- * themselves never allocate.  No counterpart in the reference (its operators that need device
- * scratch allocate it in their constructors, src/native/cuda/ops/silu_and_mul/kernel.h:19-46). */
-void* infiniops_b200_thread_scratch(int purpose, size_t bytes);
+ * library, one per (calling thread, device, purpose, stream); purpose 0 = GEMM, 1 = token sort.
+ * Keyed by stream so that two operator calls that may overlap on the GPU never share split-K
+ * counters.  It only grows; growing ALLOCATES (cudaMalloc + cudaMemset, frees the old buffer) and
+ * therefore must not happen during stream capture, and a graph captured earlier that used the old
+ * buffer must be captured again -- size it once up front.  Returns NULL on failure.  This is what
+ * the C++ / Python operators fall back to when the Handle carries no workspace; the kernel entry
+ * points themselves never allocate.  No counterpart in the reference (its operators that need
+ * device scratch allocate it in their constructors, src/native/cuda/ops/silu_and_mul/kernel.h:19-46). */
+void* infiniops_b200_thread_scratch(int purpose, size_t bytes, void* stream);
 
 /* ---- weight repacking -------------------------------------------------------------------- */
 
@@ -175,6 +177,21 @@ int infiniops_b200_moe_sum(const void* input, int dtype, int64_t num_tokens, int
  * No counterpart in the reference. */
 int infiniops_b200_scratch_status(const void* scratch, void* stream);
 
+/* Self-test of the bounded device-side wait the GEMM kernels use: launches a one-block kernel in
+ * which one thread waits, for a few thousand polls, on a barrier nobody arrives at (no copy and
+ * no tensor-core work is involved).  The wait gives up, records code 7 with (block 0, thread 0,
+ * detail 42) in the status header at the start of `scratch` (>= 256 bytes, zeroed) -- read it with
+ * infiniops_b200_scratch_status -- and the kernel ends normally, writing result[0] = 0 (the wait
+ * reported failure) and result[1] = 1 (the block's give-up flag) to the device ints at `result`.
+ * No counterpart in the reference. */
+int infiniops_b200_selftest_bounded_wait(void* scratch, size_t scratch_bytes, int* result, void* stream);
+
+/* Clears (asynchronously, on `stream`) the part of a GEMM scratch buffer that the kernels expect
+ * to find zero: the status header and the split-K arrival counters, 16 640 bytes from the start.
+ * For scratch whose previous content is unknown -- e.g. a Handle workspace that other operators
+ * also write (src/handle.h:10-41 gives no zeroing contract).  No counterpart in the reference. */
+int infiniops_b200_gemm_scratch_prepare(void* scratch, size_t scratch_bytes, void* stream);
+
 /* Bytes of scratch the dense GEMM needs for an [M, K] x [K, N] problem on the current
  * device (partial sums of K-split tiles and their arrival counters). */
 size_t infiniops_b200_marlin_gemm_scratch_bytes(int64_t size_m, int64_t size_n, int64_t size_k);
@@ -182,11 +199,13 @@ size_t infiniops_b200_marlin_gemm_scratch_bytes(int64_t size_m, int64_t size_n, 
 /* C[M, N] = A[M, K] * dequant(W)[K, N] (+ bias[N]), fp32 accumulation, C in A's type.
  * a: [M, K] F16/BF16 row-major.  b_q_weight: Marlin layout int32 [K/16, 2N] as produced by
  * the repack functions above (4-bit).  b_scales: [G, N] in A's type, plain row-major,
- * G = K / group_size (group_size a multiple of 16 that divides K; G = 1 for per-channel).  b_zeros: int32 [G, N/8],
- * field j of a word = column 8*(n/8)+j, required for IOB_QTYPE_UINT4 and NULL for
- * IOB_QTYPE_UINT4B8.  b_bias: [N] in A's type or NULL.  K % 64 == 0, N % 64 == 0.
- * `scratch` must hold *_scratch_bytes(); its first use must find the counter area zeroed
- * (cudaMemset once after allocation); every call leaves it zeroed again.
+ * G = K / group_size; this build needs K % 128 == 0 and a group size of 64 or a multiple of 128
+ * (G = 1 for per-channel) and answers IOB_UNSUPPORTED otherwise (the reference contract allows any
+ * K % 16 == 0).  b_zeros: int32 [G, N/8], field j of a word = column 8*(n/8)+j, required for
+ * IOB_QTYPE_UINT4 and NULL for IOB_QTYPE_UINT4B8.  b_bias: [N] in A's type or NULL.  N % 64 == 0.
+ * `scratch` must hold *_scratch_bytes(); its first use must find the header and counter area
+ * zeroed (cudaMemset once after allocation, or infiniops_b200_gemm_scratch_prepare on memory of
+ * unknown content); every completed call leaves it zeroed again.
  * The reference has no dense Marlin GEMM operator; this follows the argument set of its MoE
  * form (src/base/moe_wna16_marlin_gemm.h:18-34) without the routing arguments, and the value
  * semantics of tests/test_moe_wna16_gemm.py:397-404,437. */
@@ -213,6 +232,13 @@ int infiniops_b200_marlin_gemm_static_scratch(const void* a, int a_dtype, const 
                                               const int32_t* b_zeros, int64_t b_type_id,
                                               int64_t size_m, int64_t size_n, int64_t size_k,
                                               int64_t num_groups, void* out, void* stream);
+
+/* Status word of the built-in array used by infiniops_b200_marlin_gemm_static_scratch on the
+ * current device: copies it back on `stream`, clears the status header behind the copy,
+ * synchronises the stream and returns the word (0 = no wait expired since the last query,
+ * -1 = the query itself failed).  A non-zero answer means the output of some call since the last
+ * query is incomplete.  This entry point has no counterpart in the reference. */
+int infiniops_b200_static_scratch_status(void* stream);
 
 /* Bytes of scratch the routed (MoE) GEMM needs. */
 size_t infiniops_b200_moe_wna16_marlin_gemm_scratch_bytes(int64_t size_m, int64_t top_k,

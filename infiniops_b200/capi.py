@@ -28,7 +28,10 @@ PROTOTYPES = {
     "infiniops_b200_last_error": (ctypes.c_char_p, []),
     "infiniops_b200_version": (ctypes.c_char_p, []),
     "infiniops_b200_swap_device": (_int, [_int, _vp]),
-    "infiniops_b200_thread_scratch": (_vp, [_int, _sz]),
+    "infiniops_b200_thread_scratch": (_vp, [_int, _sz, _vp]),
+    "infiniops_b200_gemm_scratch_prepare": (_int, [_vp, _sz, _vp]),
+    "infiniops_b200_selftest_bounded_wait": (_int, [_vp, _sz, _vp, _vp]),
+    "infiniops_b200_static_scratch_status": (_int, [_vp]),
     "infiniops_b200_gptq_marlin_repack": (_int, [_vp, _vp, _i64, _i64, _int, _int, _vp, _vp]),
     "infiniops_b200_awq_marlin_repack": (_int, [_vp, _i64, _i64, _int, _int, _vp, _vp]),
     "infiniops_b200_topk_softmax": (_int, [_vp, _int, _vp, _vp, _int, _vp, _vp, _int, _vp, _i64, _i64, _i64, _vp]),

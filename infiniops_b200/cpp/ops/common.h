@@ -52,9 +52,12 @@ inline void Require(int status, const char* op) {
   }
 }
 
-// Scratch for a call: the Handle's workspace when it is large enough, else the library's
-// per-thread buffer for the current device (which allocates on first use / growth).
-inline void* PickScratch(void* workspace, std::size_t workspace_bytes, std::size_t need, int purpose,
+// Scratch for a call: the Handle's workspace when it is large enough, else the library's buffer
+// for (thread, device, purpose, stream), which allocates on first use / growth.  A Handle
+// workspace carries no promise about its content (other operators write it too), so for the GEMMs
+// (purpose 0), whose kernels count split-K arrivals in it, the counter area is cleared on the
+// stream first.
+inline void* PickScratch(void* workspace, std::size_t workspace_bytes, std::size_t need, int purpose, void* stream,
                          std::size_t& bytes_out) {
   if (need == 0) {
     bytes_out = 0;
@@ -62,9 +65,10 @@ inline void* PickScratch(void* workspace, std::size_t workspace_bytes, std::size
   }
   if (workspace != nullptr && workspace_bytes >= need) {
     bytes_out = workspace_bytes;
+    if (purpose == 0) Require(infiniops_b200_gemm_scratch_prepare(workspace, workspace_bytes, stream), "scratch set-up");
     return workspace;
   }
-  void* p = infiniops_b200_thread_scratch(purpose, need);
+  void* p = infiniops_b200_thread_scratch(purpose, need, stream);
   if (p == nullptr) Require(IOB_CUDA_ERROR, "scratch allocation");
   bytes_out = need;
   return p;

@@ -46,7 +46,7 @@ class Operator<MarlinGemm, Device::Type::kNvidia, 0> : public MarlinGemm {
                          use_fp32_reduce, is_zp_float);
     impl::DeviceGuard guard(device_index_);
     std::size_t scratch_bytes = 0;
-    void* scratch = impl::PickScratch(workspace_, workspace_size_in_bytes_, workspace_size_in_bytes(), 0, scratch_bytes);
+    void* scratch = impl::PickScratch(workspace_, workspace_size_in_bytes_, workspace_size_in_bytes(), 0, stream_, scratch_bytes);
     impl::Require(infiniops_b200_marlin_gemm(a.data(), impl::TypeCode(a.dtype()),
                                              static_cast<const int32_t*>(b_q_weight.data()), impl::DataOrNull(b_bias),
                                              b_scales.data(), static_cast<const int32_t*>(impl::DataOrNull(b_zeros)),
@@ -91,18 +91,17 @@ class Operator<MoeWna16MarlinGemm, Device::Type::kNvidia, 0> : public MoeWna16Ma
     INFINI_OPS_CHECK(!g_idx_or_none || g_idx_or_none->numel() == 0,
                      "`MoeWna16MarlinGemm` act-order (`g_idx` / `perm`) is not implemented");
     INFINI_OPS_CHECK(!is_zp_float, "`MoeWna16MarlinGemm` float zero points are not implemented");
-    INFINI_OPS_CHECK(topk_weights.dtype() == DataType::kFloat32, "`MoeWna16MarlinGemm` needs float32 `topk_weights`");
     impl::DeviceGuard guard(device_index_);
     std::size_t scratch_bytes = 0;
-    void* scratch = impl::PickScratch(workspace_, workspace_size_in_bytes_, workspace_size_in_bytes(), 0, scratch_bytes);
+    void* scratch = impl::PickScratch(workspace_, workspace_size_in_bytes_, workspace_size_in_bytes(), 0, stream_, scratch_bytes);
     impl::Require(
         infiniops_b200_moe_wna16_marlin_gemm(
             a.data(), impl::TypeCode(a.dtype()), static_cast<const int32_t*>(b_q_weight.data()),
             impl::DataOrNull(b_bias_or_none), b_scales.data(),
             static_cast<const int32_t*>(impl::DataOrNull(b_zeros_or_none)),
             static_cast<const int32_t*>(sorted_token_ids.data()), static_cast<const int32_t*>(expert_ids.data()),
-            static_cast<const int32_t*>(num_tokens_past_padded.data()), static_cast<const float*>(topk_weights.data()),
-            moe_block_size, top_k, mul_topk_weights ? 1 : 0, b_type_id, size_m, size_n, size_k,
+            static_cast<const int32_t*>(num_tokens_past_padded.data()), // (16-bit routing weights are only accepted when they are not applied: they are never read then)
+            mul_topk_weights ? static_cast<const float*>(topk_weights.data()) : nullptr, moe_block_size, top_k, mul_topk_weights ? 1 : 0, b_type_id, size_m, size_n, size_k,
             static_cast<int64_t>(b_scales.size(1)), static_cast<int64_t>(b_q_weight.size(0)),
             static_cast<int64_t>(sorted_token_ids.numel()), out.data(), scratch, scratch_bytes, stream_),
         kName);

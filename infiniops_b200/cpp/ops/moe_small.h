@@ -24,7 +24,7 @@ class Operator<MoeAlignBlockSize, Device::Type::kNvidia, 0> : public MoeAlignBlo
            Tensor num_tokens_post_pad) const override {
     impl::DeviceGuard guard(device_index_);
     std::size_t scratch_bytes = 0;
-    void* scratch = impl::PickScratch(workspace_, workspace_size_in_bytes_, workspace_size_in_bytes(), 1, scratch_bytes);
+    void* scratch = impl::PickScratch(workspace_, workspace_size_in_bytes_, workspace_size_in_bytes(), 1, stream_, scratch_bytes);
     impl::Require(infiniops_b200_moe_align_block_size(
                       static_cast<const int32_t*>(topk_ids.data()),
                       static_cast<const int32_t*>(impl::DataOrNull(expert_map)), static_cast<int64_t>(numel_),

@@ -1,6 +1,7 @@
 // Thread-local error text behind infiniops_b200_last_error().
 #include <cstdarg>
 #include <cstdio>
+#include <unordered_map>
 
 #include "common.cuh"
 
@@ -34,18 +35,20 @@ extern "C" int infiniops_b200_swap_device(int device, int* previous) {
   return IOB_OK;
 }
 
-extern "C" void* infiniops_b200_thread_scratch(int purpose, size_t bytes) {
+extern "C" void* infiniops_b200_thread_scratch(int purpose, size_t bytes, void* stream) {
   struct Buffer {
     void* ptr = nullptr;
     size_t size = 0;
   };
-  static thread_local Buffer buffers[64][2];
+  // One buffer per (calling thread, device, purpose, stream): two calls that can overlap on the GPU
+  // (same thread, different streams) never share split-K counters or partial sums.
+  static thread_local std::unordered_map<void*, Buffer> buffers[64][2];
   int device = 0;
   if (purpose < 0 || purpose > 1 || cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) {
     iob::Fail(IOB_INVALID_ARGUMENT, "thread_scratch: bad purpose or device");
     return nullptr;
   }
-  Buffer& b = buffers[device][purpose];
+  Buffer& b = buffers[device][purpose][stream];
   if (b.size < bytes) {
     const size_t want = bytes < (size_t{1} << 20) ? (size_t{1} << 20) : bytes + bytes / 4;
     void* fresh = nullptr;

@@ -210,10 +210,11 @@ __device__ __forceinline__ void NoteBlockedWarp(int* status, int code, int detai
 // woken with some delay; on a chain of hand-overs that is on the critical path (paired blocks:
 // commit -> activation producer -> copy -> relay -> issuer) those delays add up to more than the
 // MMAs they gate.  Only single threads wait this way, so the polling costs next to nothing.
-template <bool kClusterScope = false, bool kHot = false>
+// kPolls: a poll limit other than the default (the self-test below uses a short one).
+template <bool kClusterScope = false, bool kHot = false, uint32_t kPolls = 0>
 __device__ __forceinline__ bool MbarWait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
                                          int code, int detail = 0) {
-  constexpr uint32_t kLimit = kHot ? (kSpinLimit << 6) : kSpinLimit;
+  constexpr uint32_t kLimit = kPolls != 0 ? kPolls : kHot ? (kSpinLimit << 6) : kSpinLimit;
   for (uint32_t spin = 0;; ++spin) {
     if (kHot ? (kClusterScope ? MbarTestWaitCluster(bar, parity) : MbarTestWait(bar, parity))
              : (kClusterScope ? MbarTryWaitCluster(bar, parity) : MbarTryWait(bar, parity))) {
@@ -626,43 +627,6 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
   // overlap this kernel's tail.  Nothing of this kernel is published by it: the follower still
   // has to wait (GridDependencyWait) before it touches global memory.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  const int k_stages = p.k / kBlockK;
-  // kPair: the two blocks of a cluster walk the same sequence of (tile pair, k-stage) units; block
-  // `rank` owns output tile 2 * pair + rank.  `my_block` / `grid` below count clusters then.
-  uint32_t rank = 0;
-  if constexpr (kPair) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
-  const int my_block = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
-  const int blocks_launched = kPair ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
-  const int n_tiles = kPair ? p.n / (2 * kTileN) : (p.n + kTileN - 1) / kTileN;
-  int m_tiles;
-  if constexpr (kMoe) {
-    GridDependencyWait();  // the block count itself is a predecessor's output
-    m_tiles = *p.num_post_pad / p.block_size;
-  } else {
-    m_tiles = (p.m + kTok - 1) / kTok;
-  }
-  const long long total_units = static_cast<long long>(n_tiles) * m_tiles * k_stages;
-  // Never more ranges than units: an empty range between two sharers of a tile would break the
-  // arrival count of the tile.  Surplus blocks get nothing to do.
-  long long grid = total_units < static_cast<long long>(blocks_launched) ? (total_units > 0 ? total_units : 1)
-                                                                          : static_cast<long long>(blocks_launched);
-  // Few tiles: use a multiple of the tile count.  Then every range lies inside one tile (plain
-  // split-K), so a block has a single segment and a single hand-over instead of two ragged ones --
-  // worth more than the last few SMs when the whole GEMM is only a handful of stages per block.
-  {
-    const long long tiles = static_cast<long long>(n_tiles) * m_tiles;
-    if (tiles > 0 && tiles <= grid) {
-      const long long splits = grid / tiles < k_stages ? grid / tiles : k_stages;
-      if (tiles * splits * 5 >= grid * 4) grid = tiles * splits;
-    }
-  }
-  const bool idle = static_cast<long long>(my_block) >= grid || total_units == 0;
-  const long long u_begin = idle ? 0 : RangeStart(my_block, total_units, grid);
-  const long long u_end = idle ? 0 : RangeStart(my_block + 1, total_units, grid);
-  // output tile of a walker segment, and the block (as launched) behind a walker block number
-  auto tile_of = [&](int seg_n_tile) { return kPair ? 2 * seg_n_tile + static_cast<int>(rank) : seg_n_tile; };
-  auto launched_block = [&](int b) { return kPair ? 2 * b + static_cast<int>(rank) : b; };
-
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
       MbarInit(SmemAddr(&sh.full[i]), 1);
@@ -717,8 +681,48 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
   }
   // Paired blocks signal each other's barriers: nobody may start before both have initialised theirs.
   if constexpr (kPair) ClusterSync();
+  const int k_stages = p.k / kBlockK;
+  // kPair: the two blocks of a cluster walk the same sequence of (tile pair, k-stage) units; block
+  // `rank` owns output tile 2 * pair + rank.  `my_block` / `grid` below count clusters then.
+  uint32_t rank = 0;
+  if constexpr (kPair) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  const int my_block = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int blocks_launched = kPair ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  const int n_tiles = kPair ? p.n / (2 * kTileN) : (p.n + kTileN - 1) / kTileN;
+  int m_tiles;
+  if constexpr (kMoe) {
+    GridDependencyWait();  // the block count itself is a predecessor's output
+    m_tiles = *p.num_post_pad / p.block_size;
+  } else {
+    m_tiles = (p.m + kTok - 1) / kTok;
+  }
+  const long long total_units = static_cast<long long>(n_tiles) * m_tiles * k_stages;
+  // Never more ranges than units: an empty range between two sharers of a tile would break the
+  // arrival count of the tile.  Surplus blocks get nothing to do.
+  long long grid = total_units < static_cast<long long>(blocks_launched) ? (total_units > 0 ? total_units : 1)
+                                                                          : static_cast<long long>(blocks_launched);
+  // Few tiles: use a multiple of the tile count.  Then every range lies inside one tile (plain
+  // split-K), so a block has a single segment and a single hand-over instead of two ragged ones --
+  // worth more than the last few SMs when the whole GEMM is only a handful of stages per block.
+  {
+    const long long tiles = static_cast<long long>(n_tiles) * m_tiles;
+    if (tiles > 0 && tiles <= grid) {
+      const long long splits = grid / tiles < k_stages ? grid / tiles : k_stages;
+      if (tiles * splits * 5 >= grid * 4) grid = tiles * splits;
+    }
+  }
+  const bool idle = static_cast<long long>(my_block) >= grid || total_units == 0;
+  const long long u_begin = idle ? 0 : RangeStart(my_block, total_units, grid);
+  const long long u_end = idle ? 0 : RangeStart(my_block + 1, total_units, grid);
+  // output tile of a walker segment, and the block (as launched) behind a walker block number
+  auto tile_of = [&](int seg_n_tile) { return kPair ? 2 * seg_n_tile + static_cast<int>(rank) : seg_n_tile; };
+  auto launched_block = [&](int b) { return kPair ? 2 * b + static_cast<int>(rank) : b; };
+
   // From here on global memory is read and written: everything before was on-chip set-up.
-  if constexpr (!kMoe) GridDependencyWait();
+  // (The producer warp waits later: its first ring of weight copies does not depend on the predecessor.)
+  if constexpr (!kMoe) {
+    if (warp != 0) GridDependencyWait();
+  }
   const uint32_t tmem_base = warp == 0 ? 0u : sh.tmem_base;
   const uint32_t tmem_d = tmem_base;  // accumulators: kAcc stages x kIssuers x kTok columns
   const uint32_t tmem_a = tmem_base + kAcc * kAccSets * kTok;  // weights: kAStages x 64 columns
@@ -734,34 +738,64 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
       Cursor c{Walker{u_begin, u_end, k_stages, m_tiles}, Segment{}, static_cast<uint32_t>(lane), 0u, 0, 0};
       bool active = Locate<kMoe>(c, p.expert_ids);
       const int grp_rows = p.group_size == 64 ? 2 : 1;
+      // The copies of one stage.  Packed weights, scales and zero points are constants of the model;
+      // only the activations can be the output of the kernel before this one.
+      auto request_weights = [&](const Cursor& cur) {
+        const int s = cur.it % kStages;
+        const int ks = cur.Ks();
+        const uint32_t full = SmemAddr(&sh.full[s]);
+        // both boxes are always counted in full (rows past M and columns past N arrive as zeros)
+        MbarExpectTx(full, (kPair ? 0 : kActBytes) + 8192);
+        TmaLoad2D(stages_addr + s * kStage + kWeightsAt, &w_map, 2 * tile_of(cur.seg.n_tile) * kTileN,
+                  cur.expert * (p.k / 16) + ks * 8, full);
+        // The dequantisers read this stage's scales and zero points with plain loads one stage
+        // ahead; pull the lines into L2 now, a whole ring ahead.
+        const int n0 = tile_of(cur.seg.n_tile) * kTileN;
+        const size_t grow = static_cast<size_t>(cur.expert) * p.groups + GroupOf(p, ks);
+        const char* sc = reinterpret_cast<const char*>(static_cast<const T*>(p.scales) + grow * p.n + n0);
+        const bool wide = n0 + 64 < p.n;  // second 128-byte line of the tile's 256 bytes of scales
+        for (int r = 0; r < grp_rows; ++r) {
+          PrefetchL2(sc + static_cast<size_t>(r) * p.n * 2);
+          if (wide) PrefetchL2(sc + static_cast<size_t>(r) * p.n * 2 + 128);
+          if constexpr (kZeros) PrefetchL2(p.zeros + (grow + r) * (p.n / 8) + n0 / 8);
+        }
+      };
+      auto request_activations = [&](const Cursor& cur) {
+        if constexpr (!kPair) {
+          const int s = cur.it % kStages;
+          // a paired block loads its own half of the tile's token rows
+          const int row0 =
+              (kMoe ? cur.seg.m_tile * p.block_size : cur.seg.m_tile * kTok) + static_cast<int>(rank) * kActRows;
+          // two 64-k atoms, one after the other
+          TmaLoad3D(stages_addr + s * kStage, &a_map, 0, row0, 2 * cur.Ks(), SmemAddr(&sh.full[s]));
+        }
+      };
+      if constexpr (!kMoe) {
+        // First trip round the ring (every slot is free): the weight copies go out before this
+        // kernel waits for its predecessor, so they overlap that kernel's tail; the activation
+        // copies follow once the predecessor's output is visible.
+        Cursor ahead = c;
+        bool ahead_active = active;
+        while (ahead_active && ahead.it < static_cast<uint32_t>(kStages)) {
+          request_weights(ahead);
+          ahead.it += kProdLanes;
+          ahead_active = Locate<kMoe>(ahead, p.expert_ids);
+        }
+        GridDependencyWait();
+        while (active && c.it < static_cast<uint32_t>(kStages)) {
+          request_activations(c);
+          c.it += kProdLanes;
+          active = Locate<kMoe>(c, p.expert_ids);
+        }
+      }
       uint32_t idle = 0;
       while (__any_sync(kMask, active)) {
         bool progressed = false;
         if (active) {
           const int s = c.it % kStages;
           if (MbarTestWait(SmemAddr(&sh.empty[s]), ((c.it / kStages) & 1) ^ 1)) {
-            const int ks = c.Ks();
-            // a paired block loads its own half of the tile's token rows
-            const int row0 = (kMoe ? c.seg.m_tile * p.block_size : c.seg.m_tile * kTok) + static_cast<int>(rank) * kActRows;
-            const uint32_t full = SmemAddr(&sh.full[s]);
-            const uint32_t base = stages_addr + s * kStage;
-            // both boxes are always counted in full (rows past M and columns past N arrive as zeros)
-            MbarExpectTx(full, (kPair ? 0 : kActBytes) + 8192);
-            TmaLoad2D(base + kWeightsAt, &w_map, 2 * tile_of(c.seg.n_tile) * kTileN, c.expert * (p.k / 16) + ks * 8, full);
-            if constexpr (!kPair) TmaLoad3D(base, &a_map, 0, row0, 2 * ks, full);  // two 64-k atoms, one after the other
-            // The dequantisers read this stage's scales and zero points with plain loads one stage
-            // ahead; pull the lines into L2 now, a whole ring ahead.
-            {
-              const int n0 = tile_of(c.seg.n_tile) * kTileN;
-              const size_t grow = static_cast<size_t>(c.expert) * p.groups + GroupOf(p, ks);
-              const char* sc = reinterpret_cast<const char*>(static_cast<const T*>(p.scales) + grow * p.n + n0);
-              const bool wide = n0 + 64 < p.n;  // second 128-byte line of the tile's 256 bytes of scales
-              for (int r = 0; r < grp_rows; ++r) {
-                PrefetchL2(sc + static_cast<size_t>(r) * p.n * 2);
-                if (wide) PrefetchL2(sc + static_cast<size_t>(r) * p.n * 2 + 128);
-                if constexpr (kZeros) PrefetchL2(p.zeros + (grow + r) * (p.n / 8) + n0 / 8);
-              }
-            }
+            request_weights(c);
+            request_activations(c);
             c.it += kProdLanes;
             active = Locate<kMoe>(c, p.expert_ids);
             progressed = true;
@@ -1441,6 +1475,30 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
   }
 }
 
+// Self-test of the bounded wait: one thread waits, with a limit of a few thousand polls, on a
+// barrier that nobody ever arrives at.  The wait must give up, record (code, block, thread, detail)
+// in the status header and return false; the kernel then ends normally.  No copy engine and no
+// tensor memory is involved, so nothing is left in flight.
+constexpr int kErrSelfTest = 7;
+__global__ void BoundedWaitSelfTestKernel(int* status, int* result) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    MbarInit(SmemAddr(&bar), 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  bool ok = true;
+  if (threadIdx.x == 0) ok = MbarWait<false, true, 4096>(SmemAddr(&bar), 0, &abort_flag, status, kErrSelfTest, 42);
+  __syncthreads();
+  // the other threads see the block's abort flag, as the roles of the GEMM kernel do
+  if (threadIdx.x == 0) {
+    result[0] = ok ? 1 : 0;
+    result[1] = abort_flag;
+  }
+}
+
 // Copies the routed rows of `a` into scratch in sorted order so a TMA box of consecutive rows
 // is one routing block.
 template <typename T>
@@ -1758,6 +1816,24 @@ extern "C" int infiniops_b200_scratch_status(const void* scratch, void* stream) 
   return code;
 }
 
+extern "C" int infiniops_b200_selftest_bounded_wait(void* scratch, size_t scratch_bytes, int* result, void* stream) {
+  using namespace iob;
+  IOB_REQUIRE(scratch != nullptr && scratch_bytes >= static_cast<size_t>(kHeaderBytes) && result != nullptr,
+              "selftest_bounded_wait: needs a scratch header of %d bytes and a result pointer", kHeaderBytes);
+  BoundedWaitSelfTestKernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<int*>(scratch), result);
+  return CheckLaunch("selftest_bounded_wait launch");
+}
+
+extern "C" int infiniops_b200_gemm_scratch_prepare(void* scratch, size_t scratch_bytes, void* stream) {
+  using namespace iob;
+  const size_t need = kHeaderBytes + static_cast<size_t>(4) * kMaxGrid * sizeof(int);
+  IOB_REQUIRE(scratch != nullptr && scratch_bytes >= need, "gemm_scratch_prepare: the buffer is smaller than %zu bytes", need);
+  if (cudaMemsetAsync(scratch, 0, need, static_cast<cudaStream_t>(stream)) != cudaSuccess) {
+    return Fail(IOB_CUDA_ERROR, "gemm_scratch_prepare: clearing the header failed");
+  }
+  return IOB_OK;
+}
+
 extern "C" size_t infiniops_b200_marlin_gemm_scratch_bytes(int64_t size_m, int64_t size_n, int64_t size_k) {
   using namespace iob;
   (void)size_k;
@@ -1842,7 +1918,6 @@ extern "C" int infiniops_b200_moe_wna16_marlin_gemm(
   IOB_REQUIRE(moe_block_size == 8 || (moe_block_size >= 16 && moe_block_size <= 64 && moe_block_size % 16 == 0),
               "%s: received an unsupported `moe_block_size`", op);
   IOB_REQUIRE(!mul_topk_weights || topk_weights != nullptr, "%s: received invalid top-k weights", op);
-  if (moe_block_size == 8) return Fail(IOB_UNSUPPORTED, "%s: `moe_block_size` 8 is not implemented", op);
   const int tok = TokenTile(moe_block_size);
   // rows the routing can occupy at most (the bound the sort operator guarantees)
   int64_t sorted_cap = size_m * top_k + num_experts * (moe_block_size - 1);
@@ -1965,4 +2040,18 @@ extern "C" int infiniops_b200_marlin_gemm_static_scratch(const void* a, int a_dt
   }
   return infiniops_b200_marlin_gemm(a, a_dtype, b_q_weight, b_bias, b_scales, b_zeros, b_type_id, size_m, size_n,
                                     size_k, num_groups, out, scratch, kStaticScratchBytes, stream);
+}
+
+extern "C" int infiniops_b200_static_scratch_status(void* stream) {
+  using namespace iob;
+  void* scratch = nullptr;
+  if (StaticScratchAddress(&scratch) != IOB_OK) return -1;
+  auto s = static_cast<cudaStream_t>(stream);
+  int code = 0;
+  // read the word, then clear the header (status and the blocked-warp notes) behind it on the same stream
+  if (cudaMemcpyAsync(&code, scratch, sizeof(int), cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+      cudaMemsetAsync(scratch, 0, kHeaderBytes, s) != cudaSuccess || cudaStreamSynchronize(s) != cudaSuccess) {
+    return -1;
+  }
+  return code;
 }

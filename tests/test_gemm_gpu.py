@@ -121,3 +121,46 @@ def test_rejects_unsupported():
         capi.marlin_gemm(a, w, None, s, None, 1125899923621888, 4, 64, 128, out)
     with pytest.raises(capi.Error, match="zero points are required"):
         capi.marlin_gemm(a, w, None, s, None, capi.QTYPE_UINT4, 4, 64, 128, out)
+
+
+def test_bounded_wait_gives_up_and_reports():
+    """The bounded device-side wait in isolation: a stand-alone kernel (no copies, no tensor cores)
+    whose one waiting thread polls a barrier nobody arrives at.  It must give up after its poll
+    limit, leave (code 7, block 0, thread 0, detail 42) in the status header, end normally and
+    leave the context usable."""
+    from infiniops_b200 import capi
+
+    scratch = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    result = torch.full((2,), -1, dtype=torch.int32, device="cuda")
+    rc = capi.lib().infiniops_b200_selftest_bounded_wait(scratch.data_ptr(), scratch.numel(), result.data_ptr(), None)
+    assert rc == 0, capi.lib().infiniops_b200_last_error()
+    torch.cuda.synchronize()
+    assert result.tolist() == [0, 1]
+    assert capi.scratch_status(scratch) == 7
+    assert scratch[:16].view(torch.int32).tolist() == [7, 0, 0, 42]
+    # memory of unknown content becomes usable scratch again through the prepare call
+    scratch.fill_(0xFF)
+    assert capi.lib().infiniops_b200_gemm_scratch_prepare(scratch.data_ptr(), scratch.numel(), None) == 0
+    assert capi.scratch_status(scratch) == 0
+    q, scales, zeros = make_quantized(512, 256, 128, torch.bfloat16, True, 21)
+    a = torch.randn((16, 512)).bfloat16()
+    assert rel_max_err(_gemm(a, q, scales, zeros, "awq"), oq.w4a16_gemm(a, q, scales, zeros)) <= TOL
+
+
+def test_scratch_of_unknown_content_after_prepare():
+    """A split-K problem (one column tile, 64 k-stages over many blocks) on a scratch buffer that
+    was filled with 0xFF and then prepared: the arrival counters must work from the first call."""
+    from infiniops_b200 import capi
+
+    m, k, n = 16, 8192, 128
+    q, scales, _ = make_quantized(k, n, 128, torch.float16, False, 31)
+    a = torch.randn((m, k)).half()
+    marlin = torch.from_numpy(oq.marlin_pack(q, 4, False)).cuda()
+    need = capi.lib().infiniops_b200_marlin_gemm_scratch_bytes(m, n, k)
+    scratch = torch.full((need,), 0xFF, dtype=torch.uint8, device="cuda")
+    assert capi.lib().infiniops_b200_gemm_scratch_prepare(scratch.data_ptr(), scratch.numel(), None) == 0
+    out = torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda")
+    capi.marlin_gemm(a.cuda(), marlin, None, scales.cuda(), None, capi.QTYPE_UINT4B8, m, n, k, out, scratch_buf=scratch)
+    torch.cuda.synchronize()
+    assert capi.scratch_status(scratch) == 0
+    assert rel_max_err(out, oq.w4a16_gemm(a, q, scales, None)) <= TOL

@@ -33,6 +33,13 @@ def test_marlin_pack_roundtrip():
         assert np.array_equal(oq.marlin_unpack(packed, 64, 128, bits, a8), w)
 
 
+def test_fast_w4_unpack_matches_the_index_map():
+    rng = np.random.default_rng(1)
+    for k, n in ((16, 64), (128, 192), (512, 256)):
+        words = rng.integers(-2**31, 2**31 - 1, size=(k // 16, 2 * n), dtype=np.int64).astype(np.int32)
+        assert np.array_equal(oq.marlin_unpack_w4(words, k, n), oq.marlin_unpack(words, k, n, 4, False))
+
+
 def test_topk_softmax_golden(golden):
     g = golden["topk_softmax"]
     bias = torch.from_numpy(g["bias"])

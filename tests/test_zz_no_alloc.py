@@ -34,10 +34,16 @@ def test_static_scratch_matches_caller_scratch_twice_in_a_row():
         expect = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
         capi.marlin_gemm(a, marlin, None, scales, zeros, capi.QTYPE_UINT4, m, n, k, expect)
         got = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+        torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
+        free_before = torch.cuda.mem_get_info()[0]   # the driver's view: sees a cudaMalloc torch would not
         capi.marlin_gemm_static_scratch(a, marlin, None, scales, zeros, capi.QTYPE_UINT4, m, n, k, got)
         assert torch.cuda.memory_allocated() == before
         torch.cuda.synchronize()
+        # (the first call on a device may load the kernel's module lazily; later calls may not move it)
+        if call > 0:
+            assert torch.cuda.mem_get_info()[0] == free_before
+        assert capi.lib().infiniops_b200_static_scratch_status(None) == 0
         assert not torch.isnan(got.float()).any()
         scale = float(expect.float().abs().max())
         assert float((got.float() - expect.float()).abs().max()) <= 1e-2 * scale
@@ -47,6 +53,16 @@ def test_static_scratch_matches_caller_scratch_twice_in_a_row():
 def test_static_scratch_rejects_problems_beyond_its_capacity():
     from infiniops_b200 import capi
 
+    # the limit itself on a 148-SM GPU: 64 rows fit, 65 do not
+    lib = capi.lib()
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    if sms == 148:
+        assert lib.infiniops_b200_marlin_gemm_scratch_bytes(64, 128, 256) <= (10 << 20)
+        assert lib.infiniops_b200_marlin_gemm_scratch_bytes(65, 128, 256) > (10 << 20)
+        a, marlin, scales, zeros = _problem(65, 256, 128, 4)
+        with pytest.raises(capi.Error, match="built-in buffer holds"):
+            capi.marlin_gemm_static_scratch(a, marlin, None, scales, zeros, capi.QTYPE_UINT4, 65, 128, 256,
+                                            torch.empty((65, 128), dtype=torch.bfloat16, device="cuda"))
     m, k, n = 4096, 256, 128
     a, marlin, scales, zeros = _problem(m, k, n, 3)
     out = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
