@@ -1,27 +1,37 @@
-"""Benchmark of the W4A16 decode path (the configuration the headline metric is quoted on).
+"""Benchmark of the W4A16 linear + MoE hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-Workload (BASELINE.json configs[1]): the four Llama-3-8B-shaped AWQ int4 linears
+Headline workload (BASELINE.json configs[1]): the four Llama-3-8B-shaped AWQ int4 linears
 (K x N: qkv 4096x6144, o 4096x4096, gate_up 4096x28672, down 14336x4096; group 128, bf16
 activations ~N(0,1), int4 weights and zero points uniform in 0..15, bf16 scales
 |N(0,1)|*0.01+1e-3) at M in {1, 4, 16, 64}.  One STEP = those 16 GEMMs.  Data are seeded
-synthetic tensors of these shapes (no checkpoint is involved).
+synthetic tensors of these shapes (no checkpoint or dataset is involved).
 
 Metric: weight-stream bandwidth = int4 weight bytes of the GEMMs of a step / time.
-* `value`     inputs resident in HBM; the step is replayed as a CUDA graph; weights rotate over
-              several full copies of the layer so that no GEMM finds its weights in L2.
-* `e2e`       the same GEMMs issued one by one through the operator API with HOST activations
-              and outputs: pinned host -> device copy of A and device -> host copy of C inside
-              the timed region (weights are model state and stay on the device).
+* `value`     inputs resident in HBM; the step is the batched dense GEMM (the 16 problems as two
+              persistent launches) replayed as a CUDA graph; weights rotate over several full copies of
+              the layer so that no GEMM finds its weights in L2.  The timed region of K steps is
+              repeated; the median is reported with the spread.
+* `e2e`       the same GEMMs issued one by one through the operator API (`infini.ops.marlin_gemm`)
+              with HOST activations and outputs: pinned host -> device copy of A and device -> host
+              copy of C inside the timed region (weights are model state and stay on the device).
 * `roofline`  algorithmic bytes of the GEMM launches in the timed region / their time, against
               the measured HBM copy bandwidth of this machine pool.
 * `cpu_baseline`  the reference's CPU formulation (fp32 dequantise, then matmul) on the host
               cores for a bounded sample of the same workload.
+* `per_gemm`, `prefill`, `moe`, `small_kernels`  sub-records, each with its own CUDA-event timing:
+              the step as sixteen separate launches; the four linears at M = 4096 (TFLOP/s against the
+              measured bf16 peak); the Mixtral- and DeepSeek-shaped MoE layers (tokens/s); repack,
+              routers, token sort, silu_and_mul and moe_sum at their layer sizes (GB/s).
 
 With N > 1 (one process per GPU under torchrun) every linear is column-parallel: rank r holds
-columns [r N/g, (r+1) N/g) and the output slices are all-gathered over NCCL.  The total work is
-the same for every N (strong scaling).
+columns [r N/g, (r+1) N/g) and the GEMM epilogue stores its slice straight into the full-width
+result matrix of EVERY rank over NVLink (peer-mapped buffers, plain stores, no multicast); the last
+block of a step's last launch raises a flag on each peer and a bounded wait on the flags closes the
+step.  No NCCL call is on the decode path.  After the timed region every rank checks that each
+gathered slice equals, bit for bit, what that rank's shard computes locally.  The MoE layer is
+expert-parallel.  The total work is the same for every N (strong scaling).
 """
 
 from __future__ import annotations
@@ -46,25 +56,31 @@ MS = (1, 4, 16, 64)
 GROUP = 128
 SEED = 20260728 + 1000
 L2_BYTES = 126 * 1024 * 1024
+UINT4B8, UINT4 = 1125899907892224, 1125899906843648
+WORKLOAD = ("configs[1]: Llama-3-8B-shaped AWQ W4A16 linears (qkv, o, gate_up, down), g=128, "
+            "M in {1,4,16,64}; one step = these 16 GEMMs")
+METRIC = "W4A16 GEMM weight HBM GB/s (decode)"
 
 
 def weight_bytes(k, n):
     return k * n // 2
 
 
-def algorithmic_bytes(m, k, n):
+def algorithmic_bytes(m, k, n, zeros=True):
     g = k // GROUP
-    return k * n // 2 + g * n * 2 + g * n // 2 + m * k * 2 + m * n * 2
+    return k * n // 2 + g * n * 2 + (g * n // 2 if zeros else 0) + m * k * 2 + m * n * 2
 
 
-def measured_hbm_peak():
+def measured_peaks():
     path = ROOT / "MEASURED_PEAKS.json"
     if path.exists():
         try:
-            return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+            d = json.loads(path.read_text())
+            return {"hbm": float(d["hbm_gbs"]), "bf16": float(d["bf16_tflops"]),
+                    "bf16_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "kind": "measured"}
         except Exception:
             pass
-    return 6650.0, "fallback"
+    return {"hbm": 6650.0, "bf16": 1590.0, "bf16_sustained": 1400.0, "kind": "fallback"}
 
 
 class ClockSampler:
@@ -117,6 +133,67 @@ class ClockSampler:
         return out
 
 
+class Dist:
+    """Rank bookkeeping (one process per GPU under torchrun; a single process otherwise)."""
+
+    def __init__(self, args):
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(self.local_rank)
+        self.device = torch.device("cuda", self.local_rank)
+        if self.world > 1:
+            import torch.distributed as dist
+
+            dist.init_process_group("nccl", device_id=self.device)
+        assert self.world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={self.world}"
+
+    def barrier(self):
+        if self.world > 1:
+            import torch.distributed as dist
+
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(self, values):
+        t = torch.tensor(values, dtype=torch.float64, device=self.device)
+        if self.world > 1:
+            import torch.distributed as dist
+
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return [float(v) for v in t.cpu()]
+
+    def all_true(self, flag: bool) -> bool:
+        t = torch.tensor([1 if flag else 0], dtype=torch.int32, device=self.device)
+        if self.world > 1:
+            import torch.distributed as dist
+
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return bool(int(t.cpu()[0]))
+
+
+def timed_regions(d: Dist, run_steps, steps, repeats):
+    """`repeats` timed regions of `steps` steps each, every one bracketed by a barrier and a device
+    synchronisation, timed with CUDA events on the launching stream; max over ranks per region.
+    Returns the per-region ms-per-step values."""
+    out = []
+    for _ in range(repeats):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        d.barrier()
+        start.record()
+        run_steps(steps)
+        stop.record()
+        d.barrier()
+        out.append(d.max_over_ranks([start.elapsed_time(stop)])[0] / steps)
+    return out
+
+
+def spread_of(values):
+    med = statistics.median(values)
+    return {"median": med, "min": min(values), "max": max(values), "regions": len(values),
+            "spread": (max(values) - min(values)) / med if med else None}
+
+
 # ---------------------------------------------------------------------------------------------------
 def make_layer(rank, world, device, copy_index):
     """One copy of the four linears, column shard `rank` of `world`, prepared through the
@@ -139,197 +216,510 @@ def make_layer(rank, world, device, copy_index):
 
 
 def run_ours(args):
-    import torch.distributed as dist
+    from infiniops_b200 import capi
 
-    from infiniops_b200 import capi, parallel
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
-    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    d = Dist(args)
+    world, rank, device = d.world, d.rank, d.device
+    peaks = measured_peaks()
 
     layer_bytes = sum(weight_bytes(k, n) for _, k, n in SHAPES) // world
     # Rotate through >= 3x L2 of weights; a multiple of len(MS) so that the j-th M of a step always
     # takes copy 4 * phase + j and a (linear, copy) pair returns only after all copies were streamed.
-    copies = len(MS) * max(1, -(-3 * L2_BYTES // (layer_bytes * len(MS))))
+    # An even number of phases: the output buffers alternate with the phase (see below).
+    phases = max(2, -(-3 * L2_BYTES // (layer_bytes * len(MS))))
+    phases += phases % 2
+    copies = len(MS) * phases
     layers = [make_layer(rank, world, device, c) for c in range(copies)]
     acts = {(name, m): torch.randn((m, k), device=device, generator=torch.Generator(device=device).manual_seed(
         SEED + 7 * m + i)).bfloat16() for i, (name, k, _) in enumerate(SHAPES) for m in MS}
-    # The 16 output slices live in one arena, so that the slices of a whole step can also be exchanged
-    # with a single all-gather (--gather step); each slice starts on a 16-byte boundary.
-    arena_elems = sum(-(-(m * (n // world)) // 8) * 8 for _, _, n in SHAPES for m in MS)
-    arena = torch.empty(arena_elems, dtype=torch.bfloat16, device=device)
-    arena_all = torch.empty((world, arena_elems), dtype=torch.bfloat16, device=device) if world > 1 else None
-    outs, off = {}, 0
-    for name, _, n in SHAPES:
-        for m in MS:
-            outs[(name, m)] = arena[off:off + m * (n // world)].view(m, n // world)
-            off += -(-(m * (n // world)) // 8) * 8
-    gathered = {(name, m): torch.empty((world, m, n // world), dtype=torch.bfloat16, device=device)
-                for name, _, n in SHAPES for m in MS} if world > 1 else None
-    need = max(capi.lib().infiniops_b200_marlin_gemm_scratch_bytes(m, n // world, k) for _, k, n in SHAPES for m in MS)
-    scratch = torch.zeros(need, dtype=torch.uint8, device=device)
+    keys = [(name, m) for m in MS for name, _, _ in SHAPES]
+    full_n = {name: n for name, _, n in SHAPES}
+    full_k = {name: k for name, k, _ in SHAPES}
 
-    phases = copies // len(MS)
+    # Result matrices [M, N] (full width).  With N > 1 they live in an arena every rank maps, in two
+    # sets used by alternate steps: a rank that runs one step ahead stores into the other set.
+    group = None
+    if world > 1:
+        from infiniops_b200 import peer
 
-    if args.gather == "auto":
-        args.gather = "step"
-    comm = None
-    if world > 1 and args.gather not in ("serial", "step"):
-        comm = torch.cuda.Stream(priority=-1) if args.gather == "overlap-prio" else torch.cuda.Stream()
+        set_bytes = sum(-(-(m * full_n[name] * 2) // 256) * 256 for name, m in keys)
+        prefill_bytes = 0 if args.headline_only else 4096 * max(n for _, _, n in SHAPES) * 2 + 256
+        group = peer.PeerGroup(2 * set_bytes + prefill_bytes, device)
+        offsets = [{key: group.carve(key[1] * full_n[key[0]] * 2) for key in keys} for _ in range(2)]
+        outs = [{key: group.local(offsets[s][key], (key[1], full_n[key[0]]), torch.bfloat16) for key in keys}
+                for s in range(2)]
+    else:
+        outs = [{key: torch.empty((key[1], full_n[key[0]]), dtype=torch.bfloat16, device=device) for key in keys}] * 2
+    scratch = torch.zeros(max(capi.lib().infiniops_b200_marlin_gemm_batch_scratch_bytes(),
+                              max(capi.lib().infiniops_b200_marlin_gemm_scratch_bytes(m, n // world, k)
+                                  for _, k, n in SHAPES for m in MS)), dtype=torch.uint8, device=device)
 
-    def step(phase, stream=None):
-        """The 16 GEMMs back to back on the compute stream; with N > 1 every all-gather runs on a second
-        stream behind its GEMM, so the exchange of one linear overlaps the GEMM of the next."""
-        launches = 0
-        main = torch.cuda.current_stream()
-        for mi, m in enumerate(MS):
-            for name, k, n in SHAPES:
-                w = layers[phase * len(MS) + mi][name]
-                capi.marlin_gemm(acts[(name, m)], w["marlin"], None, w["scales"], w["zeros"], capi.QTYPE_UINT4, m,
-                                 w["n"], k, outs[(name, m)], stream=stream, scratch_buf=scratch)
-                launches += 1
-                if world > 1 and args.gather != "step":
-                    if comm is None:
-                        parallel.gather_columns(outs[(name, m)], gathered[(name, m)])
-                    else:
-                        comm.wait_stream(main)
-                        with torch.cuda.stream(comm):
-                            parallel.gather_columns(outs[(name, m)], gathered[(name, m)])
-        if comm is not None:
-            main.wait_stream(comm)
-        if world > 1 and args.gather == "step":
-            dist.all_gather_into_tensor(arena_all.view(-1), arena)  # [g, arena]: rank-major copies of every slice
-        return launches
+    def problem(phase, key, layer_set=None):
+        name, m = key
+        w = (layer_set or layers)[phase * len(MS) + MS.index(m)][name]
+        peers = [] if group is None else [group.address(r, offsets[phase % 2][key]) for r in group.others()]
+        return capi.gemm_problem(acts[key], w["marlin"], None, w["scales"], w["zeros"], outs[phase % 2][key], m, w["n"],
+                                 w["k"], out_ld=full_n[name], out_col0=rank * w["n"], peer_out=peers)
 
-    # warm-up outside any graph (function attributes, tensor maps, NCCL channels)
-    for phase in range(phases):
-        step(phase)
-    torch.cuda.synchronize()
-    assert capi.scratch_status(scratch) == 0, f"a GEMM kernel gave up on a wait: {scratch[:192].view(torch.int32).tolist()}"
+    tables = [capi.problem_array([problem(phase, key) for key in keys]) for phase in range(phases)]
+    singles = [[problem(phase, key) for key in keys] for phase in range(phases)]
+    signal = None if group is None else group.signal()
 
-    # The step as CUDA graphs, one per weight copy rotation, so replays keep rotating the weights.
-    graphs = []
-    launches_per_step = 0
-    side = torch.cuda.Stream()
-    side.wait_stream(torch.cuda.current_stream())
-    n_graphs = phases
-    with torch.cuda.stream(side):
-        for phase in range(n_graphs):
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=side):
-                launches_per_step = step(phase, stream=side.cuda_stream)
-            graphs.append(g)
-    torch.cuda.current_stream().wait_stream(side)
-    torch.cuda.synchronize()
+    def step_batched(phase, stream=None):
+        capi.marlin_gemm_batch(tables[phase], torch.bfloat16, UINT4, scratch, signal=signal, stream=stream)
+        if group is not None:
+            group.wait(stream=stream)
+        return 2 + (1 if group is not None else 0)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
+    def step_per_gemm(phase, stream=None):
+        for i, g in enumerate(singles[phase]):
+            last = i == len(keys) - 1
+            capi.marlin_gemm_placed(g, torch.bfloat16, UINT4, scratch, signal=signal if last else None, stream=stream)
+        if group is not None:
+            group.wait(stream=stream)
+        return len(keys) + (1 if group is not None else 0)
+
+    def capture(step_fn):
+        """The step as CUDA graphs, one per weight-copy phase, so that replays keep rotating the weights."""
+        for phase in range(phases):   # outside any graph first: function attributes, tensor maps
+            step_fn(phase)
         torch.cuda.synchronize()
+        d.barrier()
+        graphs, launches = [], 0
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for phase in range(phases):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    launches = step_fn(phase, stream=side.cuda_stream)
+                graphs.append(g)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        return graphs, launches
 
-    for i in range(max(args.warmup, 3)):
-        graphs[i % n_graphs].replay()
-    barrier()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local_rank) as clocks:
+    def check_status(what):
+        torch.cuda.synchronize()
+        assert capi.scratch_status(scratch) == 0, f"{what}: a GEMM kernel gave up on a wait: " \
+                                                  f"{scratch[:192].view(torch.int32).tolist()}"
+        if group is not None:
+            assert group.wait_status() == (0, 0), f"{what}: a wait for a peer's completion flag ran out: {group.wait_status()}"
+
+    counter = [0]
+
+    def replayer(graphs):
+        def run(n):
+            for _ in range(n):
+                graphs[counter[0] % phases].replay()
+                counter[0] += 1
+        return run
+
+    warmup = max(args.warmup, 3)
+    repeats = 5
+    graphs, launches_per_step = capture(step_batched)
+    run = replayer(graphs)
+    run(max(warmup, phases))   # every graph at least once before anything is timed
+    check_status("warm-up")
+    with ClockSampler(d.local_rank) as clocks:
         time.sleep(0.15)
-        barrier()
-        start.record()
-        for i in range(args.steps):
-            graphs[i % n_graphs].replay()
-        stop.record()
-        barrier()
+        regions = timed_regions(d, run, args.steps, repeats)
         time.sleep(0.15)
-    elapsed_ms = start.elapsed_time(stop)
-    assert capi.scratch_status(scratch) == 0, f"a GEMM kernel gave up on a wait: {scratch[:192].view(torch.int32).tolist()}"
+    check_status("timed region")
+    ms_per_step = statistics.median(regions)
+    last_phase = (counter[0] - 1) % phases
+
+    # ---- N > 1: what arrived from every rank must be what that rank's shard computes ---------------
+    checked = None
+    if group is not None:
+        checked = check_gathered(d, capi, layers, acts, keys, outs[last_phase % 2], last_phase, scratch, full_n, full_k)
+
+    # ---- the same step as sixteen separate launches -------------------------------------------------
+    per_gemm = None
+    if not args.headline_only:
+        graphs16, launches16 = capture(step_per_gemm)
+        run16 = replayer(graphs16)
+        run16(max(warmup, phases))
+        reg16 = timed_regions(d, run16, args.steps, 3)
+        check_status("per-GEMM step")
+        per_gemm = {"ms_per_step": statistics.median(reg16), "launches_per_step": launches16,
+                    "note": "the same 16 GEMMs as one launch each (programmatic dependent launches in a graph)"}
+        del graphs16
 
     # ---- end to end through the operator call with host buffers -------------------------------
-    host_in = {key: t.cpu().pin_memory() for key, t in acts.items()}
-    full_n = {name: n for name, _, n in SHAPES}
-    host_out = {key: torch.empty((key[1], full_n[key[0]]), dtype=torch.bfloat16).pin_memory() for key in acts}
-    dev_in = {key: torch.empty_like(t) for key, t in acts.items()}
-    h2d = sum(t.numel() * 2 for t in host_in.values())
-    d2h = sum(t.numel() * 2 for t in host_out.values())
-
-    def e2e_step(phase):
-        for mi, m in enumerate(MS):
-            for name, k, n in SHAPES:
-                w = layers[phase * len(MS) + mi][name]
-                dev_in[(name, m)].copy_(host_in[(name, m)], non_blocking=True)
-                capi.marlin_gemm(dev_in[(name, m)], w["marlin"], None, w["scales"], w["zeros"], capi.QTYPE_UINT4, m,
-                                 w["n"], k, outs[(name, m)], scratch_buf=scratch)
-                if world > 1:
-                    parallel.gather_columns(outs[(name, m)], gathered[(name, m)])
-                    full = gathered[(name, m)].permute(1, 0, 2).reshape(m, n)
-                    host_out[(name, m)].copy_(full, non_blocking=True)
-                else:
-                    host_out[(name, m)].copy_(outs[(name, m)], non_blocking=True)
-
-    for i in range(3):
-        e2e_step(i % phases)
-    barrier()
-    e2e_steps = max(3, min(args.steps, 50))
-    e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e_start.record()
-    for i in range(e2e_steps):
-        e2e_step(i % phases)
-    e_stop.record()
-    barrier()
-    e2e_ms = e_start.elapsed_time(e_stop)
-
-    times = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    elapsed_ms, e2e_ms = (float(v) for v in times.cpu())
+    e2e = e2e_decode(d, args, layers, acts, keys, full_n, phases)
 
     step_weight_bytes = sum(weight_bytes(k, n) for _, k, n in SHAPES) * len(MS)
     step_algo_bytes = sum(algorithmic_bytes(m, k, n // world) for _, k, n in SHAPES for m in MS)  # per GPU
-    ms_per_step = elapsed_ms / args.steps
     value = step_weight_bytes / (ms_per_step * 1e-3) / 1e9
-    e2e_value = step_weight_bytes / (e2e_ms / e2e_steps * 1e-3) / 1e9
-    peak, peak_kind = measured_hbm_peak()
     achieved = step_algo_bytes / (ms_per_step * 1e-3) / 1e9
+    if per_gemm is not None:
+        per_gemm["value"] = step_weight_bytes / (per_gemm["ms_per_step"] * 1e-3) / 1e9
+        per_gemm["roofline_frac"] = step_algo_bytes / (per_gemm["ms_per_step"] * 1e-3) / 1e9 / peaks["hbm"]
 
     result = {
-        "metric": "W4A16 GEMM weight HBM GB/s (decode)", "value": value, "unit": "GB/s", "n_gpus": world,
-        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "configs[1]: Llama-3-8B-shaped AWQ W4A16 linears (qkv, o, gate_up, down), g=128, "
-                               "M in {1,4,16,64}; one step = these 16 GEMMs",
+        "config": {"workload": WORKLOAD,
                    "parallelism": "single GPU" if world == 1 else
-                   f"column-parallel N-shard x{world} + " + ("one NCCL all-gather per step over the 16 output slices"
-                                                               if args.gather == "step" else
-                                                               f"NCCL all-gather per linear ({args.gather})"),
+                   f"column-parallel N-shard x{world}; the GEMM epilogue stores each slice into every rank's "
+                   "full-width result over NVLink (peer-mapped buffers), completion flags + bounded wait per step",
                    "l2": f"inputs larger than L2: {copies} full weight copies "
                          f"({copies * layer_bytes / 1e6:.0f} MB per GPU) used in rotation",
-                   "launch": "CUDA graph replay of the step"},
-        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "steps": e2e_steps, "note": "host activations in, host outputs out, one operator call per GEMM"},
-        "gpu_launches": launches_per_step * args.steps,
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_kind": f"of {peak_kind}", "traffic": TRAFFIC_BYTES_PER_STEP if world == 1 else None,
-                     "traffic_unit": "DRAM bytes per step (16 launches), scaled from one ncu capture",
-                     "kernel": "W4A16GemmKernel", "algorithmic_bytes_per_step": step_algo_bytes},
+                   "launch": "CUDA graph replay of the step; the 16 problems as two batched persistent launches"},
+        "timing": dict(spread_of(regions), unit="ms per step", note=f"{repeats} timed regions of {args.steps} steps, "
+                       "CUDA events, max over ranks per region; `ms_per_step` is the median"),
+        "e2e": e2e,
+        "gpu_launches": launches_per_step * args.steps * repeats,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
+                     "frac": achieved / peaks["hbm"], "peak_kind": f"of {peaks['kind']}",
+                     "traffic": TRAFFIC_BYTES_PER_STEP if world == 1 else None,
+                     "traffic_unit": "DRAM bytes per step, scaled from one ncu capture of the kernel",
+                     "kernel": "W4A16GemmBatchKernel", "algorithmic_bytes_per_step": step_algo_bytes},
         "clocks": clocks.summary(),
     }
+    if checked is not None:
+        result["checked"] = checked
+    if per_gemm is not None:
+        result["per_gemm"] = per_gemm
+    if not args.headline_only:
+        del graphs
+        layers_keep = layers[0]
+        layers = None
+        torch.cuda.empty_cache()
+        result["prefill"] = bench_prefill(d, group)
+        result["moe"] = bench_moe(d, args)
+        if world == 1:
+            result["small_kernels"] = bench_small(d)
+        layers = [layers_keep]
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             result["cpu_baseline"] = cpu_baseline(layers[0], sample_ms=MS, repeats=12)
         print(json.dumps(result), flush=True)
     if world > 1:
-        _shutdown(dist, graphs)
+        _shutdown(d, group)
 
 
-# DRAM bytes (read + write) of the 16 GEMM launches of one step.  From the ncu capture of the
+# DRAM bytes (read + write) of the GEMM launches of one step.  From the ncu capture of the
 # M=16, K=4096, N=28672 launch (profiles/w4a16_gemm_decode_m16_k4096_n28672.md): 61.84 MB measured
-# against 62.06 MB algorithmic, ratio 0.996; the other launches stream their weights once in the same
+# against 62.06 MB algorithmic, ratio 0.996; every launch streams its weights once in the same
 # way, so the step's traffic is taken as its algorithmic bytes times that ratio (single GPU).
 TRAFFIC_BYTES_PER_STEP = int(465084416 * 61.84 / 62.06)
+
+
+def check_gathered(d, capi, layers, acts, keys, gathered, phase, scratch, full_n, full_k):
+    """Every rank recomputes, for every rank r, the step's 16 problems on r's shard (regenerated
+    from its seed) as the same batched call, and compares the result with the slice that r stored
+    into this rank's full-width matrices: equal bit for bit, or the exchange or the kernel is wrong."""
+    ok = True
+    for r in range(d.world):
+        shard = [make_layer(r, d.world, d.device, phase * len(MS) + mi) for mi in range(len(MS))]
+        local = {key: torch.full((key[1], full_n[key[0]] // d.world), float("nan"), dtype=torch.bfloat16, device=d.device)
+                 for key in keys}
+        problems = []
+        for name, m in keys:
+            w = shard[MS.index(m)][name]
+            problems.append(capi.gemm_problem(acts[(name, m)], w["marlin"], None, w["scales"], w["zeros"],
+                                              local[(name, m)], m, w["n"], w["k"]))
+        capi.marlin_gemm_batch(capi.problem_array(problems), torch.bfloat16, UINT4, scratch)
+        torch.cuda.synchronize()
+        for key in keys:
+            width = full_n[key[0]] // d.world
+            ok = ok and torch.equal(gathered[key][:, r * width:(r + 1) * width], local[key])
+        del shard
+    return d.all_true(ok)
+
+
+def e2e_decode(d, args, layers, acts, keys, full_n, phases):
+    """The step through the public operator (`infini.ops.marlin_gemm`), one call per GEMM, with pinned
+    host activations copied in and the full-width result copied out to pinned host memory, inside the
+    timed region.  With N > 1 the slices are all-gathered (NCCL) between the GEMM and the copy out."""
+    import infini.ops
+
+    world, device = d.world, d.device
+    host_in = {key: t.cpu().pin_memory() for key, t in acts.items()}
+    host_out = {key: torch.empty((key[1], full_n[key[0]]), dtype=torch.bfloat16).pin_memory() for key in keys}
+    dev_in = {key: torch.empty_like(t) for key, t in acts.items()}
+    dev_out = {key: torch.empty((key[1], full_n[key[0]] // world), dtype=torch.bfloat16, device=device) for key in keys}
+    gathered = {key: torch.empty((world, key[1], full_n[key[0]] // world), dtype=torch.bfloat16, device=device)
+                for key in keys} if world > 1 else None
+    workspace = torch.zeros(432, dtype=torch.int32, device=device)
+    h2d = sum(t.numel() * 2 for t in host_in.values())
+    d2h = sum(t.numel() * 2 for t in host_out.values())
+
+    def step(phase):
+        stream = torch.cuda.current_stream().cuda_stream
+        for name, m in keys:
+            w = layers[phase * len(MS) + MS.index(m)][name]
+            dev_in[(name, m)].copy_(host_in[(name, m)], non_blocking=True)
+            infini.ops.marlin_gemm(dev_in[(name, m)], w["marlin"], None, w["scales"], None, None, w["zeros"], None, None,
+                                   workspace, UINT4, m, w["n"], w["k"], True, False, True, False, dev_out[(name, m)],
+                                   stream=stream)
+            if world > 1:
+                import torch.distributed as dist
+
+                dist.all_gather_into_tensor(gathered[(name, m)].view(-1, w["n"]), dev_out[(name, m)])
+                host_out[(name, m)].copy_(gathered[(name, m)].permute(1, 0, 2).reshape(m, -1), non_blocking=True)
+            else:
+                host_out[(name, m)].copy_(dev_out[(name, m)], non_blocking=True)
+
+    for i in range(3):
+        step(i % phases)
+    steps = max(3, min(args.steps, 50))
+    count = [0]
+
+    def run(n):
+        for _ in range(n):
+            step(count[0] % phases)
+            count[0] += 1
+
+    regions = timed_regions(d, run, steps, 3)
+    ms = statistics.median(regions)
+    step_weight_bytes = sum(weight_bytes(k, n) for _, k, n in SHAPES) * len(MS)
+    return {"value": step_weight_bytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+            "d2h_bytes_per_step": d2h, "steps": steps, "ms_per_step": ms,
+            "note": "infini.ops.marlin_gemm per GEMM; pinned host activations in, host outputs out"}
+
+
+# ---------------------------------------------------------------------------------------------------
+def bench_prefill(d, group):
+    """configs[2]: the four linears at M = 4096, GPTQ-symmetric, bf16.  TFLOP/s per linear and for the four
+    together, against the measured bf16 peak (burst: each GEMM is timed on its own).  With N > 1 every
+    rank computes its column shard and the epilogue stores it into every rank's full-width result."""
+    from infiniops_b200 import capi
+
+    world, rank, device = d.world, d.rank, d.device
+    peaks = measured_peaks()
+    m = 4096
+    out = {"metric": "W4A16 GEMM TFLOP/s (prefill, M=4096)", "unit": "TFLOP/s", "linears": {},
+           "workload": "configs[2]: qkv, o, gate_up, down at M=4096, GPTQ symmetric int4, g=128, bf16"}
+    gen = torch.Generator(device=device).manual_seed(SEED + 2000 + rank)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    total_ms, total_flops = 0.0, 0
+    peer_buf = None
+    if group is not None:
+        off = group.carve(m * 28672 * 2)
+    for name, k, n in SHAPES:
+        n_local = n // world
+        marlin = torch.randint(-2**31, 2**31 - 1, (k // 16, 2 * n_local), dtype=torch.int32, device=device, generator=gen)
+        scales = (torch.randn((k // GROUP, n_local), device=device, generator=gen).abs() * 0.01 + 1e-3).bfloat16()
+        a = torch.randn((m, k), device=device, generator=gen).bfloat16()
+        if group is None:
+            full = torch.empty((m, n), dtype=torch.bfloat16, device=device)
+            peers = []
+        else:
+            full = group.local(off, (m, n), torch.bfloat16)
+            peers = [group.address(r, off) for r in group.others()]
+        g = capi.gemm_problem(a, marlin, None, scales, None, full, m, n_local, k, out_ld=n, out_col0=rank * n_local,
+                              peer_out=peers)
+        scratch = torch.zeros(capi.lib().infiniops_b200_marlin_gemm_scratch_bytes(m, n_local, k), dtype=torch.uint8,
+                              device=device)
+        signal = None if group is None else group.signal()
+
+        def launch():
+            capi.marlin_gemm_placed(g, torch.bfloat16, UINT4B8, scratch, signal=signal)
+            if group is not None:
+                group.wait()
+
+        for _ in range(3):
+            launch()
+        times = []
+        for _ in range(7):
+            flush.zero_()
+            d.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            launch()
+            e1.record()
+            d.barrier()
+            times.append(d.max_over_ranks([e0.elapsed_time(e1)])[0])
+        assert capi.scratch_status(scratch) == 0
+        ms = statistics.median(times)
+        flops = 2 * m * k * n
+        out["linears"][f"{name} {k}x{n}"] = {"ms": ms, "tflops": flops / (ms * 1e-3) / 1e12,
+                                             "frac_of_bf16_peak": flops / (ms * 1e-3) / 1e12 / (peaks["bf16"] * world)}
+        total_ms += ms
+        total_flops += flops
+        del marlin, scales, a, scratch
+    out["value"] = total_flops / (total_ms * 1e-3) / 1e12
+    out["ms_per_step"] = total_ms
+    out["roofline"] = {"bound": "tensor", "achieved": out["value"] / world, "peak": peaks["bf16"], "unit": "TFLOP/s",
+                       "frac": out["value"] / world / peaks["bf16"], "peak_kind": f"of {peaks['kind']} (burst), per GPU",
+                       "frac_of_sustained": out["value"] / world / peaks["bf16_sustained"]}
+    out["timing"] = "median of 7 single launches per linear, L2 flushed in between, CUDA events, max over ranks"
+    return out
+
+
+MOE_CONFIGS = {
+    "mixtral": {"experts": 8, "top_k": 2, "hidden": 4096, "inter": 14336, "zeros": False, "router": "softmax",
+                "label": "configs[3]: Mixtral-8x7B-shaped MoE layer, E=8 top-2 H=4096 I=14336, GPTQ symmetric"},
+    "deepseek": {"experts": 256, "top_k": 8, "hidden": 7168, "inter": 2048, "zeros": True, "router": "grouped",
+                 "label": "configs[4]: DeepSeek-V3-shaped MoE layer, E=256 top-8 (8 groups, 4 kept, sigmoid + bias) "
+                          "H=7168 I=2048, AWQ zero points"},
+}
+
+
+def moe_problem(cfg, tokens, d):
+    """Expert weights of this rank (random Marlin words: the repack is measured on its own), tokens and
+    router inputs of this rank."""
+    from infiniops_b200 import moe_layer
+
+    dev = d.device
+    e_local = cfg["experts"] // d.world
+    t_local = max(1, tokens // d.world)
+    gen = torch.Generator(device=dev).manual_seed(SEED + 3000 + d.rank)
+
+    def packed(k, n):
+        w = torch.empty((e_local, k // 16, 2 * n), dtype=torch.int32, device=dev)
+        for e in range(e_local):
+            w[e] = torch.randint(-2**31, 2**31 - 1, (k // 16, 2 * n), dtype=torch.int32, device=dev, generator=gen)
+        s = (torch.randn((e_local, k // GROUP, n), device=dev, generator=gen).abs() * 0.01 + 1e-3).bfloat16()
+        z = torch.randint(-2**31, 2**31 - 1, (e_local, k // GROUP, n // 8), dtype=torch.int32, device=dev,
+                          generator=gen) if cfg["zeros"] else None
+        return w, s, z
+
+    w13, s13, z13 = packed(cfg["hidden"], 2 * cfg["inter"])
+    w2, s2, z2 = packed(cfg["inter"], cfg["hidden"])
+    weights = moe_layer.ExpertWeights(w13, s13, z13, w2, s2, z2, cfg["hidden"], cfg["inter"])
+    x = torch.randn((t_local, cfg["hidden"]), device=dev, generator=gen).bfloat16()
+    logits = torch.randn((t_local, cfg["experts"]), device=dev, generator=gen)
+    bias = torch.randn(cfg["experts"], device=dev, generator=gen) * 0.1
+    return weights, x, logits, bias, t_local
+
+
+def moe_layer_time(d, cfg, tokens, steps, warmup):
+    """ms per layer pass (router -> sort -> w13 GEMM -> silu_and_mul -> w2 GEMM -> moe_sum, with dispatch and
+    combine when sharded), median of 3 regions."""
+    from infiniops_b200 import capi, moe_layer, parallel
+
+    weights, x, logits, bias, t_local = moe_problem(cfg, tokens, d)
+    runner = moe_layer.RoutedExperts(weights, 64)
+    launches = [0]
+
+    def route():
+        if cfg["router"] == "softmax":
+            return moe_layer.route_softmax(logits, cfg["top_k"])
+        return moe_layer.route_grouped(logits, bias, 8, 4, cfg["top_k"], 2.5)
+
+    def step():
+        w, ids = route()
+        if d.world == 1:
+            launches[0] = 8   # router, sort, 2 x (gather + GEMM), silu_and_mul, moe_sum
+            return moe_layer.single_gpu_layer(x, w, ids, runner)
+        launches[0] = 9
+        return parallel.expert_parallel_layer(x, ids, w, cfg["experts"], cfg["top_k"], runner,
+                                              lambda routed: _moe_sum(capi, routed))
+
+    for _ in range(max(warmup, 3)):
+        step()
+
+    def run(n):
+        for _ in range(n):
+            step()
+
+    regions = timed_regions(d, run, steps, 3)
+    torch.cuda.synchronize()
+    assert capi.scratch_status(capi.scratch(d.device, 0)) == 0
+    return statistics.median(regions), t_local * d.world, launches[0]
+
+
+def bench_moe(d, args):
+    """configs[3] and configs[4]: tokens/s of the whole layer.  Mixtral shape at T = 1024 and 4096, DeepSeek shape
+    at T = 512 and 8192 (the largest T of each configuration fits one GPU)."""
+    peaks = measured_peaks()
+    out = {"metric": "MoE tokens/s", "unit": "tokens/s", "cases": {}}
+    for name, token_counts in (("mixtral", (1024, 4096)), ("deepseek", (512, 8192))):
+        cfg = MOE_CONFIGS[name]
+        if cfg["experts"] % d.world:
+            continue
+        for tokens in token_counts:
+            steps = 10 if tokens <= 1024 else 5
+            ms, t_global, launches = moe_layer_time(d, cfg, tokens, steps, 3)
+            flops = t_global * cfg["top_k"] * (2 * cfg["hidden"] * 2 * cfg["inter"] + 2 * cfg["inter"] * cfg["hidden"])
+            tf = flops / (ms * 1e-3) / 1e12
+            out["cases"][f"{name} T={t_global}"] = {
+                "workload": cfg["label"], "tokens_per_s": t_global / (ms * 1e-3), "ms_per_layer": ms, "tflops": tf,
+                "roofline": {"bound": "tensor", "achieved": tf / d.world, "peak": peaks["bf16"], "unit": "TFLOP/s",
+                             "frac": tf / d.world / peaks["bf16"], "peak_kind": f"of {peaks['kind']} (burst), per GPU"},
+                "launches_per_layer": launches}
+            torch.cuda.empty_cache()
+    head = out["cases"].get("mixtral T=4096")
+    if head:
+        out["value"] = head["tokens_per_s"]
+    out["parallelism"] = "single GPU" if d.world == 1 else f"expert-parallel x{d.world}, all-to-all dispatch and combine"
+    return out
+
+
+def bench_small(d):
+    """GB/s of the memory-bound kernels at their layer sizes, against the measured HBM bandwidth.  Each launch
+    is timed on its own with the L2 flushed before it (median of 7)."""
+    from infiniops_b200 import capi
+
+    dev = d.device
+    peaks = measured_peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    gen = torch.Generator(device=dev).manual_seed(SEED + 5000)
+    out = {}
+
+    def measure(name, nbytes, launch, note):
+        for _ in range(2):
+            launch()
+        times = []
+        for _ in range(7):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            launch()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        ms = statistics.median(times)
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out[name] = {"us": ms * 1e3, "algorithmic_bytes": nbytes, "gbs": gbs, "frac_of_hbm": gbs / peaks["hbm"],
+                     "note": note}
+
+    k, n = 4096, 28672
+    src = torch.randint(-2**31, 2**31 - 1, (k // 8, n), dtype=torch.int32, device=dev, generator=gen)
+    dst = torch.empty((k // 16, 2 * n), dtype=torch.int32, device=dev)
+    measure("gptq_marlin_repack", k * n, lambda: capi.gptq_marlin_repack(src, None, k, n, 4, False, dst),
+            "4096 x 28672, 4-bit: K*N/2 read + K*N/2 written")
+    src2 = torch.randint(-2**31, 2**31 - 1, (k, n // 8), dtype=torch.int32, device=dev, generator=gen)
+    measure("awq_marlin_repack", k * n, lambda: capi.awq_marlin_repack(src2, k, n, 4, False, dst), "4096 x 28672, 4-bit")
+    del src, src2, dst
+
+    t, e, topk = 4096, 8, 2
+    logits = torch.randn((t, e), device=dev, generator=gen)
+    w = torch.empty((t, topk), device=dev)
+    ids = torch.empty((t, topk), dtype=torch.int32, device=dev)
+    tei = torch.empty((t, topk), dtype=torch.int32, device=dev)
+    measure("topk_softmax", t * e * 4 + t * topk * 12, lambda: capi.topk_softmax(logits, None, None, True, w, ids, tei),
+            "T=4096, E=8, top-2 (launch-latency bound at this size)")
+    t, e, topk = 8192, 256, 8
+    scores = torch.randn((t, e), device=dev, generator=gen)
+    bias = torch.randn(e, device=dev, generator=gen) * 0.1
+    w8 = torch.empty((t, topk), device=dev)
+    ids8 = torch.empty((t, topk), dtype=torch.int32, device=dev)
+    measure("grouped_topk", t * e * 4 + t * topk * 8,
+            lambda: capi.grouped_topk(scores, bias, 8, 4, topk, True, 2.5, 1, w8, ids8), "T=8192, E=256, top-8 of 4 of 8 groups")
+    capi.grouped_topk(scores, bias, 8, 4, topk, True, 2.5, 1, w8, ids8)
+    size = t * topk + e * 63
+    sorted_ids = torch.empty(size, dtype=torch.int32, device=dev)
+    expert_ids = torch.empty((size + 63) // 64, dtype=torch.int32, device=dev)
+    npost = torch.empty(1, dtype=torch.int32, device=dev)
+    measure("moe_align_block_size", 4 * (t * topk + size + (size + 63) // 64 + 1),
+            lambda: capi.moe_align_block_size(ids8, None, e, 64, sorted_ids, expert_ids, npost),
+            "65 536 ids, E=256, block 64 (two launches)")
+
+    rows, inter = 8192, 14336
+    x = torch.randn((rows, 2 * inter), device=dev, generator=gen).bfloat16()
+    y = torch.empty((rows, inter), dtype=torch.bfloat16, device=dev)
+    measure("silu_and_mul", 3 * rows * inter * 2, lambda: capi.silu_and_mul(x, y), "[8192, 2*14336] bf16 (Mixtral, T=4096)")
+    del x, y
+    t, topk, h = 8192, 8, 7168
+    x = torch.randn((t, topk, h), device=dev, generator=gen).bfloat16()
+    y = torch.empty((t, h), dtype=torch.bfloat16, device=dev)
+    measure("moe_sum", (topk + 1) * t * h * 2, lambda: capi.moe_sum(x, y), "[8192, 8, 7168] bf16 (DeepSeek, T=8192)")
+    return out
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -378,14 +768,13 @@ def cpu_baseline(layer, sample_ms, repeats):
 
 def run_reference(args):
     """The reference's own CPU implementation of the path (the oracle port of its dequantise-
-    then-matmul formulation), all host threads, same config and metric."""
+    then-matmul formulation), all host threads, same workload, metric and step definition as the
+    repository's arm: one step = the 16 GEMMs (four linears at M in {1, 4, 16, 64})."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     torch.set_num_threads(os.cpu_count() or 1)
     gen_layer = {}
-    from oracle import quant as oq
-
     for si, (name, k, n) in enumerate(SHAPES):
         gen = torch.Generator().manual_seed(SEED + si)
         awq = torch.randint(-2**31, 2**31 - 1, (k, n // 8), dtype=torch.int32, generator=gen)
@@ -393,124 +782,62 @@ def run_reference(args):
         zeros = torch.randint(-2**31, 2**31 - 1, (k // GROUP, n // 8), dtype=torch.int32, generator=gen)
         gen_layer[name] = {"awq": awq, "scales": scales, "zeros": zeros, "n": n}
     problem = cpu_reference_problem(gen_layer)
-    sample = (16,)
-    for _ in range(min(args.warmup, 1)):
-        cpu_pass(problem, sample)
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
+        cpu_pass(problem, MS)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        cpu_pass(problem, sample)
+        cpu_pass(problem, MS)
     elapsed = time.perf_counter() - t0
-    nbytes = sum(weight_bytes(k, n) for _, k, n in SHAPES) * len(sample)
+    nbytes = sum(weight_bytes(k, n) for _, k, n in SHAPES) * len(MS)
     value = nbytes * args.steps / elapsed / 1e9
     cores = torch.get_num_threads()
     print(json.dumps({
-        "impl": "reference", "metric": "W4A16 GEMM weight HBM GB/s (decode)", "value": value, "unit": "GB/s",
-        "n_gpus": args.gpus, "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": elapsed / args.steps * 1e3,
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": warmup, "ms_per_step": elapsed / args.steps * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "configs[1]: Llama-3-8B-shaped AWQ W4A16 linears (qkv, o, gate_up, down), g=128; "
-                               "each step = the four linears at M=16 (bounded sample of the 16-GEMM step)"},
+        "config": {"workload": WORKLOAD, "parallelism": "host cores (rank 0 only)",
+                   "launch": "fp32 dequantise + torch matmul per GEMM on the host"},
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port",
-                         "sample": "four linears at M=16 per step, fp32 dequantise + torch matmul on the host"},
+                         "sample": "every step = the full 16-GEMM step, fp32 dequantise + torch matmul on the host"},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }), flush=True)
 
 
 def run_moe(args):
-    """Mixtral-8x7B-shaped MoE layer (BASELINE.json configs[3]): E=8, top-2, hidden 4096, intermediate 14336,
-    GPTQ-symmetric int4 g=128, bf16; router topk_softmax -> moe_align_block_size(64) -> w13 GEMM -> silu_and_mul
-    -> w2 GEMM -> moe_sum.  Metric: tokens/s of the whole layer for `--tokens` tokens (global).  With N > 1 the
-    experts are split over the ranks and the tokens are data-parallel (T/N each) with all-to-all dispatch and
-    combine (strong scaling: the same global batch for every N)."""
-    import torch.distributed as dist
-
-    from infiniops_b200 import capi, moe_layer, parallel
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    experts, top_k, hidden, inter, block = 8, 2, 4096, 14336, 64
-    e_local = experts // world
-    t_local = max(1, args.tokens // world)
-    gen = torch.Generator(device=dev).manual_seed(SEED + 3000 + rank)
-
-    def packed(k, n):
-        out = torch.empty((e_local, k // 16, 2 * n), dtype=torch.int32, device=dev)
-        for e in range(e_local):
-            src = torch.randint(-2**31, 2**31 - 1, (k // 8, n), dtype=torch.int32, device=dev, generator=gen)
-            capi.gptq_marlin_repack(src, None, k, n, 4, False, out[e])
-        scales = (torch.randn((e_local, k // GROUP, n), device=dev, generator=gen).abs() * 0.01 + 1e-3).bfloat16()
-        return out, scales
-
-    w13, s13 = packed(hidden, 2 * inter)
-    w2, s2 = packed(inter, hidden)
-    runner = moe_layer.RoutedExperts(moe_layer.ExpertWeights(w13, s13, None, w2, s2, None, hidden, inter), block)
-    x = torch.randn((t_local, hidden), device=dev, generator=gen).bfloat16()
-    logits = torch.randn((t_local, experts), device=dev, generator=gen)
-    launches = [0]
-
-    def step():
-        weights, ids = moe_layer.route_softmax(logits, top_k)
-        if world == 1:
-            launches[0] = 8   # router, sort, 2 x (gather + GEMM), silu_and_mul, moe_sum
-            return moe_layer.single_gpu_layer(x, weights, ids, runner)
-        launches[0] = 9
-        return parallel.expert_parallel_layer(
-            x, ids, weights, experts, top_k, runner,
-            lambda routed: _moe_sum(capi, routed))
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(max(args.warmup, 3)):
-        step()
-    barrier()
-    steps = min(args.steps, 50)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local_rank) as clocks:
-        barrier()
-        e0.record()
-        for _ in range(steps):
-            out = step()
-        e1.record()
-        barrier()
-    ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    ms_per_step = float(ms) / steps
-    assert capi.scratch_status(capi.scratch(dev, 0)) == 0
-    tokens = t_local * world
-    flops = tokens * top_k * (2 * hidden * 2 * inter + 2 * inter * hidden)
-    if rank == 0:
+    """One MoE configuration on its own: `--workload moe --moe-shape mixtral|deepseek --tokens T`."""
+    d = Dist(args)
+    cfg = MOE_CONFIGS[args.moe_shape]
+    with ClockSampler(d.local_rank) as clocks:
+        ms, tokens, launches = moe_layer_time(d, cfg, args.tokens, min(args.steps, 50), args.warmup)
+    flops = tokens * cfg["top_k"] * (2 * cfg["hidden"] * 2 * cfg["inter"] + 2 * cfg["inter"] * cfg["hidden"])
+    if d.rank == 0:
         print(json.dumps({
-            "metric": "MoE tokens/s", "value": tokens / (ms_per_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
-            "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "metric": "MoE tokens/s", "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": d.world,
+            "steps": min(args.steps, 50), "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"configs[3]: Mixtral-8x7B-shaped MoE layer, E=8 top-2 H=4096 I=14336, T={tokens}",
-                       "parallelism": "single GPU" if world == 1 else f"expert-parallel x{world}, NCCL all-to-all",
-                       "l2": "inputs larger than L2: 705 MB of expert weights per layer pass"},
-            "tflops": flops / (ms_per_step * 1e-3) / 1e12, "gpu_launches": launches[0] * steps,
+            "config": {"workload": f"{cfg['label']}, T={tokens}",
+                       "parallelism": "single GPU" if d.world == 1 else f"expert-parallel x{d.world}",
+                       "l2": "inputs larger than L2: the layer's expert weights"},
+            "tflops": flops / (ms * 1e-3) / 1e12, "gpu_launches": launches * min(args.steps, 50) * 3,
             "clocks": clocks.summary()}), flush=True)
-    if world > 1:
-        _shutdown(dist)
+    if d.world > 1:
+        _shutdown(d, None)
 
 
-def _shutdown(dist, graphs=None):
-    """Releases captured graphs (they hold NCCL kernels) before the process group goes away; a
-    watchdog ends the process if the teardown itself blocks -- the result line is already out."""
+def _shutdown(d, group):
+    """Orderly teardown; a watchdog ends the process if the teardown itself blocks -- the result line
+    is already out."""
     import gc
     import threading
 
-    threading.Thread(target=lambda: (time.sleep(20), os._exit(0)), daemon=True).start()
-    if graphs is not None:
-        graphs.clear()
+    import torch.distributed as dist
+
+    threading.Thread(target=lambda: (time.sleep(30), os._exit(0)), daemon=True).start()
     gc.collect()
     torch.cuda.synchronize()
+    if group is not None:
+        group.close()
     dist.barrier()
     dist.destroy_process_group()
 
@@ -522,18 +849,18 @@ def _moe_sum(capi, routed):
 
 
 def run_one(args):
-    """One dense AWQ bf16 GEMM `M,K,N`, launched a few times with an L2 flush in between: the small,
-    self-terminating case used for profiler captures (`ncu ... python bench.py --one 16,4096,28672`)."""
+    """One dense bf16 GEMM `M,K,N` (AWQ with zero points, or GPTQ-symmetric with --gptq), launched a few times
+    with an L2 flush in between: the small, self-terminating case used for profiler captures
+    (`ncu ... python bench.py --one 16,4096,28672`)."""
     from infiniops_b200 import capi
 
     m, k, n = (int(v) for v in args.one.split(","))
     dev = torch.device("cuda", 0)
     gen = torch.Generator(device=dev).manual_seed(SEED)
-    awq = torch.randint(-2**31, 2**31 - 1, (k, n // 8), dtype=torch.int32, device=dev, generator=gen)
-    marlin = torch.empty((k // 16, 2 * n), dtype=torch.int32, device=dev)
-    capi.awq_marlin_repack(awq, k, n, 4, False, marlin)
+    marlin = torch.randint(-2**31, 2**31 - 1, (k // 16, 2 * n), dtype=torch.int32, device=dev, generator=gen)
     scales = (torch.randn((k // GROUP, n), device=dev, generator=gen).abs() * 0.01 + 1e-3).bfloat16()
-    zeros = torch.randint(-2**31, 2**31 - 1, (k // GROUP, n // 8), dtype=torch.int32, device=dev, generator=gen)
+    zeros = None if args.gptq else torch.randint(-2**31, 2**31 - 1, (k // GROUP, n // 8), dtype=torch.int32, device=dev,
+                                                 generator=gen)
     a = torch.randn((m, k), device=dev, generator=gen).bfloat16()
     out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
@@ -542,37 +869,75 @@ def run_one(args):
         flush.zero_()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        capi.marlin_gemm(a, marlin, None, scales, zeros, capi.QTYPE_UINT4, m, n, k, out)
+        capi.marlin_gemm(a, marlin, None, scales, zeros, UINT4B8 if args.gptq else UINT4, m, n, k, out)
         e1.record()
         torch.cuda.synchronize()
         times.append(e0.elapsed_time(e1) * 1e3)
-    print(json.dumps({"case": args.one, "us_per_launch_with_launch_gap": times,
-                      "algorithmic_bytes": algorithmic_bytes(m, k, n), "flops": 2 * m * k * n}))
+    print(json.dumps({"case": args.one, "weights": "gptq symmetric" if args.gptq else "awq with zero points",
+                      "us_per_launch_with_launch_gap": times,
+                      "algorithmic_bytes": algorithmic_bytes(m, k, n, not args.gptq), "flops": 2 * m * k * n}))
+
+
+def run_one_batch(args):
+    """The batched decode step on its own, a few times (profiling case for the batched kernel):
+    `--one-batch S` runs the 16-problem step on linears scaled down by S (1 = full size)."""
+    from infiniops_b200 import capi
+
+    shrink = int(args.one_batch)
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator(device=dev).manual_seed(SEED)
+    problems, keep = [], []
+    for name, k, n in SHAPES:
+        n = max(128, n // shrink // 128 * 128)
+        marlin = torch.randint(-2**31, 2**31 - 1, (k // 16, 2 * n), dtype=torch.int32, device=dev, generator=gen)
+        scales = (torch.randn((k // GROUP, n), device=dev, generator=gen).abs() * 0.01 + 1e-3).bfloat16()
+        zeros = torch.randint(-2**31, 2**31 - 1, (k // GROUP, n // 8), dtype=torch.int32, device=dev, generator=gen)
+        for m in MS:
+            a = torch.randn((m, k), device=dev, generator=gen).bfloat16()
+            out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
+            keep.append((marlin, scales, zeros, a, out))
+            problems.append(capi.gemm_problem(a, marlin, None, scales, zeros, out, m, n, k))
+    table = capi.problem_array(problems)
+    scratch = torch.zeros(capi.lib().infiniops_b200_marlin_gemm_batch_scratch_bytes(), dtype=torch.uint8, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    times = []
+    for _ in range(3):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        capi.marlin_gemm_batch(table, torch.bfloat16, UINT4, scratch)
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3)
+    assert capi.scratch_status(scratch) == 0
+    print(json.dumps({"case": f"batched step, linears / {shrink}", "us_per_step_with_launch_gap": times}))
 
 
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--workload", default="decode", choices=("decode", "moe"),
-                        help="decode = the headline W4A16 decode step; moe = Mixtral-shaped MoE layer, tokens/s")
+                        help="decode = the headline W4A16 decode step with its sub-records; moe = one MoE layer case")
     parser.add_argument("--tokens", type=int, default=1024, help="global tokens of the MoE workload")
+    parser.add_argument("--moe-shape", default="mixtral", choices=tuple(MOE_CONFIGS))
     parser.add_argument("--one", default=None, help="M,K,N: run this single GEMM three times (profiling case)")
-    parser.add_argument("--gather", default="auto", choices=("auto", "overlap", "overlap-prio", "serial", "step"),
-                        help="N > 1, decode: one all-gather per linear on a second stream / a high-priority second "
-                             "stream / the compute stream, or one all-gather per step over all 16 output slices; "
-                             "auto = step (at 8 ranks a captured all-gather of a few KB costs ~120 us on this pool, "
-                             "2.1 ms per step for sixteen of them against 0.33 ms of GEMMs)")
+    parser.add_argument("--one-batch", default=None, help="S: the batched step on linears shrunk by S, three times")
+    parser.add_argument("--gptq", action="store_true", help="--one: GPTQ-symmetric weights instead of AWQ")
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=200)
+    parser.add_argument("--steps", type=int, default=100)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--headline-only", action="store_true", help="skip the per-GEMM, prefill, MoE and small-kernel "
+                                                                      "sub-records")
     args = parser.parse_args()
     if args.one:
         run_one(args)
-    elif args.workload == "moe" and args.impl == "ours":
-        run_moe(args)
+    elif args.one_batch:
+        run_one_batch(args)
     elif args.impl == "reference":
         run_reference(args)
+    elif args.workload == "moe":
+        run_moe(args)
     else:
         run_ours(args)
 

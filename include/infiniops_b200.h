@@ -215,6 +215,88 @@ int infiniops_b200_marlin_gemm(const void* a, int a_dtype, const int32_t* b_q_we
                                int64_t num_groups, void* out, void* scratch, size_t scratch_bytes,
                                void* stream);
 
+/* One dense problem with its output placement, for infiniops_b200_marlin_gemm_placed and
+ * infiniops_b200_marlin_gemm_batch.  Tensors as for infiniops_b200_marlin_gemm.  `out` is a matrix
+ * of `out_ld` columns (0 = size_n) of which this problem writes columns [out_col0, out_col0 +
+ * size_n): a column-parallel shard writes its slice of the full-width result directly.  The same
+ * slice is also stored, with plain global stores from the GEMM's epilogue, into `n_peers` further
+ * matrices of the same shape -- the result buffers of the other GPUs of a tensor-parallel group,
+ * mapped into this process (infiniops_b200_peer_open) -- which replaces the all-gather that would
+ * otherwise follow the GEMM.  Zero-initialise the struct; unused fields stay zero.
+ * No counterpart in the reference (it has no communication layer). */
+#define IOB_MAX_PEERS 7
+typedef struct {
+  const void* a;
+  const int32_t* b_q_weight;
+  const void* b_bias;
+  const void* b_scales;
+  const int32_t* b_zeros;
+  void* out;
+  int64_t size_m, size_n, size_k, num_groups;
+  int64_t out_ld, out_col0;
+  int n_peers;
+  void* peer_out[IOB_MAX_PEERS];
+} iob_gemm_problem;
+
+/* Completion signal of a launch towards the other GPUs.  When the last thread block of the launch
+ * has finished -- all stores into the peers' matrices issued and fenced -- it adds one to `*epoch`
+ * (device int, owned by the caller, starts at 0) and stores the new value, with release semantics
+ * at system scope, into word `flag_slot` of each `peer_flags[r]` (a device int array on GPU r,
+ * mapped into this process).  `done_counter` is a zeroed device int the launch counts its blocks
+ * in.  The receiving side waits with infiniops_b200_peer_wait.  No counterpart in the reference. */
+typedef struct {
+  int* done_counter;
+  int* epoch;
+  int n_peers;
+  int* peer_flags[IOB_MAX_PEERS];
+  int flag_slot;
+} iob_peer_signal;
+
+/* infiniops_b200_marlin_gemm for a problem given as a struct, with output placement, peer outputs
+ * and an optional completion signal (NULL = none).  No counterpart in the reference. */
+int infiniops_b200_marlin_gemm_placed(const iob_gemm_problem* problem, int a_dtype,
+                                      int64_t b_type_id, const iob_peer_signal* signal,
+                                      void* scratch, size_t scratch_bytes, void* stream);
+
+/* Scratch bytes of infiniops_b200_marlin_gemm_batch on the current device (any problem list). */
+size_t infiniops_b200_marlin_gemm_batch_scratch_bytes(void);
+
+/* `count` independent dense problems of decode size (at most 64 rows each, group sizes that are
+ * multiples of 128, one activation type and one weight type) in as few launches as possible: the
+ * problems with up to 16 rows form one persistent launch, those with 17..64 rows another (16
+ * problems per launch at most).  Inside a launch the (tile, k-stage) units of all problems form
+ * one sequence cut into equal ranges, one per thread block, so pipelines never drain between
+ * problems and launch, set-up and tail are paid once per launch instead of once per GEMM.
+ * Results are identical to calling infiniops_b200_marlin_gemm per problem up to the order of the
+ * fp32 split-K additions (deterministic for a given problem list).  `signal` (or NULL) rides on
+ * the last launch.  Same scratch rules as infiniops_b200_marlin_gemm.
+ * No counterpart in the reference. */
+int infiniops_b200_marlin_gemm_batch(const iob_gemm_problem* problems, int count, int a_dtype,
+                                     int64_t b_type_id, const iob_peer_signal* signal,
+                                     void* scratch, size_t scratch_bytes, void* stream);
+
+/* ---- peer memory (one process per GPU, NVLink) ------------------------------------------------- */
+
+/* Device buffers that other processes on the same machine can map: allocate (zero-filled) / free
+ * on the current device, export a 64-byte handle to send to the other processes by any host
+ * channel, open a handle received from another process (enables peer access on first use) /
+ * close the mapping.  Wrappers of cudaMalloc, cudaIpcGetMemHandle, cudaIpcOpenMemHandle and their
+ * inverses, so that a host without the CUDA runtime headers can set up the peer outputs above.
+ * No counterpart in the reference. */
+int infiniops_b200_peer_alloc(size_t bytes, void** ptr);
+int infiniops_b200_peer_free(void* ptr);
+int infiniops_b200_peer_export(const void* ptr, unsigned char handle[64]);
+int infiniops_b200_peer_open(const unsigned char handle[64], void** ptr);
+int infiniops_b200_peer_close(void* ptr);
+
+/* Receiving side of iob_peer_signal: a one-warp kernel on `stream` that adds one to `*wait_epoch`
+ * (device int, starts at 0) and waits until words 0..n_slots-1 of `flags` (this GPU's flag array,
+ * written by the peers), except `skip_slot`, have all reached that value.  The wait is bounded
+ * (about a second): on expiry the kernel stores code 8 and the missing slot in `status[0..1]`
+ * (a zeroed device int[2]) and returns, so the stream never hangs.  No counterpart in the reference. */
+int infiniops_b200_peer_wait(const int* flags, int n_slots, int skip_slot, int* wait_epoch,
+                             int* status, void* stream);
+
 /* The same dense GEMM for callers that have no device memory to lend and may not allocate any:
  * an engine whose arena already owns the whole GPU, or code that only runs while its host is
  * recording work and cudaMalloc is off limits.  The scratch is a 10 MiB array inside the library

@@ -55,6 +55,36 @@ PROTOTYPES = {
                                                     _vp]),
 }
 
+MAX_PEERS = 7
+
+
+class GemmProblem(ctypes.Structure):
+    """`iob_gemm_problem` of include/infiniops_b200.h."""
+    _fields_ = [("a", _vp), ("b_q_weight", _vp), ("b_bias", _vp), ("b_scales", _vp), ("b_zeros", _vp), ("out", _vp),
+                ("size_m", _i64), ("size_n", _i64), ("size_k", _i64), ("num_groups", _i64),
+                ("out_ld", _i64), ("out_col0", _i64), ("n_peers", _int), ("peer_out", _vp * MAX_PEERS)]
+
+
+class PeerSignal(ctypes.Structure):
+    """`iob_peer_signal` of include/infiniops_b200.h."""
+    _fields_ = [("done_counter", _vp), ("epoch", _vp), ("n_peers", _int), ("peer_flags", _vp * MAX_PEERS),
+                ("flag_slot", _int)]
+
+
+PROTOTYPES.update({
+    "infiniops_b200_marlin_gemm_placed": (_int, [ctypes.POINTER(GemmProblem), _int, _i64, ctypes.POINTER(PeerSignal),
+                                                 _vp, _sz, _vp]),
+    "infiniops_b200_marlin_gemm_batch_scratch_bytes": (_sz, []),
+    "infiniops_b200_marlin_gemm_batch": (_int, [ctypes.POINTER(GemmProblem), _int, _int, _i64,
+                                                ctypes.POINTER(PeerSignal), _vp, _sz, _vp]),
+    "infiniops_b200_peer_alloc": (_int, [_sz, ctypes.POINTER(_vp)]),
+    "infiniops_b200_peer_free": (_int, [_vp]),
+    "infiniops_b200_peer_export": (_int, [_vp, ctypes.c_char_p]),
+    "infiniops_b200_peer_open": (_int, [ctypes.c_char_p, ctypes.POINTER(_vp)]),
+    "infiniops_b200_peer_close": (_int, [_vp]),
+    "infiniops_b200_peer_wait": (_int, [_vp, _int, _int, _vp, _vp, _vp]),
+})
+
 _lib = None
 
 
@@ -202,3 +232,36 @@ def moe_wna16_marlin_gemm(a, b_q_weight, b_bias, b_scales, b_zeros, sorted_token
         _ptr(sorted_token_ids), _ptr(expert_ids), _ptr(num_tokens_past_padded), _ptr(topk_weights), moe_block_size,
         top_k, int(mul_topk_weights), b_type_id, size_m, size_n, size_k, b_scales.shape[-2], e,
         sorted_token_ids.numel(), _ptr(out), _ptr(buf), buf.numel(), _stream(stream)))
+
+
+def gemm_problem(a, b_q_weight, b_bias, b_scales, b_zeros, out, size_m, size_n, size_k, out_ld=0, out_col0=0,
+                 peer_out=()) -> GemmProblem:
+    """One entry of a problem list.  `out` may be a tensor or a raw device address; `peer_out` are the
+    addresses of the other GPUs' result matrices (already mapped into this process)."""
+    g = GemmProblem()
+    g.a, g.b_q_weight, g.b_scales = a.data_ptr(), b_q_weight.data_ptr(), b_scales.data_ptr()
+    g.b_bias = None if b_bias is None else b_bias.data_ptr()
+    g.b_zeros = None if b_zeros is None else b_zeros.data_ptr()
+    g.out = out if isinstance(out, int) else out.data_ptr()
+    g.size_m, g.size_n, g.size_k, g.num_groups = size_m, size_n, size_k, b_scales.shape[-2]
+    g.out_ld, g.out_col0, g.n_peers = out_ld, out_col0, len(peer_out)
+    for i, ptr in enumerate(peer_out):
+        g.peer_out[i] = ptr
+    return g
+
+
+def problem_array(problems):
+    return (GemmProblem * len(problems))(*problems)
+
+
+def marlin_gemm_batch(problems, a_dtype, b_type_id, scratch_buf, signal=None, stream=None):
+    """`problems`: a ctypes array from `problem_array` (build it once, outside the hot loop)."""
+    _check(lib().infiniops_b200_marlin_gemm_batch(problems, len(problems), _DTYPE[a_dtype], b_type_id,
+                                                  None if signal is None else ctypes.byref(signal),
+                                                  _ptr(scratch_buf), scratch_buf.numel(), _stream(stream)))
+
+
+def marlin_gemm_placed(problem, a_dtype, b_type_id, scratch_buf, signal=None, stream=None):
+    _check(lib().infiniops_b200_marlin_gemm_placed(ctypes.byref(problem), _DTYPE[a_dtype], b_type_id,
+                                                   None if signal is None else ctypes.byref(signal),
+                                                   _ptr(scratch_buf), scratch_buf.numel(), _stream(stream)))

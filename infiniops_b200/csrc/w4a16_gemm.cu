@@ -50,6 +50,9 @@ constexpr uint32_t kSpinLimit = 1u << 16;
 constexpr int kHeaderBytes = 256;        // scratch: status word first, then arrival counters
 constexpr int kMaxGrid = 1024;           // counters are laid out for at most this many thread blocks
 
+constexpr int kMaxPeers = 7;             // other GPUs whose buffers a dense launch can also write
+constexpr int kMaxBatch = 16;            // problems one batched launch can hold
+
 constexpr int kErrFull = 1, kErrEmpty = 2, kErrAFull = 3, kErrAEmpty = 4, kErrDFull = 5, kErrDEmpty = 6;
 
 __host__ __device__ constexpr int StagesFor(int tok) {
@@ -101,12 +104,41 @@ struct GemmParams {
   int m, n, k, groups, group_size;
   int pair;            // dense 256-token tiles: blocks work in pairs (the activation map's box is 128 rows then)
   int g_mul, g_shift;  // scale row of k-stage ks = (ks * g_mul) >> g_shift; g_shift < 0: divide instead
+  // Where the result goes.  `out` is a matrix with `out_ld` columns; this problem's N columns start
+  // at column `out_col0` of it (a column-parallel shard writes its slice of the full-width matrix).
+  // The same slice is also stored into `n_peers` other buffers of the same shape -- the full-width
+  // matrices of the other GPUs, mapped into this process -- with plain global stores.
+  int out_ld, out_col0, n_peers;
+  void* peer_out[kMaxPeers];
+  // Completion signal of a launch (null: none).  The block that finishes last adds one to `*epoch`
+  // and stores the new value to `peer_flags[r][flag_slot]` of every peer, after all blocks' stores
+  // to the peers' buffers.
+  int* done_counter;
+  int* epoch;
+  int* peer_flags[kMaxPeers];
+  int flag_slot, n_flag_peers;
   // routed form only
   const int32_t* sorted_ids;
   const int32_t* expert_ids;
   const int32_t* num_post_pad;
   const float* topk_weights;
   int top_k, block_size, mul_weights, out_rows;
+};
+
+// One GEMM as the kernel sees it: its three tensor maps, its parameters and, in a batched launch,
+// its place in the launch's sequence of work units.
+struct alignas(64) Problem {
+  CUtensorMap a_map, w_map, c_map;
+  GemmParams p;
+  int n_tiles, m_tiles, k_stages;  // batched launches
+  long long unit_end;              // batched launches: units of this and all earlier problems
+};
+// A batched launch: independent dense problems of one token-tile class, worked through as ONE
+// stream of (tile, k-stage) units cut into equal ranges, so that the pipelines of a block never
+// drain between problems and the launch, set-up and tail costs are paid once.
+struct BatchTable {
+  int count;
+  Problem prob[kMaxBatch];
 };
 
 // Scale / zero-point row that the first k of stage `ks` falls in.
@@ -485,18 +517,38 @@ __device__ __forceinline__ uint32_t CentreHigh2(uint32_t word, uint32_t minus_64
 // ---- work walker ------------------------------------------------------------------------------
 struct Segment {
   int tile, n_tile, m_tile, k_begin, k_end;
+  int prob, k_stages;    // problem of a batched launch (else 0) and its number of k-stages
+  long long tile_u0;     // unit number of the tile's first k-stage
 };
+// Walks a block's range of units.  In a batched launch the units of the problems follow one
+// another (`probs[i].unit_end`); a segment never crosses a tile, hence never a problem.
 struct Walker {
   long long u, u_end;
   int k_stages, m_tiles;
+  const Problem* probs = nullptr;  // batched launch: the table
+  int prob = 0;
+  long long base = 0;              // first unit of problem `prob`
+  template <bool kBatch = false>
   __device__ __forceinline__ bool Next(Segment& s) {
     if (u >= u_end) return false;
-    s.tile = static_cast<int>(static_cast<unsigned>(u) / static_cast<unsigned>(k_stages));
-    s.k_begin = static_cast<int>(u - static_cast<long long>(s.tile) * k_stages);
+    if constexpr (kBatch) {
+      while (u >= probs[prob].unit_end) {
+        base = probs[prob].unit_end;
+        ++prob;
+        k_stages = probs[prob].k_stages;
+        m_tiles = probs[prob].m_tiles;
+      }
+    }
+    const unsigned local = static_cast<unsigned>(u - base);
+    s.tile = static_cast<int>(local / static_cast<unsigned>(k_stages));
+    s.k_begin = static_cast<int>(local - static_cast<unsigned>(s.tile) * static_cast<unsigned>(k_stages));
     const long long left = u_end - u;
     s.k_end = left < k_stages - s.k_begin ? s.k_begin + static_cast<int>(left) : k_stages;
     s.n_tile = s.tile / m_tiles;
     s.m_tile = s.tile - s.n_tile * m_tiles;
+    s.prob = prob;
+    s.k_stages = k_stages;
+    s.tile_u0 = base + static_cast<long long>(s.tile) * k_stages;
     u += s.k_end - s.k_begin;
     return true;
   }
@@ -511,12 +563,12 @@ struct Cursor {
   int seg_len, expert;
   __device__ __forceinline__ int Ks() const { return seg.k_begin + static_cast<int>(it - seg_it); }
 };
-template <bool kMoe>
+template <bool kMoe, bool kBatch = false>
 __device__ __forceinline__ bool Locate(Cursor& c, const int32_t* expert_ids) {
   while (c.it >= c.seg_it + c.seg_len) {
     c.seg_it += c.seg_len;
     c.seg_len = 0;
-    if (!c.walk.Next(c.seg)) return false;
+    if (!c.walk.template Next<kBatch>(c.seg)) return false;
     if constexpr (kMoe) {
       c.expert = expert_ids[c.seg.m_tile];
       if (c.expert < 0) continue;
@@ -571,10 +623,14 @@ struct Shared {
 // that run on both SMs and read the two activation halves from the two shared memories.  Per
 // block and stage that is 40 KB of copies for the arithmetic that costs 72 KB alone -- the
 // single-block prefill kernel is bound by how fast an SM can pull operands out of L2.
-template <typename T, int kTok, bool kZeros, bool kMoe, int kSets, bool kLate, bool kPair = false>
-__global__ void __launch_bounds__((5 + IssuersFor(kTok) + 4 * kSets) * 32, 1)
-W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant__ CUtensorMap w_map,
-                const __grid_constant__ CUtensorMap c_map, const GemmParams p) {
+//
+// kBatch: `probs` is a table of `count` dense problems that are worked through as one sequence of
+// units (see BatchTable); otherwise it points to the launch's single problem.  `cur` is the problem
+// the executing thread is currently working on -- every role moves it forward with its own walker.
+template <typename T, int kTok, bool kZeros, bool kMoe, int kSets, bool kLate, bool kPair, bool kBatch>
+__device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
+  static_assert(!kBatch || (!kMoe && !kPair && kLate), "batched launches: dense late-scale tiles only");
+  const Problem* cur = probs;
   using Sh = Shared<kTok, kSets, kPair>;
   constexpr int kStages = Sh::kStages;
   constexpr int kAcc = Sh::kAcc;
@@ -650,8 +706,8 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (threadIdx.x == 32) {
-    asm volatile("prefetch.tensormap [%0];" ::"l"(&a_map) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(&w_map) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&cur->a_map) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&cur->w_map) : "memory");
   }
   if (warp == 1) {
     // paired blocks allocate together: the same warp of each block, the same columns in both
@@ -681,22 +737,25 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
   }
   // Paired blocks signal each other's barriers: nobody may start before both have initialised theirs.
   if constexpr (kPair) ClusterSync();
-  const int k_stages = p.k / kBlockK;
+  const int k_stages = kBatch ? cur->k_stages : cur->p.k / kBlockK;  // (batched: of the first problem)
   // kPair: the two blocks of a cluster walk the same sequence of (tile pair, k-stage) units; block
   // `rank` owns output tile 2 * pair + rank.  `my_block` / `grid` below count clusters then.
   uint32_t rank = 0;
   if constexpr (kPair) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
   const int my_block = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
   const int blocks_launched = kPair ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
-  const int n_tiles = kPair ? p.n / (2 * kTileN) : (p.n + kTileN - 1) / kTileN;
+  const int n_tiles = kPair ? cur->p.n / (2 * kTileN) : (cur->p.n + kTileN - 1) / kTileN;
   int m_tiles;
   if constexpr (kMoe) {
     GridDependencyWait();  // the block count itself is a predecessor's output
-    m_tiles = *p.num_post_pad / p.block_size;
+    m_tiles = *cur->p.num_post_pad / cur->p.block_size;
+  } else if constexpr (kBatch) {
+    m_tiles = cur->m_tiles;
   } else {
-    m_tiles = (p.m + kTok - 1) / kTok;
+    m_tiles = (cur->p.m + kTok - 1) / kTok;
   }
-  const long long total_units = static_cast<long long>(n_tiles) * m_tiles * k_stages;
+  const long long total_units =
+      kBatch ? probs[count - 1].unit_end : static_cast<long long>(n_tiles) * m_tiles * k_stages;
   // Never more ranges than units: an empty range between two sharers of a tile would break the
   // arrival count of the tile.  Surplus blocks get nothing to do.
   long long grid = total_units < static_cast<long long>(blocks_launched) ? (total_units > 0 ? total_units : 1)
@@ -704,7 +763,7 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
   // Few tiles: use a multiple of the tile count.  Then every range lies inside one tile (plain
   // split-K), so a block has a single segment and a single hand-over instead of two ragged ones --
   // worth more than the last few SMs when the whole GEMM is only a handful of stages per block.
-  {
+  if constexpr (!kBatch) {
     const long long tiles = static_cast<long long>(n_tiles) * m_tiles;
     if (tiles > 0 && tiles <= grid) {
       const long long splits = grid / tiles < k_stages ? grid / tiles : k_stages;
@@ -717,6 +776,12 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
   // output tile of a walker segment, and the block (as launched) behind a walker block number
   auto tile_of = [&](int seg_n_tile) { return kPair ? 2 * seg_n_tile + static_cast<int>(rank) : seg_n_tile; };
   auto launched_block = [&](int b) { return kPair ? 2 * b + static_cast<int>(rank) : b; };
+  // a walker over this block's range (batched: starting in the first problem, it finds its own)
+  auto make_walker = [&]() {
+    Walker w{u_begin, u_end, k_stages, m_tiles};
+    if constexpr (kBatch) w.probs = probs;
+    return w;
+  };
 
   // From here on global memory is read and written: everything before was on-chip set-up.
   // (The producer warp waits later: its first ring of weight copies does not depend on the predecessor.)
@@ -735,39 +800,41 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
     // so one slow slot does not hold back the requests for the others.
     if (lane < kProdLanes) {
       constexpr unsigned kMask = (1u << kProdLanes) - 1u;
-      Cursor c{Walker{u_begin, u_end, k_stages, m_tiles}, Segment{}, static_cast<uint32_t>(lane), 0u, 0, 0};
-      bool active = Locate<kMoe>(c, p.expert_ids);
-      const int grp_rows = p.group_size == 64 ? 2 : 1;
+      Cursor c{make_walker(), Segment{}, static_cast<uint32_t>(lane), 0u, 0, 0};
+      bool active = Locate<kMoe, kBatch>(c, cur->p.expert_ids);
+      const int grp_rows = cur->p.group_size == 64 ? 2 : 1;
       // The copies of one stage.  Packed weights, scales and zero points are constants of the model;
       // only the activations can be the output of the kernel before this one.
-      auto request_weights = [&](const Cursor& cur) {
-        const int s = cur.it % kStages;
-        const int ks = cur.Ks();
+      auto request_weights = [&](const Cursor& at) {
+        [[maybe_unused]] const Problem* cur = kBatch ? probs + at.seg.prob : probs;
+        const int s = at.it % kStages;
+        const int ks = at.Ks();
         const uint32_t full = SmemAddr(&sh.full[s]);
         // both boxes are always counted in full (rows past M and columns past N arrive as zeros)
         MbarExpectTx(full, (kPair ? 0 : kActBytes) + 8192);
-        TmaLoad2D(stages_addr + s * kStage + kWeightsAt, &w_map, 2 * tile_of(cur.seg.n_tile) * kTileN,
-                  cur.expert * (p.k / 16) + ks * 8, full);
+        TmaLoad2D(stages_addr + s * kStage + kWeightsAt, &cur->w_map, 2 * tile_of(at.seg.n_tile) * kTileN,
+                  at.expert * (cur->p.k / 16) + ks * 8, full);
         // The dequantisers read this stage's scales and zero points with plain loads one stage
         // ahead; pull the lines into L2 now, a whole ring ahead.
-        const int n0 = tile_of(cur.seg.n_tile) * kTileN;
-        const size_t grow = static_cast<size_t>(cur.expert) * p.groups + GroupOf(p, ks);
-        const char* sc = reinterpret_cast<const char*>(static_cast<const T*>(p.scales) + grow * p.n + n0);
-        const bool wide = n0 + 64 < p.n;  // second 128-byte line of the tile's 256 bytes of scales
+        const int n0 = tile_of(at.seg.n_tile) * kTileN;
+        const size_t grow = static_cast<size_t>(at.expert) * cur->p.groups + GroupOf(cur->p, ks);
+        const char* sc = reinterpret_cast<const char*>(static_cast<const T*>(cur->p.scales) + grow * cur->p.n + n0);
+        const bool wide = n0 + 64 < cur->p.n;  // second 128-byte line of the tile's 256 bytes of scales
         for (int r = 0; r < grp_rows; ++r) {
-          PrefetchL2(sc + static_cast<size_t>(r) * p.n * 2);
-          if (wide) PrefetchL2(sc + static_cast<size_t>(r) * p.n * 2 + 128);
-          if constexpr (kZeros) PrefetchL2(p.zeros + (grow + r) * (p.n / 8) + n0 / 8);
+          PrefetchL2(sc + static_cast<size_t>(r) * cur->p.n * 2);
+          if (wide) PrefetchL2(sc + static_cast<size_t>(r) * cur->p.n * 2 + 128);
+          if constexpr (kZeros) PrefetchL2(cur->p.zeros + (grow + r) * (cur->p.n / 8) + n0 / 8);
         }
       };
-      auto request_activations = [&](const Cursor& cur) {
+      auto request_activations = [&](const Cursor& at) {
+        [[maybe_unused]] const Problem* cur = kBatch ? probs + at.seg.prob : probs;
         if constexpr (!kPair) {
-          const int s = cur.it % kStages;
+          const int s = at.it % kStages;
           // a paired block loads its own half of the tile's token rows
           const int row0 =
-              (kMoe ? cur.seg.m_tile * p.block_size : cur.seg.m_tile * kTok) + static_cast<int>(rank) * kActRows;
+              (kMoe ? at.seg.m_tile * cur->p.block_size : at.seg.m_tile * kTok) + static_cast<int>(rank) * kActRows;
           // two 64-k atoms, one after the other
-          TmaLoad3D(stages_addr + s * kStage, &a_map, 0, row0, 2 * cur.Ks(), SmemAddr(&sh.full[s]));
+          TmaLoad3D(stages_addr + s * kStage, &cur->a_map, 0, row0, 2 * at.Ks(), SmemAddr(&sh.full[s]));
         }
       };
       if constexpr (!kMoe) {
@@ -779,13 +846,13 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
         while (ahead_active && ahead.it < static_cast<uint32_t>(kStages)) {
           request_weights(ahead);
           ahead.it += kProdLanes;
-          ahead_active = Locate<kMoe>(ahead, p.expert_ids);
+          ahead_active = Locate<kMoe, kBatch>(ahead, cur->p.expert_ids);
         }
         GridDependencyWait();
         while (active && c.it < static_cast<uint32_t>(kStages)) {
           request_activations(c);
           c.it += kProdLanes;
-          active = Locate<kMoe>(c, p.expert_ids);
+          active = Locate<kMoe, kBatch>(c, cur->p.expert_ids);
         }
       }
       uint32_t idle = 0;
@@ -797,7 +864,7 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
             request_weights(c);
             request_activations(c);
             c.it += kProdLanes;
-            active = Locate<kMoe>(c, p.expert_ids);
+            active = Locate<kMoe, kBatch>(c, cur->p.expert_ids);
             progressed = true;
             idle = 0;
           }
@@ -807,14 +874,14 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
           __nanosleep(32);
           if ((++idle & 0xff) == 0xff) {
             if (*abort_flag) {
-              if (active) NoteBlockedWarp(p.status, kErrEmpty, static_cast<int>(c.it));
+              if (active) NoteBlockedWarp(cur->p.status, kErrEmpty, static_cast<int>(c.it));
               break;
             }
             if (idle > kSpinLimit) {
-              if (active && atomicCAS(p.status, 0, kErrEmpty) == 0) {
-                p.status[1] = static_cast<int>(blockIdx.x);
-                p.status[2] = static_cast<int>(threadIdx.x);
-                p.status[3] = static_cast<int>(c.it);
+              if (active && atomicCAS(cur->p.status, 0, kErrEmpty) == 0) {
+                cur->p.status[1] = static_cast<int>(blockIdx.x);
+                cur->p.status[2] = static_cast<int>(threadIdx.x);
+                cur->p.status[3] = static_cast<int>(c.it);
                 __threadfence();
               }
               *abort_flag = 1;
@@ -841,13 +908,13 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
         }
       };
       int first_it = -1, last_it = -1;
-      Walker walk{u_begin, u_end, k_stages, m_tiles};
+      Walker walk = make_walker();
       Segment seg;
       uint32_t it = 0, seg_idx = 0;
       bool alive = true;
-      while (alive && walk.Next(seg)) {
+      while (alive && walk.template Next<kBatch>(seg)) {
         if constexpr (kMoe) {
-          if (p.expert_ids[seg.m_tile] < 0) continue;
+          if (cur->p.expert_ids[seg.m_tile] < 0) continue;
         }
         int acc = 0;
         uint32_t d_addr = tmem_d;
@@ -855,7 +922,7 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
           acc = seg_idx % kAcc;
           if (issuing) {
             // (paired blocks: arrivals come from both blocks, hence the cluster-scope acquire)
-            if (!MbarWait<kPair>(SmemAddr(&sh.d_empty[acc]), ((seg_idx / kAcc) & 1) ^ 1, abort_flag, p.status, kErrDEmpty,
+            if (!MbarWait<kPair>(SmemAddr(&sh.d_empty[acc]), ((seg_idx / kAcc) & 1) ^ 1, abort_flag, cur->p.status, kErrDEmpty,
                                  static_cast<int>(seg_idx))) {
               break;
             }
@@ -875,7 +942,7 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
           if constexpr (kLate) {
             // this stage's own accumulator must have been read out by the epilogue
             acc = it % kSlots;
-            if (!MbarWait(SmemAddr(&sh.d_empty[acc]), ((it / kSlots) & 1) ^ 1, abort_flag, p.status, kErrDEmpty,
+            if (!MbarWait(SmemAddr(&sh.d_empty[acc]), ((it / kSlots) & 1) ^ 1, abort_flag, cur->p.status, kErrDEmpty,
                           static_cast<int>(it))) {
               alive = false;
               break;
@@ -884,14 +951,14 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
           }
           // `a_full` is raised by warps that waited for this stage's copies themselves, so it
           // also covers the activation tile (in both blocks of a pair).
-          if (!MbarWait<kPair, kPair>(SmemAddr(&sh.a_full[a]), (it / kAStages) & 1, abort_flag, p.status, kErrAFull,
+          if (!MbarWait<kPair, kPair>(SmemAddr(&sh.a_full[a]), (it / kAStages) & 1, abort_flag, cur->p.status, kErrAFull,
                                       static_cast<int>(it))) {
             alive = false;
             break;
           }
           if constexpr (kPair) {
             // both halves of the activation tile (the other block's copy counts on this barrier too)
-            if (!MbarWait<true, true>(SmemAddr(&sh.act_full[sa]), sa_phase, abort_flag, p.status, kErrFull,
+            if (!MbarWait<true, true>(SmemAddr(&sh.act_full[sa]), sa_phase, abort_flag, cur->p.status, kErrFull,
                                       static_cast<int>(it))) {
               alive = false;
               break;
@@ -946,15 +1013,15 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
           if (step < first_it) break;
           if constexpr (kPair) {
             if (d < kActStages && !MbarWait(SmemAddr(&sh.act_empty[step % kActStages]), (step / kActStages) & 1, abort_flag,
-                                            p.status, kErrEmpty, step)) {
+                                            cur->p.status, kErrEmpty, step)) {
               break;
             }
-          } else if (!MbarWait(SmemAddr(&sh.empty[step % kStages]), (step / kStages) & 1, abort_flag, p.status, kErrEmpty,
+          } else if (!MbarWait(SmemAddr(&sh.empty[step % kStages]), (step / kStages) & 1, abort_flag, cur->p.status, kErrEmpty,
                                step)) {
             break;
           }
           if (d * kIssueStride < kAStages &&
-              !MbarWait(SmemAddr(&sh.a_empty[step % kAStages]), (step / kAStages) & 1, abort_flag, p.status, kErrAEmpty,
+              !MbarWait(SmemAddr(&sh.a_empty[step % kAStages]), (step / kAStages) & 1, abort_flag, cur->p.status, kErrAEmpty,
                         step)) {
             break;
           }
@@ -965,17 +1032,17 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
       if (lane == 0 && warp == 2) {
         // ================= activation producer (paired blocks) =================
         // this block's 128 token rows of every stage, into the activation ring
-        Cursor c{Walker{u_begin, u_end, k_stages, m_tiles}, Segment{}, 0u, 0u, 0, 0};
-        while (Locate<kMoe>(c, p.expert_ids)) {
+        Cursor c{make_walker(), Segment{}, 0u, 0u, 0, 0};
+        while (Locate<kMoe, kBatch>(c, cur->p.expert_ids)) {
           const int sa = c.it % kActStages;
-          if (!MbarWait<false, true>(SmemAddr(&sh.act_empty[sa]), ((c.it / kActStages) & 1) ^ 1, abort_flag, p.status,
+          if (!MbarWait<false, true>(SmemAddr(&sh.act_empty[sa]), ((c.it / kActStages) & 1) ^ 1, abort_flag, cur->p.status,
                                      kErrEmpty, static_cast<int>(c.it))) {
             break;
           }
           // Both halves of the tile are counted on the even block's barrier, which that block arms
           // for the two of them; the odd block's copy reports there directly.
           if (rank == 0) MbarExpectTx(SmemAddr(&sh.act_full[sa]), 2 * kActBytes);
-          TmaLoad3DPair(acts_addr + sa * kActBytes, &a_map, 0, c.seg.m_tile * kTok + static_cast<int>(rank) * kActRows,
+          TmaLoad3DPair(acts_addr + sa * kActBytes, &cur->a_map, 0, c.seg.m_tile * kTok + static_cast<int>(rank) * kActRows,
                         2 * c.Ks(), MapToBlock(SmemAddr(&sh.act_full[sa]), 0));
           ++c.it;
         }
@@ -987,7 +1054,7 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
     const int q = warp & 3;  // tensor-memory lane quarter this warp may touch
     // symmetric types: implicit zero point 8
     const uint32_t zero_sym = Half2Of<T>::kMagic | 0x00080008u;
-    const int rows = p.group_size == 64 ? 2 : 1;  // scale / zero rows a 128-k stage spans
+    const int rows = cur->p.group_size == 64 ? 2 : 1;  // scale / zero rows a 128-k stage spans
     // Scales and zero points come straight from global memory (they are tiny and mostly L2 hits),
     // one stage ahead of their use, so the producer has only the two big copies to request.
     // This thread owns tile columns c0 = 16 (2q + h) + lane / 4 and c0 + 8 for h = 0, 1; `sc`
@@ -1004,35 +1071,36 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
     const uint4* zbase = nullptr;
     int col = 0;
     auto fetch_groups = [&](const Cursor& c) {
+      [[maybe_unused]] const Problem* cur = kBatch ? probs + c.seg.prob : probs;
       if (c.seg_it != based_on) {
         based_on = c.seg_it;
         const int n0 = tile_of(c.seg.n_tile) * kTileN;
-        const size_t g0 = static_cast<size_t>(c.expert) * p.groups;
-        const bool inside = n0 + 32 * q < p.n;
+        const size_t g0 = static_cast<size_t>(c.expert) * cur->p.groups;
+        const bool inside = n0 + 32 * q < cur->p.n;
         col = 32 * q + (lane >> 2) - (inside ? 0 : 64);
-        sbase = reinterpret_cast<const unsigned short*>(p.scales) + g0 * p.n + n0;
-        if constexpr (kZeros) zbase = reinterpret_cast<const uint4*>(p.zeros + g0 * (p.n / 8) + n0 / 8) + (inside ? q : q - 2);
+        sbase = reinterpret_cast<const unsigned short*>(cur->p.scales) + g0 * cur->p.n + n0;
+        if constexpr (kZeros) zbase = reinterpret_cast<const uint4*>(cur->p.zeros + g0 * (cur->p.n / 8) + n0 / 8) + (inside ? q : q - 2);
       }
       GroupRegs g;
-      const uint32_t grp = static_cast<uint32_t>(GroupOf(p, c.Ks()));
-      const unsigned short* sp = sbase + static_cast<size_t>(grp) * static_cast<uint32_t>(p.n) + col;
+      const uint32_t grp = static_cast<uint32_t>(GroupOf(cur->p, c.Ks()));
+      const unsigned short* sp = sbase + static_cast<size_t>(grp) * static_cast<uint32_t>(cur->p.n) + col;
       g.sc[0][0] = g.sc[0][1] = g.sc[1][0] = g.sc[1][1] = 0;
       if constexpr (!kLate) {
         g.sc[0][0] = LdGlobalU16Here(sp) | (LdGlobalU16Here(sp + 8) << 16);
         g.sc[0][1] = LdGlobalU16Here(sp + 16) | (LdGlobalU16Here(sp + 24) << 16);
       }
       g.zp[0] = g.zp[1] = make_uint4(0, 0, 0, 0);
-      if constexpr (kZeros) g.zp[0] = LdGlobalV4Here(zbase + static_cast<size_t>(grp) * static_cast<uint32_t>(p.n / 32));
+      if constexpr (kZeros) g.zp[0] = LdGlobalV4Here(zbase + static_cast<size_t>(grp) * static_cast<uint32_t>(cur->p.n / 32));
       if (!kLate && rows == 2) {
-        sp += p.n;
+        sp += cur->p.n;
         g.sc[1][0] = LdGlobalU16Here(sp) | (LdGlobalU16Here(sp + 8) << 16);
         g.sc[1][1] = LdGlobalU16Here(sp + 16) | (LdGlobalU16Here(sp + 24) << 16);
-        if constexpr (kZeros) g.zp[1] = LdGlobalV4Here(zbase + static_cast<size_t>(grp + 1) * static_cast<uint32_t>(p.n / 32));
+        if constexpr (kZeros) g.zp[1] = LdGlobalV4Here(zbase + static_cast<size_t>(grp + 1) * static_cast<uint32_t>(cur->p.n / 32));
       }
       return g;
     };
-    Cursor nx{Walker{u_begin, u_end, k_stages, m_tiles}, Segment{}, static_cast<uint32_t>(set), 0u, 0, 0};
-    bool more = Locate<kMoe>(nx, p.expert_ids);
+    Cursor nx{make_walker(), Segment{}, static_cast<uint32_t>(set), 0u, 0, 0};
+    bool more = Locate<kMoe, kBatch>(nx, cur->p.expert_ids);
     GroupRegs coming{};
     if (more) coming = fetch_groups(nx);
     uint32_t early = 0;  // lane 0: early barrier tests for the coming stage
@@ -1044,7 +1112,7 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
       const uint32_t it = nx.it;
       const GroupRegs gr = coming;
       nx.it += kSets;
-      more = Locate<kMoe>(nx, p.expert_ids);
+      more = Locate<kMoe, kBatch>(nx, cur->p.expert_ids);
       if (more) coming = fetch_groups(nx);
       // `early` holds lane 0's tests of this stage's two barriers, made while the previous stage
       // was still being converted (bit 0: copies landed, bit 1: tensor-memory stage free), so
@@ -1052,7 +1120,7 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
       // runs ahead of this warp.  The shuffle hands the outcome to the warp and orders the other
       // lanes' reads behind lane 0's acquire.
       const uint32_t seen = __shfl_sync(0xffffffffu, early, 0);
-      if (!(seen & 1u) && !MbarWaitWarp(0xffffffffu, 0, SmemAddr(&sh.full[s]), s_phase, abort_flag, p.status, kErrFull,
+      if (!(seen & 1u) && !MbarWaitWarp(0xffffffffu, 0, SmemAddr(&sh.full[s]), s_phase, abort_flag, cur->p.status, kErrFull,
                                         false, static_cast<int>(it))) {
         break;
       }
@@ -1065,7 +1133,7 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
       // first store of the stage: this tensor-memory stage must have been read out by the MMAs
       // that used it last
       auto before_first_store = [&]() {
-        if (!(seen & 2u) && !MbarWaitWarp(0xffffffffu, 0, SmemAddr(&sh.a_empty[a]), a_phase ^ 1, abort_flag, p.status,
+        if (!(seen & 2u) && !MbarWaitWarp(0xffffffffu, 0, SmemAddr(&sh.a_empty[a]), a_phase ^ 1, abort_flag, cur->p.status,
                                           kErrAEmpty, false, static_cast<int>(it))) {
           alive = false;
         }
@@ -1186,46 +1254,50 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
   } else {
     // ================= epilogue =================
     const int q = warp & 3;
-    Walker walk{u_begin, u_end, k_stages, m_tiles};
+    Walker walk = make_walker();
     Segment seg;
     uint32_t seg_idx = 0, it = 0;
     uint32_t early = 0;  // kLate, lane 0: early test of the coming stage's accumulator barrier
     uint32_t staged = 0;  // output chunks this warp has sent through its staging buffers
-    T* out = static_cast<T*>(p.out);
-    while (walk.Next(seg)) {
+    while (walk.template Next<kBatch>(seg)) {
+      if constexpr (kBatch) cur = probs + seg.prob;
+      T* out = static_cast<T*>(cur->p.out);
       int expert = 0;
       if constexpr (kMoe) {
-        expert = p.expert_ids[seg.m_tile];
+        expert = cur->p.expert_ids[seg.m_tile];
         if (expert < 0) continue;
       }
       const int n_local = 32 * q + lane;
       const int n = tile_of(seg.n_tile) * kTileN + n_local;
-      const bool n_ok = n < p.n;
-      const int row0 = kMoe ? seg.m_tile * p.block_size : seg.m_tile * kTok;
-      const int m_valid = kMoe ? p.block_size : min(kTok, p.m - row0);
-      const bool whole = seg.k_begin == 0 && seg.k_end == k_stages;
+      const bool n_ok = n < cur->p.n;
+      const int row0 = kMoe ? seg.m_tile * cur->p.block_size : seg.m_tile * kTok;
+      const int m_valid = kMoe ? cur->p.block_size : min(kTok, cur->p.m - row0);
+      const bool whole = seg.k_begin == 0 && seg.k_end == seg.k_stages;
       const int n_steps = seg.k_end - seg.k_begin;
       float bias_v = 0.0f;
-      if (p.bias != nullptr && n_ok) bias_v = ToFloat<T>(static_cast<const T*>(p.bias)[static_cast<size_t>(expert) * p.n + n]);
+      if (cur->p.bias != nullptr && n_ok) bias_v = ToFloat<T>(static_cast<const T*>(cur->p.bias)[static_cast<size_t>(expert) * cur->p.n + n]);
 
       // Writes one finished value; `j` is the token column of the tile.
       auto emit = [&](int j, float v) {
         v += bias_v;
         if constexpr (kMoe) {
-          const int id = p.sorted_ids[row0 + j];
-          if (id < p.out_rows) {
-            if (p.mul_weights) v *= p.topk_weights[id];
-            out[static_cast<size_t>(id) * p.n + n] = FromFloat<T>(v);
+          const int id = cur->p.sorted_ids[row0 + j];
+          if (id < cur->p.out_rows) {
+            if (cur->p.mul_weights) v *= cur->p.topk_weights[id];
+            out[static_cast<size_t>(id) * cur->p.n + n] = FromFloat<T>(v);
           }
         } else {
-          out[static_cast<size_t>(row0 + j) * p.n + n] = FromFloat<T>(v);
+          const size_t at = static_cast<size_t>(row0 + j) * cur->p.out_ld + cur->p.out_col0 + n;
+          const T value = FromFloat<T>(v);
+          out[at] = value;
+          for (int r = 0; r < cur->p.n_peers; ++r) static_cast<T*>(cur->p.peer_out[r])[at] = value;
         }
       };
 
       const bool first_of_block = walk.u - (seg.k_end - seg.k_begin) == u_begin;
       // partial slot layout: [128 tile columns][kTok tokens], so a thread's tokens are contiguous
       float* my_partial =
-          p.partial + (static_cast<size_t>(2 * blockIdx.x + (first_of_block ? 0 : 1)) * kTileN + n_local) * kTok;
+          cur->p.partial + (static_cast<size_t>(2 * blockIdx.x + (first_of_block ? 0 : 1)) * kTileN + n_local) * kTok;
       // 16 token columns of this thread's output row, summed over the segment: final values of a
       // whole tile, else this block's partial
       auto finish_chunk = [&](int c, const uint32_t (&r)[16]) {
@@ -1247,8 +1319,26 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
               FenceProxyAsyncShared();
               __syncwarp();
               if (lane == 0) {
-                TmaStore2D(&c_map, buf, n - lane, row0 + c);
+                TmaStore2D(&cur->c_map, buf, cur->p.out_col0 + n - lane, row0 + c);
                 BulkCommitGroup();
+              }
+              if (cur->p.n_peers > 0) {
+                // The same 16 x 32 tile into the other GPUs' matrices: read back from the staging
+                // buffer as 16-byte pieces (four per row) and stored with plain global stores.
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                  const int row = half * 8 + (lane >> 2), part = lane & 3;
+                  if (row0 + c + row < cur->p.m) {
+                    uint4 piece;
+                    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(piece.x), "=r"(piece.y), "=r"(piece.z), "=r"(piece.w)
+                                 : "r"(buf + row * 64 + part * 16));
+                    const size_t at = static_cast<size_t>(row0 + c + row) * cur->p.out_ld + cur->p.out_col0 + (n - lane) + part * 8;
+                    for (int r = 0; r < cur->p.n_peers; ++r) {
+                      *reinterpret_cast<uint4*>(static_cast<T*>(cur->p.peer_out[r]) + at) = piece;
+                    }
+                  }
+                }
               }
               ++staged;
             }
@@ -1272,18 +1362,18 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
         float sum[kTok];
 #pragma unroll
         for (int j = 0; j < kTok; ++j) sum[j] = 0.0f;
-        const T* srow = static_cast<const T*>(p.scales) + static_cast<size_t>(expert) * p.groups * p.n +
+        const T* srow = static_cast<const T*>(cur->p.scales) + static_cast<size_t>(expert) * cur->p.groups * cur->p.n +
                         (n_ok ? n : n - 64);  // a column past N borrows a valid one; it is never written
-        uint32_t coming = LdGlobalU16Here(srow + static_cast<size_t>(GroupOf(p, seg.k_begin)) * p.n);
+        uint32_t coming = LdGlobalU16Here(srow + static_cast<size_t>(GroupOf(cur->p, seg.k_begin)) * cur->p.n);
         bool alive = true;
         for (int ks = seg.k_begin; ks < seg.k_end; ++ks, ++it) {
           const unsigned short raw = static_cast<unsigned short>(coming);
           const float scale = ToFloat<T>(*reinterpret_cast<const T*>(&raw));
-          if (ks + 1 < seg.k_end) coming = LdGlobalU16Here(srow + static_cast<size_t>(GroupOf(p, ks + 1)) * p.n);
+          if (ks + 1 < seg.k_end) coming = LdGlobalU16Here(srow + static_cast<size_t>(GroupOf(cur->p, ks + 1)) * cur->p.n);
           const int slot = it % kSlots;
           const uint32_t seen = __shfl_sync(0xffffffffu, early, 0);
           if (!(seen & 1u) && !MbarWaitWarp(0xffffffffu, 0, SmemAddr(&sh.d_full[slot]), (it / kSlots) & 1, abort_flag,
-                                            p.status, kErrDFull, /*relaxed=*/false, static_cast<int>(it))) {
+                                            cur->p.status, kErrDFull, /*relaxed=*/false, static_cast<int>(it))) {
             alive = false;
             break;
           }
@@ -1324,7 +1414,7 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
         ++seg_idx;
       } else {
         const int acc = seg_idx % kAcc;
-        if (!MbarWaitWarp(0xffffffffu, 0, SmemAddr(&sh.d_full[acc]), (seg_idx / kAcc) & 1, abort_flag, p.status,
+        if (!MbarWaitWarp(0xffffffffu, 0, SmemAddr(&sh.d_full[acc]), (seg_idx / kAcc) & 1, abort_flag, cur->p.status,
                           kErrDFull, /*relaxed=*/true, static_cast<int>(seg_idx))) {
           break;
         }
@@ -1396,11 +1486,11 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
         // Each lane quarter of the tile has its own arrival counter, so the four epilogue
         // warps never have to meet at a barrier: the warp that arrives last for its quarter
         // (over all blocks sharing the tile) sums that quarter.
-        const long long tile_u0 = static_cast<long long>(seg.tile) * k_stages;
+        const long long tile_u0 = seg.tile_u0;
         const int first_block = OwnerOf(tile_u0, total_units, grid);
-        const int last_block = OwnerOf(tile_u0 + k_stages - 1, total_units, grid);
+        const int last_block = OwnerOf(tile_u0 + seg.k_stages - 1, total_units, grid);
         // A split tile is identified by the first block working on it: no two split tiles share one.
-        int* counter = p.counters + 4 * launched_block(first_block) + q;
+        int* counter = cur->p.counters + 4 * launched_block(first_block) + q;
         // Publish the partial and take a ticket in one acquire-release atomic: the warp barrier
         // orders every lane's stores before lane 0's release, and the shuffle orders the other lanes'
         // loads after its acquire.
@@ -1415,7 +1505,7 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
             // a block's first segment uses slot 2b, any later one slot 2b + 1
             auto slot_of = [&](int b) -> const float* {
               const bool is_first = RangeStart(b, total_units, grid) >= tile_u0;
-              return p.partial + (static_cast<size_t>(2 * launched_block(b) + (is_first ? 0 : 1)) * kTileN + n_local) * kTok;
+              return cur->p.partial + (static_cast<size_t>(2 * launched_block(b) + (is_first ? 0 : 1)) * kTileN + n_local) * kTok;
             };
             for (int c = 0; c < m_valid; c += 16) {
               float sum[16];
@@ -1458,6 +1548,29 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
   }
 
   // ---- teardown -----------------------------------------------------------------------------
+  if constexpr (!kMoe) {
+    // Completion signal to the other GPUs (launches that were given one).  Every block makes its
+    // own stores visible system-wide and counts itself done; the block that comes last bumps the
+    // epoch and publishes it in every peer's flag word.  Nobody waits here.
+    if (probs[0].p.done_counter != nullptr) {
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        const GemmParams& sp = probs[0].p;
+        __threadfence_system();
+        int arrived;
+        asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(arrived) : "l"(sp.done_counter) : "memory");
+        if (arrived == static_cast<int>(gridDim.x) - 1) {
+          *sp.done_counter = 0;
+          const int epoch = *sp.epoch + 1;
+          *sp.epoch = epoch;
+          __threadfence_system();
+          for (int r = 0; r < sp.n_flag_peers; ++r) {
+            asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(sp.peer_flags[r] + sp.flag_slot), "r"(epoch) : "memory");
+          }
+        }
+      }
+    }
+  }
   if (*abort_flag) {
     // give copies in flight time to land before shared memory is released
     for (int i = 0; i < 1000; ++i) __nanosleep(1000);
@@ -1473,6 +1586,19 @@ W4A16GemmKernel(const __grid_constant__ CUtensorMap a_map, const __grid_constant
   } else if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
+}
+
+// One problem per launch.
+template <typename T, int kTok, bool kZeros, bool kMoe, int kSets, bool kLate, bool kPair = false>
+__global__ void __launch_bounds__((5 + IssuersFor(kTok) + 4 * kSets) * 32, 1)
+W4A16GemmKernel(const __grid_constant__ Problem problem) {
+  GemmBody<T, kTok, kZeros, kMoe, kSets, kLate, kPair, false>(&problem, 1);
+}
+// A table of dense problems per launch.
+template <typename T, int kTok, bool kZeros, int kSets>
+__global__ void __launch_bounds__((5 + IssuersFor(kTok) + 4 * kSets) * 32, 1)
+W4A16GemmBatchKernel(const __grid_constant__ BatchTable table) {
+  GemmBody<T, kTok, kZeros, false, kSets, true, false, true>(table.prob, table.count);
 }
 
 // Self-test of the bounded wait: one thread waits, with a limit of a few thousand polls, on a
@@ -1733,9 +1859,60 @@ int LaunchVariant(const CUtensorMap& map, const CUtensorMap& w_map, const CUtens
     attr[1].val.clusterDim.z = 1;
     config.numAttrs = 2;
   }
-  const cudaError_t err = cudaLaunchKernelEx(&config, kernel, map, w_map, c_map, p);
+  Problem problem{};
+  problem.a_map = map;
+  problem.w_map = w_map;
+  problem.c_map = c_map;
+  problem.p = p;
+  const cudaError_t err = cudaLaunchKernelEx(&config, kernel, problem);
   if (err != cudaSuccess) return Fail(IOB_CUDA_ERROR, "W4A16 GEMM launch: %s", cudaGetErrorString(err));
   return CheckLaunch("W4A16 GEMM launch");
+}
+
+// A table of dense problems (late-scale tiles of kTok tokens) as one launch.
+template <typename T, int kTok, bool kZeros>
+int LaunchBatchVariant(const BatchTable& table, int grid, cudaStream_t stream) {
+  constexpr int kSets = SetsFor(kTok);
+  auto kernel = W4A16GemmBatchKernel<T, kTok, kZeros, kSets>;
+  constexpr int smem = StagesFor(kTok) * StageBytes(kTok) + 8192 + 1024;
+  static thread_local bool configured[64] = {};
+  int device = 0;
+  cudaGetDevice(&device);
+  if (device < 0 || device >= 64 || !configured[device]) {
+    const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (err != cudaSuccess) return Fail(IOB_CUDA_ERROR, "W4A16 GEMM batch: %s", cudaGetErrorString(err));
+    if (device >= 0 && device < 64) configured[device] = true;
+  }
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(grid);
+  config.blockDim = dim3((5 + IssuersFor(kTok) + 4 * kSets) * 32);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = 1;
+  const cudaError_t err = cudaLaunchKernelEx(&config, kernel, table);
+  if (err != cudaSuccess) return Fail(IOB_CUDA_ERROR, "W4A16 GEMM batch launch: %s", cudaGetErrorString(err));
+  return CheckLaunch("W4A16 GEMM batch launch");
+}
+
+int LaunchBatch(int a_dtype, bool zeros, int tok, const BatchTable& table, int grid, cudaStream_t stream) {
+  if (a_dtype == IOB_BF16) {
+    if (tok == 16) {
+      return zeros ? LaunchBatchVariant<__nv_bfloat16, 16, true>(table, grid, stream)
+                   : LaunchBatchVariant<__nv_bfloat16, 16, false>(table, grid, stream);
+    }
+    return zeros ? LaunchBatchVariant<__nv_bfloat16, 32, true>(table, grid, stream)
+                 : LaunchBatchVariant<__nv_bfloat16, 32, false>(table, grid, stream);
+  }
+  if (tok == 16) {
+    return zeros ? LaunchBatchVariant<__half, 16, true>(table, grid, stream)
+                 : LaunchBatchVariant<__half, 16, false>(table, grid, stream);
+  }
+  return zeros ? LaunchBatchVariant<__half, 32, true>(table, grid, stream)
+               : LaunchBatchVariant<__half, 32, false>(table, grid, stream);
 }
 
 // Token tiles up to 32 with groups of at least one k-stage take the variant that scales the
@@ -1842,50 +2019,185 @@ extern "C" size_t infiniops_b200_marlin_gemm_scratch_bytes(int64_t size_m, int64
   return PlanScratch(tiles, tok, 0).total;
 }
 
+namespace iob {
+namespace {
+
+// Validates the placement and peer fields of a problem and copies them into the kernel parameters.
+int SetPlacement(const char* op, const iob_gemm_problem& g, GemmParams& p) {
+  const int64_t ld = g.out_ld > 0 ? g.out_ld : g.size_n;
+  IOB_REQUIRE(g.out_col0 >= 0 && g.out_col0 + g.size_n <= ld && ld % 8 == 0 && g.out_col0 % 8 == 0 && ld <= INT32_MAX,
+              "%s: columns [out_col0, out_col0 + size_n) must lie inside a row of out_ld elements, both multiples of 8", op);
+  IOB_REQUIRE(g.n_peers >= 0 && g.n_peers <= kMaxPeers, "%s: at most %d peer outputs", op, kMaxPeers);
+  p.out_ld = static_cast<int>(ld);
+  p.out_col0 = static_cast<int>(g.out_col0);
+  p.n_peers = g.n_peers;
+  for (int r = 0; r < g.n_peers; ++r) {
+    IOB_REQUIRE(g.peer_out[r] != nullptr && reinterpret_cast<uintptr_t>(g.peer_out[r]) % 16 == 0,
+                "%s: peer outputs must be non-null and 16-byte aligned", op);
+    p.peer_out[r] = g.peer_out[r];
+  }
+  return IOB_OK;
+}
+
+int SetSignal(const char* op, const iob_peer_signal* signal, GemmParams& p) {
+  if (signal == nullptr) return IOB_OK;
+  IOB_REQUIRE(signal->done_counter != nullptr && signal->epoch != nullptr && signal->n_peers >= 0 &&
+                  signal->n_peers <= kMaxPeers && signal->flag_slot >= 0,
+              "%s: incomplete completion signal", op);
+  p.done_counter = signal->done_counter;
+  p.epoch = signal->epoch;
+  p.flag_slot = signal->flag_slot;
+  p.n_flag_peers = signal->n_peers;
+  for (int r = 0; r < signal->n_peers; ++r) {
+    IOB_REQUIRE(signal->peer_flags[r] != nullptr, "%s: null peer flag pointer", op);
+    p.peer_flags[r] = signal->peer_flags[r];
+  }
+  return IOB_OK;
+}
+
+void FillDense(const iob_gemm_problem& g, unsigned char* scratch, const ScratchPlan& plan, GemmParams& p) {
+  p.wq = reinterpret_cast<const uint32_t*>(g.b_q_weight);
+  p.scales = g.b_scales;
+  p.zeros = reinterpret_cast<const uint32_t*>(g.b_zeros);
+  p.bias = g.b_bias;
+  p.out = g.out;
+  p.partial = reinterpret_cast<float*>(scratch + plan.partial_off);
+  p.counters = reinterpret_cast<int*>(scratch + plan.counters_off);
+  p.status = reinterpret_cast<int*>(scratch);
+  p.m = static_cast<int>(g.size_m);
+  p.n = static_cast<int>(g.size_n);
+  p.k = static_cast<int>(g.size_k);
+  p.groups = static_cast<int>(g.num_groups);
+  p.group_size = static_cast<int>(g.size_k / g.num_groups);
+  SetGroupMap(p);
+}
+
+}  // namespace
+}  // namespace iob
+
+extern "C" int infiniops_b200_marlin_gemm_placed(const iob_gemm_problem* problem, int a_dtype, int64_t b_type_id,
+                                                 const iob_peer_signal* signal, void* scratch, size_t scratch_bytes,
+                                                 void* stream) {
+  using namespace iob;
+  const char* op = "marlin_gemm";
+  IOB_REQUIRE(problem != nullptr, "%s: null problem", op);
+  const iob_gemm_problem& g = *problem;
+  if (const int rc = CheckProblem(op, g.a, a_dtype, g.b_q_weight, g.b_scales, g.b_zeros, b_type_id, g.size_m, g.size_n,
+                                  g.size_k, g.num_groups, g.out)) {
+    return rc;
+  }
+  const int tok = DenseTokenTile(g.size_m, g.size_n, g.size_k / (g.num_groups > 0 ? g.num_groups : 1));
+  const int64_t n_tiles = (g.size_n + kTileN - 1) / kTileN, m_tiles = (g.size_m + tok - 1) / tok;
+  // (the scratch query does not know the group size and answers for the larger plan)
+  const ScratchPlan plan = PlanScratch(n_tiles * m_tiles, tok, 0);
+  if (scratch == nullptr || scratch_bytes < plan.total) {
+    return Fail(IOB_SCRATCH_TOO_SMALL, "%s: needs %zu bytes of scratch, got %zu", op, plan.total, scratch_bytes);
+  }
+  GemmParams p{};
+  if (const int rc = SetPlacement(op, g, p)) return rc;
+  if (const int rc = SetSignal(op, signal, p)) return rc;
+  // Prefill-sized problems whose columns pair up run two blocks per 256 x 256 output tile.
+  const bool pair = tok == 256 && g.size_n % (2 * kTileN) == 0 && NumSms() >= 2;
+  CUtensorMap map;
+  if (const int rc = ActivationMap(g.a, g.size_m, g.size_k, pair ? tok / 2 : tok, a_dtype, &map)) return rc;
+  CUtensorMap w_map;
+  if (const int rc = WeightMap(g.b_q_weight, 1, g.size_k, g.size_n, &w_map)) return rc;
+  CUtensorMap c_map;
+  if (const int rc = OutputMap(g.out, g.size_m, p.out_ld, a_dtype, &c_map)) return rc;
+  p.pair = pair ? 1 : 0;
+  FillDense(g, static_cast<unsigned char*>(scratch), plan, p);
+  const int64_t units = n_tiles * m_tiles * (g.size_k / kBlockK);
+  const int grid = pair ? NumSms() : static_cast<int>(units < NumSms() ? units : NumSms());
+  return Dispatch<false>(a_dtype, g.b_zeros != nullptr, tok, map, w_map, c_map, p, grid, static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int infiniops_b200_marlin_gemm(const void* a, int a_dtype, const int32_t* b_q_weight, const void* b_bias,
                                           const void* b_scales, const int32_t* b_zeros, int64_t b_type_id,
                                           int64_t size_m, int64_t size_n, int64_t size_k, int64_t num_groups,
                                           void* out, void* scratch, size_t scratch_bytes, void* stream) {
+  iob_gemm_problem g{};
+  g.a = a;
+  g.b_q_weight = b_q_weight;
+  g.b_bias = b_bias;
+  g.b_scales = b_scales;
+  g.b_zeros = b_zeros;
+  g.out = out;
+  g.size_m = size_m;
+  g.size_n = size_n;
+  g.size_k = size_k;
+  g.num_groups = num_groups;
+  return infiniops_b200_marlin_gemm_placed(&g, a_dtype, b_type_id, nullptr, scratch, scratch_bytes, stream);
+}
+
+extern "C" size_t infiniops_b200_marlin_gemm_batch_scratch_bytes(void) {
   using namespace iob;
-  if (const int rc = CheckProblem("marlin_gemm", a, a_dtype, b_q_weight, b_scales, b_zeros, b_type_id, size_m, size_n,
-                                  size_k, num_groups, out)) {
-    return rc;
-  }
-  const int tok = DenseTokenTile(size_m, size_n, size_k / (num_groups > 0 ? num_groups : 1));
-  const int64_t n_tiles = (size_n + kTileN - 1) / kTileN, m_tiles = (size_m + tok - 1) / tok;
-  // (the scratch query does not know the group size and answers for the larger plan)
-  const ScratchPlan plan = PlanScratch(n_tiles * m_tiles, tok, 0);
+  return PlanScratch(0, 32, 0).total;
+}
+
+extern "C" int infiniops_b200_marlin_gemm_batch(const iob_gemm_problem* problems, int count, int a_dtype,
+                                                int64_t b_type_id, const iob_peer_signal* signal, void* scratch,
+                                                size_t scratch_bytes, void* stream) {
+  using namespace iob;
+  const char* op = "marlin_gemm_batch";
+  IOB_REQUIRE(problems != nullptr && count > 0, "%s: no problems", op);
+  const ScratchPlan plan = PlanScratch(0, 32, 0);
   if (scratch == nullptr || scratch_bytes < plan.total) {
-    return Fail(IOB_SCRATCH_TOO_SMALL, "marlin_gemm: needs %zu bytes of scratch, got %zu", plan.total, scratch_bytes);
+    return Fail(IOB_SCRATCH_TOO_SMALL, "%s: needs %zu bytes of scratch, got %zu", op, plan.total, scratch_bytes);
   }
-  // Prefill-sized problems whose columns pair up run two blocks per 256 x 256 output tile.
-  const bool pair = tok == 256 && size_n % (2 * kTileN) == 0 && NumSms() >= 2;
-  CUtensorMap map;
-  if (const int rc = ActivationMap(a, size_m, size_k, pair ? tok / 2 : tok, a_dtype, &map)) return rc;
-  CUtensorMap w_map;
-  if (const int rc = WeightMap(b_q_weight, 1, size_k, size_n, &w_map)) return rc;
-  CUtensorMap c_map;
-  if (const int rc = OutputMap(out, size_m, size_n, a_dtype, &c_map)) return rc;
-  auto* base = static_cast<unsigned char*>(scratch);
-  GemmParams p{};
-  p.pair = pair ? 1 : 0;
-  p.wq = reinterpret_cast<const uint32_t*>(b_q_weight);
-  p.scales = b_scales;
-  p.zeros = reinterpret_cast<const uint32_t*>(b_zeros);
-  p.bias = b_bias;
-  p.out = out;
-  p.partial = reinterpret_cast<float*>(base + plan.partial_off);
-  p.counters = reinterpret_cast<int*>(base + plan.counters_off);
-  p.status = reinterpret_cast<int*>(base);
-  p.m = static_cast<int>(size_m);
-  p.n = static_cast<int>(size_n);
-  p.k = static_cast<int>(size_k);
-  p.groups = static_cast<int>(num_groups);
-  p.group_size = static_cast<int>(size_k / num_groups);
-  SetGroupMap(p);
-  const int64_t units = n_tiles * m_tiles * (size_k / kBlockK);
-  const int grid = pair ? NumSms() : static_cast<int>(units < NumSms() ? units : NumSms());
-  return Dispatch<false>(a_dtype, b_zeros != nullptr, tok, map, w_map, c_map, p, grid, static_cast<cudaStream_t>(stream));
+  // Two classes of token tile: up to 16 rows, and 17..64 rows as 32-row tiles.  Each class is one
+  // launch (or several, kMaxBatch problems at a time); the completion signal rides on the last.
+  int order[2][1024];
+  int n_of[2] = {0, 0};
+  IOB_REQUIRE(count <= 1024, "%s: at most 1024 problems per call", op);
+  for (int i = 0; i < count; ++i) {
+    const iob_gemm_problem& g = problems[i];
+    if (const int rc = CheckProblem(op, g.a, a_dtype, g.b_q_weight, g.b_scales, g.b_zeros, b_type_id, g.size_m,
+                                    g.size_n, g.size_k, g.num_groups, g.out)) {
+      return rc;
+    }
+    if (g.size_m > 64 || (g.size_k / g.num_groups) % kBlockK != 0) {
+      return Fail(IOB_UNSUPPORTED, "%s: problem %d: batched launches take at most 64 rows and group sizes that are "
+                  "multiples of 128; use marlin_gemm", op, i);
+    }
+    const int cls = g.size_m <= 16 ? 0 : 1;
+    order[cls][n_of[cls]++] = i;
+  }
+  const int launches = (n_of[0] + kMaxBatch - 1) / kMaxBatch + (n_of[1] + kMaxBatch - 1) / kMaxBatch;
+  int launched = 0;
+  for (int cls = 0; cls < 2; ++cls) {
+    const int tok = cls == 0 ? 16 : 32;
+    for (int first = 0; first < n_of[cls]; first += kMaxBatch) {
+      BatchTable table{};
+      table.count = std::min(kMaxBatch, n_of[cls] - first);
+      long long units = 0;
+      for (int j = 0; j < table.count; ++j) {
+        const iob_gemm_problem& g = problems[order[cls][first + j]];
+        Problem& pr = table.prob[j];
+        if (const int rc = SetPlacement(op, g, pr.p)) return rc;
+        if (const int rc = ActivationMap(g.a, g.size_m, g.size_k, tok, a_dtype, &pr.a_map)) return rc;
+        if (const int rc = WeightMap(g.b_q_weight, 1, g.size_k, g.size_n, &pr.w_map)) return rc;
+        if (const int rc = OutputMap(g.out, g.size_m, pr.p.out_ld, a_dtype, &pr.c_map)) return rc;
+        FillDense(g, static_cast<unsigned char*>(scratch), plan, pr.p);
+        pr.n_tiles = static_cast<int>((g.size_n + kTileN - 1) / kTileN);
+        pr.m_tiles = static_cast<int>((g.size_m + tok - 1) / tok);
+        pr.k_stages = static_cast<int>(g.size_k / kBlockK);
+        units += static_cast<long long>(pr.n_tiles) * pr.m_tiles * pr.k_stages;
+        IOB_REQUIRE(units < (1ll << 31), "%s: too many work units in one launch", op);
+        pr.unit_end = units;
+      }
+      ++launched;
+      if (launched == launches) {
+        // the kernel reads the signal from the first problem of the table; its peers are those of the flags
+        if (const int rc = SetSignal(op, signal, table.prob[0].p)) return rc;
+      }
+      const int grid = static_cast<int>(units < NumSms() ? units : NumSms());
+      if (const int rc = LaunchBatch(a_dtype, problems[order[cls][first]].b_zeros != nullptr, tok, table, grid,
+                                     static_cast<cudaStream_t>(stream))) {
+        return rc;
+      }
+    }
+  }
+  return IOB_OK;
 }
 
 extern "C" size_t infiniops_b200_moe_wna16_marlin_gemm_scratch_bytes(int64_t size_m, int64_t top_k, int64_t size_n,
