@@ -344,6 +344,81 @@ int infiniops_b200_moe_wna16_marlin_gemm(
     int64_t size_m, int64_t size_n, int64_t size_k, int64_t num_groups, int64_t num_experts,
     int64_t sorted_size, void* out, void* scratch, size_t scratch_bytes, void* stream);
 
+/* Where the routed GEMM stores its result rows when they do not stay on this GPU (the combine
+ * step of expert parallelism fused into the GEMM's epilogue).  `row_dest` holds, per output row
+ * (a flat routing id of this call), two int32: the GPU the row belongs to and its row in that GPU's
+ * destination matrix [rows, size_n]; `dest_base[g]` is that matrix of GPU g as mapped into this
+ * process (this GPU's own included), `n_dest` their number (at most 8).  `signal` (or NULL) is
+ * raised when the launch has finished.  No counterpart in the reference. */
+typedef struct {
+  const int32_t* row_dest;
+  void* dest_base[IOB_MAX_PEERS + 1];
+  int n_dest;
+  const iob_peer_signal* signal;
+} iob_routed_scatter;
+
+/* infiniops_b200_moe_wna16_marlin_gemm with an optional scatter of the result rows (NULL = rows go
+ * to `out` as usual; with a scatter `out` is only validated).  No counterpart in the reference. */
+int infiniops_b200_moe_wna16_marlin_gemm_scattered(
+    const void* a, int a_dtype, const int32_t* b_q_weight, const void* b_bias,
+    const void* b_scales, const int32_t* b_zeros, const int32_t* sorted_token_ids,
+    const int32_t* expert_ids, const int32_t* num_tokens_past_padded, const float* topk_weights,
+    int64_t moe_block_size, int64_t top_k, int mul_topk_weights, int64_t b_type_id,
+    int64_t size_m, int64_t size_n, int64_t size_k, int64_t num_groups, int64_t num_experts,
+    int64_t sorted_size, void* out, const iob_routed_scatter* scatter, void* scratch,
+    size_t scratch_bytes, void* stream);
+
+/* ---- expert-parallel MoE layer (one process per GPU, NVLink) ------------------------------------ */
+
+/* Geometry and peer mappings of an expert-parallel group.  Rank r owns experts
+ * [r * experts_per_rank, (r + 1) * experts_per_rank).  Every rank owns an arena of
+ * infiniops_b200_ep_arena_bytes() that all ranks map (`arena[g]` = rank g's arena as seen from this
+ * process) and a flag array of `world` ints that all ranks map (`flags[g]`); `ctrl` is a zeroed
+ * local int[8] (block counter, epoch, wait epoch, wait status[2]).  `capacity` is the largest number
+ * of routes (tokens x top_k) any one rank dispatches per layer call. */
+typedef struct {
+  int world, rank;
+  int64_t top_k, hidden, inter, experts_per_rank, capacity, moe_block_size;
+  int a_dtype;
+  int64_t b_type_id;
+  void* arena[IOB_MAX_PEERS + 1];
+  int* flags[IOB_MAX_PEERS + 1];
+  int* ctrl;
+} iob_ep_context;
+
+/* This rank's experts, Marlin layout: w13 [E, H/16, 2*2I], w2 [E, I/16, 2H], scales [E, G, N],
+ * zero points [E, G, N/8] or NULL. */
+typedef struct {
+  const int32_t* w13;
+  const void* s13;
+  const int32_t* z13;
+  int64_t groups13;
+  const int32_t* w2;
+  const void* s2;
+  const int32_t* z2;
+  int64_t groups2;
+} iob_expert_weights;
+
+size_t infiniops_b200_ep_arena_bytes(int world, int64_t capacity, int64_t hidden);
+size_t infiniops_b200_ep_workspace_bytes(const iob_ep_context* ctx);
+
+/* One expert-parallel MoE layer, entirely on the device and on `stream` (no host read-back, no
+ * collective library): the routes of this rank's `tokens` tokens are placed per owner of their
+ * expert (stable order), the token rows are stored straight into the owners' arenas with each
+ * route's expert, weight and origin, completion flags are exchanged and awaited (bounded wait), the
+ * received rows run through moe_align_block_size, the w13 GEMM, silu_and_mul and the w2 GEMM
+ * (x routing weight) whose epilogue stores every result row back into the arena of the rank the
+ * token came from, flags again, and moe_sum adds each token's top_k rows into `out` [tokens, hidden].
+ * x [tokens, hidden], topk_ids int32 [tokens, top_k] (global expert ids), topk_weights float
+ * [tokens, top_k].  Every rank of the group must make the same sequence of calls.
+ * Stands for the chain topk -> moe_align_block_size ->
+ * moe_wna16_marlin_gemm -> silu_and_mul -> moe_wna16_marlin_gemm -> moe_sum for a sharded layer;
+ * the reference has no communication layer of its own. */
+int infiniops_b200_ep_moe_layer(const iob_ep_context* ctx, const iob_expert_weights* weights,
+                                const void* x, const int32_t* topk_ids, const float* topk_weights,
+                                int64_t tokens, void* out, void* workspace, size_t workspace_bytes,
+                                void* stream);
+
 #ifdef __cplusplus
 }
 #endif

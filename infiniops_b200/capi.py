@@ -71,7 +71,33 @@ class PeerSignal(ctypes.Structure):
                 ("flag_slot", _int)]
 
 
+class RoutedScatter(ctypes.Structure):
+    """`iob_routed_scatter`."""
+    _fields_ = [("row_dest", _vp), ("dest_base", _vp * (MAX_PEERS + 1)), ("n_dest", _int),
+                ("signal", ctypes.POINTER(PeerSignal))]
+
+
+class EpContext(ctypes.Structure):
+    """`iob_ep_context`."""
+    _fields_ = [("world", _int), ("rank", _int), ("top_k", _i64), ("hidden", _i64), ("inter", _i64),
+                ("experts_per_rank", _i64), ("capacity", _i64), ("moe_block_size", _i64), ("a_dtype", _int),
+                ("b_type_id", _i64), ("arena", _vp * (MAX_PEERS + 1)), ("flags", _vp * (MAX_PEERS + 1)), ("ctrl", _vp)]
+
+
+class ExpertWeightsC(ctypes.Structure):
+    """`iob_expert_weights`."""
+    _fields_ = [("w13", _vp), ("s13", _vp), ("z13", _vp), ("groups13", _i64), ("w2", _vp), ("s2", _vp), ("z2", _vp),
+                ("groups2", _i64)]
+
+
 PROTOTYPES.update({
+    "infiniops_b200_moe_wna16_marlin_gemm_scattered": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
+                                                              _i64, _int, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _vp,
+                                                              ctypes.POINTER(RoutedScatter), _vp, _sz, _vp]),
+    "infiniops_b200_ep_arena_bytes": (_sz, [_int, _i64, _i64]),
+    "infiniops_b200_ep_workspace_bytes": (_sz, [ctypes.POINTER(EpContext)]),
+    "infiniops_b200_ep_moe_layer": (_int, [ctypes.POINTER(EpContext), ctypes.POINTER(ExpertWeightsC), _vp, _vp, _vp,
+                                           _i64, _vp, _vp, _sz, _vp]),
     "infiniops_b200_marlin_gemm_placed": (_int, [ctypes.POINTER(GemmProblem), _int, _i64, ctypes.POINTER(PeerSignal),
                                                  _vp, _sz, _vp]),
     "infiniops_b200_marlin_gemm_batch_scratch_bytes": (_sz, []),

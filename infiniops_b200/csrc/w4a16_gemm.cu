@@ -118,6 +118,8 @@ struct GemmParams {
   int* peer_flags[kMaxPeers];
   int flag_slot, n_flag_peers;
   // routed form only
+  const int2* row_dest;             // null, or per output row: (GPU, row there) the result row is stored to
+  void* dest_base[kMaxPeers + 1];   // with `row_dest`: the destination matrix of every GPU (own included)
   const int32_t* sorted_ids;
   const int32_t* expert_ids;
   const int32_t* num_post_pad;
@@ -1284,7 +1286,14 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
           const int id = cur->p.sorted_ids[row0 + j];
           if (id < cur->p.out_rows) {
             if (cur->p.mul_weights) v *= cur->p.topk_weights[id];
-            out[static_cast<size_t>(id) * cur->p.n + n] = FromFloat<T>(v);
+            if (cur->p.row_dest != nullptr) {
+              // expert-parallel combine: the row goes back to the GPU the token came from, to the
+              // row its route has there (a plain store into that GPU's mapped buffer)
+              const int2 dest = cur->p.row_dest[id];
+              static_cast<T*>(cur->p.dest_base[dest.x])[static_cast<size_t>(dest.y) * cur->p.n + n] = FromFloat<T>(v);
+            } else {
+              out[static_cast<size_t>(id) * cur->p.n + n] = FromFloat<T>(v);
+            }
           }
         } else {
           const size_t at = static_cast<size_t>(row0 + j) * cur->p.out_ld + cur->p.out_col0 + n;
@@ -1548,7 +1557,7 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
   }
 
   // ---- teardown -----------------------------------------------------------------------------
-  if constexpr (!kMoe) {
+  {
     // Completion signal to the other GPUs (launches that were given one).  Every block makes its
     // own stores visible system-wide and counts itself done; the block that comes last bumps the
     // epoch and publishes it in every peer's flag word.  Nobody waits here.
@@ -2219,6 +2228,19 @@ extern "C" int infiniops_b200_moe_wna16_marlin_gemm(
     const int32_t* num_tokens_past_padded, const float* topk_weights, int64_t moe_block_size, int64_t top_k,
     int mul_topk_weights, int64_t b_type_id, int64_t size_m, int64_t size_n, int64_t size_k, int64_t num_groups,
     int64_t num_experts, int64_t sorted_size, void* out, void* scratch, size_t scratch_bytes, void* stream) {
+  return infiniops_b200_moe_wna16_marlin_gemm_scattered(
+      a, a_dtype, b_q_weight, b_bias, b_scales, b_zeros, sorted_token_ids, expert_ids, num_tokens_past_padded,
+      topk_weights, moe_block_size, top_k, mul_topk_weights, b_type_id, size_m, size_n, size_k, num_groups, num_experts,
+      sorted_size, out, nullptr, scratch, scratch_bytes, stream);
+}
+
+extern "C" int infiniops_b200_moe_wna16_marlin_gemm_scattered(
+    const void* a, int a_dtype, const int32_t* b_q_weight, const void* b_bias, const void* b_scales,
+    const int32_t* b_zeros, const int32_t* sorted_token_ids, const int32_t* expert_ids,
+    const int32_t* num_tokens_past_padded, const float* topk_weights, int64_t moe_block_size, int64_t top_k,
+    int mul_topk_weights, int64_t b_type_id, int64_t size_m, int64_t size_n, int64_t size_k, int64_t num_groups,
+    int64_t num_experts, int64_t sorted_size, void* out, const iob_routed_scatter* scatter, void* scratch,
+    size_t scratch_bytes, void* stream) {
   using namespace iob;
   const char* op = "moe_wna16_marlin_gemm";
   if (const int rc = CheckProblem(op, a, a_dtype, b_q_weight, b_scales, b_zeros, b_type_id, size_m, size_n, size_k,
@@ -2283,6 +2305,16 @@ extern "C" int infiniops_b200_moe_wna16_marlin_gemm(
   p.block_size = static_cast<int>(moe_block_size);
   p.mul_weights = mul_topk_weights;
   p.out_rows = out_rows;
+  if (scatter != nullptr) {
+    IOB_REQUIRE(scatter->row_dest != nullptr && scatter->n_dest > 0 && scatter->n_dest <= kMaxPeers + 1,
+                "%s: incomplete scatter description", op);
+    p.row_dest = reinterpret_cast<const int2*>(scatter->row_dest);
+    for (int r = 0; r < scatter->n_dest; ++r) {
+      IOB_REQUIRE(scatter->dest_base[r] != nullptr, "%s: null scatter destination", op);
+      p.dest_base[r] = scatter->dest_base[r];
+    }
+    if (const int rc = SetSignal(op, scatter->signal, p)) return rc;
+  }
   return Dispatch<true>(a_dtype, b_zeros != nullptr, tok, map, w_map, /*c_map (unused: rows are scattered)=*/w_map, p, NumSms(), s);
 }
 

@@ -143,3 +143,76 @@ def expert_parallel_layer(x, topk_ids, topk_weights, num_experts, top_k, local_e
     y = local_experts_forward(rows, plan.local_expert, plan.weights)
     routed = combine(y, plan, group)
     return moe_sum(routed.view(x.shape[0], top_k, x.shape[1]))
+
+
+# ---- MoE: expert-parallel on the device (peer-mapped memory, no host read-back) ---------------------
+class DeviceExpertParallel:
+    """One expert-parallel MoE layer per call through `infiniops_b200_ep_moe_layer`: dispatch, the
+    routed GEMM pair and combine run on the device over peer-mapped arenas, the flags between the
+    ranks are exchanged by the kernels themselves, and nothing is read back by the host -- so a call
+    can be recorded into a CUDA graph.  This class only sets the buffers up (`peer.PeerGroup` moves
+    the memory handles between the processes) and keeps them alive.
+
+    With a world of 1 no process group is needed (`group=None`, `world=1`): the same kernels run
+    with this rank as the only owner."""
+
+    def __init__(self, weights, top_k: int, max_tokens: int, device, block: int = 64, group=None, world=None):
+        from . import capi, peer
+
+        self.capi, self.weights, self.device = capi, weights, device
+        lib = capi.lib()
+        if world == 1:
+            self.peers, self.world, self.rank = None, 1, 0
+        else:
+            self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        capacity = max_tokens * top_k
+        arena_bytes = lib.infiniops_b200_ep_arena_bytes(self.world, capacity, weights.hidden)
+        ctx = capi.EpContext()
+        ctx.world, ctx.rank, ctx.top_k, ctx.hidden, ctx.inter = self.world, self.rank, top_k, weights.hidden, weights.inter
+        ctx.experts_per_rank, ctx.capacity, ctx.moe_block_size = weights.num_experts, capacity, block
+        ctx.a_dtype, ctx.b_type_id = capi._DTYPE[weights.s13.dtype], weights.qtype
+        if self.world == 1:
+            self._arena = torch.zeros(arena_bytes, dtype=torch.uint8, device=device)
+            self._flags = torch.zeros(64, dtype=torch.int32, device=device)
+            self._ctrl = torch.zeros(8, dtype=torch.int32, device=device)
+            ctx.arena[0], ctx.flags[0], ctx.ctrl = self._arena.data_ptr(), self._flags.data_ptr(), self._ctrl.data_ptr()
+        else:
+            self.peers = peer.PeerGroup(arena_bytes, device, group)
+            off = self.peers.carve(arena_bytes)
+            for r in range(self.world):
+                ctx.arena[r] = self.peers.address(r, off)
+                ctx.flags[r] = self.peers.peer_base[r]
+            self._ctrl = self.peers.ctrl
+            ctx.ctrl = self._ctrl.data_ptr()
+        self.ctx = ctx
+        w = weights
+        cw = capi.ExpertWeightsC()
+        cw.w13, cw.s13, cw.groups13 = w.w13.data_ptr(), w.s13.data_ptr(), w.s13.shape[1]
+        cw.w2, cw.s2, cw.groups2 = w.w2.data_ptr(), w.s2.data_ptr(), w.s2.shape[1]
+        cw.z13 = None if w.z13 is None else w.z13.data_ptr()
+        cw.z2 = None if w.z2 is None else w.z2.data_ptr()
+        self.cw = cw
+        need = lib.infiniops_b200_ep_workspace_bytes(ctx)
+        if need == 0:
+            raise capi.Error(lib.infiniops_b200_last_error().decode())
+        self.workspace = torch.zeros(need, dtype=torch.uint8, device=device)
+        self.max_tokens = max_tokens
+
+    def __call__(self, x, topk_ids, topk_weights, out=None, stream=None):
+        capi = self.capi
+        if out is None:
+            out = torch.empty_like(x)
+        capi._check(capi.lib().infiniops_b200_ep_moe_layer(
+            self.ctx, self.cw, x.data_ptr(), topk_ids.data_ptr(), topk_weights.data_ptr(), x.shape[0], out.data_ptr(),
+            self.workspace.data_ptr(), self.workspace.numel(), capi._stream(stream)))
+        return out
+
+    def status(self) -> tuple[int, int, int]:
+        """(GEMM scratch status, wait status, slot): all zero unless a bounded device wait ran out."""
+        s = self._ctrl[3:5].tolist()
+        gemm = 0
+        return gemm, int(s[0]), int(s[1])
+
+    def close(self):
+        if self.peers is not None:
+            self.peers.close()

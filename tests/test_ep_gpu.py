@@ -1,5 +1,11 @@
-"""GPU, two ranks over NCCL: expert-parallel MoE layer and column-parallel linear against the
-single-GPU result.  Needs two GPUs; skipped otherwise."""
+"""GPU: the expert-parallel MoE layer and the column-parallel linear against the single-GPU result.
+
+* one GPU: the device-side expert-parallel layer with a world of one (same kernels: placement,
+  dispatch into the arena, unpack, routed GEMM pair with the scattered epilogue, sum) against the
+  oracle chain;
+* two ranks (needs two GPUs, skipped otherwise): the same layer across two GPUs over peer-mapped
+  arenas, the NCCL all-to-all formulation of it, the column-parallel linear whose epilogue stores
+  its slice into both ranks' result matrices, and the NCCL all-gather formulation of that."""
 
 import os
 import socket
@@ -65,6 +71,17 @@ def _worker(rank, world, port):
         err = float((got.float() - expect[t0:t1].float()).abs().max() / expect.float().abs().max())
         assert err <= 1e-2, err
 
+        # the same layer on the device-side path: peer-mapped arenas, flags, no host read-back; twice,
+        # so that the second call meets the buffers and epochs the first one left
+        ep = parallel.DeviceExpertParallel(local.w, top_k, tokens // world + 8, dev, block)
+        for _ in range(2):
+            got2 = ep(x[t0:t1].contiguous(), ids[t0:t1].contiguous(), weights[t0:t1].contiguous())
+            torch.cuda.synchronize()
+            assert ep.status() == (0, 0, 0), ep.status()
+            err = float((got2.float() - expect[t0:t1].float()).abs().max() / expect.float().abs().max())
+            assert err <= 1e-2, err
+        ep.close()
+
         # column-parallel dense linear
         k, n, m = 1024, 1024, 16
         awq = torch.randint(-2**31, 2**31 - 1, (k, n // 8), dtype=torch.int32, generator=gen).to(dev)
@@ -85,6 +102,28 @@ def _worker(rank, world, port):
         torch.cuda.synchronize()
         assert torch.equal(sharded, whole)
         assert capi.scratch_status(capi.scratch(dev, 0)) == 0
+
+        # the same shard, its slice stored by the GEMM epilogue into both ranks' [m, n] matrices
+        from infiniops_b200 import peer
+
+        group = peer.PeerGroup(m * n * 2, dev)
+        off = group.carve(m * n * 2)
+        full_out = group.local(off, (m, n), torch.bfloat16)
+        marlin = torch.empty((k // 16, 2 * (n // world)), dtype=torch.int32, device=dev)
+        capi.awq_marlin_repack(w, k, n // world, 4, False, marlin)
+        g = capi.gemm_problem(a, marlin, None, s, z, full_out, m, n // world, k, out_ld=n, out_col0=rank * (n // world),
+                              peer_out=[group.address(r, off) for r in group.others()])
+        scratch = torch.zeros(capi.lib().infiniops_b200_marlin_gemm_batch_scratch_bytes(), dtype=torch.uint8, device=dev)
+        for _ in range(2):
+            capi.marlin_gemm_batch(capi.problem_array([g]), torch.bfloat16, capi.QTYPE_UINT4, scratch,
+                                   signal=group.signal())
+            group.wait()
+            torch.cuda.synchronize()
+            assert group.wait_status() == (0, 0) and capi.scratch_status(scratch) == 0
+            # each rank's slice equals what the all-gather formulation delivered
+            assert torch.equal(full_out, sharded)
+            dist.barrier()
+        group.close()
     finally:
         dist.destroy_process_group()
 
@@ -95,3 +134,44 @@ def test_expert_parallel_and_column_parallel_on_two_gpus():
     import torch.multiprocessing as mp
 
     mp.spawn(_worker, args=(2, _free_port()), nprocs=2, join=True)
+
+
+def test_device_expert_parallel_world_of_one_against_oracle():
+    """The device-side expert-parallel layer with this GPU as the only rank, against the oracle chain
+    router -> sort -> w13 -> silu_and_mul -> w2 (x weight) -> sum.  One token carries an expert id
+    outside the table: its route must contribute nothing."""
+    import numpy as np
+
+    from infiniops_b200 import capi, moe_layer, parallel
+    from oracle import moe as omoe
+    from oracle import quant as oq
+
+    experts, top_k, hidden, inter, block, tokens = 8, 2, 256, 128, 16, 50
+    dev = torch.device("cuda", 0)
+    gen = torch.Generator().manual_seed(11)
+
+    def packed(k, n):
+        q = torch.randint(0, 16, (experts, k, n), generator=gen, dtype=torch.int32).numpy().astype(np.uint8)
+        s = (torch.randn((experts, k // 128, n), generator=gen).abs() * 0.01 + 1e-3).bfloat16()
+        w = torch.stack([torch.from_numpy(oq.marlin_pack(q[e], 4, False)) for e in range(experts)]).to(dev)
+        return q, s, w
+
+    q13, s13, w13 = packed(hidden, 2 * inter)
+    q2, s2, w2 = packed(inter, hidden)
+    x = torch.randn((tokens, hidden), generator=gen).bfloat16()
+    logits = torch.randn((tokens, experts), generator=gen)
+    rw, rids, _ = omoe.topk_softmax(logits, None, None, top_k, True)
+    ids = rids.to(torch.int32)
+    ids[7, 1] = experts + 3   # a route to nowhere
+    weights = moe_layer.ExpertWeights(w13, s13.to(dev), None, w2, s2.to(dev), None, hidden, inter)
+    ep = parallel.DeviceExpertParallel(weights, top_k, tokens, dev, block, world=1)
+    for _ in range(2):
+        got = ep(x.to(dev), ids.to(dev), rw.to(dev))
+        torch.cuda.synchronize()
+    rs, re, rn = omoe.moe_align_block_size(ids, None, experts, block)
+    g = omoe.moe_w4a16_gemm(x, q13, s13, None, rs, re, rn, None, block, top_k, False).bfloat16()
+    h = omoe.silu_and_mul(g)
+    y = omoe.moe_w4a16_gemm(h, q2, s2, None, rs, re, rn, rw.flatten(), block, 1, True).bfloat16()
+    ref = omoe.moe_sum(y.view(tokens, top_k, hidden))
+    err = float((got.float().cpu() - ref.float()).abs().max() / ref.float().abs().max())
+    assert err <= 3e-2, err
