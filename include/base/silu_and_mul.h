@@ -27,8 +27,20 @@ class SiluAndMul : public Operator<SiluAndMul> {
 
   virtual void operator()(const Tensor input, Tensor out) const = 0;
 
-  // Output geometry for an input (the reference pairs this with an owning tensor type's `Empty`;
-  // views do not allocate, so here it yields the shape only).
+  // An empty output for `input`, made by the caller's own tensor type: anything with `Shape`,
+  // `shape()`, `dtype()`, `device()` and a static `Empty(shape, dtype, device)` (same contract as
+  // src/base/silu_and_mul.h:38-46 of the reference; the view type `Tensor` itself owns no memory
+  // and has no `Empty`).
+  template <typename TensorLike>
+  static auto MakeReturnValue(const TensorLike& input) {
+    typename TensorLike::Shape out_shape{input.shape()};
+    INFINI_OPS_CHECK(!out_shape.empty() && out_shape.back() % 2 == 0,
+                     "`SiluAndMul` requires an even input last dimension");
+    out_shape.back() /= 2;
+    return TensorLike::Empty(out_shape, input.dtype(), input.device());
+  }
+
+  // Output geometry alone, for callers that hold plain views.
   static Tensor::Shape OutputShape(const Tensor& input) {
     Tensor::Shape shape{input.shape()};
     INFINI_OPS_CHECK(!shape.empty() && shape.back() % 2 == 0, "`SiluAndMul` requires an even input last dimension");

@@ -3,6 +3,7 @@
 #define INFINI_OPS_H_
 
 #include "ops/gemm.h"
+#include "ops/moe_siblings.h"
 #include "ops/moe_small.h"
 #include "ops/repack.h"
 #include "ops/router.h"

@@ -106,6 +106,18 @@ int infiniops_b200_topk_softmax(const void* gating_output, int gating_dtype, con
                                 int64_t num_tokens, int64_t num_experts, int64_t topk,
                                 void* stream);
 
+/* Sigmoid router: score = 1 / (1 + exp(-x)) (non-finite -> 0), top-k on score + correction bias,
+ * ties to the smaller index; weights are the un-biased scores, optionally renormalised (divided by
+ * their sum when it is positive), then multiplied by `routed_scaling_factor`; rows flagged in
+ * `is_padding` get index -1; token_expert_indices[t, r] = r * T + t.  Types as for topk_softmax.
+ * Replaces: TopkSigmoid::operator(), src/base/topk_sigmoid.h:41-47 and the kernel
+ * src/native/cuda/nvidia/ops/topk_sigmoid/kernel.cuh:60-136. */
+int infiniops_b200_topk_sigmoid(const void* gating_output, int gating_dtype,
+                                const float* e_score_correction_bias, const uint8_t* is_padding,
+                                int renormalize, double routed_scaling_factor, float* topk_weights,
+                                void* topk_ids, int index_dtype, int32_t* token_expert_indices,
+                                int64_t num_tokens, int64_t num_experts, int64_t topk, void* stream);
+
 /* Group-limited top-k (DeepSeek style): score = x or sigmoid(x) rounded to the score type,
  * selection score = score + bias rounded to the score type, group score = sum of the two
  * largest selection scores of the group, `topk_group` best groups kept, `topk` best
@@ -142,6 +154,22 @@ int infiniops_b200_moe_align_block_size(const int32_t* topk_ids, const int32_t* 
                                         int32_t* experts_ids, int64_t experts_size,
                                         int32_t* num_tokens_post_pad, void* scratch,
                                         size_t scratch_bytes, void* stream);
+
+/* Bookkeeping for a grouped GEMM over routed tokens: expert_offsets [E + 1] (exclusive prefix of the
+ * per-expert route counts), problem_sizes1 / problem_sizes2 [E, 3] ((count, 2n or n, k) and
+ * (count, k, n); with at most 64 routes and no `blockscale_offsets` the first two entries are
+ * swapped), input_permutation [numel] (source token of every grouped row, -1 beyond the routed
+ * rows), output_permutation [numel] (grouped row of every route; the total for id -1, -1 for any
+ * other id outside [0, E)), blockscale_offsets [E + 1] or NULL (prefix of the counts rounded up
+ * to 128).  Routes of one expert are placed by ascending route index.  E < 1024.
+ * Replaces: GetCutlassMoeMmData::operator(), src/base/get_cutlass_moe_mm_data.h:69-75 and the
+ * kernel src/native/cuda/nvidia/ops/get_cutlass_moe_mm_data/kernel.cuh:15-100. */
+int infiniops_b200_get_cutlass_moe_mm_data(const int32_t* topk_ids, int64_t numel, int64_t topk,
+                                           int64_t num_experts, int64_t n, int64_t k, int is_gated,
+                                           int32_t* expert_offsets, int32_t* problem_sizes1,
+                                           int32_t* problem_sizes2, int32_t* input_permutation,
+                                           int32_t* output_permutation, int32_t* blockscale_offsets,
+                                           void* stream);
 
 /* ---- activation and combine ------------------------------------------------------------------ */
 
@@ -343,6 +371,23 @@ int infiniops_b200_moe_wna16_marlin_gemm(
     int64_t moe_block_size, int64_t top_k, int mul_topk_weights, int64_t b_type_id,
     int64_t size_m, int64_t size_n, int64_t size_k, int64_t num_groups, int64_t num_experts,
     int64_t sorted_size, void* out, void* scratch, size_t scratch_bytes, void* stream);
+
+/* Routed weight-only GEMM on the plain layout: b_qweight uint8 [E, N, K / (8 / bit)] (4-bit: low
+ * nibble = even k), b_scales [E, N, G] in the input type, b_qzeros uint8 [E, N / (8 / bit), G]
+ * (4-bit: low nibble = even n) or NULL (zero point 2^(bit-1)), topk_weights float [M * top_k] or NULL,
+ * output [M * top_k, N]: cleared, then row r of every routing block below num_tokens_post_pad whose
+ * expert is not -1 gets input[r / top_k] * dequant(W[expert])^T (x topk_weights[r]); a route id of
+ * M * top_k or more ends its block.  bit 4 or 8, block_size_m <= 64, fp32 accumulation.
+ * Replaces: MoeWna16Gemm::operator(), src/base/moe_wna16_gemm.h:47-54 and the kernel
+ * src/native/cuda/nvidia/ops/moe_wna16_gemm/kernel.cuh:173-378. */
+int infiniops_b200_moe_wna16_gemm(const void* input, int dtype, const uint8_t* b_qweight,
+                                  const void* b_scales, const uint8_t* b_qzeros,
+                                  const float* topk_weights, const int32_t* sorted_token_ids,
+                                  const int32_t* expert_ids, const int32_t* num_tokens_post_pad,
+                                  int64_t sorted_size, int64_t expert_ids_size, int64_t top_k,
+                                  int64_t block_size_m, int64_t bit, int64_t size_m, int64_t size_n,
+                                  int64_t size_k, int64_t num_groups, int64_t num_experts,
+                                  void* output, void* stream);
 
 /* Where the routed GEMM stores its result rows when they do not stay on this GPU (the combine
  * step of expert parallelism fused into the GEMM's epilogue).  `row_dest` holds, per output row

@@ -8,7 +8,7 @@ Produces, next to this file:
 * ``lib/libinfiniops_b200.so`` -- the CUDA kernels and their C ABI (``include/infiniops_b200.h``),
   compiled by nvcc for sm_100a only;
 * ``../infini/ops*.so``         -- the pybind11 module ``infini.ops`` (the C++ ``infini::ops``
-  operator layer on top of the C ABI), compiled by g++.
+  operator layer of ``include/`` -- ``#include <infini/ops.h>`` -- on top of the C ABI), compiled by g++.
 """
 
 from __future__ import annotations

@@ -94,6 +94,11 @@ PROTOTYPES.update({
     "infiniops_b200_moe_wna16_marlin_gemm_scattered": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
                                                               _i64, _int, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _vp,
                                                               ctypes.POINTER(RoutedScatter), _vp, _sz, _vp]),
+    "infiniops_b200_topk_sigmoid": (_int, [_vp, _int, _vp, _vp, _int, _dbl, _vp, _vp, _int, _vp, _i64, _i64, _i64, _vp]),
+    "infiniops_b200_get_cutlass_moe_mm_data": (_int, [_vp, _i64, _i64, _i64, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp,
+                                                      _vp, _vp]),
+    "infiniops_b200_moe_wna16_gemm": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64,
+                                             _i64, _i64, _i64, _i64, _i64, _vp, _vp]),
     "infiniops_b200_ep_arena_bytes": (_sz, [_int, _i64, _i64]),
     "infiniops_b200_ep_workspace_bytes": (_sz, [ctypes.POINTER(EpContext)]),
     "infiniops_b200_ep_moe_layer": (_int, [ctypes.POINTER(EpContext), ctypes.POINTER(ExpertWeightsC), _vp, _vp, _vp,

@@ -11,6 +11,7 @@
 #include "binding_utils.h"
 
 void RegisterMoeBindings(pybind11::module_& m);
+void RegisterSiblingBindings(pybind11::module_& m);
 
 PYBIND11_MODULE(ops, m) {
   m.doc() = "B200 (sm_100a) W4A16 linear and MoE operators behind the infini.ops interface";
@@ -134,4 +135,5 @@ PYBIND11_MODULE(ops, m) {
 
   // the remaining operators are registered in bindings_moe.cc
   RegisterMoeBindings(m);
+  RegisterSiblingBindings(m);
 }

@@ -195,6 +195,84 @@ AlignScatterKernel(const int32_t* __restrict__ topk_ids, const int32_t* __restri
   }
 }
 
+// get_cutlass_moe_mm_data: per-expert row counts and offsets, the two grouped-GEMM problem-size
+// tables, and the permutation that groups the routes by expert.  One block; the routes are walked
+// twice in chunks of 1024 (count, then place) with the same stable ranking as the sort above, so the
+// placement inside an expert is by ascending route index and does not vary from run to run (the
+// reference places with atomics, in any order).
+__global__ void __launch_bounds__(kChunk)
+MmDataKernel(const int32_t* __restrict__ topk_ids, int32_t* __restrict__ expert_offsets,
+             int32_t* __restrict__ problem_sizes1, int32_t* __restrict__ problem_sizes2,
+             int32_t* __restrict__ input_permutation, int32_t* __restrict__ output_permutation,
+             int32_t* __restrict__ blockscale_offsets, int numel, int topk, int num_experts, int n, int k,
+             bool is_gated) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const Smem s = CarveSmem(smem_raw, num_experts);
+  const int tid = threadIdx.x;
+  const bool swap_ab = blockscale_offsets == nullptr && numel <= 64;
+  const int count_index = swap_ab ? 1 : 0;
+  const int n1 = is_gated ? 2 * n : n;
+  for (int e = tid; e < num_experts; e += kChunk) s.expert_total[e] = 0;
+  for (int i = tid; i < numel; i += kChunk) input_permutation[i] = -1;
+  __syncthreads();
+  auto expert_of = [&](int i) {
+    if (i >= numel) return -1;
+    const int e = topk_ids[i];
+    return e >= 0 && e < num_experts ? e : -1;
+  };
+  for (int start = 0; start < numel; start += kChunk) {
+    ChunkRank(s, expert_of(start + tid), num_experts, [&](int e, int total) { s.expert_total[e] += total; });
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int offset = 0, scale_offset = 0;
+    expert_offsets[0] = 0;
+    if (blockscale_offsets != nullptr) blockscale_offsets[0] = 0;
+    for (int e = 0; e < num_experts; ++e) {
+      const int count = s.expert_total[e];
+      s.expert_base[e] = offset;
+      offset += count;
+      expert_offsets[e + 1] = offset;
+      if (blockscale_offsets != nullptr) {
+        scale_offset += (count + 127) / 128 * 128;
+        blockscale_offsets[e + 1] = scale_offset;
+      }
+    }
+    s.warp_sums[0] = offset;
+  }
+  __syncthreads();
+  const int valid_total = s.warp_sums[0];
+  for (int e = tid; e < num_experts; e += kChunk) {
+    const int count = s.expert_total[e];
+    int* p1 = problem_sizes1 + 3 * e;
+    int* p2 = problem_sizes2 + 3 * e;
+    p1[0] = swap_ab ? n1 : count;
+    p1[1] = swap_ab ? count : n1;
+    p1[2] = k;
+    p2[0] = swap_ab ? k : count;
+    p2[1] = swap_ab ? count : k;
+    p2[2] = n;
+    (void)count_index;
+  }
+  __syncthreads();
+  for (int start = 0; start < numel; start += kChunk) {
+    const int i = start + tid;
+    const int expert = expert_of(i);
+    const int rank = ChunkRank(s, expert, num_experts, [&](int e, int total) { s.expert_total[e] = total; });
+    if (i < numel) {
+      if (expert >= 0) {
+        const int destination = s.expert_base[expert] + rank;
+        input_permutation[destination] = i / topk;
+        output_permutation[i] = destination;
+      } else {
+        output_permutation[i] = topk_ids[i] == -1 ? valid_total : -1;
+      }
+    }
+    __syncthreads();
+    for (int e = tid; e < num_experts; e += kChunk) s.expert_base[e] += s.expert_total[e];
+  }
+}
+
 template <typename Kernel>
 int AllowSmem(Kernel kernel, size_t bytes) {
   if (bytes > 48 * 1024) {
@@ -259,4 +337,27 @@ extern "C" int infiniops_b200_moe_align_block_size(const int32_t* topk_ids, cons
   if (const int rc = CheckLaunch("moe_align_block_size count launch")) return rc;
   AlignScatterKernel<<<chunks, kChunk, smem, s>>>(topk_ids, expert_map, n, e, sorted_token_ids, scratch_i32);
   return CheckLaunch("moe_align_block_size scatter launch");
+}
+
+extern "C" int infiniops_b200_get_cutlass_moe_mm_data(const int32_t* topk_ids, int64_t numel, int64_t topk,
+                                                      int64_t num_experts, int64_t n, int64_t k, int is_gated,
+                                                      int32_t* expert_offsets, int32_t* problem_sizes1,
+                                                      int32_t* problem_sizes2, int32_t* input_permutation,
+                                                      int32_t* output_permutation, int32_t* blockscale_offsets,
+                                                      void* stream) {
+  using namespace iob;
+  const char* op = "get_cutlass_moe_mm_data";
+  IOB_REQUIRE(numel > 0 && topk > 0 && numel <= INT32_MAX, "%s: requires non-empty int32-addressable `topk_ids`", op);
+  IOB_REQUIRE(num_experts > 0 && n > 0 && k > 0 && k <= INT32_MAX && n <= (is_gated ? INT32_MAX / 2 : INT32_MAX),
+              "%s: requires positive int32 GEMM dimensions", op);
+  if (num_experts >= 1024) return Fail(IOB_UNSUPPORTED, "%s: more than 1023 experts are not implemented", op);
+  IOB_REQUIRE(topk_ids && expert_offsets && problem_sizes1 && problem_sizes2 && input_permutation && output_permutation,
+              "%s: null tensor pointer", op);
+  const size_t smem = SmemBytes(num_experts);
+  if (const int rc = AllowSmem(MmDataKernel, smem)) return rc;
+  MmDataKernel<<<1, kChunk, smem, static_cast<cudaStream_t>(stream)>>>(
+      topk_ids, expert_offsets, problem_sizes1, problem_sizes2, input_permutation, output_permutation,
+      blockscale_offsets, static_cast<int>(numel), static_cast<int>(topk), static_cast<int>(num_experts),
+      static_cast<int>(n), static_cast<int>(k), is_gated != 0);
+  return CheckLaunch("get_cutlass_moe_mm_data launch");
 }

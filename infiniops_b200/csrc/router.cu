@@ -43,14 +43,18 @@ template <typename Index>
 __device__ __forceinline__ void StoreIndex(Index* p, int v) { *p = static_cast<Index>(v); }
 
 // ------------------------------------------------------------------------------------------
-// topk_softmax
+// topk_softmax and topk_sigmoid
 // ------------------------------------------------------------------------------------------
-template <typename In, typename Index>
+// kSigmoid: the per-expert score is sigmoid(x) = 1 / (1 + exp(-x)) instead of the softmax over the
+// row, the selection adds the correction bias in the same way, and the selected weights are
+// multiplied by `scaling` (after the optional renormalisation).
+template <typename In, typename Index, bool kSigmoid = false>
 __global__ void TopkSoftmaxKernel(const In* __restrict__ gating, const float* __restrict__ bias,
                                   const uint8_t* __restrict__ is_padding,
                                   float* __restrict__ topk_weights, Index* __restrict__ topk_indices,
                                   int32_t* __restrict__ token_expert_indices, int num_tokens,
-                                  int num_experts, int topk, bool renormalize, int warps_per_block) {
+                                  int num_experts, int topk, bool renormalize, int warps_per_block,
+                                  float scaling = 1.0f) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int token = blockIdx.x * warps_per_block + warp;
@@ -61,6 +65,14 @@ __global__ void TopkSoftmaxKernel(const In* __restrict__ gating, const float* __
                    static_cast<size_t>(warp) * padded;
 
   const In* row = gating + static_cast<int64_t>(token) * num_experts;
+  if constexpr (kSigmoid) {
+    for (int e = lane; e < num_experts; e += 32) {
+      float sc = 1.0f / (1.0f + expf(-ToFloat<In>(row[e])));
+      if (!isfinite(sc)) sc = 0.0f;
+      score[e] = sc;
+      taken[e] = 0;
+    }
+  } else {
   float row_max = -FLT_MAX;
   for (int e = lane; e < num_experts; e += 32) {
     const float v = ToFloat<In>(row[e]);
@@ -78,6 +90,7 @@ __global__ void TopkSoftmaxKernel(const In* __restrict__ gating, const float* __
     float s = expf(score[e] - row_max) / row_sum;
     if (!isfinite(s)) s = 0.0f;
     score[e] = s;
+  }
   }
   __syncwarp();
 
@@ -106,7 +119,8 @@ __global__ void TopkSoftmaxKernel(const In* __restrict__ gating, const float* __
     __syncwarp();
   }
   if (lane == 0) {
-    const float scale = renormalize && selected_sum > 0.0f ? 1.0f / selected_sum : 1.0f;
+    float scale = renormalize && selected_sum > 0.0f ? 1.0f / selected_sum : 1.0f;
+    if constexpr (kSigmoid) scale = renormalize ? scaling / (selected_sum > 0.0f ? selected_sum : 1.0f) : scaling;
     const bool padding = is_padding != nullptr && is_padding[token] != 0;
     for (int rank = 0; rank < topk; ++rank) {
       topk_weights[out + rank] *= scale;
@@ -142,34 +156,34 @@ int PickWarps(Kernel kernel, int64_t num_experts, int& warps, size_t& smem) {
   return IOB_OK;
 }
 
-template <typename In, typename Index>
+template <typename In, typename Index, bool kSigmoid = false>
 int LaunchTopkSoftmax(const void* gating, const float* bias, const uint8_t* is_padding, bool renormalize,
                       float* weights, void* indices, int32_t* tei, int64_t t, int64_t e, int64_t k,
-                      cudaStream_t stream) {
-  auto kernel = TopkSoftmaxKernel<In, Index>;
+                      cudaStream_t stream, float scaling = 1.0f) {
+  auto kernel = TopkSoftmaxKernel<In, Index, kSigmoid>;
   int warps;
   size_t smem;
   if (const int rc = PickWarps(kernel, e, warps, smem)) return rc;
   const unsigned grid = static_cast<unsigned>((t + warps - 1) / warps);
   kernel<<<grid, warps * 32, smem, stream>>>(static_cast<const In*>(gating), bias, is_padding, weights,
                                              static_cast<Index*>(indices), tei, static_cast<int>(t),
-                                             static_cast<int>(e), static_cast<int>(k), renormalize, warps);
-  return CheckLaunch("topk_softmax launch");
+                                             static_cast<int>(e), static_cast<int>(k), renormalize, warps, scaling);
+  return CheckLaunch(kSigmoid ? "topk_sigmoid launch" : "topk_softmax launch");
 }
 
-template <typename In>
+template <typename In, bool kSigmoid = false>
 int DispatchTopkIndex(int index_dtype, const void* gating, const float* bias, const uint8_t* is_padding,
                       bool renormalize, float* weights, void* indices, int32_t* tei, int64_t t, int64_t e,
-                      int64_t k, cudaStream_t stream) {
+                      int64_t k, cudaStream_t stream, float scaling = 1.0f) {
   switch (index_dtype) {
     case IOB_I32:
-      return LaunchTopkSoftmax<In, int32_t>(gating, bias, is_padding, renormalize, weights, indices, tei, t, e, k, stream);
+      return LaunchTopkSoftmax<In, int32_t, kSigmoid>(gating, bias, is_padding, renormalize, weights, indices, tei, t, e, k, stream, scaling);
     case IOB_U32:
-      return LaunchTopkSoftmax<In, uint32_t>(gating, bias, is_padding, renormalize, weights, indices, tei, t, e, k, stream);
+      return LaunchTopkSoftmax<In, uint32_t, kSigmoid>(gating, bias, is_padding, renormalize, weights, indices, tei, t, e, k, stream, scaling);
     case IOB_I64:
-      return LaunchTopkSoftmax<In, int64_t>(gating, bias, is_padding, renormalize, weights, indices, tei, t, e, k, stream);
+      return LaunchTopkSoftmax<In, int64_t, kSigmoid>(gating, bias, is_padding, renormalize, weights, indices, tei, t, e, k, stream, scaling);
     default:
-      return Fail(IOB_INVALID_ARGUMENT, "topk_softmax: `topk_indices` must be int32, uint32 or int64");
+      return Fail(IOB_INVALID_ARGUMENT, "top-k router: `topk_indices` must be int32, uint32 or int64");
   }
 }
 
@@ -377,6 +391,34 @@ extern "C" int infiniops_b200_topk_softmax(const void* gating_output, int gating
       return DispatchTopkIndex<__nv_bfloat16>(index_dtype, gating_output, bias, is_padding, renorm, topk_weights, topk_indices, token_expert_indices, num_tokens, num_experts, topk, s);
     default:
       return Fail(IOB_INVALID_ARGUMENT, "topk_softmax: supports float32, float16 and bfloat16 input");
+  }
+}
+
+extern "C" int infiniops_b200_topk_sigmoid(const void* gating_output, int gating_dtype,
+                                           const float* e_score_correction_bias, const uint8_t* is_padding,
+                                           int renormalize, double routed_scaling_factor, float* topk_weights,
+                                           void* topk_ids, int index_dtype, int32_t* token_expert_indices,
+                                           int64_t num_tokens, int64_t num_experts, int64_t topk, void* stream) {
+  using namespace iob;
+  IOB_REQUIRE(num_tokens >= 0 && num_experts > 0 && topk > 0 && topk <= num_experts,
+              "topk_sigmoid: requires `topk` in [1, num_experts]");
+  IOB_REQUIRE(num_tokens <= INT32_MAX / topk && num_experts <= INT32_MAX,
+              "topk_sigmoid: output indices must fit int32 indexing");
+  IOB_REQUIRE(std::isfinite(routed_scaling_factor), "topk_sigmoid: requires a finite `routed_scaling_factor`");
+  if (num_tokens == 0) return IOB_OK;
+  IOB_REQUIRE(gating_output && topk_weights && topk_ids && token_expert_indices, "topk_sigmoid: null tensor pointer");
+  auto s = static_cast<cudaStream_t>(stream);
+  const bool renorm = renormalize != 0;
+  const float scaling = static_cast<float>(routed_scaling_factor);
+  switch (gating_dtype) {
+    case IOB_F32:
+      return DispatchTopkIndex<float, true>(index_dtype, gating_output, e_score_correction_bias, is_padding, renorm, topk_weights, topk_ids, token_expert_indices, num_tokens, num_experts, topk, s, scaling);
+    case IOB_F16:
+      return DispatchTopkIndex<__half, true>(index_dtype, gating_output, e_score_correction_bias, is_padding, renorm, topk_weights, topk_ids, token_expert_indices, num_tokens, num_experts, topk, s, scaling);
+    case IOB_BF16:
+      return DispatchTopkIndex<__nv_bfloat16, true>(index_dtype, gating_output, e_score_correction_bias, is_padding, renorm, topk_weights, topk_ids, token_expert_indices, num_tokens, num_experts, topk, s, scaling);
+    default:
+      return Fail(IOB_INVALID_ARGUMENT, "topk_sigmoid: supports float32, float16 and bfloat16 input");
   }
 }
 

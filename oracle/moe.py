@@ -12,6 +12,9 @@ torch reference the reference's own test file uses for that operator:
                             routed row), output row = flat routing id
 * silu_and_mul           -- tests/test_silu_and_mul.py:108-113
 * moe_sum                -- tests/test_moe_sum.py:50,95-99
+* topk_sigmoid           -- tests/test_topk_sigmoid.py:352-381
+* moe_wna16_gemm         -- tests/test_moe_wna16_gemm.py:384-442 (plain [E, N, K] layout)
+* get_cutlass_moe_mm_data -- tests/test_get_cutlass_moe_mm_data.py:412-491
 """
 
 from __future__ import annotations
@@ -174,3 +177,77 @@ def moe_w4a16_gemm(a, q, scales, zeros, sorted_token_ids, expert_ids, num_tokens
             val = val * tw[r].unsqueeze(-1)
         out[r] = val
     return out
+
+
+def topk_sigmoid(gating_output, e_score_correction_bias, is_padding, topk: int, renormalize: bool,
+                 routed_scaling_factor: float):
+    """Returns (weights f32 [T,k], ids i64 [T,k], token_expert_indices i32 [T,k]).
+
+    tests/test_topk_sigmoid.py:352-381 of the reference, with the two details its kernel adds
+    (src/native/cuda/nvidia/ops/topk_sigmoid/kernel.cuh:103-106,55-64): a non-finite score counts as
+    0, and equal selection scores go to the smaller expert index (a stable descending sort)."""
+    g = torch.as_tensor(gating_output).cpu()
+    scores = torch.sigmoid(g.to(torch.float32))
+    scores = torch.where(torch.isfinite(scores), scores, torch.zeros_like(scores))
+    selection = scores if e_score_correction_bias is None else scores + torch.as_tensor(e_score_correction_bias).cpu()
+    ids = torch.argsort(selection, dim=-1, descending=True, stable=True)[:, :topk]
+    weights = scores.gather(1, ids)
+    if renormalize:
+        denominator = weights.sum(dim=-1, keepdim=True)
+        weights = weights / torch.where(denominator > 0, denominator, torch.ones_like(denominator))
+    weights = weights * routed_scaling_factor
+    if is_padding is not None:
+        ids = ids.masked_fill(torch.as_tensor(is_padding).cpu().bool().unsqueeze(-1), -1)
+    t = g.shape[0]
+    tei = (torch.arange(topk, dtype=torch.int32).unsqueeze(0).expand(t, -1) * t
+           + torch.arange(t, dtype=torch.int32).unsqueeze(-1))
+    return weights, ids, tei
+
+
+def moe_wna16_gemm(x, quantized_weight, scales, zero_points, bit: int, topk_weights, sorted_token_ids, expert_ids,
+                   num_tokens_post_pad, block_size_m: int, top_k: int) -> torch.Tensor:
+    """fp32 [M, top_k, N] for the plain layout: quantized_weight [E, N, K] integers, scales [E, N, G],
+    zero_points [E, N, G] integers or None (tests/test_moe_wna16_gemm.py:384-442 of the reference;
+    its bfloat16 / 8-bit rounding model is NOT restated: the tolerance of that case covers it)."""
+    q = quant._as_np(quantized_weight).transpose(0, 2, 1)
+    s = torch.as_tensor(scales).permute(0, 2, 1)
+    z = None if zero_points is None else quant._as_np(zero_points).transpose(0, 2, 1)
+    m = torch.as_tensor(x).shape[0]
+    out = moe_w4a16_gemm(x, q, s, z, sorted_token_ids, expert_ids, num_tokens_post_pad, topk_weights, block_size_m,
+                         top_k, topk_weights is not None, num_bits=bit)
+    return out.reshape(m, top_k, -1)
+
+
+def get_cutlass_moe_mm_data(topk_ids, num_experts: int, n: int, k: int, is_gated: bool = True,
+                            with_blockscale: bool = False):
+    """Returns (expert_offsets, problem_sizes1, problem_sizes2, input_permutation, output_permutation,
+    blockscale_offsets or None) as int32 numpy arrays, routes of one expert placed by ascending route
+    index (the reference places them in any order, tests/test_get_cutlass_moe_mm_data.py:412-491)."""
+    ids = quant._as_np(topk_ids).astype(np.int64)
+    topk = ids.shape[1]
+    flat = ids.reshape(-1)
+    valid = (flat >= 0) & (flat < num_experts)
+    counts = np.bincount(flat[valid], minlength=num_experts)
+    offsets = np.concatenate(([0], np.cumsum(counts))).astype(np.int32)
+    swap = not with_blockscale and flat.size <= 64
+    n1 = 2 * n if is_gated else n
+    if swap:
+        ps1 = np.stack((np.full(num_experts, n1), counts, np.full(num_experts, k)), axis=1)
+        ps2 = np.stack((np.full(num_experts, k), counts, np.full(num_experts, n)), axis=1)
+    else:
+        ps1 = np.stack((counts, np.full(num_experts, n1), np.full(num_experts, k)), axis=1)
+        ps2 = np.stack((counts, np.full(num_experts, k), np.full(num_experts, n)), axis=1)
+    in_perm = np.full(flat.size, -1, dtype=np.int32)
+    out_perm = np.full(flat.size, -1, dtype=np.int32)
+    cursor = offsets[:-1].astype(np.int64).copy()
+    for route, e in enumerate(flat.tolist()):
+        if 0 <= e < num_experts:
+            in_perm[cursor[e]] = route // topk
+            out_perm[route] = cursor[e]
+            cursor[e] += 1
+        elif e == -1:
+            out_perm[route] = offsets[-1]
+    scale_offsets = None
+    if with_blockscale:
+        scale_offsets = np.concatenate(([0], np.cumsum((counts + 127) // 128 * 128))).astype(np.int32)
+    return offsets, ps1.astype(np.int32), ps2.astype(np.int32), in_perm, out_perm, scale_offsets

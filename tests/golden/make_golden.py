@@ -1,6 +1,6 @@
 """Generate the golden fixtures in this folder from the reference's own test helpers.
 
-Run once, in a container where the reference checkout is available:
+Run in a container where the reference checkout is available (its path is a required argument):
 
     python tests/golden/make_golden.py /path/to/reference
 
@@ -29,14 +29,16 @@ def _load_reference_tests(ref_root: str):
     stub = types.ModuleType("infini")
     ops = types.ModuleType("infini.ops")
     for name in ("GptqMarlinRepack", "AwqMarlinRepack", "MoeWna16MarlinGemm", "TopkSoftmax",
-                 "GroupedTopk", "MoeAlignBlockSize", "SiluAndMul", "MoeSum", "MoeWna16Gemm"):
+                 "GroupedTopk", "MoeAlignBlockSize", "SiluAndMul", "MoeSum", "MoeWna16Gemm", "TopkSigmoid",
+                 "GetCutlassMoeMmData"):
         setattr(ops, name, type(name, (), {"active_implementation_indices": staticmethod(lambda d: ())}))
     stub.ops = ops
     sys.modules["infini"] = stub
     sys.modules["infini.ops"] = ops
     sys.path.insert(0, ref_root)
     names = ("test_gptq_marlin_repack", "test_awq_marlin_repack", "test_topk_softmax",
-             "test_grouped_topk", "test_moe_align_block_size", "test_moe_wna16_gemm")
+             "test_grouped_topk", "test_moe_align_block_size", "test_moe_wna16_gemm", "test_topk_sigmoid",
+             "test_get_cutlass_moe_mm_data")
     return {n: importlib.import_module(f"tests.{n}") for n in names}
 
 
@@ -206,6 +208,78 @@ def main(ref_root: str) -> None:
     np.savez_compressed(HERE / "moe_dequant_matmul.npz", **out)
     print(f"dequantise-then-matmul: {i} cases pinned")
 
+    # ---- sibling operators: topk_sigmoid, moe_wna16_gemm (4- and 8-bit), get_cutlass_moe_mm_data ---------
+    ts = ref["test_topk_sigmoid"]
+    out = {}
+    gate = torch.tensor(((1.25, -0.5, 0.75, 2.0, -1.0), (-0.25, 1.5, 0.5, -1.25, 2.25), (0.125, 0.75, 2.5, 1.0, -0.75)))
+    bias = torch.tensor((0.0, 0.75, -0.5, -1.0, 1.25))
+    i = 0
+    for dtype in (torch.float32, torch.float16, torch.bfloat16):
+        for has_bias in (False, True):
+            for renorm in (False, True):
+                g_in = gate.to(dtype)
+                expect = ts._reference(g_in, bias if has_bias else None, None, 2, renorm, 0.75)
+                mine = omoe.topk_sigmoid(g_in, bias if has_bias else None, None, 2, renorm, 0.75)
+                torch.testing.assert_close(mine[0], expect[0], rtol=0, atol=0)
+                assert torch.equal(mine[1], expect[1]) and torch.equal(mine[2], expect[2])
+                out[f"c{i}_gate"] = g_in.float().numpy()
+                out[f"c{i}_meta"] = np.array([code[dtype], int(has_bias), int(renorm)])
+                out[f"c{i}_w"], out[f"c{i}_ids"], out[f"c{i}_tei"] = (v.numpy() for v in expect)
+                i += 1
+    out["bias"], out["n_cases"] = bias.numpy(), np.array([i])
+    pad_gate = torch.tensor(((0.25, 2.0, -0.5, 1.0), (1.5, -0.25, 0.75, 0.0), (-1.0, 0.5, 2.25, 1.25)), dtype=torch.float16)
+    pad = torch.tensor((False, True, False))
+    expect = ts._reference(pad_gate, None, pad, 3, True, 1.0)
+    mine = omoe.topk_sigmoid(pad_gate, None, pad, 3, True, 1.0)
+    assert torch.equal(mine[1], expect[1]) and torch.equal(mine[2], expect[2])
+    out["pad_gate"], out["pad_mask"] = pad_gate.float().numpy(), pad.numpy()
+    out["pad_w"], out["pad_ids"], out["pad_tei"] = (v.numpy() for v in expect)
+    np.savez_compressed(HERE / "topk_sigmoid.npz", **out)
+    print(f"topk_sigmoid: {i + 1} cases pinned")
+
+    out = {}
+    i = 0
+    for bit, group_size, k in ((4, 16, 32), (4, 32, 64), (8, 4, 32), (8, 16, 32)):
+        for has_zp in (False, True):
+            for mul in (False, True):
+                for dtype in (torch.float16, torch.bfloat16):
+                    (x, qw, scales, qz, tw, sorted_ids, expert_ids, npost, _o, qweight, zps) = mg._make_case(
+                        bit, has_zp, mul, dtype, "cpu", group_size=group_size, k=k)
+                    expect = mg._reference(x, qweight, scales, zps, bit, tw, sorted_ids, expert_ids, npost, block_size_m=2)
+                    mine = omoe.moe_wna16_gemm(x, qweight, scales, zps, bit, tw, sorted_ids, expert_ids, npost, 2, 2)
+                    tol = 2e-2 if dtype == torch.float16 else 5e-2
+                    torch.testing.assert_close(mine.to(dtype), expect, rtol=tol, atol=tol)
+                    out[f"c{i}_x"], out[f"c{i}_qw"], out[f"c{i}_s"] = x.float().numpy(), qw.numpy(), scales.float().numpy()
+                    out[f"c{i}_qz"] = np.zeros(0, np.uint8) if qz is None else qz.numpy()
+                    out[f"c{i}_tw"] = np.zeros(0, np.float32) if tw is None else tw.numpy()
+                    out[f"c{i}_sorted"], out[f"c{i}_experts"], out[f"c{i}_npost"] = (
+                        sorted_ids.numpy(), expert_ids.numpy(), npost.numpy())
+                    out[f"c{i}_meta"] = np.array([bit, int(has_zp), int(mul), code[dtype], group_size, k])
+                    out[f"c{i}_out"] = expect.float().numpy()
+                    i += 1
+    out["n_cases"] = np.array([i])
+    np.savez_compressed(HERE / "moe_wna16_gemm.npz", **out)
+    print(f"moe_wna16_gemm: {i} cases pinned")
+
+    md = ref["test_get_cutlass_moe_mm_data"]
+    out = {}
+    tables = [(((2, 0), (1, 2), (0, 3), (3, 1)), 4, False), (((0, 1), (2, 3), (0, 3), (2, 1)), 4, True),
+              (tuple((0, 1) for _ in range(130)), 4, True), (((0, -1), (2, 1), (-1, 2)), 4, False),
+              ((torch.arange(513, dtype=torch.int32) % 4).reshape(513, 1).tolist(), 4, False),
+              ((torch.arange(2600, dtype=torch.int32) * 7 % 61).reshape(650, 4).tolist(), 61, False)]
+    for i, (ids, experts, blockscale) in enumerate(tables):
+        ids_t = torch.tensor(ids, dtype=torch.int32)
+        for gated in (True, False):
+            res = omoe.get_cutlass_moe_mm_data(ids_t, experts, 64, 128, gated, blockscale)
+            tensors = [None if r is None else torch.from_numpy(r) for r in res]
+            md._assert_matches_reference(ids_t, experts, 64, 128, gated, *tensors[:5], tensors[5])
+        out[f"c{i}_ids"], out[f"c{i}_meta"] = ids_t.numpy(), np.array([experts, int(blockscale)])
+    out["n_cases"] = np.array([len(tables)])
+    np.savez_compressed(HERE / "moe_mm_data.npz", **out)
+    print(f"get_cutlass_moe_mm_data: {len(tables)} routing tables checked by the reference's checker")
+
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: python tests/golden/make_golden.py /path/to/reference-checkout")
+    main(sys.argv[1])

@@ -235,3 +235,35 @@ def test_dense_marlin_gemm_through_module_and_trace_line():
                        cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     assert r.returncode == 0, r.stderr
     assert '[INFINI_OPS_TRACE_CALLS] {"operator_name": "SiluAndMul", "device_type": "nvidia", "implementation": 0}' in r.stderr
+
+
+def test_device_guard_runs_on_the_tensors_device_and_restores_the_callers():
+    """Tensors on cuda:1 while cuda:0 is current: the operators launch on the tensors' device and leave
+    the caller's current device alone (tests/test_topk_softmax.py:258-288 of the reference).  Needs two GPUs."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import infini.ops
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 1)
+    logits = torch.randn((33, 8))
+    w = torch.empty((33, 2), device=dev)
+    ids = torch.empty((33, 2), dtype=torch.int32, device=dev)
+    tei = torch.empty((33, 2), dtype=torch.int32, device=dev)
+    with torch.cuda.device(1):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+    infini.ops.topk_softmax(logits.to(dev), None, None, True, w, ids, tei, stream=stream)
+    assert torch.cuda.current_device() == 0
+    rw, rids, _ = omoe.topk_softmax(logits, None, None, 2, True)
+    assert torch.equal(ids.cpu().long(), rids)
+    # a GEMM too: its tensor maps and scratch belong to device 1
+    m, k, n = 16, 512, 256
+    q, scales, zeros = make_quantized(k, n, 128, torch.float16, True, 5)
+    a = torch.randn((m, k)).half()
+    packed = torch.from_numpy(oq.marlin_pack(q, 4, False)).to(dev)
+    out = torch.empty((m, n), dtype=torch.float16, device=dev)
+    workspace = torch.zeros(432, dtype=torch.int32, device=dev)
+    infini.ops.marlin_gemm(a.to(dev), packed, None, scales.to(dev), None, None, torch.from_numpy(oq.pack_zeros(zeros)).to(dev),
+                           None, None, workspace, UINT4, m, n, k, True, False, True, False, out, stream=stream)
+    assert torch.cuda.current_device() == 0
+    assert rel_max_err(out, oq.w4a16_gemm(a, q, scales, zeros)) <= 1e-2

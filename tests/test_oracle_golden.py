@@ -117,3 +117,53 @@ def test_silu_and_moe_sum_oracle():
     emap = torch.tensor((0, -1, 1), dtype=torch.int32)
     active = (ids >= 0) & (emap[ids.clamp_min(0)] >= 0)
     torch.testing.assert_close(omoe.moe_sum(y, ids, emap), (y * active.unsqueeze(-1)).sum(1))
+
+
+def test_topk_sigmoid_golden(golden):
+    g = golden["topk_sigmoid"]
+    bias = torch.from_numpy(g["bias"])
+    for i in range(int(g["n_cases"][0])):
+        dt, has_bias, renorm = (int(v) for v in g[f"c{i}_meta"])
+        gate = torch.from_numpy(g[f"c{i}_gate"]).to(_DT[dt])
+        w, ids, tei = omoe.topk_sigmoid(gate, bias if has_bias else None, None, 2, bool(renorm), 0.75)
+        assert np.array_equal(ids.numpy(), g[f"c{i}_ids"]) and np.array_equal(tei.numpy(), g[f"c{i}_tei"])
+        np.testing.assert_allclose(w.numpy(), g[f"c{i}_w"], rtol=0, atol=0)
+    w, ids, tei = omoe.topk_sigmoid(torch.from_numpy(g["pad_gate"]).half(), None, torch.from_numpy(g["pad_mask"]), 3, True, 1.0)
+    assert np.array_equal(ids.numpy(), g["pad_ids"]) and np.array_equal(tei.numpy(), g["pad_tei"])
+    w, ids, _ = omoe.topk_sigmoid(torch.full((1, 4), float("nan")), None, None, 2, False, 1.0)
+    assert ids.tolist() == [[0, 1]] and w.tolist() == [[0.0, 0.0]]
+
+
+def test_moe_wna16_gemm_golden(golden):
+    g = golden["moe_wna16_gemm"]
+    for i in range(int(g["n_cases"][0])):
+        bit, has_zp, mul, dt, group_size, k = (int(v) for v in g[f"c{i}_meta"])
+        q, z = _unpack_plain(g[f"c{i}_qw"], g[f"c{i}_qz"] if has_zp else None, bit)
+        x = torch.from_numpy(g[f"c{i}_x"]).to(_DT[dt])
+        s = torch.from_numpy(g[f"c{i}_s"]).to(_DT[dt])
+        out = omoe.moe_wna16_gemm(x, q, s, z, bit, torch.from_numpy(g[f"c{i}_tw"]) if mul else None, g[f"c{i}_sorted"],
+                                  g[f"c{i}_experts"], g[f"c{i}_npost"], 2, 2)
+        tol = 2e-2 if dt == 1 else 5e-2
+        torch.testing.assert_close(out.to(_DT[dt]).float(), torch.from_numpy(g[f"c{i}_out"]), rtol=tol, atol=tol)
+
+
+def _unpack_plain(qw, qz, bit):
+    """uint8-packed weight [E, N, K / (8 / bit)] and zero points [E, N / (8 / bit), G] -> integers."""
+    if bit == 8:
+        return qw.astype(np.int64), None if qz is None else qz.astype(np.int64)
+    q = np.stack((qw & 0xF, qw >> 4), axis=-1).reshape(qw.shape[0], qw.shape[1], -1).astype(np.int64)
+    z = None
+    if qz is not None:
+        z = np.stack((qz & 0xF, qz >> 4), axis=2).reshape(qz.shape[0], -1, qz.shape[2]).astype(np.int64)
+    return q, z
+
+
+def test_moe_mm_data_oracle_shapes(golden):
+    g = golden["moe_mm_data"]
+    for i in range(int(g["n_cases"][0])):
+        experts, blockscale = (int(v) for v in g[f"c{i}_meta"])
+        ids = g[f"c{i}_ids"]
+        offsets, ps1, ps2, in_perm, out_perm, scale = omoe.get_cutlass_moe_mm_data(ids, experts, 64, 128, True, bool(blockscale))
+        valid = int(((ids >= 0) & (ids < experts)).sum())
+        assert offsets[-1] == valid and sorted(out_perm[(ids.reshape(-1) >= 0) & (ids.reshape(-1) < experts)].tolist()) == list(range(valid))
+        assert (scale is not None) == bool(blockscale)
