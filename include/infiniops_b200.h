@@ -264,6 +264,7 @@ typedef struct {
   int64_t out_ld, out_col0;
   int n_peers;
   void* peer_out[IOB_MAX_PEERS];
+  int scale_layout; /* 0 = plain scales / zero points, 1 = vLLM Marlin layouts (see iob_routed_options) */
 } iob_gemm_problem;
 
 /* Completion signal of a launch towards the other GPUs.  When the last thread block of the launch
@@ -389,28 +390,35 @@ int infiniops_b200_moe_wna16_gemm(const void* input, int dtype, const uint8_t* b
                                   int64_t size_k, int64_t num_groups, int64_t num_experts,
                                   void* output, void* stream);
 
-/* Where the routed GEMM stores its result rows when they do not stay on this GPU (the combine
- * step of expert parallelism fused into the GEMM's epilogue).  `row_dest` holds, per output row
- * (a flat routing id of this call), two int32: the GPU the row belongs to and its row in that GPU's
- * destination matrix [rows, size_n]; `dest_base[g]` is that matrix of GPU g as mapped into this
- * process (this GPU's own included), `n_dest` their number (at most 8).  `signal` (or NULL) is
- * raised when the launch has finished.  No counterpart in the reference. */
+/* Options of the routed GEMM beyond the reference's argument list.
+ * `scale_layout`: 0 = `b_scales` [E, G, N] and `b_zeros` [E, G, N/8] in plain column order (field j
+ * of a zero-point word = column 8 (n/8) + j); 1 = the layouts vLLM's Marlin kernels take, i.e. what
+ * a checkpoint prepared for the reference's linked provider holds (scale columns permuted inside
+ * blocks of 64 -- 32 with a single group --, zero points permuted alike and interleaved inside each
+ * word; src/base/moe_wna16_marlin_gemm.h:204-210,231-240 fix only their shapes).
+ * `row_dest` (or NULL): where the result rows go when they do not stay on this GPU -- the combine
+ * step of expert parallelism fused into the epilogue.  Per output row (a flat routing id of this
+ * call) two int32: the GPU the row belongs to and its row in that GPU's destination matrix
+ * [rows, size_n]; `dest_base[g]` is that matrix of GPU g as mapped into this process (this GPU's
+ * own included), `n_dest` their number (at most 8).  With a `row_dest`, `out` is only validated.
+ * `signal` (or NULL) is raised when the launch has finished.  Zero-initialise the struct.
+ * No counterpart in the reference. */
 typedef struct {
+  int scale_layout;
   const int32_t* row_dest;
   void* dest_base[IOB_MAX_PEERS + 1];
   int n_dest;
   const iob_peer_signal* signal;
-} iob_routed_scatter;
+} iob_routed_options;
 
-/* infiniops_b200_moe_wna16_marlin_gemm with an optional scatter of the result rows (NULL = rows go
- * to `out` as usual; with a scatter `out` is only validated).  No counterpart in the reference. */
-int infiniops_b200_moe_wna16_marlin_gemm_scattered(
+/* infiniops_b200_moe_wna16_marlin_gemm with options (NULL = none).  No counterpart in the reference. */
+int infiniops_b200_moe_wna16_marlin_gemm_ex(
     const void* a, int a_dtype, const int32_t* b_q_weight, const void* b_bias,
     const void* b_scales, const int32_t* b_zeros, const int32_t* sorted_token_ids,
     const int32_t* expert_ids, const int32_t* num_tokens_past_padded, const float* topk_weights,
     int64_t moe_block_size, int64_t top_k, int mul_topk_weights, int64_t b_type_id,
     int64_t size_m, int64_t size_n, int64_t size_k, int64_t num_groups, int64_t num_experts,
-    int64_t sorted_size, void* out, const iob_routed_scatter* scatter, void* scratch,
+    int64_t sorted_size, void* out, const iob_routed_options* options, void* scratch,
     size_t scratch_bytes, void* stream);
 
 /* ---- expert-parallel MoE layer (one process per GPU, NVLink) ------------------------------------ */

@@ -5,7 +5,7 @@
 // args...)`, `Op::active_implementation_indices(device_type)`, `Op::clear_cache()`, and the
 // `INFINI_OPS_TRACE_CALLS` line per dispatched call (src/operator.h:126-171) -- but with a single
 // back end: an operator `Key` is implemented by the specialisation
-// `Operator<Key, Device::Type::kNvidia, 0>` or not at all.  A request for any other device or
+// `Operator<Key, Device::Type::kNvidia, 0>` (plus, for the Marlin GEMMs, slot 16) or not at all.  A request for any other device or
 // slot prints a message and aborts, like a dispatcher miss in the reference
 // (src/dispatcher.h:44-49).
 #ifndef INFINI_OPS_OPERATOR_H_
@@ -121,6 +121,13 @@ class Operator {};
 template <typename Key, Device::Type device_type, std::size_t implementation_index>
 inline constexpr bool kIsImplemented = std::is_base_of_v<Key, Operator<Key, device_type, implementation_index>>;
 
+// Slot 16 is where the reference registers a linked provider (vLLM) implementation
+// (docs/linked-operators.md:106-110 of the reference).  Operators whose provider takes tensors in
+// a layout of its own -- the Marlin GEMMs' permuted scales and zero points -- register a second
+// implementation there that reads exactly those layouts, so a caller that selects the provider
+// slot keeps working with the tensors it prepared for it.
+inline constexpr std::size_t kProviderSlot = 16;
+
 template <typename Key>
 class Operator<Key, Device::Type::kCount, 0> : public OperatorBase {
  public:
@@ -130,13 +137,22 @@ class Operator<Key, Device::Type::kCount, 0> : public OperatorBase {
   static void clear_cache() { cache_generation_.fetch_add(1, std::memory_order_relaxed); }
 
   static std::vector<std::size_t> active_implementation_indices(Device::Type type) {
-    if (type == Device::Type::kNvidia && kIsImplemented<Key, Device::Type::kNvidia, 0>) return {0};
-    return {};
+    std::vector<std::size_t> slots;
+    if (type == Device::Type::kNvidia && kIsImplemented<Key, Device::Type::kNvidia, 0>) slots.push_back(0);
+    if (type == Device::Type::kNvidia && kIsImplemented<Key, Device::Type::kNvidia, kProviderSlot>) slots.push_back(kProviderSlot);
+    return slots;
   }
 
   template <typename... Args>
   static std::unique_ptr<Front> Make(const Config& config, const Tensor tensor, Args&&... args) {
     RequireBackend(tensor.device().type(), config.implementation_index());
+    if constexpr (kIsImplemented<Key, Device::Type::kNvidia, kProviderSlot>) {
+      if (config.implementation_index() == kProviderSlot) {
+        auto op = std::make_unique<Operator<Key, Device::Type::kNvidia, kProviderSlot>>(tensor, std::forward<Args>(args)...);
+        op->set_config(config);
+        return op;
+      }
+    }
     if constexpr (kIsImplemented<Key, Device::Type::kNvidia, 0>) {
       auto op = std::make_unique<Operator<Key, Device::Type::kNvidia, 0>>(tensor, std::forward<Args>(args)...);
       op->set_config(config);
@@ -198,9 +214,11 @@ class Operator<Key, Device::Type::kCount, 0> : public OperatorBase {
 
  private:
   static void RequireBackend(Device::Type type, std::size_t index) {
-    if (type != Device::Type::kNvidia || index != 0 || !kIsImplemented<Key, Device::Type::kNvidia, 0>) {
+    const bool known = (index == 0 && kIsImplemented<Key, Device::Type::kNvidia, 0>) ||
+                       (index == kProviderSlot && kIsImplemented<Key, Device::Type::kNvidia, kProviderSlot>);
+    if (type != Device::Type::kNvidia || !known) {
       const auto name = Device::StringFromType(type);
-      std::fprintf(stderr, "`%s` has no implementation %zu for device `%.*s` (this build: nvidia, slot 0 only)\n",
+      std::fprintf(stderr, "`%s` has no implementation %zu for device `%.*s` (this build: nvidia, slot 0, and slot 16 for the Marlin GEMMs)\n",
                    Key::kName, index, static_cast<int>(name.size()), name.data());
       std::fflush(stderr);
       std::abort();

@@ -47,13 +47,35 @@ class Operator<MarlinGemm, Device::Type::kNvidia, 0> : public MarlinGemm {
     impl::DeviceGuard guard(device_index_);
     std::size_t scratch_bytes = 0;
     void* scratch = impl::PickScratch(workspace_, workspace_size_in_bytes_, workspace_size_in_bytes(), 0, stream_, scratch_bytes);
-    impl::Require(infiniops_b200_marlin_gemm(a.data(), impl::TypeCode(a.dtype()),
-                                             static_cast<const int32_t*>(b_q_weight.data()), impl::DataOrNull(b_bias),
-                                             b_scales.data(), static_cast<const int32_t*>(impl::DataOrNull(b_zeros)),
-                                             b_type_id, size_m, size_n, size_k, static_cast<int64_t>(b_scales.size(0)),
-                                             out.data(), scratch, scratch_bytes, stream_),
+    iob_gemm_problem problem{};
+    problem.a = a.data();
+    problem.b_q_weight = static_cast<const int32_t*>(b_q_weight.data());
+    problem.b_bias = impl::DataOrNull(b_bias);
+    problem.b_scales = b_scales.data();
+    problem.b_zeros = static_cast<const int32_t*>(impl::DataOrNull(b_zeros));
+    problem.out = out.data();
+    problem.size_m = size_m;
+    problem.size_n = size_n;
+    problem.size_k = size_k;
+    problem.num_groups = static_cast<int64_t>(b_scales.size(0));
+    problem.scale_layout = scale_layout();
+    impl::Require(infiniops_b200_marlin_gemm_placed(&problem, impl::TypeCode(a.dtype()), b_type_id, nullptr, scratch,
+                                                    scratch_bytes, stream_),
                   kName);
   }
+
+ protected:
+  // 0: `b_scales` / `b_zeros` in plain column order; the provider slot reads vLLM's Marlin layouts.
+  virtual int scale_layout() const { return 0; }
+};
+
+template <>
+class Operator<MarlinGemm, Device::Type::kNvidia, kProviderSlot> : public Operator<MarlinGemm, Device::Type::kNvidia, 0> {
+ public:
+  using Operator<MarlinGemm, Device::Type::kNvidia, 0>::Operator;
+
+ protected:
+  int scale_layout() const override { return 1; }
 };
 
 template <>
@@ -94,8 +116,10 @@ class Operator<MoeWna16MarlinGemm, Device::Type::kNvidia, 0> : public MoeWna16Ma
     impl::DeviceGuard guard(device_index_);
     std::size_t scratch_bytes = 0;
     void* scratch = impl::PickScratch(workspace_, workspace_size_in_bytes_, workspace_size_in_bytes(), 0, stream_, scratch_bytes);
+    iob_routed_options options{};
+    options.scale_layout = scale_layout();
     impl::Require(
-        infiniops_b200_moe_wna16_marlin_gemm(
+        infiniops_b200_moe_wna16_marlin_gemm_ex(
             a.data(), impl::TypeCode(a.dtype()), static_cast<const int32_t*>(b_q_weight.data()),
             impl::DataOrNull(b_bias_or_none), b_scales.data(),
             static_cast<const int32_t*>(impl::DataOrNull(b_zeros_or_none)),
@@ -103,9 +127,22 @@ class Operator<MoeWna16MarlinGemm, Device::Type::kNvidia, 0> : public MoeWna16Ma
             static_cast<const int32_t*>(num_tokens_past_padded.data()), // (16-bit routing weights are only accepted when they are not applied: they are never read then)
             mul_topk_weights ? static_cast<const float*>(topk_weights.data()) : nullptr, moe_block_size, top_k, mul_topk_weights ? 1 : 0, b_type_id, size_m, size_n, size_k,
             static_cast<int64_t>(b_scales.size(1)), static_cast<int64_t>(b_q_weight.size(0)),
-            static_cast<int64_t>(sorted_token_ids.numel()), out.data(), scratch, scratch_bytes, stream_),
+            static_cast<int64_t>(sorted_token_ids.numel()), out.data(), &options, scratch, scratch_bytes, stream_),
         kName);
   }
+
+ protected:
+  virtual int scale_layout() const { return 0; }
+};
+
+template <>
+class Operator<MoeWna16MarlinGemm, Device::Type::kNvidia, kProviderSlot>
+    : public Operator<MoeWna16MarlinGemm, Device::Type::kNvidia, 0> {
+ public:
+  using Operator<MoeWna16MarlinGemm, Device::Type::kNvidia, 0>::Operator;
+
+ protected:
+  int scale_layout() const override { return 1; }
 };
 
 }  // namespace infini::ops

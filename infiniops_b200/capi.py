@@ -62,7 +62,8 @@ class GemmProblem(ctypes.Structure):
     """`iob_gemm_problem` of include/infiniops_b200.h."""
     _fields_ = [("a", _vp), ("b_q_weight", _vp), ("b_bias", _vp), ("b_scales", _vp), ("b_zeros", _vp), ("out", _vp),
                 ("size_m", _i64), ("size_n", _i64), ("size_k", _i64), ("num_groups", _i64),
-                ("out_ld", _i64), ("out_col0", _i64), ("n_peers", _int), ("peer_out", _vp * MAX_PEERS)]
+                ("out_ld", _i64), ("out_col0", _i64), ("n_peers", _int), ("peer_out", _vp * MAX_PEERS),
+                ("scale_layout", _int)]
 
 
 class PeerSignal(ctypes.Structure):
@@ -71,9 +72,9 @@ class PeerSignal(ctypes.Structure):
                 ("flag_slot", _int)]
 
 
-class RoutedScatter(ctypes.Structure):
-    """`iob_routed_scatter`."""
-    _fields_ = [("row_dest", _vp), ("dest_base", _vp * (MAX_PEERS + 1)), ("n_dest", _int),
+class RoutedOptions(ctypes.Structure):
+    """`iob_routed_options`."""
+    _fields_ = [("scale_layout", _int), ("row_dest", _vp), ("dest_base", _vp * (MAX_PEERS + 1)), ("n_dest", _int),
                 ("signal", ctypes.POINTER(PeerSignal))]
 
 
@@ -91,9 +92,9 @@ class ExpertWeightsC(ctypes.Structure):
 
 
 PROTOTYPES.update({
-    "infiniops_b200_moe_wna16_marlin_gemm_scattered": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
+    "infiniops_b200_moe_wna16_marlin_gemm_ex": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
                                                               _i64, _int, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _vp,
-                                                              ctypes.POINTER(RoutedScatter), _vp, _sz, _vp]),
+                                                              ctypes.POINTER(RoutedOptions), _vp, _sz, _vp]),
     "infiniops_b200_topk_sigmoid": (_int, [_vp, _int, _vp, _vp, _int, _dbl, _vp, _vp, _int, _vp, _i64, _i64, _i64, _vp]),
     "infiniops_b200_get_cutlass_moe_mm_data": (_int, [_vp, _i64, _i64, _i64, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp,
                                                       _vp, _vp]),
@@ -253,20 +254,22 @@ def marlin_gemm_static_scratch(a, b_q_weight, b_bias, b_scales, b_zeros, b_type_
 
 def moe_wna16_marlin_gemm(a, b_q_weight, b_bias, b_scales, b_zeros, sorted_token_ids, expert_ids,
                           num_tokens_past_padded, topk_weights, moe_block_size, top_k, mul_topk_weights, b_type_id,
-                          size_m, size_n, size_k, out, stream=None, scratch_buf=None):
+                          size_m, size_n, size_k, out, stream=None, scratch_buf=None, scale_layout=0):
     e = b_q_weight.shape[0]
     need = lib().infiniops_b200_moe_wna16_marlin_gemm_scratch_bytes(size_m, top_k, size_n, size_k, e,
                                                                     moe_block_size)
     buf = scratch_buf if scratch_buf is not None else scratch(a.device, need)
-    _check(lib().infiniops_b200_moe_wna16_marlin_gemm(
+    options = RoutedOptions()
+    options.scale_layout = scale_layout
+    _check(lib().infiniops_b200_moe_wna16_marlin_gemm_ex(
         _ptr(a), _DTYPE[a.dtype], _ptr(b_q_weight), _ptr(b_bias), _ptr(b_scales), _ptr(b_zeros),
         _ptr(sorted_token_ids), _ptr(expert_ids), _ptr(num_tokens_past_padded), _ptr(topk_weights), moe_block_size,
         top_k, int(mul_topk_weights), b_type_id, size_m, size_n, size_k, b_scales.shape[-2], e,
-        sorted_token_ids.numel(), _ptr(out), _ptr(buf), buf.numel(), _stream(stream)))
+        sorted_token_ids.numel(), _ptr(out), ctypes.byref(options), _ptr(buf), buf.numel(), _stream(stream)))
 
 
 def gemm_problem(a, b_q_weight, b_bias, b_scales, b_zeros, out, size_m, size_n, size_k, out_ld=0, out_col0=0,
-                 peer_out=()) -> GemmProblem:
+                 peer_out=(), scale_layout=0) -> GemmProblem:
     """One entry of a problem list.  `out` may be a tensor or a raw device address; `peer_out` are the
     addresses of the other GPUs' result matrices (already mapped into this process)."""
     g = GemmProblem()
@@ -275,7 +278,7 @@ def gemm_problem(a, b_q_weight, b_bias, b_scales, b_zeros, out, size_m, size_n, 
     g.b_zeros = None if b_zeros is None else b_zeros.data_ptr()
     g.out = out if isinstance(out, int) else out.data_ptr()
     g.size_m, g.size_n, g.size_k, g.num_groups = size_m, size_n, size_k, b_scales.shape[-2]
-    g.out_ld, g.out_col0, g.n_peers = out_ld, out_col0, len(peer_out)
+    g.out_ld, g.out_col0, g.n_peers, g.scale_layout = out_ld, out_col0, len(peer_out), scale_layout
     for i, ptr in enumerate(peer_out):
         g.peer_out[i] = ptr
     return g

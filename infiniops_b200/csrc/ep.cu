@@ -316,12 +316,12 @@ extern "C" int infiniops_b200_ep_moe_layer(const iob_ep_context* ctx, const iob_
   for (int g = 0; g < c.world; ++g) {
     if (g != c.rank) signal.peer_flags[signal.n_peers++] = c.flags[g];
   }
-  iob_routed_scatter scatter{};
+  iob_routed_options scatter{};
   scatter.row_dest = reinterpret_cast<const int32_t*>(row_dest);
   scatter.n_dest = c.world;
   for (int g = 0; g < c.world; ++g) scatter.dest_base[g] = peers.arena[g] + lay.routed;
   scatter.signal = c.world > 1 ? &signal : nullptr;
-  if (const int rc = infiniops_b200_moe_wna16_marlin_gemm_scattered(
+  if (const int rc = infiniops_b200_moe_wna16_marlin_gemm_ex(
           ws + w.h, c.a_dtype, weights->w2, nullptr, weights->s2, weights->z2, sorted, expert_ids, npost, row_weights,
           c.moe_block_size, 1, 1, c.b_type_id, w.rows, c.hidden, c.inter, weights->groups2, c.experts_per_rank,
           w.sorted_size, ws + w.g /* validated only */, &scatter, ws + w.gemm, w.gemm_bytes, stream)) {

@@ -102,6 +102,10 @@ struct GemmParams {
   int* counters;           // [kMaxGrid][4]: one per (first block of a split tile, lane quarter)
   int* status;
   int m, n, k, groups, group_size;
+  // 0: scales [G, N] and zero points [G, N/8] in plain column order.  1: the layouts vLLM's Marlin
+  // kernels take -- scale columns permuted inside blocks of 64 (32 for one group), zero-point
+  // nibbles permuted the same way and interleaved inside each word (see ScaleColumn / ZeroNibble).
+  int layout;
   int pair;            // dense 256-token tiles: blocks work in pairs (the activation map's box is 128 rows then)
   int g_mul, g_shift;  // scale row of k-stage ks = (ks * g_mul) >> g_shift; g_shift < 0: divide instead
   // Where the result goes.  `out` is a matrix with `out_ld` columns; this problem's N columns start
@@ -142,6 +146,18 @@ struct BatchTable {
   int count;
   Problem prob[kMaxBatch];
 };
+
+// Position of logical column n inside a row of scales.  Provider layout: a row is cut into blocks
+// of 64 columns stored as [n % 8][n / 8] (so that the four columns c, c + 8, c + 16, c + 24 an MMA
+// thread owns are adjacent); with a single group, blocks of 32 stored as [(n % 8) / 2][n / 8][n % 2].
+__device__ __forceinline__ int ScaleColumn(const GemmParams& p, int n) {
+  if (p.layout == 0) return n;
+  if (p.groups > 1) return (n & ~63) + ((n & 7) << 3) + ((n & 63) >> 3);
+  return (n & ~31) + (((n & 7) >> 1) << 3) + (((n & 31) >> 3) << 1) + (n & 1);
+}
+// Provider layout of the zero points: word (n / 64) * 8 + n % 8 of a row holds the eight columns
+// n % 8 + 8 j of the block, column j in nibble j / 2 + 4 (j % 2).
+__device__ __forceinline__ int ZeroNibble(int j) { return (j >> 1) + 4 * (j & 1); }
 
 // Scale / zero-point row that the first k of stage `ks` falls in.
 __device__ __forceinline__ int GroupOf(const GemmParams& p, int ks) {
@@ -1071,7 +1087,8 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
     uint32_t based_on = 0xffffffffu;
     const unsigned short* sbase = nullptr;
     const uint4* zbase = nullptr;
-    int col = 0;
+    const uint32_t* zword = nullptr;  // provider layout: the one word that holds this thread's four zero points
+    int col = 0, sstride = 8;
     auto fetch_groups = [&](const Cursor& c) {
       [[maybe_unused]] const Problem* cur = kBatch ? probs + c.seg.prob : probs;
       if (c.seg_it != based_on) {
@@ -1079,25 +1096,52 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
         const int n0 = tile_of(c.seg.n_tile) * kTileN;
         const size_t g0 = static_cast<size_t>(c.expert) * cur->p.groups;
         const bool inside = n0 + 32 * q < cur->p.n;
-        col = 32 * q + (lane >> 2) - (inside ? 0 : 64);
+        const int r = lane >> 2;
+        // this thread's columns 32 q + r + {0, 8, 16, 24}: first one and the step between them in a scale row
+        if (cur->p.layout == 0) {
+          col = 32 * q + r;
+          sstride = 8;
+        } else if (cur->p.groups > 1) {
+          col = 64 * (q >> 1) + 8 * r + 4 * (q & 1);
+          sstride = 1;
+        } else {
+          col = 32 * q + 8 * (r >> 1) + (r & 1);
+          sstride = 2;
+        }
+        col -= inside ? 0 : 64;
         sbase = reinterpret_cast<const unsigned short*>(cur->p.scales) + g0 * cur->p.n + n0;
-        if constexpr (kZeros) zbase = reinterpret_cast<const uint4*>(cur->p.zeros + g0 * (cur->p.n / 8) + n0 / 8) + (inside ? q : q - 2);
+        if constexpr (kZeros) {
+          zbase = reinterpret_cast<const uint4*>(cur->p.zeros + g0 * (cur->p.n / 8) + n0 / 8) + (inside ? q : q - 2);
+          zword = cur->p.layout == 0 ? nullptr
+                                     : cur->p.zeros + g0 * (cur->p.n / 8) + n0 / 8 + 8 * ((q >> 1) - (inside ? 0 : 1)) + r;
+        }
       }
+      // Zero points of the provider layout, rearranged to where the plain layout has them (nibble
+      // lane / 4 of words x, y, z, w = this thread's columns +0, +8, +16, +24), so that the
+      // conversion code below is the same for both.
+      auto load_zeros = [&](uint32_t row) -> uint4 {
+        if (zword == nullptr) return LdGlobalV4Here(zbase + static_cast<size_t>(row) * static_cast<uint32_t>(cur->p.n / 32));
+        uint32_t w;
+        asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(w) : "l"(zword + static_cast<size_t>(row) * static_cast<uint32_t>(cur->p.n / 8)));
+        const int j0 = 4 * (q & 1), at = 4 * (lane >> 2);
+        return make_uint4(((w >> (4 * ZeroNibble(j0))) & 0xFu) << at, ((w >> (4 * ZeroNibble(j0 + 1))) & 0xFu) << at,
+                          ((w >> (4 * ZeroNibble(j0 + 2))) & 0xFu) << at, ((w >> (4 * ZeroNibble(j0 + 3))) & 0xFu) << at);
+      };
       GroupRegs g;
       const uint32_t grp = static_cast<uint32_t>(GroupOf(cur->p, c.Ks()));
       const unsigned short* sp = sbase + static_cast<size_t>(grp) * static_cast<uint32_t>(cur->p.n) + col;
       g.sc[0][0] = g.sc[0][1] = g.sc[1][0] = g.sc[1][1] = 0;
       if constexpr (!kLate) {
-        g.sc[0][0] = LdGlobalU16Here(sp) | (LdGlobalU16Here(sp + 8) << 16);
-        g.sc[0][1] = LdGlobalU16Here(sp + 16) | (LdGlobalU16Here(sp + 24) << 16);
+        g.sc[0][0] = LdGlobalU16Here(sp) | (LdGlobalU16Here(sp + sstride) << 16);
+        g.sc[0][1] = LdGlobalU16Here(sp + 2 * sstride) | (LdGlobalU16Here(sp + 3 * sstride) << 16);
       }
       g.zp[0] = g.zp[1] = make_uint4(0, 0, 0, 0);
-      if constexpr (kZeros) g.zp[0] = LdGlobalV4Here(zbase + static_cast<size_t>(grp) * static_cast<uint32_t>(cur->p.n / 32));
+      if constexpr (kZeros) g.zp[0] = load_zeros(grp);
       if (!kLate && rows == 2) {
         sp += cur->p.n;
-        g.sc[1][0] = LdGlobalU16Here(sp) | (LdGlobalU16Here(sp + 8) << 16);
-        g.sc[1][1] = LdGlobalU16Here(sp + 16) | (LdGlobalU16Here(sp + 24) << 16);
-        if constexpr (kZeros) g.zp[1] = LdGlobalV4Here(zbase + static_cast<size_t>(grp + 1) * static_cast<uint32_t>(cur->p.n / 32));
+        g.sc[1][0] = LdGlobalU16Here(sp) | (LdGlobalU16Here(sp + sstride) << 16);
+        g.sc[1][1] = LdGlobalU16Here(sp + 2 * sstride) | (LdGlobalU16Here(sp + 3 * sstride) << 16);
+        if constexpr (kZeros) g.zp[1] = load_zeros(grp + 1);
       }
       return g;
     };
@@ -1372,7 +1416,7 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
 #pragma unroll
         for (int j = 0; j < kTok; ++j) sum[j] = 0.0f;
         const T* srow = static_cast<const T*>(cur->p.scales) + static_cast<size_t>(expert) * cur->p.groups * cur->p.n +
-                        (n_ok ? n : n - 64);  // a column past N borrows a valid one; it is never written
+                        ScaleColumn(cur->p, n_ok ? n : n - 64);  // a column past N borrows a valid one; it is never written
         uint32_t coming = LdGlobalU16Here(srow + static_cast<size_t>(GroupOf(cur->p, seg.k_begin)) * cur->p.n);
         bool alive = true;
         for (int ks = seg.k_begin; ks < seg.k_end; ++ks, ++it) {
@@ -2037,6 +2081,8 @@ int SetPlacement(const char* op, const iob_gemm_problem& g, GemmParams& p) {
   IOB_REQUIRE(g.out_col0 >= 0 && g.out_col0 + g.size_n <= ld && ld % 8 == 0 && g.out_col0 % 8 == 0 && ld <= INT32_MAX,
               "%s: columns [out_col0, out_col0 + size_n) must lie inside a row of out_ld elements, both multiples of 8", op);
   IOB_REQUIRE(g.n_peers >= 0 && g.n_peers <= kMaxPeers, "%s: at most %d peer outputs", op, kMaxPeers);
+  IOB_REQUIRE(g.scale_layout == 0 || g.scale_layout == 1, "%s: `scale_layout` must be 0 (plain) or 1 (provider)", op);
+  p.layout = g.scale_layout;
   p.out_ld = static_cast<int>(ld);
   p.out_col0 = static_cast<int>(g.out_col0);
   p.n_peers = g.n_peers;
@@ -2228,18 +2274,18 @@ extern "C" int infiniops_b200_moe_wna16_marlin_gemm(
     const int32_t* num_tokens_past_padded, const float* topk_weights, int64_t moe_block_size, int64_t top_k,
     int mul_topk_weights, int64_t b_type_id, int64_t size_m, int64_t size_n, int64_t size_k, int64_t num_groups,
     int64_t num_experts, int64_t sorted_size, void* out, void* scratch, size_t scratch_bytes, void* stream) {
-  return infiniops_b200_moe_wna16_marlin_gemm_scattered(
+  return infiniops_b200_moe_wna16_marlin_gemm_ex(
       a, a_dtype, b_q_weight, b_bias, b_scales, b_zeros, sorted_token_ids, expert_ids, num_tokens_past_padded,
       topk_weights, moe_block_size, top_k, mul_topk_weights, b_type_id, size_m, size_n, size_k, num_groups, num_experts,
       sorted_size, out, nullptr, scratch, scratch_bytes, stream);
 }
 
-extern "C" int infiniops_b200_moe_wna16_marlin_gemm_scattered(
+extern "C" int infiniops_b200_moe_wna16_marlin_gemm_ex(
     const void* a, int a_dtype, const int32_t* b_q_weight, const void* b_bias, const void* b_scales,
     const int32_t* b_zeros, const int32_t* sorted_token_ids, const int32_t* expert_ids,
     const int32_t* num_tokens_past_padded, const float* topk_weights, int64_t moe_block_size, int64_t top_k,
     int mul_topk_weights, int64_t b_type_id, int64_t size_m, int64_t size_n, int64_t size_k, int64_t num_groups,
-    int64_t num_experts, int64_t sorted_size, void* out, const iob_routed_scatter* scatter, void* scratch,
+    int64_t num_experts, int64_t sorted_size, void* out, const iob_routed_options* options, void* scratch,
     size_t scratch_bytes, void* stream) {
   using namespace iob;
   const char* op = "moe_wna16_marlin_gemm";
@@ -2305,15 +2351,19 @@ extern "C" int infiniops_b200_moe_wna16_marlin_gemm_scattered(
   p.block_size = static_cast<int>(moe_block_size);
   p.mul_weights = mul_topk_weights;
   p.out_rows = out_rows;
-  if (scatter != nullptr) {
-    IOB_REQUIRE(scatter->row_dest != nullptr && scatter->n_dest > 0 && scatter->n_dest <= kMaxPeers + 1,
-                "%s: incomplete scatter description", op);
-    p.row_dest = reinterpret_cast<const int2*>(scatter->row_dest);
-    for (int r = 0; r < scatter->n_dest; ++r) {
-      IOB_REQUIRE(scatter->dest_base[r] != nullptr, "%s: null scatter destination", op);
-      p.dest_base[r] = scatter->dest_base[r];
+  if (options != nullptr) {
+    IOB_REQUIRE(options->scale_layout == 0 || options->scale_layout == 1,
+                "%s: `scale_layout` must be 0 (plain) or 1 (provider)", op);
+    p.layout = options->scale_layout;
+    if (options->row_dest != nullptr) {
+      IOB_REQUIRE(options->n_dest > 0 && options->n_dest <= kMaxPeers + 1, "%s: incomplete scatter description", op);
+      p.row_dest = reinterpret_cast<const int2*>(options->row_dest);
+      for (int r = 0; r < options->n_dest; ++r) {
+        IOB_REQUIRE(options->dest_base[r] != nullptr, "%s: null scatter destination", op);
+        p.dest_base[r] = options->dest_base[r];
+      }
     }
-    if (const int rc = SetSignal(op, scatter->signal, p)) return rc;
+    if (const int rc = SetSignal(op, options->signal, p)) return rc;
   }
   return Dispatch<true>(a_dtype, b_zeros != nullptr, tok, map, w_map, /*c_map (unused: rows are scattered)=*/w_map, p, NumSms(), s);
 }
