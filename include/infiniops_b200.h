@@ -401,10 +401,17 @@ int infiniops_b200_moe_wna16_gemm(const void* input, int dtype, const uint8_t* b
  * call) two int32: the GPU the row belongs to and its row in that GPU's destination matrix
  * [rows, size_n]; `dest_base[g]` is that matrix of GPU g as mapped into this process (this GPU's
  * own included), `n_dest` their number (at most 8).  With a `row_dest`, `out` is only validated.
- * `signal` (or NULL) is raised when the launch has finished.  Zero-initialise the struct.
- * No counterpart in the reference. */
+ * `signal` (or NULL) is raised when the launch has finished.
+ * `a_sorted`: `a` is not [size_m, K] but already holds one row per position of `sorted_token_ids`
+ * ([>= sorted_size rows, K]: row i belongs to entry i), so the GEMM reads it in place instead of
+ * gathering.  `out_sorted`: the result is written as [sorted_size, N] in the same sorted order (row i
+ * = entry i, padding entries included) with tile stores instead of one scattered row per entry; not
+ * together with `mul_topk_weights` or `row_dest`.  Chaining w13 (out_sorted) -> silu_and_mul -> w2
+ * (a_sorted) keeps the intermediate in expert order and scatters only once, at the end.
+ * Zero-initialise the struct.  No counterpart in the reference. */
 typedef struct {
   int scale_layout;
+  int a_sorted, out_sorted;
   const int32_t* row_dest;
   void* dest_base[IOB_MAX_PEERS + 1];
   int n_dest;

@@ -74,7 +74,8 @@ class PeerSignal(ctypes.Structure):
 
 class RoutedOptions(ctypes.Structure):
     """`iob_routed_options`."""
-    _fields_ = [("scale_layout", _int), ("row_dest", _vp), ("dest_base", _vp * (MAX_PEERS + 1)), ("n_dest", _int),
+    _fields_ = [("scale_layout", _int), ("a_sorted", _int), ("out_sorted", _int), ("row_dest", _vp),
+                ("dest_base", _vp * (MAX_PEERS + 1)), ("n_dest", _int),
                 ("signal", ctypes.POINTER(PeerSignal))]
 
 
@@ -254,13 +255,14 @@ def marlin_gemm_static_scratch(a, b_q_weight, b_bias, b_scales, b_zeros, b_type_
 
 def moe_wna16_marlin_gemm(a, b_q_weight, b_bias, b_scales, b_zeros, sorted_token_ids, expert_ids,
                           num_tokens_past_padded, topk_weights, moe_block_size, top_k, mul_topk_weights, b_type_id,
-                          size_m, size_n, size_k, out, stream=None, scratch_buf=None, scale_layout=0):
+                          size_m, size_n, size_k, out, stream=None, scratch_buf=None, scale_layout=0, a_sorted=False,
+                          out_sorted=False):
     e = b_q_weight.shape[0]
     need = lib().infiniops_b200_moe_wna16_marlin_gemm_scratch_bytes(size_m, top_k, size_n, size_k, e,
                                                                     moe_block_size)
     buf = scratch_buf if scratch_buf is not None else scratch(a.device, need)
     options = RoutedOptions()
-    options.scale_layout = scale_layout
+    options.scale_layout, options.a_sorted, options.out_sorted = scale_layout, int(a_sorted), int(out_sorted)
     _check(lib().infiniops_b200_moe_wna16_marlin_gemm_ex(
         _ptr(a), _DTYPE[a.dtype], _ptr(b_q_weight), _ptr(b_bias), _ptr(b_scales), _ptr(b_zeros),
         _ptr(sorted_token_ids), _ptr(expert_ids), _ptr(num_tokens_past_padded), _ptr(topk_weights), moe_block_size,

@@ -10,7 +10,8 @@
 //   wait      bounded wait for every other rank's epoch
 //   unpack    received (expert, weight, origin) -> the id / weight / destination arrays of the
 //             routed GEMMs; slots beyond a sender's count become id -1
-//   experts   moe_align_block_size -> w13 GEMM -> silu_and_mul -> w2 GEMM whose epilogue stores each
+//   experts   moe_align_block_size -> w13 GEMM (result kept in sorted order, stored as tiles) ->
+//             silu_and_mul -> w2 GEMM (reads the sorted rows in place) whose epilogue stores each
 //             result row into the arena of the rank the token came from and raises the epoch again
 //   wait, moe_sum
 //
@@ -194,8 +195,9 @@ Workspace PlanWorkspace(const iob_ep_context& c) {
   w.sorted = take(static_cast<size_t>(w.sorted_size) * 4);
   w.experts = take(static_cast<size_t>(w.blocks) * 4);
   w.npost = take(4);
-  w.g = take(static_cast<size_t>(w.rows) * 2 * c.inter * 2);
-  w.h = take(static_cast<size_t>(w.rows) * c.inter * 2);
+  // the intermediates stay in sorted (expert) order: one row per position of the sorted id list
+  w.g = take(static_cast<size_t>(w.sorted_size) * 2 * c.inter * 2);
+  w.h = take(static_cast<size_t>(w.sorted_size) * c.inter * 2);
   w.gemm_bytes = std::max(
       infiniops_b200_moe_wna16_marlin_gemm_scratch_bytes(w.rows, 1, 2 * c.inter, c.hidden, c.experts_per_rank, c.moe_block_size),
       infiniops_b200_moe_wna16_marlin_gemm_scratch_bytes(w.rows, 1, c.hidden, c.inter, c.experts_per_rank, c.moe_block_size));
@@ -296,14 +298,16 @@ extern "C" int infiniops_b200_ep_moe_layer(const iob_ep_context* ctx, const iob_
                                                          w.align_bytes ? ws + w.align : nullptr, w.align_bytes, stream)) {
     return rc;
   }
-  if (const int rc = infiniops_b200_moe_wna16_marlin_gemm(
+  iob_routed_options first{};
+  first.out_sorted = 1;
+  if (const int rc = infiniops_b200_moe_wna16_marlin_gemm_ex(
           own + lay.rows, c.a_dtype, weights->w13, nullptr, weights->s13, weights->z13, sorted, expert_ids, npost,
           row_weights, c.moe_block_size, 1, 0, c.b_type_id, w.rows, 2 * c.inter, c.hidden, weights->groups13,
-          c.experts_per_rank, w.sorted_size, ws + w.g, ws + w.gemm, w.gemm_bytes, stream)) {
+          c.experts_per_rank, w.sorted_size, ws + w.g, &first, ws + w.gemm, w.gemm_bytes, stream)) {
     return rc;
   }
   {
-    const int64_t shape[2] = {w.rows, c.inter};
+    const int64_t shape[2] = {w.sorted_size, c.inter};
     const int64_t in_strides[2] = {2 * c.inter, 1}, out_strides[2] = {c.inter, 1};
     if (const int rc = infiniops_b200_silu_and_mul(ws + w.g, ws + w.h, c.a_dtype, 2, shape, in_strides, out_strides, stream)) {
       return rc;
@@ -321,6 +325,7 @@ extern "C" int infiniops_b200_ep_moe_layer(const iob_ep_context* ctx, const iob_
   scatter.n_dest = c.world;
   for (int g = 0; g < c.world; ++g) scatter.dest_base[g] = peers.arena[g] + lay.routed;
   scatter.signal = c.world > 1 ? &signal : nullptr;
+  scatter.a_sorted = 1;
   if (const int rc = infiniops_b200_moe_wna16_marlin_gemm_ex(
           ws + w.h, c.a_dtype, weights->w2, nullptr, weights->s2, weights->z2, sorted, expert_ids, npost, row_weights,
           c.moe_block_size, 1, 1, c.b_type_id, w.rows, c.hidden, c.inter, weights->groups2, c.experts_per_rank,

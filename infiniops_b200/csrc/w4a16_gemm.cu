@@ -122,6 +122,7 @@ struct GemmParams {
   int* peer_flags[kMaxPeers];
   int flag_slot, n_flag_peers;
   // routed form only
+  int out_sorted;                   // 1: result rows stay in sorted order (row = position in `sorted_ids`), stored as tiles
   const int2* row_dest;             // null, or per output row: (GPU, row there) the result row is stored to
   void* dest_base[kMaxPeers + 1];   // with `row_dest`: the destination matrix of every GPU (own included)
   const int32_t* sorted_ids;
@@ -635,7 +636,8 @@ struct Shared {
 // read it out stage by stage and apply the group's scale in fp32.  That takes the multiply off the
 // dequantisers, whose instruction issue is what bounds small-M problems.
 //
-// kPair (256-token tiles, dense, N a multiple of 256): two blocks of a cluster work as one.  Each
+// kPair (256-token tiles, N a multiple of 256; dense, or routed with routing blocks of 256 rows): two
+// blocks of a cluster work as one.  Each
 // dequantises its own 128 output columns into its own tensor memory and loads only half of the
 // 256 activation rows; one thread of the even block issues `cta_group::2` MMAs (M = 256, N = 256)
 // that run on both SMs and read the two activation halves from the two shared memories.  Per
@@ -656,7 +658,7 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
   static_assert(kStages % kSets == 0 && kAStages % kSets == 0, "a ring slot must always meet the same dequantiser set");
   static_assert(kPair || SplitTokens(kTok) || (kStages % IssuersFor(kTok) == 0 && kAStages % IssuersFor(kTok) == 0),
                 "a ring slot must always meet the same issuer");
-  static_assert(!kPair || (kTok == 256 && !kMoe && !kLate), "paired blocks: dense 256-token tiles only");
+  static_assert(!kPair || (kTok == 256 && !kLate), "paired blocks: 256-token tiles only");
   constexpr int kActRows = kPair ? kTok / 2 : kTok;  // activation rows this block loads per stage
   constexpr int kAtomBytes = kActRows * 128;          // one 64-k activation atom
   constexpr int kActBytes = 2 * kAtomBytes;
@@ -1060,7 +1062,8 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
           // Both halves of the tile are counted on the even block's barrier, which that block arms
           // for the two of them; the odd block's copy reports there directly.
           if (rank == 0) MbarExpectTx(SmemAddr(&sh.act_full[sa]), 2 * kActBytes);
-          TmaLoad3DPair(acts_addr + sa * kActBytes, &cur->a_map, 0, c.seg.m_tile * kTok + static_cast<int>(rank) * kActRows,
+          TmaLoad3DPair(acts_addr + sa * kActBytes, &cur->a_map, 0,
+                        (kMoe ? c.seg.m_tile * cur->p.block_size : c.seg.m_tile * kTok) + static_cast<int>(rank) * kActRows,
                         2 * c.Ks(), MapToBlock(SmemAddr(&sh.act_full[sa]), 0));
           ++c.it;
         }
@@ -1327,6 +1330,10 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
       auto emit = [&](int j, float v) {
         v += bias_v;
         if constexpr (kMoe) {
+          if (cur->p.out_sorted) {
+            out[static_cast<size_t>(row0 + j) * cur->p.n + n] = FromFloat<T>(v);
+            return;
+          }
           const int id = cur->p.sorted_ids[row0 + j];
           if (id < cur->p.out_rows) {
             if (cur->p.mul_weights) v *= cur->p.topk_weights[id];
@@ -1355,7 +1362,7 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
       // whole tile, else this block's partial
       auto finish_chunk = [&](int c, const uint32_t (&r)[16]) {
         if (whole) {
-          if constexpr (!kMoe) {
+          if (!kMoe || cur->p.out_sorted) {
             // Dense output: the warp's 16 rows x 32 columns are transposed through shared memory
             // and leave as one asynchronous tile store (clipped at M and N by the tensor map), so
             // the warp is not held up by 16 strided 64-byte store instructions per chunk and the
@@ -1396,9 +1403,11 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
               ++staged;
             }
           } else if (n_ok) {
+            if constexpr (kMoe) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              if (c + j < m_valid) emit(c + j, __uint_as_float(r[j]));
+              for (int j = 0; j < 16; ++j) {
+                if (c + j < m_valid) emit(c + j, __uint_as_float(r[j]));
+              }
             }
           }
         } else {
@@ -1978,7 +1987,7 @@ int LaunchKernel(const CUtensorMap& map, const CUtensorMap& w_map, const CUtenso
   if constexpr (kTok <= 32 || (kTok == 64 && !kMoe)) {
     if (p.group_size >= kBlockK) return LaunchVariant<T, kTok, kZeros, kMoe, true>(map, w_map, c_map, p, grid, stream);
   }
-  if constexpr (kTok == 256 && !kMoe) {
+  if constexpr (kTok == 256) {
     if (p.pair) return LaunchVariant<T, kTok, kZeros, kMoe, false, true>(map, w_map, c_map, p, grid, stream);
   }
   return LaunchVariant<T, kTok, kZeros, kMoe, false>(map, w_map, c_map, p, grid, stream);
@@ -1993,10 +2002,8 @@ int DispatchTok(int tok, const CUtensorMap& map, const CUtensorMap& w_map, const
     case 64: return LaunchKernel<T, 64, kZeros, kMoe>(map, w_map, c_map, p, grid, stream);
     default: break;
   }
-  if constexpr (!kMoe) {
-    if (tok == 128) return LaunchKernel<T, 128, kZeros, kMoe>(map, w_map, c_map, p, grid, stream);
-    if (tok == 256) return LaunchKernel<T, 256, kZeros, kMoe>(map, w_map, c_map, p, grid, stream);
-  }
+  if (tok == 128) return LaunchKernel<T, 128, kZeros, kMoe>(map, w_map, c_map, p, grid, stream);
+  if (tok == 256) return LaunchKernel<T, 256, kZeros, kMoe>(map, w_map, c_map, p, grid, stream);
   return Fail(IOB_UNSUPPORTED, "W4A16 GEMM: no kernel for a token tile of %d", tok);
 }
 
@@ -2295,7 +2302,10 @@ extern "C" int infiniops_b200_moe_wna16_marlin_gemm_ex(
   }
   IOB_REQUIRE(sorted_token_ids && expert_ids && num_tokens_past_padded, "%s: received invalid routing metadata", op);
   IOB_REQUIRE(top_k > 0 && num_experts > 0 && size_m <= INT32_MAX / top_k, "%s: output dimensions overflow", op);
-  IOB_REQUIRE(moe_block_size == 8 || (moe_block_size >= 16 && moe_block_size <= 64 && moe_block_size % 16 == 0),
+  // (8..64: the sizes the reference accepts; 128 and 256: larger routing blocks for callers that sort
+  // with them -- each weight is then converted once per 128 / 256 rows instead of once per 64)
+  IOB_REQUIRE(moe_block_size == 8 || (moe_block_size >= 16 && moe_block_size <= 64 && moe_block_size % 16 == 0) ||
+                  moe_block_size == 128 || moe_block_size == 256,
               "%s: received an unsupported `moe_block_size`", op);
   IOB_REQUIRE(!mul_topk_weights || topk_weights != nullptr, "%s: received invalid top-k weights", op);
   const int tok = TokenTile(moe_block_size);
@@ -2311,24 +2321,33 @@ extern "C" int infiniops_b200_moe_wna16_marlin_gemm_ex(
   }
   auto s = static_cast<cudaStream_t>(stream);
   auto* base = static_cast<unsigned char*>(scratch);
-  void* gathered = base + plan.gathered_off;
+  const bool a_sorted = options != nullptr && options->a_sorted != 0;
+  const void* gathered = a_sorted ? a : base + plan.gathered_off;
   const int out_rows = static_cast<int>(size_m * top_k);
   const int gather_grid = static_cast<int>(std::min<int64_t>(sorted_cap, 4 * NumSms()));
-  if (a_dtype == IOB_BF16) {
+  if (a_sorted) {
+    // `a` already holds one row per sorted position: nothing to gather
+  } else if (a_dtype == IOB_BF16) {
     GatherRowsKernel<__nv_bfloat16><<<gather_grid, 256, 0, s>>>(
-        static_cast<const __nv_bfloat16*>(a), static_cast<__nv_bfloat16*>(gathered), sorted_token_ids,
+        static_cast<const __nv_bfloat16*>(a), reinterpret_cast<__nv_bfloat16*>(base + plan.gathered_off), sorted_token_ids,
         num_tokens_past_padded, static_cast<int>(size_k), static_cast<int>(top_k), out_rows);
   } else {
-    GatherRowsKernel<__half><<<gather_grid, 256, 0, s>>>(static_cast<const __half*>(a), static_cast<__half*>(gathered),
+    GatherRowsKernel<__half><<<gather_grid, 256, 0, s>>>(static_cast<const __half*>(a), reinterpret_cast<__half*>(base + plan.gathered_off),
                                                         sorted_token_ids, num_tokens_past_padded,
                                                         static_cast<int>(size_k), static_cast<int>(top_k), out_rows);
   }
   if (const int rc = CheckLaunch("moe_wna16_marlin_gemm gather launch")) return rc;
+  // 256-row routing blocks whose columns pair up run two blocks of a cluster per 256 x 256 tile
+  const bool pair = tok == 256 && size_n % (2 * kTileN) == 0 && NumSms() >= 2;
   CUtensorMap map;
-  if (const int rc = ActivationMap(gathered, sorted_cap + tok, size_k, tok, a_dtype, &map)) return rc;
+  // (rows past the end of a caller's sorted buffer read as zeros; the scratch copy has a spare box of rows)
+  if (const int rc = ActivationMap(gathered, a_sorted ? sorted_cap : sorted_cap + tok, size_k, pair ? tok / 2 : tok, a_dtype, &map)) {
+    return rc;
+  }
   CUtensorMap w_map;
   if (const int rc = WeightMap(b_q_weight, num_experts, size_k, size_n, &w_map)) return rc;
   GemmParams p{};
+  p.pair = pair ? 1 : 0;
   p.wq = reinterpret_cast<const uint32_t*>(b_q_weight);
   p.scales = b_scales;
   p.zeros = reinterpret_cast<const uint32_t*>(b_zeros);
@@ -2355,6 +2374,9 @@ extern "C" int infiniops_b200_moe_wna16_marlin_gemm_ex(
     IOB_REQUIRE(options->scale_layout == 0 || options->scale_layout == 1,
                 "%s: `scale_layout` must be 0 (plain) or 1 (provider)", op);
     p.layout = options->scale_layout;
+    p.out_sorted = options->out_sorted ? 1 : 0;
+    IOB_REQUIRE(!p.out_sorted || (!mul_topk_weights && options->row_dest == nullptr),
+                "%s: sorted output takes neither routing weights nor a scatter", op);
     if (options->row_dest != nullptr) {
       IOB_REQUIRE(options->n_dest > 0 && options->n_dest <= kMaxPeers + 1, "%s: incomplete scatter description", op);
       p.row_dest = reinterpret_cast<const int2*>(options->row_dest);
@@ -2365,7 +2387,11 @@ extern "C" int infiniops_b200_moe_wna16_marlin_gemm_ex(
     }
     if (const int rc = SetSignal(op, options->signal, p)) return rc;
   }
-  return Dispatch<true>(a_dtype, b_zeros != nullptr, tok, map, w_map, /*c_map (unused: rows are scattered)=*/w_map, p, NumSms(), s);
+  CUtensorMap c_map = w_map;  // unused while rows are scattered
+  if (p.out_sorted) {
+    if (const int rc = OutputMap(out, sorted_cap, size_n, a_dtype, &c_map)) return rc;
+  }
+  return Dispatch<true>(a_dtype, b_zeros != nullptr, tok, map, w_map, c_map, p, NumSms(), s);
 }
 
 // ---- dense GEMM for callers that may not allocate device memory ---------------------------------

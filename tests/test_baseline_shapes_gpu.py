@@ -273,3 +273,76 @@ def test_every_accepted_block_size(block):
     _scratch_ok()
     seen = _check_routed(x, w, s, None, None, sorted_ids, expert_ids, npost, tw.reshape(-1), block, top_k, True, out)
     assert bool(seen.all()) and not torch.isnan(out.float()).any()
+
+
+@pytest.mark.parametrize("block,n,zeros,mul", ((128, 384, False, True), (256, 512, True, True), (256, 384, False, False),
+                                               (256, 2048, True, False)))
+def test_large_routing_blocks(block, n, zeros, mul):
+    """Routing blocks of 128 and 256 rows (beyond the reference's set; the sort accepts any block size):
+    the 128-token kernel, the 256-token kernel, and -- when the columns pair up -- the paired-block
+    kernel in its routed form, with whole and K-split tiles."""
+    from infiniops_b200 import capi
+
+    tokens, experts, top_k, hidden = 700, 8, 2, 1024
+    ids = torch.randint(0, experts, (tokens, top_k), dtype=torch.int32, device="cuda")
+    tw = torch.rand((tokens, top_k), device="cuda")
+    w, s, z = _experts(experts, hidden, n, zeros, 70 + block + n)
+    size, blocks = omoe.padded_sizes(tokens * top_k, experts, block)
+    sorted_ids = torch.empty(size, dtype=torch.int32, device="cuda")
+    expert_ids = torch.empty(blocks, dtype=torch.int32, device="cuda")
+    npost = torch.empty(1, dtype=torch.int32, device="cuda")
+    capi.moe_align_block_size(ids, None, experts, block, sorted_ids, expert_ids, npost)
+    rs, re, rn = omoe.moe_align_block_size(ids.cpu(), None, experts, block)
+    assert np.array_equal(sorted_ids.cpu().numpy(), rs) and np.array_equal(expert_ids.cpu().numpy(), re)
+    x = torch.randn((tokens, hidden), device="cuda").bfloat16()
+    out = torch.full((tokens * top_k, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    capi.moe_wna16_marlin_gemm(x, w, None, s, z, sorted_ids, expert_ids, npost, tw.reshape(-1), block, top_k, mul,
+                               capi.QTYPE_UINT4 if zeros else capi.QTYPE_UINT4B8, tokens, n, hidden, out)
+    _scratch_ok()
+    seen = _check_routed(x, w, s, z, None, sorted_ids, expert_ids, npost, tw.reshape(-1), block, top_k, mul, out)
+    assert bool(seen.all()) and not torch.isnan(out.float()).any()
+
+
+@pytest.mark.parametrize("block,zeros", ((16, False), (64, True), (128, False), (256, True)))
+def test_sorted_order_chain_equals_the_scattered_chain(block, zeros):
+    """w13 with `out_sorted` (dense tile stores, rows in sorted order) -> silu_and_mul -> w2 with `a_sorted`
+    (reads the sorted rows in place) must give, row for row, what the chain through route-ordered
+    intermediates gives: the arithmetic per row is the same, only where the rows live differs."""
+    from infiniops_b200 import capi
+
+    tokens, experts, top_k, hidden, inter = 600, 8, 2, 512, 256
+    qtype = capi.QTYPE_UINT4 if zeros else capi.QTYPE_UINT4B8
+    ids = torch.randint(0, experts, (tokens, top_k), dtype=torch.int32, device="cuda")
+    tw = torch.rand((tokens, top_k), device="cuda").reshape(-1)
+    w13, s13, z13 = _experts(experts, hidden, 2 * inter, zeros, 80 + block)
+    w2, s2, z2 = _experts(experts, inter, hidden, zeros, 81 + block)
+    size, blocks = omoe.padded_sizes(tokens * top_k, experts, block)
+    sorted_ids = torch.empty(size, dtype=torch.int32, device="cuda")
+    expert_ids = torch.empty(blocks, dtype=torch.int32, device="cuda")
+    npost = torch.empty(1, dtype=torch.int32, device="cuda")
+    capi.moe_align_block_size(ids, None, experts, block, sorted_ids, expert_ids, npost)
+    x = torch.randn((tokens, hidden), device="cuda").bfloat16()
+    rows = tokens * top_k
+
+    g = torch.full((rows, 2 * inter), float("nan"), dtype=torch.bfloat16, device="cuda")
+    capi.moe_wna16_marlin_gemm(x, w13, None, s13, z13, sorted_ids, expert_ids, npost, tw, block, top_k, False, qtype,
+                               tokens, 2 * inter, hidden, g)
+    h = torch.empty((rows, inter), dtype=torch.bfloat16, device="cuda")
+    capi.silu_and_mul(g, h)
+    y = torch.full((rows, hidden), float("nan"), dtype=torch.bfloat16, device="cuda")
+    capi.moe_wna16_marlin_gemm(h, w2, None, s2, z2, sorted_ids, expert_ids, npost, tw, block, 1, True, qtype, rows, hidden,
+                               inter, y)
+
+    gs = torch.full((size, 2 * inter), float("nan"), dtype=torch.bfloat16, device="cuda")
+    capi.moe_wna16_marlin_gemm(x, w13, None, s13, z13, sorted_ids, expert_ids, npost, tw, block, top_k, False, qtype,
+                               tokens, 2 * inter, hidden, gs, out_sorted=True)
+    hs = torch.empty((size, inter), dtype=torch.bfloat16, device="cuda")
+    capi.silu_and_mul(gs, hs)
+    ys = torch.full((rows, hidden), float("nan"), dtype=torch.bfloat16, device="cuda")
+    capi.moe_wna16_marlin_gemm(hs, w2, None, s2, z2, sorted_ids, expert_ids, npost, tw, block, 1, True, qtype, rows, hidden,
+                               inter, ys, a_sorted=True)
+    _scratch_ok()
+    sorted_cpu = sorted_ids.cpu().long()
+    live = torch.nonzero(sorted_cpu[: int(npost.cpu()[0])] < rows).flatten()
+    assert torch.equal(gs[live.cuda()], g[sorted_cpu[live].cuda()])
+    assert not torch.isnan(ys.float()).any() and torch.equal(ys, y)
