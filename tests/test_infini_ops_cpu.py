@@ -7,7 +7,8 @@ import textwrap
 import pytest
 
 NAMES = ("gptq_marlin_repack", "awq_marlin_repack", "marlin_gemm", "moe_wna16_marlin_gemm", "topk_softmax",
-         "grouped_topk", "moe_align_block_size", "silu_and_mul", "moe_sum")
+         "grouped_topk", "moe_align_block_size", "silu_and_mul", "moe_sum", "topk_sigmoid", "moe_wna16_gemm",
+         "get_cutlass_moe_mm_data")
 
 
 @pytest.fixture(scope="module")
@@ -24,8 +25,10 @@ def test_module_surface(ops):
     for name in NAMES:
         assert callable(getattr(ops, name))
         cls = getattr(ops, "".join(part.capitalize() for part in name.split("_")))
-        assert cls.active_implementation_indices("cuda") == [0]
-        assert cls.active_implementation_indices("nvidia") == [0]
+        # slot 0 everywhere; the two Marlin GEMMs also answer at the provider slot (vLLM's scale layouts)
+        slots = [0, 16] if name in ("marlin_gemm", "moe_wna16_marlin_gemm") else [0]
+        assert cls.active_implementation_indices("cuda") == slots
+        assert cls.active_implementation_indices("nvidia") == slots
         assert cls.active_implementation_indices("cpu") == []
         cls.clear_cache()
     with pytest.raises(ValueError):
