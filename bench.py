@@ -269,7 +269,7 @@ def run_ours(args):
         capi.marlin_gemm_batch(tables[phase], torch.bfloat16, UINT4, scratch, signal=signal, stream=stream)
         if group is not None:
             group.wait(stream=stream)
-        return 2 + (1 if group is not None else 0)
+        return 2 + (1 if group is not None else 0)   # two classes of token tile (M <= 16, M = 64): one launch each
 
     def step_per_gemm(phase, stream=None):
         for i, g in enumerate(singles[phase]):
@@ -484,7 +484,8 @@ def e2e_decode(d, args, layers, acts, keys, full_n, phases):
 # ---------------------------------------------------------------------------------------------------
 def bench_prefill(d, group):
     """configs[2]: the four linears at M = 4096, GPTQ-symmetric, bf16.  TFLOP/s per linear and for the four
-    together, against the measured bf16 peak (burst: each GEMM is timed on its own).  With N > 1 every
+    together, against the measured bf16 burst peak (the fraction of the sustained figure is reported beside
+    it); every linear is timed as short runs of back-to-back launches.  With N > 1 every
     rank computes its column shard and the epilogue stores it into every rank's full-width result."""
     from infiniops_b200 import capi
 
@@ -494,45 +495,42 @@ def bench_prefill(d, group):
     out = {"metric": "W4A16 GEMM TFLOP/s (prefill, M=4096)", "unit": "TFLOP/s", "linears": {},
            "workload": "configs[2]: qkv, o, gate_up, down at M=4096, GPTQ symmetric int4, g=128, bf16"}
     gen = torch.Generator(device=device).manual_seed(SEED + 2000 + rank)
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
     total_ms, total_flops = 0.0, 0
-    peer_buf = None
     if group is not None:
         off = group.carve(m * 28672 * 2)
+    sets = 3   # activations / results in rotation: A + C of a linear are 67..270 MB, three sets exceed the 126 MB L2
+    reps = 6
     for name, k, n in SHAPES:
         n_local = n // world
         marlin = torch.randint(-2**31, 2**31 - 1, (k // 16, 2 * n_local), dtype=torch.int32, device=device, generator=gen)
         scales = (torch.randn((k // GROUP, n_local), device=device, generator=gen).abs() * 0.01 + 1e-3).bfloat16()
-        a = torch.randn((m, k), device=device, generator=gen).bfloat16()
+        acts = [torch.randn((m, k), device=device, generator=gen).bfloat16() for _ in range(sets)]
         if group is None:
-            full = torch.empty((m, n), dtype=torch.bfloat16, device=device)
-            peers = []
-        else:
-            full = group.local(off, (m, n), torch.bfloat16)
-            peers = [group.address(r, off) for r in group.others()]
-        g = capi.gemm_problem(a, marlin, None, scales, None, full, m, n_local, k, out_ld=n, out_col0=rank * n_local,
-                              peer_out=peers)
+            fulls = [torch.empty((m, n), dtype=torch.bfloat16, device=device) for _ in range(sets)]
+            peers = [[]] * sets
+        else:   # one peer-mapped result matrix (the largest linear alone is 235 MB, more than L2)
+            fulls = [group.local(off, (m, n), torch.bfloat16)] * sets
+            peers = [[group.address(r, off) for r in group.others()]] * sets
+        problems = [capi.gemm_problem(acts[i], marlin, None, scales, None, fulls[i], m, n_local, k, out_ld=n,
+                                      out_col0=rank * n_local, peer_out=peers[i]) for i in range(sets)]
         scratch = torch.zeros(capi.lib().infiniops_b200_marlin_gemm_scratch_bytes(m, n_local, k), dtype=torch.uint8,
                               device=device)
         signal = None if group is None else group.signal()
 
-        def launch():
-            capi.marlin_gemm_placed(g, torch.bfloat16, UINT4B8, scratch, signal=signal)
+        def launch(i):
+            capi.marlin_gemm_placed(problems[i % sets], torch.bfloat16, UINT4B8, scratch, signal=signal)
             if group is not None:
                 group.wait()
 
-        for _ in range(3):
-            launch()
-        times = []
-        for _ in range(7):
-            flush.zero_()
-            d.barrier()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            launch()
-            e1.record()
-            d.barrier()
-            times.append(d.max_over_ranks([e0.elapsed_time(e1)])[0])
+        for i in range(3):
+            launch(i)
+
+        def run(count):
+            for i in range(count):
+                launch(i)
+
+        times = timed_regions(d, run, reps, 5)   # ms per launch, back to back as in a prefill pass
+        torch.cuda.synchronize()
         assert capi.scratch_status(scratch) == 0
         ms = statistics.median(times)
         flops = 2 * m * k * n
@@ -540,13 +538,14 @@ def bench_prefill(d, group):
                                              "frac_of_bf16_peak": flops / (ms * 1e-3) / 1e12 / (peaks["bf16"] * world)}
         total_ms += ms
         total_flops += flops
-        del marlin, scales, a, scratch
+        del marlin, scales, acts, fulls, problems, scratch
     out["value"] = total_flops / (total_ms * 1e-3) / 1e12
     out["ms_per_step"] = total_ms
     out["roofline"] = {"bound": "tensor", "achieved": out["value"] / world, "peak": peaks["bf16"], "unit": "TFLOP/s",
                        "frac": out["value"] / world / peaks["bf16"], "peak_kind": f"of {peaks['kind']} (burst), per GPU",
                        "frac_of_sustained": out["value"] / world / peaks["bf16_sustained"]}
-    out["timing"] = "median of 7 single launches per linear, L2 flushed in between, CUDA events, max over ranks"
+    out["timing"] = ("per linear: 5 regions of 6 back-to-back launches over 3 sets of activations and results in rotation "
+                     "(inputs larger than L2), CUDA events, max over ranks; median")
     return out
 
 
@@ -925,10 +924,10 @@ def run_one_batch(args):
     problems, keep = [], []
     for name, k, n in SHAPES:
         n = max(128, n // shrink // 128 * 128)
-        marlin = torch.randint(-2**31, 2**31 - 1, (k // 16, 2 * n), dtype=torch.int32, device=dev, generator=gen)
-        scales = (torch.randn((k // GROUP, n), device=dev, generator=gen).abs() * 0.01 + 1e-3).bfloat16()
-        zeros = torch.randint(-2**31, 2**31 - 1, (k // GROUP, n // 8), dtype=torch.int32, device=dev, generator=gen)
-        for m in MS:
+        for m in (tuple(int(v) for v in args.ms.split(",")) if args.ms else MS):   # weights of their own for every problem, as in the step (nothing is shared through L2)
+            marlin = torch.randint(-2**31, 2**31 - 1, (k // 16, 2 * n), dtype=torch.int32, device=dev, generator=gen)
+            scales = (torch.randn((k // GROUP, n), device=dev, generator=gen).abs() * 0.01 + 1e-3).bfloat16()
+            zeros = torch.randint(-2**31, 2**31 - 1, (k // GROUP, n // 8), dtype=torch.int32, device=dev, generator=gen)
             a = torch.randn((m, k), device=dev, generator=gen).bfloat16()
             out = torch.empty((m, n), dtype=torch.bfloat16, device=dev)
             keep.append((marlin, scales, zeros, a, out))
@@ -958,6 +957,7 @@ def main():
     parser.add_argument("--moe-block", type=int, default=64, help="routing block of the MoE workload (0 = adaptive)")
     parser.add_argument("--one", default=None, help="M,K,N: run this single GEMM three times (profiling case)")
     parser.add_argument("--one-batch", default=None, help="S: the batched step on linears shrunk by S, three times")
+    parser.add_argument("--ms", default=None, help="--one-batch: the row counts to include, e.g. 1,4,16")
     parser.add_argument("--gptq", action="store_true", help="--one: GPTQ-symmetric weights instead of AWQ")
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=100)

@@ -161,6 +161,14 @@ __device__ __forceinline__ int ScaleColumn(const GemmParams& p, int n) {
 __device__ __forceinline__ int ZeroNibble(int j) { return (j >> 1) + 4 * (j & 1); }
 
 // Scale / zero-point row that the first k of stage `ks` falls in.
+// The same with the problem's constants held in registers: in a batched launch the parameters of
+// the problem at hand sit behind a pointer that moves, and reading them stage after stage costs a
+// chain of dependent constant loads in the roles that pace the pipeline.
+struct GroupMap {
+  int mul, shift, size, n;
+  __device__ __forceinline__ int Of(int ks) const { return shift >= 0 ? (ks * mul) >> shift : ks * kBlockK / size; }
+};
+__device__ __forceinline__ GroupMap MakeGroupMap(const GemmParams& p) { return GroupMap{p.g_mul, p.g_shift, p.group_size, p.n}; }
 __device__ __forceinline__ int GroupOf(const GemmParams& p, int ks) {
   return p.g_shift >= 0 ? (ks * p.g_mul) >> p.g_shift : ks * kBlockK / p.group_size;
 }
@@ -651,6 +659,7 @@ template <typename T, int kTok, bool kZeros, bool kMoe, int kSets, bool kLate, b
 __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
   static_assert(!kBatch || (!kMoe && !kPair && kLate), "batched launches: dense late-scale tiles only");
   const Problem* cur = probs;
+  int* const status_word = probs->p.status;  // one status header per launch
   using Sh = Shared<kTok, kSets, kPair>;
   constexpr int kStages = Sh::kStages;
   constexpr int kAcc = Sh::kAcc;
@@ -894,14 +903,14 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
           __nanosleep(32);
           if ((++idle & 0xff) == 0xff) {
             if (*abort_flag) {
-              if (active) NoteBlockedWarp(cur->p.status, kErrEmpty, static_cast<int>(c.it));
+              if (active) NoteBlockedWarp(status_word, kErrEmpty, static_cast<int>(c.it));
               break;
             }
             if (idle > kSpinLimit) {
-              if (active && atomicCAS(cur->p.status, 0, kErrEmpty) == 0) {
-                cur->p.status[1] = static_cast<int>(blockIdx.x);
-                cur->p.status[2] = static_cast<int>(threadIdx.x);
-                cur->p.status[3] = static_cast<int>(c.it);
+              if (active && atomicCAS(status_word, 0, kErrEmpty) == 0) {
+                status_word[1] = static_cast<int>(blockIdx.x);
+                status_word[2] = static_cast<int>(threadIdx.x);
+                status_word[3] = static_cast<int>(c.it);
                 __threadfence();
               }
               *abort_flag = 1;
@@ -942,7 +951,7 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
           acc = seg_idx % kAcc;
           if (issuing) {
             // (paired blocks: arrivals come from both blocks, hence the cluster-scope acquire)
-            if (!MbarWait<kPair>(SmemAddr(&sh.d_empty[acc]), ((seg_idx / kAcc) & 1) ^ 1, abort_flag, cur->p.status, kErrDEmpty,
+            if (!MbarWait<kPair>(SmemAddr(&sh.d_empty[acc]), ((seg_idx / kAcc) & 1) ^ 1, abort_flag, status_word, kErrDEmpty,
                                  static_cast<int>(seg_idx))) {
               break;
             }
@@ -962,7 +971,7 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
           if constexpr (kLate) {
             // this stage's own accumulator must have been read out by the epilogue
             acc = it % kSlots;
-            if (!MbarWait(SmemAddr(&sh.d_empty[acc]), ((it / kSlots) & 1) ^ 1, abort_flag, cur->p.status, kErrDEmpty,
+            if (!MbarWait(SmemAddr(&sh.d_empty[acc]), ((it / kSlots) & 1) ^ 1, abort_flag, status_word, kErrDEmpty,
                           static_cast<int>(it))) {
               alive = false;
               break;
@@ -971,14 +980,14 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
           }
           // `a_full` is raised by warps that waited for this stage's copies themselves, so it
           // also covers the activation tile (in both blocks of a pair).
-          if (!MbarWait<kPair, kPair>(SmemAddr(&sh.a_full[a]), (it / kAStages) & 1, abort_flag, cur->p.status, kErrAFull,
+          if (!MbarWait<kPair, kPair>(SmemAddr(&sh.a_full[a]), (it / kAStages) & 1, abort_flag, status_word, kErrAFull,
                                       static_cast<int>(it))) {
             alive = false;
             break;
           }
           if constexpr (kPair) {
             // both halves of the activation tile (the other block's copy counts on this barrier too)
-            if (!MbarWait<true, true>(SmemAddr(&sh.act_full[sa]), sa_phase, abort_flag, cur->p.status, kErrFull,
+            if (!MbarWait<true, true>(SmemAddr(&sh.act_full[sa]), sa_phase, abort_flag, status_word, kErrFull,
                                       static_cast<int>(it))) {
               alive = false;
               break;
@@ -1033,15 +1042,15 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
           if (step < first_it) break;
           if constexpr (kPair) {
             if (d < kActStages && !MbarWait(SmemAddr(&sh.act_empty[step % kActStages]), (step / kActStages) & 1, abort_flag,
-                                            cur->p.status, kErrEmpty, step)) {
+                                            status_word, kErrEmpty, step)) {
               break;
             }
-          } else if (!MbarWait(SmemAddr(&sh.empty[step % kStages]), (step / kStages) & 1, abort_flag, cur->p.status, kErrEmpty,
+          } else if (!MbarWait(SmemAddr(&sh.empty[step % kStages]), (step / kStages) & 1, abort_flag, status_word, kErrEmpty,
                                step)) {
             break;
           }
           if (d * kIssueStride < kAStages &&
-              !MbarWait(SmemAddr(&sh.a_empty[step % kAStages]), (step / kAStages) & 1, abort_flag, cur->p.status, kErrAEmpty,
+              !MbarWait(SmemAddr(&sh.a_empty[step % kAStages]), (step / kAStages) & 1, abort_flag, status_word, kErrAEmpty,
                         step)) {
             break;
           }
@@ -1055,7 +1064,7 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
         Cursor c{make_walker(), Segment{}, 0u, 0u, 0, 0};
         while (Locate<kMoe, kBatch>(c, cur->p.expert_ids)) {
           const int sa = c.it % kActStages;
-          if (!MbarWait<false, true>(SmemAddr(&sh.act_empty[sa]), ((c.it / kActStages) & 1) ^ 1, abort_flag, cur->p.status,
+          if (!MbarWait<false, true>(SmemAddr(&sh.act_empty[sa]), ((c.it / kActStages) & 1) ^ 1, abort_flag, status_word,
                                      kErrEmpty, static_cast<int>(c.it))) {
             break;
           }
@@ -1092,10 +1101,12 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
     const uint4* zbase = nullptr;
     const uint32_t* zword = nullptr;  // provider layout: the one word that holds this thread's four zero points
     int col = 0, sstride = 8;
+    GroupMap gmap{};  // of the segment's problem
     auto fetch_groups = [&](const Cursor& c) {
       [[maybe_unused]] const Problem* cur = kBatch ? probs + c.seg.prob : probs;
       if (c.seg_it != based_on) {
         based_on = c.seg_it;
+        gmap = MakeGroupMap(cur->p);
         const int n0 = tile_of(c.seg.n_tile) * kTileN;
         const size_t g0 = static_cast<size_t>(c.expert) * cur->p.groups;
         const bool inside = n0 + 32 * q < cur->p.n;
@@ -1123,16 +1134,16 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
       // lane / 4 of words x, y, z, w = this thread's columns +0, +8, +16, +24), so that the
       // conversion code below is the same for both.
       auto load_zeros = [&](uint32_t row) -> uint4 {
-        if (zword == nullptr) return LdGlobalV4Here(zbase + static_cast<size_t>(row) * static_cast<uint32_t>(cur->p.n / 32));
+        if (zword == nullptr) return LdGlobalV4Here(zbase + static_cast<size_t>(row) * static_cast<uint32_t>(gmap.n / 32));
         uint32_t w;
-        asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(w) : "l"(zword + static_cast<size_t>(row) * static_cast<uint32_t>(cur->p.n / 8)));
+        asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(w) : "l"(zword + static_cast<size_t>(row) * static_cast<uint32_t>(gmap.n / 8)));
         const int j0 = 4 * (q & 1), at = 4 * (lane >> 2);
         return make_uint4(((w >> (4 * ZeroNibble(j0))) & 0xFu) << at, ((w >> (4 * ZeroNibble(j0 + 1))) & 0xFu) << at,
                           ((w >> (4 * ZeroNibble(j0 + 2))) & 0xFu) << at, ((w >> (4 * ZeroNibble(j0 + 3))) & 0xFu) << at);
       };
       GroupRegs g;
-      const uint32_t grp = static_cast<uint32_t>(GroupOf(cur->p, c.Ks()));
-      const unsigned short* sp = sbase + static_cast<size_t>(grp) * static_cast<uint32_t>(cur->p.n) + col;
+      const uint32_t grp = static_cast<uint32_t>(gmap.Of(c.Ks()));
+      const unsigned short* sp = sbase + static_cast<size_t>(grp) * static_cast<uint32_t>(gmap.n) + col;
       g.sc[0][0] = g.sc[0][1] = g.sc[1][0] = g.sc[1][1] = 0;
       if constexpr (!kLate) {
         g.sc[0][0] = LdGlobalU16Here(sp) | (LdGlobalU16Here(sp + sstride) << 16);
@@ -1141,7 +1152,7 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
       g.zp[0] = g.zp[1] = make_uint4(0, 0, 0, 0);
       if constexpr (kZeros) g.zp[0] = load_zeros(grp);
       if (!kLate && rows == 2) {
-        sp += cur->p.n;
+        sp += gmap.n;
         g.sc[1][0] = LdGlobalU16Here(sp) | (LdGlobalU16Here(sp + sstride) << 16);
         g.sc[1][1] = LdGlobalU16Here(sp + 2 * sstride) | (LdGlobalU16Here(sp + 3 * sstride) << 16);
         if constexpr (kZeros) g.zp[1] = load_zeros(grp + 1);
@@ -1169,7 +1180,7 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
       // runs ahead of this warp.  The shuffle hands the outcome to the warp and orders the other
       // lanes' reads behind lane 0's acquire.
       const uint32_t seen = __shfl_sync(0xffffffffu, early, 0);
-      if (!(seen & 1u) && !MbarWaitWarp(0xffffffffu, 0, SmemAddr(&sh.full[s]), s_phase, abort_flag, cur->p.status, kErrFull,
+      if (!(seen & 1u) && !MbarWaitWarp(0xffffffffu, 0, SmemAddr(&sh.full[s]), s_phase, abort_flag, status_word, kErrFull,
                                         false, static_cast<int>(it))) {
         break;
       }
@@ -1182,7 +1193,7 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
       // first store of the stage: this tensor-memory stage must have been read out by the MMAs
       // that used it last
       auto before_first_store = [&]() {
-        if (!(seen & 2u) && !MbarWaitWarp(0xffffffffu, 0, SmemAddr(&sh.a_empty[a]), a_phase ^ 1, abort_flag, cur->p.status,
+        if (!(seen & 2u) && !MbarWaitWarp(0xffffffffu, 0, SmemAddr(&sh.a_empty[a]), a_phase ^ 1, abort_flag, status_word,
                                           kErrAEmpty, false, static_cast<int>(it))) {
           alive = false;
         }
@@ -1426,16 +1437,17 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
         for (int j = 0; j < kTok; ++j) sum[j] = 0.0f;
         const T* srow = static_cast<const T*>(cur->p.scales) + static_cast<size_t>(expert) * cur->p.groups * cur->p.n +
                         ScaleColumn(cur->p, n_ok ? n : n - 64);  // a column past N borrows a valid one; it is never written
-        uint32_t coming = LdGlobalU16Here(srow + static_cast<size_t>(GroupOf(cur->p, seg.k_begin)) * cur->p.n);
+        const GroupMap gmap = MakeGroupMap(cur->p);
+        uint32_t coming = LdGlobalU16Here(srow + static_cast<size_t>(gmap.Of(seg.k_begin)) * gmap.n);
         bool alive = true;
         for (int ks = seg.k_begin; ks < seg.k_end; ++ks, ++it) {
           const unsigned short raw = static_cast<unsigned short>(coming);
           const float scale = ToFloat<T>(*reinterpret_cast<const T*>(&raw));
-          if (ks + 1 < seg.k_end) coming = LdGlobalU16Here(srow + static_cast<size_t>(GroupOf(cur->p, ks + 1)) * cur->p.n);
+          if (ks + 1 < seg.k_end) coming = LdGlobalU16Here(srow + static_cast<size_t>(gmap.Of(ks + 1)) * gmap.n);
           const int slot = it % kSlots;
           const uint32_t seen = __shfl_sync(0xffffffffu, early, 0);
           if (!(seen & 1u) && !MbarWaitWarp(0xffffffffu, 0, SmemAddr(&sh.d_full[slot]), (it / kSlots) & 1, abort_flag,
-                                            cur->p.status, kErrDFull, /*relaxed=*/false, static_cast<int>(it))) {
+                                            status_word, kErrDFull, /*relaxed=*/false, static_cast<int>(it))) {
             alive = false;
             break;
           }
@@ -1476,7 +1488,7 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
         ++seg_idx;
       } else {
         const int acc = seg_idx % kAcc;
-        if (!MbarWaitWarp(0xffffffffu, 0, SmemAddr(&sh.d_full[acc]), (seg_idx / kAcc) & 1, abort_flag, cur->p.status,
+        if (!MbarWaitWarp(0xffffffffu, 0, SmemAddr(&sh.d_full[acc]), (seg_idx / kAcc) & 1, abort_flag, status_word,
                           kErrDFull, /*relaxed=*/true, static_cast<int>(seg_idx))) {
           break;
         }
@@ -1960,21 +1972,20 @@ int LaunchBatchVariant(const BatchTable& table, int grid, cudaStream_t stream) {
   return CheckLaunch("W4A16 GEMM batch launch");
 }
 
+template <typename T>
+int LaunchBatchTyped(bool zeros, int tok, const BatchTable& table, int grid, cudaStream_t stream) {
+  switch (tok) {
+    case 16:
+      return zeros ? LaunchBatchVariant<T, 16, true>(table, grid, stream) : LaunchBatchVariant<T, 16, false>(table, grid, stream);
+    case 32:
+      return zeros ? LaunchBatchVariant<T, 32, true>(table, grid, stream) : LaunchBatchVariant<T, 32, false>(table, grid, stream);
+    default:
+      return zeros ? LaunchBatchVariant<T, 64, true>(table, grid, stream) : LaunchBatchVariant<T, 64, false>(table, grid, stream);
+  }
+}
 int LaunchBatch(int a_dtype, bool zeros, int tok, const BatchTable& table, int grid, cudaStream_t stream) {
-  if (a_dtype == IOB_BF16) {
-    if (tok == 16) {
-      return zeros ? LaunchBatchVariant<__nv_bfloat16, 16, true>(table, grid, stream)
-                   : LaunchBatchVariant<__nv_bfloat16, 16, false>(table, grid, stream);
-    }
-    return zeros ? LaunchBatchVariant<__nv_bfloat16, 32, true>(table, grid, stream)
-                 : LaunchBatchVariant<__nv_bfloat16, 32, false>(table, grid, stream);
-  }
-  if (tok == 16) {
-    return zeros ? LaunchBatchVariant<__half, 16, true>(table, grid, stream)
-                 : LaunchBatchVariant<__half, 16, false>(table, grid, stream);
-  }
-  return zeros ? LaunchBatchVariant<__half, 32, true>(table, grid, stream)
-               : LaunchBatchVariant<__half, 32, false>(table, grid, stream);
+  return a_dtype == IOB_BF16 ? LaunchBatchTyped<__nv_bfloat16>(zeros, tok, table, grid, stream)
+                             : LaunchBatchTyped<__half>(zeros, tok, table, grid, stream);
 }
 
 // Token tiles up to 32 with groups of at least one k-stage take the variant that scales the
@@ -2193,7 +2204,7 @@ extern "C" int infiniops_b200_marlin_gemm(const void* a, int a_dtype, const int3
 
 extern "C" size_t infiniops_b200_marlin_gemm_batch_scratch_bytes(void) {
   using namespace iob;
-  return PlanScratch(0, 32, 0).total;
+  return PlanScratch(0, 64, 0).total;
 }
 
 extern "C" int infiniops_b200_marlin_gemm_batch(const iob_gemm_problem* problems, int count, int a_dtype,
@@ -2202,14 +2213,18 @@ extern "C" int infiniops_b200_marlin_gemm_batch(const iob_gemm_problem* problems
   using namespace iob;
   const char* op = "marlin_gemm_batch";
   IOB_REQUIRE(problems != nullptr && count > 0, "%s: no problems", op);
-  const ScratchPlan plan = PlanScratch(0, 32, 0);
+  const ScratchPlan plan = PlanScratch(0, 64, 0);
   if (scratch == nullptr || scratch_bytes < plan.total) {
     return Fail(IOB_SCRATCH_TOO_SMALL, "%s: needs %zu bytes of scratch, got %zu", op, plan.total, scratch_bytes);
   }
-  // Two classes of token tile: up to 16 rows, and 17..64 rows as 32-row tiles.  Each class is one
-  // launch (or several, kMaxBatch problems at a time); the completion signal rides on the last.
-  int order[2][1024];
-  int n_of[2] = {0, 0};
+  // Three classes of token tile: up to 16 rows, 17..32 and 33..64 (inside one launch the whole grid
+  // works on every tile in turn, so a 64-row tile -- each weight converted once -- beats two 32-row
+  // ones).  Each class is one launch (or several, kMaxBatch problems at a time); the completion
+  // signal rides on the last.
+  constexpr int kClasses = 3;
+  constexpr int kTokOf[kClasses] = {16, 32, 64};
+  int order[kClasses][1024];
+  int n_of[kClasses] = {0, 0, 0};
   IOB_REQUIRE(count <= 1024, "%s: at most 1024 problems per call", op);
   for (int i = 0; i < count; ++i) {
     const iob_gemm_problem& g = problems[i];
@@ -2221,13 +2236,14 @@ extern "C" int infiniops_b200_marlin_gemm_batch(const iob_gemm_problem* problems
       return Fail(IOB_UNSUPPORTED, "%s: problem %d: batched launches take at most 64 rows and group sizes that are "
                   "multiples of 128; use marlin_gemm", op, i);
     }
-    const int cls = g.size_m <= 16 ? 0 : 1;
+    const int cls = g.size_m <= 16 ? 0 : g.size_m <= 32 ? 1 : 2;
     order[cls][n_of[cls]++] = i;
   }
-  const int launches = (n_of[0] + kMaxBatch - 1) / kMaxBatch + (n_of[1] + kMaxBatch - 1) / kMaxBatch;
+  int launches = 0;
+  for (int cls = 0; cls < kClasses; ++cls) launches += (n_of[cls] + kMaxBatch - 1) / kMaxBatch;
   int launched = 0;
-  for (int cls = 0; cls < 2; ++cls) {
-    const int tok = cls == 0 ? 16 : 32;
+  for (int cls = 0; cls < kClasses; ++cls) {
+    const int tok = kTokOf[cls];
     for (int first = 0; first < n_of[cls]; first += kMaxBatch) {
       BatchTable table{};
       table.count = std::min(kMaxBatch, n_of[cls] - first);
