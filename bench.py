@@ -586,15 +586,27 @@ def moe_problem(cfg, tokens, d):
     return weights, x, logits, bias, t_local
 
 
-def moe_layer_time(d, cfg, tokens, steps, warmup, block=64):
+def moe_layer_time(d, cfg, tokens, steps, warmup, block=64, fuse=None):
     """ms per layer pass (router -> sort -> w13 GEMM -> silu_and_mul -> w2 GEMM -> moe_sum, with dispatch and
     combine when sharded), median of 3 regions."""
     from infiniops_b200 import capi, moe_layer, parallel
 
     weights, x, logits, bias, t_local = moe_problem(cfg, tokens, d)
     # routing block: 64 as BASELINE.json's chain states it, or chosen from the rows per expert
+    fused = False
+    block_arg = block
     if block == 0:
         block = moe_layer.routing_block(t_local * d.world * cfg["top_k"] // d.world, weights.num_experts)
+        # ... and with w13 taken as gate/up interleaved, silu_and_mul done by the first GEMM's epilogue
+        # (the weights are random words either way: only the reading of the columns changes)
+        # (only with 128-row blocks: with small token tiles the epilogue warps are busy scaling every
+        # stage's accumulator, and the extra arithmetic per tile costs more than the launch it saves)
+        fused = (2 * cfg["inter"]) % 128 == 0 and block >= 128
+    if fuse is not None:
+        fused = fuse in ("silu", "all")
+    # router + sort as one launch: one thread block routes all tokens, so only for a handful of them
+    fuse_router = (block_arg == 0 and t_local <= 32) if fuse is None else fuse in ("router", "all")
+    weights.interleaved = fused
     runner = moe_layer.RoutedExperts(weights, block)
     launches = [0]
     ep = None
@@ -608,12 +620,22 @@ def moe_layer_time(d, cfg, tokens, steps, warmup, block=64):
             return moe_layer.route_softmax(logits, cfg["top_k"])
         return moe_layer.route_grouped(logits, bias, 8, 4, cfg["top_k"], 2.5)
 
+    router = ({"kind": "softmax", "top_k": cfg["top_k"]} if cfg["router"] == "softmax" else
+              {"kind": "grouped", "top_k": cfg["top_k"], "bias": bias, "groups": 8, "topk_group": 4, "scaling": 2.5})
+
     def step(stream=None):
+        sort = 1 if t_local * cfg["top_k"] <= 1024 else 2
+        if ep is None and fuse_router and sort == 1:
+            # router + sort as one launch, row gather + w13 GEMM (with silu_and_mul), w2 GEMM, moe_sum
+            launches[0] = 1 + 2 + (0 if fused else 1) + 1 + 1
+            return moe_layer.layer_from_logits(x, logits, router, runner, stream=stream)
         w, ids = route() if stream is None else route_on(stream)
         if ep is None:
-            launches[0] = 8   # router, sort, 2 x (gather + GEMM), silu_and_mul, moe_sum
+            # router, sort, row gather + w13 GEMM, silu_and_mul (unless fused), w2 GEMM, moe_sum
+            launches[0] = 1 + sort + 2 + (0 if fused else 1) + 1 + 1
             return moe_layer.single_gpu_layer(x, w, ids, runner, stream=stream)
-        launches[0] = 13      # router, plan, dispatch, wait, unpack, sort, 2 x (gather + GEMM), silu_and_mul, wait, moe_sum
+        # router, plan, dispatch, wait, unpack, sort, w13 GEMM, silu_and_mul (unless fused), w2 GEMM, wait, moe_sum
+        launches[0] = 5 + sort + 1 + (0 if fused else 1) + 1 + 2
         return ep(x, ids, w, out=out, stream=stream)
 
     def route_on(stream):
@@ -663,8 +685,9 @@ def bench_moe(d, args):
             steps = 10 if tokens <= 1024 else 5
             flops = tokens * cfg["top_k"] * (2 * cfg["hidden"] * 2 * cfg["inter"] + 2 * cfg["inter"] * cfg["hidden"])
             case = {"workload": cfg["label"]}
-            # block 64: the chain exactly as BASELINE.json states it; adaptive: the same chain with the
-            # routing block chosen from the rows per expert (identical results within the tolerance)
+            # block 64: the chain exactly as BASELINE.json states it; adaptive: the routing block chosen
+            # from the rows per expert and, with 128-row blocks, silu_and_mul fused into the first GEMM
+            # (results within the same tolerance)
             for label, block in (("block64", 64), ("adaptive_block", 0)):
                 ms, t_global, launches, used = moe_layer_time(d, cfg, tokens, steps, 3, block)
                 tf = flops / (ms * 1e-3) / 1e12
@@ -844,7 +867,7 @@ def run_moe(args):
     d = Dist(args)
     cfg = MOE_CONFIGS[args.moe_shape]
     with ClockSampler(d.local_rank) as clocks:
-        ms, tokens, launches, block = moe_layer_time(d, cfg, args.tokens, min(args.steps, 50), args.warmup, args.moe_block)
+        ms, tokens, launches, block = moe_layer_time(d, cfg, args.tokens, min(args.steps, 50), args.warmup, args.moe_block, args.moe_fuse)
     flops = tokens * cfg["top_k"] * (2 * cfg["hidden"] * 2 * cfg["inter"] + 2 * cfg["inter"] * cfg["hidden"])
     if d.rank == 0:
         print(json.dumps({
@@ -955,6 +978,8 @@ def main():
     parser.add_argument("--tokens", type=int, default=1024, help="global tokens of the MoE workload")
     parser.add_argument("--moe-shape", default="mixtral", choices=tuple(MOE_CONFIGS))
     parser.add_argument("--moe-block", type=int, default=64, help="routing block of the MoE workload (0 = adaptive)")
+    parser.add_argument("--moe-fuse", default=None, choices=("none", "silu", "router", "all"),
+                        help="MoE workload: which fused launches to use (default: all with --moe-block 0, else none)")
     parser.add_argument("--one", default=None, help="M,K,N: run this single GEMM three times (profiling case)")
     parser.add_argument("--one-batch", default=None, help="S: the batched step on linears shrunk by S, three times")
     parser.add_argument("--ms", default=None, help="--one-batch: the row counts to include, e.g. 1,4,16")

@@ -155,6 +155,37 @@ int infiniops_b200_moe_align_block_size(const int32_t* topk_ids, const int32_t* 
                                         int32_t* num_tokens_post_pad, void* scratch,
                                         size_t scratch_bytes, void* stream);
 
+/* Router and token sort as ONE launch: infiniops_b200_topk_softmax (or, with `sigmoid` != 0,
+ * infiniops_b200_topk_sigmoid with `routed_scaling_factor`) followed by
+ * infiniops_b200_moe_align_block_size on the [num_tokens, topk] int32 ids it has just produced.
+ * Same outputs, bit for bit, as the two calls.  One thread block does both while
+ * num_tokens * topk <= 1024 (the decode regime, where each operator is a few microseconds behind a
+ * launch); beyond that the call issues the separate launches and needs the sort's scratch.
+ * The reference has the two operators only (src/base/topk_softmax.h:89-153,
+ * src/base/moe_align_block_size.h:37-45); the chain is the caller's. */
+int infiniops_b200_topk_softmax_align(const void* gating_output, int gating_dtype, const float* bias,
+                                      const uint8_t* is_padding, int renormalize, int sigmoid,
+                                      double routed_scaling_factor, float* topk_weights,
+                                      int32_t* topk_ids, int32_t* token_expert_indices,
+                                      int64_t num_tokens, int64_t num_experts, int64_t topk,
+                                      const int32_t* expert_map, int64_t block_size,
+                                      int32_t* sorted_token_ids, int64_t sorted_size,
+                                      int32_t* experts_ids, int64_t experts_size,
+                                      int32_t* num_tokens_post_pad, void* scratch,
+                                      size_t scratch_bytes, void* stream);
+
+/* The same for infiniops_b200_grouped_topk (src/base/grouped_topk.h:92-150).  The single-block form
+ * needs a float32 `bias`; other bias types take the separate launches. */
+int infiniops_b200_grouped_topk_align(const void* scores, int scores_dtype, const void* bias,
+                                      int bias_dtype, int64_t num_tokens, int64_t num_experts,
+                                      int64_t num_expert_group, int64_t topk_group, int64_t topk,
+                                      int renormalize, double routed_scaling_factor, int scoring_func,
+                                      float* topk_values, int32_t* topk_ids, const int32_t* expert_map,
+                                      int64_t block_size, int32_t* sorted_token_ids,
+                                      int64_t sorted_size, int32_t* experts_ids, int64_t experts_size,
+                                      int32_t* num_tokens_post_pad, void* scratch,
+                                      size_t scratch_bytes, void* stream);
+
 /* Bookkeeping for a grouped GEMM over routed tokens: expert_offsets [E + 1] (exclusive prefix of the
  * per-expert route counts), problem_sizes1 / problem_sizes2 [E, 3] ((count, 2n or n, k) and
  * (count, k, n); with at most 64 routes and no `blockscale_offsets` the first two entries are
@@ -408,10 +439,17 @@ int infiniops_b200_moe_wna16_gemm(const void* input, int dtype, const uint8_t* b
  * = entry i, padding entries included) with tile stores instead of one scattered row per entry; not
  * together with `mul_topk_weights` or `row_dest`.  Chaining w13 (out_sorted) -> silu_and_mul -> w2
  * (a_sorted) keeps the intermediate in expert order and scatters only once, at the end.
+ * `fuse_silu` (with `out_sorted`, `size_n` a multiple of 128): the weight, scale and zero-point
+ * columns of this call are the gate and up halves of a gated MLP interleaved in runs of 16 --
+ * column 32 b + c holds gate feature 16 b + c for c < 16 and up feature 16 b + c - 16 for c >= 16 --
+ * and the epilogue applies `silu_and_mul` itself: `out` is [sorted_size, size_n / 2], each value
+ * silu(gate) * up computed from the two products rounded to the activation type, bit for bit what
+ * infiniops_b200_silu_and_mul makes of the stored product.  The [rows, size_n] intermediate never
+ * exists.
  * Zero-initialise the struct.  No counterpart in the reference. */
 typedef struct {
   int scale_layout;
-  int a_sorted, out_sorted;
+  int a_sorted, out_sorted, fuse_silu;
   const int32_t* row_dest;
   void* dest_base[IOB_MAX_PEERS + 1];
   int n_dest;
@@ -447,7 +485,9 @@ typedef struct {
 } iob_ep_context;
 
 /* This rank's experts, Marlin layout: w13 [E, H/16, 2*2I], w2 [E, I/16, 2H], scales [E, G, N],
- * zero points [E, G, N/8] or NULL. */
+ * zero points [E, G, N/8] or NULL.  `w13_interleaved` != 0: the columns of w13 / s13 / z13 are gate
+ * and up interleaved in runs of 16 (iob_routed_options::fuse_silu) and the layer applies
+ * silu_and_mul in the first GEMM's epilogue. */
 typedef struct {
   const int32_t* w13;
   const void* s13;
@@ -457,6 +497,7 @@ typedef struct {
   const void* s2;
   const int32_t* z2;
   int64_t groups2;
+  int w13_interleaved;
 } iob_expert_weights;
 
 size_t infiniops_b200_ep_arena_bytes(int world, int64_t capacity, int64_t hidden);

@@ -74,7 +74,8 @@ class PeerSignal(ctypes.Structure):
 
 class RoutedOptions(ctypes.Structure):
     """`iob_routed_options`."""
-    _fields_ = [("scale_layout", _int), ("a_sorted", _int), ("out_sorted", _int), ("row_dest", _vp),
+    _fields_ = [("scale_layout", _int), ("a_sorted", _int), ("out_sorted", _int), ("fuse_silu", _int),
+                ("row_dest", _vp),
                 ("dest_base", _vp * (MAX_PEERS + 1)), ("n_dest", _int),
                 ("signal", ctypes.POINTER(PeerSignal))]
 
@@ -89,13 +90,17 @@ class EpContext(ctypes.Structure):
 class ExpertWeightsC(ctypes.Structure):
     """`iob_expert_weights`."""
     _fields_ = [("w13", _vp), ("s13", _vp), ("z13", _vp), ("groups13", _i64), ("w2", _vp), ("s2", _vp), ("z2", _vp),
-                ("groups2", _i64)]
+                ("groups2", _i64), ("w13_interleaved", _int)]
 
 
 PROTOTYPES.update({
     "infiniops_b200_moe_wna16_marlin_gemm_ex": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64,
                                                               _i64, _int, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _vp,
                                                               ctypes.POINTER(RoutedOptions), _vp, _sz, _vp]),
+    "infiniops_b200_topk_softmax_align": (_int, [_vp, _int, _vp, _vp, _int, _int, _dbl, _vp, _vp, _vp, _i64, _i64, _i64,
+                                                 _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _sz, _vp]),
+    "infiniops_b200_grouped_topk_align": (_int, [_vp, _int, _vp, _int, _i64, _i64, _i64, _i64, _i64, _int, _dbl, _int,
+                                                 _vp, _vp, _vp, _i64, _vp, _i64, _vp, _i64, _vp, _vp, _sz, _vp]),
     "infiniops_b200_topk_sigmoid": (_int, [_vp, _int, _vp, _vp, _int, _dbl, _vp, _vp, _int, _vp, _i64, _i64, _i64, _vp]),
     "infiniops_b200_get_cutlass_moe_mm_data": (_int, [_vp, _i64, _i64, _i64, _i64, _i64, _int, _vp, _vp, _vp, _vp, _vp,
                                                       _vp, _vp]),
@@ -191,6 +196,15 @@ def topk_softmax(gating, bias, is_padding, renormalize, topk_weights, topk_indic
                                              topk_weights.shape[1], _stream(stream)))
 
 
+def topk_sigmoid(gating, bias, is_padding, renormalize, routed_scaling_factor, topk_weights, topk_ids,
+                 token_expert_indices, stream=None):
+    t, e = gating.shape
+    _check(lib().infiniops_b200_topk_sigmoid(_ptr(gating), _DTYPE[gating.dtype], _ptr(bias), _ptr(is_padding),
+                                             int(renormalize), float(routed_scaling_factor), _ptr(topk_weights),
+                                             _ptr(topk_ids), _DTYPE[topk_ids.dtype], _ptr(token_expert_indices), t, e,
+                                             topk_weights.shape[1], _stream(stream)))
+
+
 def grouped_topk(scores, bias, num_expert_group, topk_group, topk, renormalize, routed_scaling_factor,
                  scoring_func, topk_values, topk_indices, stream=None):
     t, e = scores.shape
@@ -210,6 +224,38 @@ def moe_align_block_size(topk_ids, expert_map, num_experts, block_size, sorted_t
                                                      _ptr(experts_ids), experts_ids.numel(),
                                                      _ptr(num_tokens_post_pad), _ptr(buf),
                                                      0 if buf is None else buf.numel(), _stream(stream)))
+
+
+def _sort_scratch(device, numel, num_experts):
+    need = lib().infiniops_b200_moe_align_block_size_scratch_bytes(numel, num_experts)
+    return scratch(device, need, "align") if need else None
+
+
+def topk_softmax_align(gating, bias, is_padding, renormalize, topk_weights, topk_ids, token_expert_indices,
+                       expert_map, block_size, sorted_token_ids, experts_ids, num_tokens_post_pad, sigmoid=False,
+                       routed_scaling_factor=1.0, stream=None):
+    """Router and token sort in one call (one launch while tokens x top_k <= 1024)."""
+    t, e = gating.shape
+    buf = _sort_scratch(gating.device, topk_ids.numel(), e)
+    _check(lib().infiniops_b200_topk_softmax_align(
+        _ptr(gating), _DTYPE[gating.dtype], _ptr(bias), _ptr(is_padding), int(renormalize), int(sigmoid),
+        float(routed_scaling_factor), _ptr(topk_weights), _ptr(topk_ids), _ptr(token_expert_indices), t, e,
+        topk_weights.shape[1], _ptr(expert_map), block_size, _ptr(sorted_token_ids), sorted_token_ids.numel(),
+        _ptr(experts_ids), experts_ids.numel(), _ptr(num_tokens_post_pad), _ptr(buf),
+        0 if buf is None else buf.numel(), _stream(stream)))
+
+
+def grouped_topk_align(scores, bias, num_expert_group, topk_group, topk, renormalize, routed_scaling_factor,
+                       scoring_func, topk_values, topk_ids, expert_map, block_size, sorted_token_ids, experts_ids,
+                       num_tokens_post_pad, stream=None):
+    t, e = scores.shape
+    buf = _sort_scratch(scores.device, topk_ids.numel(), e)
+    _check(lib().infiniops_b200_grouped_topk_align(
+        _ptr(scores), _DTYPE[scores.dtype], _ptr(bias), _DTYPE[bias.dtype], t, e, num_expert_group, topk_group, topk,
+        int(renormalize), float(routed_scaling_factor), scoring_func, _ptr(topk_values), _ptr(topk_ids),
+        _ptr(expert_map), block_size, _ptr(sorted_token_ids), sorted_token_ids.numel(), _ptr(experts_ids),
+        experts_ids.numel(), _ptr(num_tokens_post_pad), _ptr(buf), 0 if buf is None else buf.numel(),
+        _stream(stream)))
 
 
 def silu_and_mul(x, out, stream=None):
@@ -256,13 +302,14 @@ def marlin_gemm_static_scratch(a, b_q_weight, b_bias, b_scales, b_zeros, b_type_
 def moe_wna16_marlin_gemm(a, b_q_weight, b_bias, b_scales, b_zeros, sorted_token_ids, expert_ids,
                           num_tokens_past_padded, topk_weights, moe_block_size, top_k, mul_topk_weights, b_type_id,
                           size_m, size_n, size_k, out, stream=None, scratch_buf=None, scale_layout=0, a_sorted=False,
-                          out_sorted=False):
+                          out_sorted=False, fuse_silu=False):
     e = b_q_weight.shape[0]
     need = lib().infiniops_b200_moe_wna16_marlin_gemm_scratch_bytes(size_m, top_k, size_n, size_k, e,
                                                                     moe_block_size)
     buf = scratch_buf if scratch_buf is not None else scratch(a.device, need)
     options = RoutedOptions()
     options.scale_layout, options.a_sorted, options.out_sorted = scale_layout, int(a_sorted), int(out_sorted)
+    options.fuse_silu = int(fuse_silu)
     _check(lib().infiniops_b200_moe_wna16_marlin_gemm_ex(
         _ptr(a), _DTYPE[a.dtype], _ptr(b_q_weight), _ptr(b_bias), _ptr(b_scales), _ptr(b_zeros),
         _ptr(sorted_token_ids), _ptr(expert_ids), _ptr(num_tokens_past_padded), _ptr(topk_weights), moe_block_size,

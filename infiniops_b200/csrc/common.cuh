@@ -59,6 +59,14 @@ __device__ __forceinline__ __half FromFloat<__half>(float v) { return __float2ha
 template <>
 __device__ __forceinline__ __nv_bfloat16 FromFloat<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+// silu(gate) * up from values already rounded to T, one rounding at the end: the arithmetic of
+// `silu_and_mul`, shared with the GEMM epilogue that fuses it so that both give the same bits.
+template <typename T>
+__device__ __forceinline__ T SiluMulRounded(float g, float u) {
+  const float sig = __frcp_rn(__fadd_rn(1.0f, __expf(-g)));
+  return FromFloat<T>(__fmul_rn(__fmul_rn(g, sig), u));
+}
+
 }  // namespace iob
 
 #endif  // INFINIOPS_B200_COMMON_CUH_

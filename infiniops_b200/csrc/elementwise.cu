@@ -30,9 +30,7 @@ __device__ __forceinline__ void RowOffsets(const RowLayout& l, int64_t row, int6
 
 template <typename T>
 __device__ __forceinline__ T SiluMul(T gate, T up) {
-  const float g = ToFloat<T>(gate), u = ToFloat<T>(up);
-  const float sig = __frcp_rn(__fadd_rn(1.0f, __expf(-g)));
-  return FromFloat<T>(__fmul_rn(__fmul_rn(g, sig), u));
+  return SiluMulRounded<T>(ToFloat<T>(gate), ToFloat<T>(up));
 }
 
 template <typename T, int kVec>

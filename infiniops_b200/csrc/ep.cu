@@ -300,13 +300,15 @@ extern "C" int infiniops_b200_ep_moe_layer(const iob_ep_context* ctx, const iob_
   }
   iob_routed_options first{};
   first.out_sorted = 1;
+  const bool fused = weights->w13_interleaved != 0 && (2 * c.inter) % 128 == 0;
+  first.fuse_silu = fused ? 1 : 0;
   if (const int rc = infiniops_b200_moe_wna16_marlin_gemm_ex(
           own + lay.rows, c.a_dtype, weights->w13, nullptr, weights->s13, weights->z13, sorted, expert_ids, npost,
           row_weights, c.moe_block_size, 1, 0, c.b_type_id, w.rows, 2 * c.inter, c.hidden, weights->groups13,
-          c.experts_per_rank, w.sorted_size, ws + w.g, &first, ws + w.gemm, w.gemm_bytes, stream)) {
+          c.experts_per_rank, w.sorted_size, fused ? ws + w.h : ws + w.g, &first, ws + w.gemm, w.gemm_bytes, stream)) {
     return rc;
   }
-  {
+  if (!fused) {
     const int64_t shape[2] = {w.sorted_size, c.inter};
     const int64_t in_strides[2] = {2 * c.inter, 1}, out_strides[2] = {c.inter, 1};
     if (const int rc = infiniops_b200_silu_and_mul(ws + w.g, ws + w.h, c.a_dtype, 2, shape, in_strides, out_strides, stream)) {

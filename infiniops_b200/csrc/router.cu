@@ -5,8 +5,10 @@
 // (max, sum, arg-max rounds, top-2 per group) with register shuffles; there is no
 // block-wide barrier and no serial single-thread scan over experts.
 #include <cfloat>
+#include <algorithm>
 #include <cmath>
 
+#include "align_block.cuh"
 #include "common.cuh"
 
 namespace iob {
@@ -49,16 +51,12 @@ __device__ __forceinline__ void StoreIndex(Index* p, int v) { *p = static_cast<I
 // row, the selection adds the correction bias in the same way, and the selected weights are
 // multiplied by `scaling` (after the optional renormalisation).
 template <typename In, typename Index, bool kSigmoid = false>
-__global__ void TopkSoftmaxKernel(const In* __restrict__ gating, const float* __restrict__ bias,
-                                  const uint8_t* __restrict__ is_padding,
-                                  float* __restrict__ topk_weights, Index* __restrict__ topk_indices,
-                                  int32_t* __restrict__ token_expert_indices, int num_tokens,
-                                  int num_experts, int topk, bool renormalize, int warps_per_block,
-                                  float scaling = 1.0f) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int token = blockIdx.x * warps_per_block + warp;
-  if (token >= num_tokens) return;
+__device__ __forceinline__ void RouteTokenSoftmax(unsigned char* smem_raw, int warp, int warps_per_block, int token,
+                                                  const In* __restrict__ gating, const float* __restrict__ bias,
+                                                  const uint8_t* __restrict__ is_padding, float* topk_weights,
+                                                  Index* topk_indices, int32_t* token_expert_indices, int num_tokens,
+                                                  int num_experts, int topk, bool renormalize, float scaling) {
+  const int lane = threadIdx.x & 31;
   const int padded = (num_experts + 3) & ~3;
   float* score = reinterpret_cast<float*>(smem_raw) + static_cast<size_t>(warp) * num_experts;
   uint8_t* taken = smem_raw + static_cast<size_t>(warps_per_block) * (num_experts + kMaxGroups) * sizeof(float) +
@@ -127,6 +125,22 @@ __global__ void TopkSoftmaxKernel(const In* __restrict__ gating, const float* __
       if (padding) StoreIndex(topk_indices + out + rank, -1);
     }
   }
+}
+
+template <typename In, typename Index, bool kSigmoid = false>
+__global__ void TopkSoftmaxKernel(const In* __restrict__ gating, const float* __restrict__ bias,
+                                  const uint8_t* __restrict__ is_padding,
+                                  float* __restrict__ topk_weights, Index* __restrict__ topk_indices,
+                                  int32_t* __restrict__ token_expert_indices, int num_tokens,
+                                  int num_experts, int topk, bool renormalize, int warps_per_block,
+                                  float scaling = 1.0f) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int warp = threadIdx.x >> 5;
+  const int token = blockIdx.x * warps_per_block + warp;
+  if (token >= num_tokens) return;
+  RouteTokenSoftmax<In, Index, kSigmoid>(smem_raw, warp, warps_per_block, token, gating, bias, is_padding, topk_weights,
+                                         topk_indices, token_expert_indices, num_tokens, num_experts, topk, renormalize,
+                                         scaling);
 }
 
 // Shared memory per warp: one float and one flag byte (padded to 4) per expert, plus one
@@ -218,14 +232,12 @@ __device__ __forceinline__ void InsertTopTwo(float v, float& first, float& secon
 }
 
 template <typename Score, typename Bias, int kScoring>
-__global__ void GroupedTopkKernel(const Score* __restrict__ scores, const Bias* __restrict__ bias,
-                                  float* __restrict__ topk_values, int32_t* __restrict__ topk_indices,
-                                  int num_tokens, int num_experts, int num_groups, int topk_group, int topk,
-                                  bool renormalize, float routed_scaling_factor, int warps_per_block) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int token = blockIdx.x * warps_per_block + warp;
-  if (token >= num_tokens) return;
+__device__ __forceinline__ void RouteTokenGrouped(unsigned char* smem_raw, int warp, int warps_per_block, int token,
+                                                  const Score* __restrict__ scores, const Bias* __restrict__ bias,
+                                                  float* topk_values, int32_t* topk_indices, int num_experts,
+                                                  int num_groups, int topk_group, int topk, bool renormalize,
+                                                  float routed_scaling_factor) {
+  const int lane = threadIdx.x & 31;
   const int padded = (num_experts + 3) & ~3;
   float* sel = reinterpret_cast<float*>(smem_raw) + static_cast<size_t>(warp) * num_experts;
   float* group_scores = reinterpret_cast<float*>(smem_raw) + static_cast<size_t>(warps_per_block) * num_experts +
@@ -319,6 +331,20 @@ __global__ void GroupedTopkKernel(const Score* __restrict__ scores, const Bias* 
     }
     for (int rank = 0; rank < topk; ++rank) topk_values[out + rank] *= scale;
   }
+}
+
+template <typename Score, typename Bias, int kScoring>
+__global__ void GroupedTopkKernel(const Score* __restrict__ scores, const Bias* __restrict__ bias,
+                                  float* __restrict__ topk_values, int32_t* __restrict__ topk_indices,
+                                  int num_tokens, int num_experts, int num_groups, int topk_group, int topk,
+                                  bool renormalize, float routed_scaling_factor, int warps_per_block) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int warp = threadIdx.x >> 5;
+  const int token = blockIdx.x * warps_per_block + warp;
+  if (token >= num_tokens) return;
+  RouteTokenGrouped<Score, Bias, kScoring>(smem_raw, warp, warps_per_block, token, scores, bias, topk_values,
+                                           topk_indices, num_experts, num_groups, topk_group, topk, renormalize,
+                                           routed_scaling_factor);
 }
 
 template <typename Score, typename Bias, int kScoring>
@@ -449,5 +475,213 @@ extern "C" int infiniops_b200_grouped_topk(const void* scores, int scores_dtype,
       return DispatchBias<__nv_bfloat16>(bias_dtype, scoring_func, scores, bias, num_tokens, num_experts, num_expert_group, topk_group, topk, renorm, routed_scaling_factor, topk_values, topk_indices, s);
     default:
       return Fail(IOB_INVALID_ARGUMENT, "grouped_topk: `scores` must be float32, float16 or bfloat16");
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// router + token sort in one launch
+// ------------------------------------------------------------------------------------------
+// At decode sizes (tokens x top_k <= 1024) the router and moe_align_block_size are each a few
+// microseconds of work behind a launch; here one block of 1024 threads does both: its 32 warps
+// route the tokens (one token per warp at a time, the same per-token code as the operators above),
+// and after a block barrier the same threads sort the routing ids they have just written.
+namespace iob {
+namespace {
+
+inline size_t FusedAlignBytes(int64_t num_experts) { return (align::SmemBytes(num_experts) + 15) & ~size_t{15}; }
+
+template <typename In, bool kSigmoid>
+__global__ void __launch_bounds__(align::kChunk)
+SoftmaxAlignKernel(const In* __restrict__ gating, const float* __restrict__ bias, const uint8_t* __restrict__ is_padding,
+                   float* topk_weights, int32_t* topk_ids, int32_t* token_expert_indices, int num_tokens, int num_experts,
+                   int topk, bool renormalize, float scaling, const int32_t* __restrict__ expert_map, int block_size,
+                   int32_t* sorted_token_ids, int64_t sorted_size, int32_t* experts_ids, int64_t experts_size,
+                   int32_t* num_tokens_post_pad, unsigned align_bytes) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int warp = threadIdx.x >> 5;
+  for (int token = warp; token < num_tokens; token += align::kWarps) {
+    RouteTokenSoftmax<In, int32_t, kSigmoid>(smem_raw + align_bytes, warp, align::kWarps, token, gating, bias, is_padding,
+                                             topk_weights, topk_ids, token_expert_indices, num_tokens, num_experts, topk,
+                                             renormalize, scaling);
+    __syncwarp();
+  }
+  __syncthreads();  // the ids are in global memory and visible to the whole block
+  align::AlignOneBlock(smem_raw, topk_ids, expert_map, num_tokens * topk, num_experts, block_size, sorted_token_ids,
+                       sorted_size, experts_ids, experts_size, num_tokens_post_pad);
+}
+
+template <typename Score, int kScoring>
+__global__ void __launch_bounds__(align::kChunk)
+GroupedAlignKernel(const Score* __restrict__ scores, const float* __restrict__ bias, float* topk_values,
+                   int32_t* topk_ids, int num_tokens, int num_experts, int num_groups, int topk_group, int topk,
+                   bool renormalize, float scaling, const int32_t* __restrict__ expert_map, int block_size,
+                   int32_t* sorted_token_ids, int64_t sorted_size, int32_t* experts_ids, int64_t experts_size,
+                   int32_t* num_tokens_post_pad, unsigned align_bytes) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int warp = threadIdx.x >> 5;
+  for (int token = warp; token < num_tokens; token += align::kWarps) {
+    RouteTokenGrouped<Score, float, kScoring>(smem_raw + align_bytes, warp, align::kWarps, token, scores, bias, topk_values,
+                                              topk_ids, num_experts, num_groups, topk_group, topk, renormalize, scaling);
+    __syncwarp();
+  }
+  __syncthreads();
+  align::AlignOneBlock(smem_raw, topk_ids, expert_map, num_tokens * topk, num_experts, block_size, sorted_token_ids,
+                       sorted_size, experts_ids, experts_size, num_tokens_post_pad);
+}
+
+// Whether the fused launch applies, and its shared memory.
+bool FusedFits(int64_t num_tokens, int64_t num_experts, int64_t topk, size_t& smem) {
+  if (num_tokens <= 0 || topk <= 0 || num_tokens * topk > align::kChunk || num_experts <= 0 || num_experts >= 1024) {
+    return false;
+  }
+  smem = FusedAlignBytes(num_experts) + RouterSmemBytes(align::kWarps, num_experts);
+  return smem <= 200 * 1024;
+}
+
+template <typename Kernel>
+int AllowFusedSmem(Kernel kernel, size_t smem) {
+  if (smem > 48 * 1024) {
+    const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (err != cudaSuccess) return Fail(IOB_CUDA_ERROR, "router + sort: %s", cudaGetErrorString(err));
+  }
+  return IOB_OK;
+}
+
+int CheckSortOutputs(const char* op, int64_t numel, int64_t num_experts, int64_t block_size, const int32_t* sorted,
+                     int64_t sorted_size, const int32_t* experts_ids, int64_t experts_size, const int32_t* npost) {
+  IOB_REQUIRE(block_size > 0 && block_size <= INT32_MAX, "%s: requires a positive `block_size`", op);
+  int64_t need_sorted = numel + num_experts * (block_size - 1);
+  if (numel < num_experts) need_sorted = std::min(need_sorted, numel * block_size);
+  const int64_t need_blocks = (need_sorted + block_size - 1) / block_size;
+  IOB_REQUIRE(sorted_size >= need_sorted && experts_size >= need_blocks, "%s: the sort's output tensors are too small", op);
+  IOB_REQUIRE(npost != nullptr && sorted != nullptr && experts_ids != nullptr, "%s: null tensor pointer", op);
+  return IOB_OK;
+}
+
+template <typename In>
+int LaunchSoftmaxAlign(bool sigmoid, const void* gating, const float* bias, const uint8_t* is_padding, float* w,
+                       int32_t* ids, int32_t* tei, int t, int e, int k, bool renorm, float scaling,
+                       const int32_t* expert_map, int bs, int32_t* sorted, int64_t sorted_size, int32_t* experts_ids,
+                       int64_t experts_size, int32_t* npost, size_t smem, cudaStream_t s) {
+  const unsigned align_bytes = static_cast<unsigned>(FusedAlignBytes(e));
+  auto launch = [&](auto kernel) {
+    if (const int rc = AllowFusedSmem(kernel, smem)) return rc;
+    kernel<<<1, align::kChunk, smem, s>>>(static_cast<const In*>(gating), bias, is_padding, w, ids, tei, t, e, k, renorm,
+                                          scaling, expert_map, bs, sorted, sorted_size, experts_ids, experts_size, npost,
+                                          align_bytes);
+    return CheckLaunch("router + sort launch");
+  };
+  return sigmoid ? launch(SoftmaxAlignKernel<In, true>) : launch(SoftmaxAlignKernel<In, false>);
+}
+
+template <typename Score>
+int LaunchGroupedAlign(int scoring, const void* scores, const float* bias, float* values, int32_t* ids, int t, int e,
+                       int groups, int topk_group, int k, bool renorm, float scaling, const int32_t* expert_map, int bs,
+                       int32_t* sorted, int64_t sorted_size, int32_t* experts_ids, int64_t experts_size, int32_t* npost,
+                       size_t smem, cudaStream_t s) {
+  const unsigned align_bytes = static_cast<unsigned>(FusedAlignBytes(e));
+  auto launch = [&](auto kernel) {
+    if (const int rc = AllowFusedSmem(kernel, smem)) return rc;
+    kernel<<<1, align::kChunk, smem, s>>>(static_cast<const Score*>(scores), bias, values, ids, t, e, groups, topk_group, k,
+                                          renorm, scaling, expert_map, bs, sorted, sorted_size, experts_ids, experts_size,
+                                          npost, align_bytes);
+    return CheckLaunch("grouped router + sort launch");
+  };
+  return scoring == 1 ? launch(GroupedAlignKernel<Score, 1>) : launch(GroupedAlignKernel<Score, 0>);
+}
+
+}  // namespace
+}  // namespace iob
+
+extern "C" int infiniops_b200_moe_align_block_size(const int32_t*, const int32_t*, int64_t, int64_t, int64_t, int32_t*,
+                                                   int64_t, int32_t*, int64_t, int32_t*, void*, size_t, void*);
+
+extern "C" int infiniops_b200_topk_softmax_align(const void* gating_output, int gating_dtype, const float* bias,
+                                                 const uint8_t* is_padding, int renormalize, int sigmoid,
+                                                 double routed_scaling_factor, float* topk_weights, int32_t* topk_ids,
+                                                 int32_t* token_expert_indices, int64_t num_tokens, int64_t num_experts,
+                                                 int64_t topk, const int32_t* expert_map, int64_t block_size,
+                                                 int32_t* sorted_token_ids, int64_t sorted_size, int32_t* experts_ids,
+                                                 int64_t experts_size, int32_t* num_tokens_post_pad, void* scratch,
+                                                 size_t scratch_bytes, void* stream) {
+  using namespace iob;
+  size_t smem = 0;
+  const bool known = gating_dtype == IOB_F32 || gating_dtype == IOB_F16 || gating_dtype == IOB_BF16;
+  if (!known || !FusedFits(num_tokens, num_experts, topk, smem) || topk > num_experts) {
+    // two launches (or three): the operators themselves, which also report what is wrong with the arguments
+    const int rc = sigmoid ? infiniops_b200_topk_sigmoid(gating_output, gating_dtype, bias, is_padding, renormalize,
+                                                         routed_scaling_factor, topk_weights, topk_ids, IOB_I32,
+                                                         token_expert_indices, num_tokens, num_experts, topk, stream)
+                           : infiniops_b200_topk_softmax(gating_output, gating_dtype, bias, is_padding, renormalize,
+                                                         topk_weights, topk_ids, IOB_I32, token_expert_indices, num_tokens,
+                                                         num_experts, topk, stream);
+    if (rc != IOB_OK) return rc;
+    return infiniops_b200_moe_align_block_size(topk_ids, expert_map, num_tokens * topk, num_experts, block_size,
+                                               sorted_token_ids, sorted_size, experts_ids, experts_size,
+                                               num_tokens_post_pad, scratch, scratch_bytes, stream);
+  }
+  IOB_REQUIRE(gating_output && topk_weights && topk_ids && token_expert_indices, "topk_softmax_align: null tensor pointer");
+  IOB_REQUIRE(!sigmoid || std::isfinite(routed_scaling_factor), "topk_softmax_align: requires a finite scaling factor");
+  if (const int rc = CheckSortOutputs("topk_softmax_align", num_tokens * topk, num_experts, block_size, sorted_token_ids,
+                                      sorted_size, experts_ids, experts_size, num_tokens_post_pad)) {
+    return rc;
+  }
+  auto s = static_cast<cudaStream_t>(stream);
+  const int t = static_cast<int>(num_tokens), e = static_cast<int>(num_experts), k = static_cast<int>(topk);
+  const float scaling = sigmoid ? static_cast<float>(routed_scaling_factor) : 1.0f;
+  const bool renorm = renormalize != 0, sig = sigmoid != 0;
+  const int bs = static_cast<int>(block_size);
+  switch (gating_dtype) {
+    case IOB_F32:
+      return LaunchSoftmaxAlign<float>(sig, gating_output, bias, is_padding, topk_weights, topk_ids, token_expert_indices, t, e, k, renorm, scaling, expert_map, bs, sorted_token_ids, sorted_size, experts_ids, experts_size, num_tokens_post_pad, smem, s);
+    case IOB_F16:
+      return LaunchSoftmaxAlign<__half>(sig, gating_output, bias, is_padding, topk_weights, topk_ids, token_expert_indices, t, e, k, renorm, scaling, expert_map, bs, sorted_token_ids, sorted_size, experts_ids, experts_size, num_tokens_post_pad, smem, s);
+    default:
+      return LaunchSoftmaxAlign<__nv_bfloat16>(sig, gating_output, bias, is_padding, topk_weights, topk_ids, token_expert_indices, t, e, k, renorm, scaling, expert_map, bs, sorted_token_ids, sorted_size, experts_ids, experts_size, num_tokens_post_pad, smem, s);
+  }
+}
+
+extern "C" int infiniops_b200_grouped_topk_align(const void* scores, int scores_dtype, const void* bias, int bias_dtype,
+                                                 int64_t num_tokens, int64_t num_experts, int64_t num_expert_group,
+                                                 int64_t topk_group, int64_t topk, int renormalize,
+                                                 double routed_scaling_factor, int scoring_func, float* topk_values,
+                                                 int32_t* topk_ids, const int32_t* expert_map, int64_t block_size,
+                                                 int32_t* sorted_token_ids, int64_t sorted_size, int32_t* experts_ids,
+                                                 int64_t experts_size, int32_t* num_tokens_post_pad, void* scratch,
+                                                 size_t scratch_bytes, void* stream) {
+  using namespace iob;
+  size_t smem = 0;
+  const bool known = scores_dtype == IOB_F32 || scores_dtype == IOB_F16 || scores_dtype == IOB_BF16;
+  const bool valid = num_expert_group > 0 && num_expert_group <= kMaxGroups && num_experts > 0 &&
+                     num_experts % num_expert_group == 0 && num_experts / num_expert_group >= 2 && topk_group > 0 &&
+                     topk_group <= num_expert_group && topk > 0 && topk <= num_experts &&
+                     (scoring_func == 0 || scoring_func == 1) && scores && bias && topk_values && topk_ids;
+  if (!known || !valid || bias_dtype != IOB_F32 || !FusedFits(num_tokens, num_experts, topk, smem)) {
+    const int rc = infiniops_b200_grouped_topk(scores, scores_dtype, bias, bias_dtype, num_tokens, num_experts,
+                                               num_expert_group, topk_group, topk, renormalize, routed_scaling_factor,
+                                               scoring_func, topk_values, topk_ids, stream);
+    if (rc != IOB_OK) return rc;
+    return infiniops_b200_moe_align_block_size(topk_ids, expert_map, num_tokens * topk, num_experts, block_size,
+                                               sorted_token_ids, sorted_size, experts_ids, experts_size,
+                                               num_tokens_post_pad, scratch, scratch_bytes, stream);
+  }
+  if (const int rc = CheckSortOutputs("grouped_topk_align", num_tokens * topk, num_experts, block_size, sorted_token_ids,
+                                      sorted_size, experts_ids, experts_size, num_tokens_post_pad)) {
+    return rc;
+  }
+  auto s = static_cast<cudaStream_t>(stream);
+  const int t = static_cast<int>(num_tokens), e = static_cast<int>(num_experts), k = static_cast<int>(topk);
+  const int groups = static_cast<int>(num_expert_group), tg = static_cast<int>(topk_group);
+  const float scaling = static_cast<float>(routed_scaling_factor);
+  const bool renorm = renormalize != 0;
+  const int bs = static_cast<int>(block_size);
+  const float* fbias = static_cast<const float*>(bias);
+  switch (scores_dtype) {
+    case IOB_F32:
+      return LaunchGroupedAlign<float>(scoring_func, scores, fbias, topk_values, topk_ids, t, e, groups, tg, k, renorm, scaling, expert_map, bs, sorted_token_ids, sorted_size, experts_ids, experts_size, num_tokens_post_pad, smem, s);
+    case IOB_F16:
+      return LaunchGroupedAlign<__half>(scoring_func, scores, fbias, topk_values, topk_ids, t, e, groups, tg, k, renorm, scaling, expert_map, bs, sorted_token_ids, sorted_size, experts_ids, experts_size, num_tokens_post_pad, smem, s);
+    default:
+      return LaunchGroupedAlign<__nv_bfloat16>(scoring_func, scores, fbias, topk_values, topk_ids, t, e, groups, tg, k, renorm, scaling, expert_map, bs, sorted_token_ids, sorted_size, experts_ids, experts_size, num_tokens_post_pad, smem, s);
   }
 }

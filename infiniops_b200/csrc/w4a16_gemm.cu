@@ -123,6 +123,10 @@ struct GemmParams {
   int flag_slot, n_flag_peers;
   // routed form only
   int out_sorted;                   // 1: result rows stay in sorted order (row = position in `sorted_ids`), stored as tiles
+  // 1 (sorted output only; kernels built with kSilu): the weight columns come as gate/up interleaved
+  // in runs of 16 (columns 32b..32b+15 = gate features 16b.., columns 32b+16..32b+31 = the matching up
+  // features) and the epilogue stores silu(gate) * up, [rows][N/2], instead of the [rows][N] product.
+  int fuse_silu;
   const int2* row_dest;             // null, or per output row: (GPU, row there) the result row is stored to
   void* dest_base[kMaxPeers + 1];   // with `row_dest`: the destination matrix of every GPU (own included)
   const int32_t* sorted_ids;
@@ -655,9 +659,10 @@ struct Shared {
 // kBatch: `probs` is a table of `count` dense problems that are worked through as one sequence of
 // units (see BatchTable); otherwise it points to the launch's single problem.  `cur` is the problem
 // the executing thread is currently working on -- every role moves it forward with its own walker.
-template <typename T, int kTok, bool kZeros, bool kMoe, int kSets, bool kLate, bool kPair, bool kBatch>
+template <typename T, int kTok, bool kZeros, bool kMoe, int kSets, bool kLate, bool kPair, bool kBatch, bool kSilu = false>
 __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
   static_assert(!kBatch || (!kMoe && !kPair && kLate), "batched launches: dense late-scale tiles only");
+  static_assert(!kSilu || kMoe, "silu_and_mul in the epilogue: routed form only (sorted output)");
   const Problem* cur = probs;
   int* const status_word = probs->p.status;  // one status header per launch
   using Sh = Shared<kTok, kSets, kPair>;
@@ -941,6 +946,51 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
       Segment seg;
       uint32_t it = 0, seg_idx = 0;
       bool alive = true;
+      if constexpr (kLate && !kMoe) {
+        // Late-scale dense tiles: nothing the issuer does depends on where a tile or a problem ends
+        // -- every stage has its own accumulator, and ring slots follow from the stage number --
+        // so this thread walks its own stages (me, me + kIssuers, ...) of the block's range directly,
+        // with ring positions kept incrementally.  This thread's latency from "weights converted"
+        // to "MMAs issued" paces the pipeline, so its instruction count matters.
+        const uint32_t total = static_cast<uint32_t>(u_end - u_begin);
+        int s = me % kStages, a = me % kAStages, slot = me % kSlots;
+        uint32_t a_phase = 0, slot_phase = 0;
+        for (it = me; it < total; it += kIssuers) {
+          if (!MbarWait(SmemAddr(&sh.d_empty[slot]), slot_phase ^ 1, abort_flag, status_word, kErrDEmpty,
+                        static_cast<int>(it)) ||
+              !MbarWait(SmemAddr(&sh.a_full[a]), a_phase, abort_flag, status_word, kErrAFull, static_cast<int>(it))) {
+            alive = false;
+            break;
+          }
+          TcFenceAfter();
+          const uint32_t act = stages_addr + s * kStage;
+          const uint64_t desc0 = static_cast<uint64_t>((act >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) | (1ull << 46) |
+                                 (2ull << 61);
+          const uint32_t d_addr = tmem_d + slot * kTok;
+#pragma unroll
+          for (int j = 0; j < kBlockK / 16; ++j) {
+            const uint64_t desc = desc0 + static_cast<uint64_t>((j >> 2) * (kAtomBytes >> 4) + 2 * (j & 3));
+            MmaTs(d_addr, tmem_a + a * kAStageCols + 8 * j, desc, kIdesc, j > 0 ? 1u : 0u);
+          }
+          TcCommit(SmemAddr(&sh.empty[s]));
+          TcCommit(SmemAddr(&sh.a_empty[a]));
+          TcCommit(SmemAddr(&sh.d_full[slot]));
+          last_it = static_cast<int>(it);
+          s += kIssuers;
+          if (s >= kStages) s -= kStages;
+          a += kIssuers;
+          if (a >= kAStages) {
+            a -= kAStages;
+            a_phase ^= 1;
+          }
+          slot += kIssuers;
+          if (slot >= kSlots) {
+            slot -= kSlots;
+            slot_phase ^= 1;
+          }
+        }
+        if (last_it >= 0) first_it = me;
+      } else
       while (alive && walk.template Next<kBatch>(seg)) {
         if constexpr (kMoe) {
           if (cur->p.expert_ids[seg.m_tile] < 0) continue;
@@ -1341,6 +1391,15 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
       auto emit = [&](int j, float v) {
         v += bias_v;
         if constexpr (kMoe) {
+          if constexpr (kSilu) {
+            // lanes 0..15 hold gate features, lanes 16..31 the matching up features (sorted output)
+            const float mine = ToFloat<T>(FromFloat<T>(v));
+            const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
+            if (lane < 16) {
+              out[static_cast<size_t>(row0 + j) * (cur->p.n >> 1) + ((n - lane) >> 1) + lane] = SiluMulRounded<T>(mine, other);
+            }
+            return;
+          }
           if (cur->p.out_sorted) {
             out[static_cast<size_t>(row0 + j) * cur->p.n + n] = FromFloat<T>(v);
             return;
@@ -1382,15 +1441,27 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
               const uint32_t buf = out_stage_addr + q * 2048 + (staged & 1) * 1024;
               if (lane == 0) BulkWaitRead1();  // the store that used this buffer two chunks ago has read it
               __syncwarp();
+              if constexpr (kSilu) {
+                // 16 rows x 16 features: gate (lanes 0..15) meets up (lanes 16..31) by shuffle, both
+                // rounded to the storage type first, as a stored-then-reloaded product would be
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const T v = FromFloat<T>(__uint_as_float(r[j]) + bias_v);
-                StShared16(buf + j * 64 + lane * 2, *reinterpret_cast<const unsigned short*>(&v));
+                for (int j = 0; j < 16; ++j) {
+                  const float mine = ToFloat<T>(FromFloat<T>(__uint_as_float(r[j]) + bias_v));
+                  const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
+                  const T v = SiluMulRounded<T>(mine, other);
+                  if (lane < 16) StShared16(buf + j * 32 + lane * 2, *reinterpret_cast<const unsigned short*>(&v));
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  const T v = FromFloat<T>(__uint_as_float(r[j]) + bias_v);
+                  StShared16(buf + j * 64 + lane * 2, *reinterpret_cast<const unsigned short*>(&v));
+                }
               }
               FenceProxyAsyncShared();
               __syncwarp();
               if (lane == 0) {
-                TmaStore2D(&cur->c_map, buf, cur->p.out_col0 + n - lane, row0 + c);
+                TmaStore2D(&cur->c_map, buf, kSilu ? (n - lane) >> 1 : cur->p.out_col0 + n - lane, row0 + c);
                 BulkCommitGroup();
               }
               if (cur->p.n_peers > 0) {
@@ -1663,10 +1734,10 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
 }
 
 // One problem per launch.
-template <typename T, int kTok, bool kZeros, bool kMoe, int kSets, bool kLate, bool kPair = false>
+template <typename T, int kTok, bool kZeros, bool kMoe, int kSets, bool kLate, bool kPair = false, bool kSilu = false>
 __global__ void __launch_bounds__((5 + IssuersFor(kTok) + 4 * kSets) * 32, 1)
 W4A16GemmKernel(const __grid_constant__ Problem problem) {
-  GemmBody<T, kTok, kZeros, kMoe, kSets, kLate, kPair, false>(&problem, 1);
+  GemmBody<T, kTok, kZeros, kMoe, kSets, kLate, kPair, false, kSilu>(&problem, 1);
 }
 // A table of dense problems per launch.
 template <typename T, int kTok, bool kZeros, int kSets>
@@ -1819,9 +1890,9 @@ int ActivationMap(const void* ptr, int64_t rows, int64_t cols, int box_rows, int
 
 // Output [rows, cols] of a 16-bit type, box = 16 rows x 32 columns: the tile one epilogue warp
 // stages and stores at a time.
-int OutputMap(const void* ptr, int64_t rows, int64_t cols, int dtype, CUtensorMap* out) {
+int OutputMap(const void* ptr, int64_t rows, int64_t cols, int dtype, CUtensorMap* out, int box_cols = 32) {
   static thread_local std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-  const MapKey key{ptr, rows, cols, 16, 32, dtype == IOB_BF16 ? kMapBf16 : kMapF16};
+  const MapKey key{ptr, rows, cols, 16, box_cols, dtype == IOB_BF16 ? kMapBf16 : kMapF16};
   auto it = cache.find(key);
   if (it != cache.end()) {
     *out = it->second;
@@ -1831,7 +1902,7 @@ int OutputMap(const void* ptr, int64_t rows, int64_t cols, int dtype, CUtensorMa
   if (encode == nullptr) return Fail(IOB_CUDA_ERROR, "W4A16 GEMM: cuTensorMapEncodeTiled is not available");
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
-  const cuuint32_t box[2] = {32, 16};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), 16};
   const cuuint32_t elem[2] = {1, 1};
   const CUresult rc = encode(out, dtype == IOB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
                              2, const_cast<void*>(ptr), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -1895,11 +1966,11 @@ ScratchPlan PlanScratch(int64_t tiles, int tok, int64_t gathered_bytes) {
   return plan;
 }
 
-template <typename T, int kTok, bool kZeros, bool kMoe, bool kLate, bool kPair = false>
+template <typename T, int kTok, bool kZeros, bool kMoe, bool kLate, bool kPair = false, bool kSilu = false>
 int LaunchVariant(const CUtensorMap& map, const CUtensorMap& w_map, const CUtensorMap& c_map, const GemmParams& p,
                   int grid, cudaStream_t stream) {
   constexpr int kSets = kPair ? kPairSets : SetsFor(kTok);
-  auto kernel = W4A16GemmKernel<T, kTok, kZeros, kMoe, kSets, kLate, kPair>;
+  auto kernel = W4A16GemmKernel<T, kTok, kZeros, kMoe, kSets, kLate, kPair, kSilu>;
   // rings + 8 KB of output staging + slack for the 1024-byte alignment
   constexpr int smem =
       (kPair ? kPairStages * 8192 + kPairActStages * kTok * 128 : StagesFor(kTok) * StageBytes(kTok)) + 8192 + 1024;
@@ -1990,18 +2061,25 @@ int LaunchBatch(int a_dtype, bool zeros, int tok, const BatchTable& table, int g
 
 // Token tiles up to 32 with groups of at least one k-stage take the variant that scales the
 // accumulators instead of the weights.
-template <typename T, int kTok, bool kZeros, bool kMoe>
+template <typename T, int kTok, bool kZeros, bool kMoe, bool kSilu = false>
 int LaunchKernel(const CUtensorMap& map, const CUtensorMap& w_map, const CUtensorMap& c_map, const GemmParams& p, int grid,
                  cudaStream_t stream) {
+  // silu_and_mul in the epilogue is a kernel variant of its own (routed form only), so that the
+  // kernels without it carry none of its code
+  if constexpr (kMoe && !kSilu) {
+    if (p.fuse_silu) return LaunchKernel<T, kTok, kZeros, kMoe, true>(map, w_map, c_map, p, grid, stream);
+  }
   // (64-row tiles: dense only -- the routed form, with its many whole tiles per block and its
   // scattered tile-end stores, measured 40 % slower that way than with scaled weights)
   if constexpr (kTok <= 32 || (kTok == 64 && !kMoe)) {
-    if (p.group_size >= kBlockK) return LaunchVariant<T, kTok, kZeros, kMoe, true>(map, w_map, c_map, p, grid, stream);
+    if (p.group_size >= kBlockK) {
+      return LaunchVariant<T, kTok, kZeros, kMoe, true, false, kSilu>(map, w_map, c_map, p, grid, stream);
+    }
   }
   if constexpr (kTok == 256) {
-    if (p.pair) return LaunchVariant<T, kTok, kZeros, kMoe, false, true>(map, w_map, c_map, p, grid, stream);
+    if (p.pair) return LaunchVariant<T, kTok, kZeros, kMoe, false, true, kSilu>(map, w_map, c_map, p, grid, stream);
   }
-  return LaunchVariant<T, kTok, kZeros, kMoe, false>(map, w_map, c_map, p, grid, stream);
+  return LaunchVariant<T, kTok, kZeros, kMoe, false, false, kSilu>(map, w_map, c_map, p, grid, stream);
 }
 
 template <typename T, bool kZeros, bool kMoe>
@@ -2393,6 +2471,9 @@ extern "C" int infiniops_b200_moe_wna16_marlin_gemm_ex(
     p.out_sorted = options->out_sorted ? 1 : 0;
     IOB_REQUIRE(!p.out_sorted || (!mul_topk_weights && options->row_dest == nullptr),
                 "%s: sorted output takes neither routing weights nor a scatter", op);
+    p.fuse_silu = options->fuse_silu ? 1 : 0;
+    IOB_REQUIRE(!p.fuse_silu || (p.out_sorted && size_n % 128 == 0),
+                "%s: the fused silu needs sorted output and `size_n` a multiple of 128", op);
     if (options->row_dest != nullptr) {
       IOB_REQUIRE(options->n_dest > 0 && options->n_dest <= kMaxPeers + 1, "%s: incomplete scatter description", op);
       p.row_dest = reinterpret_cast<const int2*>(options->row_dest);
@@ -2405,7 +2486,10 @@ extern "C" int infiniops_b200_moe_wna16_marlin_gemm_ex(
   }
   CUtensorMap c_map = w_map;  // unused while rows are scattered
   if (p.out_sorted) {
-    if (const int rc = OutputMap(out, sorted_cap, size_n, a_dtype, &c_map)) return rc;
+    if (const int rc = p.fuse_silu ? OutputMap(out, sorted_cap, size_n / 2, a_dtype, &c_map, 16)
+                                   : OutputMap(out, sorted_cap, size_n, a_dtype, &c_map)) {
+      return rc;
+    }
   }
   return Dispatch<true>(a_dtype, b_zeros != nullptr, tok, map, w_map, c_map, p, NumSms(), s);
 }

@@ -22,7 +22,9 @@ def padded_sizes(numel: int, num_experts: int, block: int) -> tuple[int, int]:
 
 @dataclasses.dataclass
 class ExpertWeights:
-    """Marlin-packed experts of one rank: w13 [E, H/16, 2*2I], w2 [E, I/16, 2H], scales, optional zeros."""
+    """Marlin-packed experts of one rank: w13 [E, H/16, 2*2I], w2 [E, I/16, 2H], scales, optional zeros.
+    `interleaved`: the columns of w13 / s13 / z13 were reordered with `gate_up_interleave` before
+    packing, so the first GEMM can apply silu_and_mul in its epilogue."""
     w13: torch.Tensor
     s13: torch.Tensor
     z13: torch.Tensor | None
@@ -31,6 +33,7 @@ class ExpertWeights:
     z2: torch.Tensor | None
     hidden: int
     inter: int
+    interleaved: bool = False
 
     @property
     def num_experts(self) -> int:
@@ -39,6 +42,17 @@ class ExpertWeights:
     @property
     def qtype(self) -> int:
         return capi.QTYPE_UINT4 if self.z13 is not None else capi.QTYPE_UINT4B8
+
+
+def gate_up_interleave(inter: int, device=None) -> torch.Tensor:
+    """Column order of a gate/up projection for the fused silu epilogue: index tensor `idx` [2 * inter]
+    such that `w13[..., idx]` holds, in every run of 32 columns, 16 gate features followed by the
+    same 16 up features (`w13` being [gate | up] along its last axis, as `silu_and_mul` reads it).
+    Apply it to the unpacked weights, the scales and the unpacked zero points before packing."""
+    if inter % 16:
+        raise ValueError("the fused silu epilogue needs an intermediate size that is a multiple of 16")
+    p = torch.arange(2 * inter, device=device)
+    return (p // 32) * 16 + p % 16 + (p % 32 >= 16) * inter
 
 
 class RoutedExperts:
@@ -86,10 +100,16 @@ def routing_block(routes: int, num_experts: int) -> int:
     blocks do a quarter of the conversion work (and 256-row blocks run on paired thread blocks).
     The padding (at most block - 1 rows per expert) must stay small against the rows themselves."""
     per_expert = routes / max(1, num_experts)
-    # (measured on a B200, Mixtral- and DeepSeek-shaped layers: 128-row blocks beat 64-row ones by 12-37 %
-    # from about 256 rows per expert on; 256-row blocks on paired thread blocks come out level with
-    # 128-row ones, their second GEMM still scattering its rows one by one, and pad more)
-    return 128 if per_expert >= 192 else 64
+    # Measured on a B200 with Mixtral- and DeepSeek-shaped layers.  Many rows per expert: 128-row
+    # blocks beat 64-row ones by 12-37 % from about 256 rows per expert on (256-row blocks on paired
+    # thread blocks come out level with 128-row ones and pad more).  Few rows per expert: a block is
+    # mostly padding, and the GEMM's token tile follows the block, so 16-row blocks win below about 8
+    # rows per expert (by 25-50 %) and 32-row blocks up to about 32.
+    if per_expert >= 192:
+        return 128
+    if per_expert >= 32:
+        return 64
+    return 32 if per_expert >= 8 else 16
 
 
 def route_softmax(logits: torch.Tensor, top_k: int, renormalize: bool = True, stream=None):
@@ -109,25 +129,56 @@ def route_grouped(scores, bias, groups, topk_group, top_k, scaling, stream=None)
     return w, ids
 
 
-def single_gpu_layer(x, topk_weights, topk_ids, experts: RoutedExperts, stream=None) -> torch.Tensor:
+def _sort_buffers(experts: RoutedExperts, routes: int, dev):
+    size, blocks = padded_sizes(routes, experts.w.num_experts, experts.block)
+    return (experts._buf("L_sorted", (size,), torch.int32, dev), experts._buf("L_eids", (blocks,), torch.int32, dev),
+            experts._buf("L_npost", (1,), torch.int32, dev))
+
+
+def layer_from_logits(x, logits, router: dict, experts: RoutedExperts, stream=None) -> torch.Tensor:
+    """The whole layer from the router's input, with router and token sort issued as one call (one
+    launch while tokens x top_k <= 1024).  `router`: {"kind": "softmax", "top_k": k, "renormalize": bool}
+    or {"kind": "grouped", "top_k": k, "bias": tensor, "groups": g, "topk_group": n, "scaling": f}."""
+    t, dev, k = logits.shape[0], logits.device, router["top_k"]
+    w = experts._buf("L_tw", (t, k), torch.float32, dev)
+    ids = experts._buf("L_ids", (t, k), torch.int32, dev)
+    sorted_ids, expert_ids, npost = _sort_buffers(experts, t * k, dev)
+    if router["kind"] == "softmax":
+        tei = experts._buf("L_tei", (t, k), torch.int32, dev)
+        capi.topk_softmax_align(logits, None, None, router.get("renormalize", True), w, ids, tei, None, experts.block,
+                                sorted_ids, expert_ids, npost, stream=stream)
+    else:
+        capi.grouped_topk_align(logits, router["bias"], router["groups"], router["topk_group"], k, True,
+                                router["scaling"], 1, w, ids, None, experts.block, sorted_ids, expert_ids, npost,
+                                stream=stream)
+    return single_gpu_layer(x, w, ids, experts, stream=stream, presorted=True)
+
+
+def single_gpu_layer(x, topk_weights, topk_ids, experts: RoutedExperts, stream=None, presorted=False) -> torch.Tensor:
     """The layer on one GPU in the reference's chaining: the sort runs on the [T, k] ids and the first
-    GEMM reads token `route // k` directly (no row duplication)."""
+    GEMM reads token `route // k` directly (no row duplication).  `presorted`: the sort's outputs for
+    these ids are already in the runner's buffers (see `layer_from_logits`)."""
     w, block, dev = experts.w, experts.block, x.device
     t, k = topk_ids.shape
-    size, blocks = padded_sizes(t * k, w.num_experts, block)
-    sorted_ids = experts._buf("L_sorted", (size,), torch.int32, dev)
-    expert_ids = experts._buf("L_eids", (blocks,), torch.int32, dev)
-    npost = experts._buf("L_npost", (1,), torch.int32, dev)
-    capi.moe_align_block_size(topk_ids, None, w.num_experts, block, sorted_ids, expert_ids, npost, stream=stream)
+    size, _ = padded_sizes(t * k, w.num_experts, block)
+    sorted_ids, expert_ids, npost = _sort_buffers(experts, t * k, dev)
+    if not presorted:
+        capi.moe_align_block_size(topk_ids, None, w.num_experts, block, sorted_ids, expert_ids, npost, stream=stream)
     flat_w = topk_weights.reshape(-1)
     # The intermediates stay in sorted (expert) order -- one row per entry of `sorted_ids` -- so the
     # first GEMM stores dense tiles and the second reads them in place; only the last result is
     # scattered to its route.
-    g = experts._buf("L_g", (size, 2 * w.inter), x.dtype, dev)
-    capi.moe_wna16_marlin_gemm(x, w.w13, None, w.s13, w.z13, sorted_ids, expert_ids, npost, flat_w, block, k, False,
-                               w.qtype, t, 2 * w.inter, w.hidden, g, stream=stream, out_sorted=True)
     h = experts._buf("L_h", (size, w.inter), x.dtype, dev)
-    capi.silu_and_mul(g, h, stream=stream)
+    if w.interleaved and (2 * w.inter) % 128 == 0:
+        # gate and up meet in the epilogue: the [size, 2I] product is never stored
+        capi.moe_wna16_marlin_gemm(x, w.w13, None, w.s13, w.z13, sorted_ids, expert_ids, npost, flat_w, block, k,
+                                   False, w.qtype, t, 2 * w.inter, w.hidden, h, stream=stream, out_sorted=True,
+                                   fuse_silu=True)
+    else:
+        g = experts._buf("L_g", (size, 2 * w.inter), x.dtype, dev)
+        capi.moe_wna16_marlin_gemm(x, w.w13, None, w.s13, w.z13, sorted_ids, expert_ids, npost, flat_w, block, k,
+                                   False, w.qtype, t, 2 * w.inter, w.hidden, g, stream=stream, out_sorted=True)
+        capi.silu_and_mul(g, h, stream=stream)
     y = experts._buf("L_y", (t * k, w.hidden), x.dtype, dev)
     capi.moe_wna16_marlin_gemm(h, w.w2, None, w.s2, w.z2, sorted_ids, expert_ids, npost, flat_w, block, 1, True,
                                w.qtype, t * k, w.hidden, w.inter, y, stream=stream, a_sorted=True)

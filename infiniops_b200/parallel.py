@@ -191,6 +191,7 @@ class DeviceExpertParallel:
         cw.w2, cw.s2, cw.groups2 = w.w2.data_ptr(), w.s2.data_ptr(), w.s2.shape[1]
         cw.z13 = None if w.z13 is None else w.z13.data_ptr()
         cw.z2 = None if w.z2 is None else w.z2.data_ptr()
+        cw.w13_interleaved = int(w.interleaved)
         self.cw = cw
         need = lib.infiniops_b200_ep_workspace_bytes(ctx)
         if need == 0:

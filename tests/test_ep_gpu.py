@@ -81,6 +81,17 @@ def _worker(rank, world, port):
             err = float((got2.float() - expect[t0:t1].float()).abs().max() / expect.float().abs().max())
             assert err <= 1e-2, err
         ep.close()
+        # ... and with the columns of w13 read as gate/up interleaved (silu_and_mul in the GEMM epilogue),
+        # against the single-GPU layer reading them the same way
+        full.w.interleaved = local.w.interleaved = True
+        expect_fused = moe_layer.single_gpu_layer(x, weights, ids, full).clone()
+        ep_fused = parallel.DeviceExpertParallel(local.w, top_k, tokens // world + 8, dev, block)
+        got3 = ep_fused(x[t0:t1].contiguous(), ids[t0:t1].contiguous(), weights[t0:t1].contiguous())
+        torch.cuda.synchronize()
+        assert ep_fused.status() == (0, 0, 0), ep_fused.status()
+        err3 = float((got3.float() - expect_fused[t0:t1].float()).abs().max() / expect_fused.float().abs().max())
+        assert err3 <= 1e-2, err3
+        ep_fused.close()
 
         # column-parallel dense linear
         k, n, m = 1024, 1024, 16
@@ -136,10 +147,12 @@ def test_expert_parallel_and_column_parallel_on_two_gpus():
     mp.spawn(_worker, args=(2, _free_port()), nprocs=2, join=True)
 
 
-def test_device_expert_parallel_world_of_one_against_oracle():
+@pytest.mark.parametrize("interleaved", (False, True))
+def test_device_expert_parallel_world_of_one_against_oracle(interleaved):
     """The device-side expert-parallel layer with this GPU as the only rank, against the oracle chain
     router -> sort -> w13 -> silu_and_mul -> w2 (x weight) -> sum.  One token carries an expert id
-    outside the table: its route must contribute nothing."""
+    outside the table: its route must contribute nothing.  `interleaved`: w13 is packed with gate and
+    up interleaved and the layer applies silu_and_mul in the first GEMM's epilogue."""
     import numpy as np
 
     from infiniops_b200 import capi, moe_layer, parallel
@@ -150,20 +163,23 @@ def test_device_expert_parallel_world_of_one_against_oracle():
     dev = torch.device("cuda", 0)
     gen = torch.Generator().manual_seed(11)
 
-    def packed(k, n):
+    def packed(k, n, order=None):
         q = torch.randint(0, 16, (experts, k, n), generator=gen, dtype=torch.int32).numpy().astype(np.uint8)
         s = (torch.randn((experts, k // 128, n), generator=gen).abs() * 0.01 + 1e-3).bfloat16()
-        w = torch.stack([torch.from_numpy(oq.marlin_pack(q[e], 4, False)) for e in range(experts)]).to(dev)
-        return q, s, w
+        qd, sd = (q, s) if order is None else (q[:, :, order], s[:, :, order])
+        w = torch.stack([torch.from_numpy(oq.marlin_pack(qd[e], 4, False)) for e in range(experts)]).to(dev)
+        return q, s, w, sd
 
-    q13, s13, w13 = packed(hidden, 2 * inter)
-    q2, s2, w2 = packed(inter, hidden)
+    order = moe_layer.gate_up_interleave(inter).numpy() if interleaved else None
+    q13, s13, w13, s13_dev = packed(hidden, 2 * inter, order)
+    q2, s2, w2, _ = packed(inter, hidden)
     x = torch.randn((tokens, hidden), generator=gen).bfloat16()
     logits = torch.randn((tokens, experts), generator=gen)
     rw, rids, _ = omoe.topk_softmax(logits, None, None, top_k, True)
     ids = rids.to(torch.int32)
     ids[7, 1] = experts + 3   # a route to nowhere
-    weights = moe_layer.ExpertWeights(w13, s13.to(dev), None, w2, s2.to(dev), None, hidden, inter)
+    weights = moe_layer.ExpertWeights(w13, s13_dev.to(dev).contiguous(), None, w2, s2.to(dev), None, hidden, inter,
+                                      interleaved=interleaved)
     ep = parallel.DeviceExpertParallel(weights, top_k, tokens, dev, block, world=1)
     for _ in range(2):
         got = ep(x.to(dev), ids.to(dev), rw.to(dev))
