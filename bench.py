@@ -400,11 +400,11 @@ def run_ours(args):
         _shutdown(d, group)
 
 
-# DRAM bytes (read + write) of the GEMM launches of one step.  From the ncu capture of the
-# M=16, K=4096, N=28672 launch (profiles/w4a16_gemm_decode_m16_k4096_n28672.md): 61.84 MB measured
-# against 62.06 MB algorithmic, ratio 0.996; every launch streams its weights once in the same
-# way, so the step's traffic is taken as its algorithmic bytes times that ratio (single GPU).
-TRAFFIC_BYTES_PER_STEP = int(465084416 * 61.84 / 62.06)
+# DRAM bytes (read + write) of the GEMM launches of one step.  From the ncu capture of the batched
+# launch of the step's twelve M <= 16 problems (profiles/w4a16_gemm_batch_decode_step.md): 349.25 MB
+# measured against 342.86 MB algorithmic, ratio 1.019; the M = 64 launch streams its weights once in
+# the same way, so the step's traffic is taken as its algorithmic bytes times that ratio (single GPU).
+TRAFFIC_BYTES_PER_STEP = int(465084416 * 349.25 / 342.86)
 
 
 def check_gathered(d, capi, layers, acts, keys, gathered, phase, scratch, full_n, full_k):

@@ -446,10 +446,18 @@ int infiniops_b200_moe_wna16_gemm(const void* input, int dtype, const uint8_t* b
  * silu(gate) * up computed from the two products rounded to the activation type, bit for bit what
  * infiniops_b200_silu_and_mul makes of the stored product.  The [rows, size_n] intermediate never
  * exists.
- * Zero-initialise the struct.  No counterpart in the reference. */
+ * `g_idx`, `perm` (both or neither; int32 [num_experts, size_k]): activation order, the
+ * `g_idx_or_none` / `perm_or_none` of src/base/moe_wna16_marlin_gemm.h:258-271.  `perm[e]` is the row
+ * order expert e's weights were repacked with (gptq_marlin_repack's `perm`): the GEMM reads
+ * activation column perm[e][k] against weight row k.  `g_idx[e][k]` must be the group of row k in
+ * that order, i.e. k / group_size (what a provider passes with `is_k_full`); any other table is
+ * reported as code 9 in the scratch status word (expert in word 1), not misread.
+ * Zero-initialise the struct.  No counterpart in the reference beyond `g_idx` / `perm`. */
 typedef struct {
   int scale_layout;
   int a_sorted, out_sorted, fuse_silu;
+  const int32_t* g_idx;
+  const int32_t* perm;
   const int32_t* row_dest;
   void* dest_base[IOB_MAX_PEERS + 1];
   int n_dest;

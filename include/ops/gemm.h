@@ -110,14 +110,19 @@ class Operator<MoeWna16MarlinGemm, Device::Type::kNvidia, 0> : public MoeWna16Ma
     impl::RequireFourBit(b_type_id, kName);
     INFINI_OPS_CHECK(a.dtype() != DataType::kInt8 && !a_scales && !global_scale,
                      "`MoeWna16MarlinGemm` int8 activations and global scales are not implemented");
-    INFINI_OPS_CHECK(!g_idx_or_none || g_idx_or_none->numel() == 0,
-                     "`MoeWna16MarlinGemm` act-order (`g_idx` / `perm`) is not implemented");
     INFINI_OPS_CHECK(!is_zp_float, "`MoeWna16MarlinGemm` float zero points are not implemented");
     impl::DeviceGuard guard(device_index_);
     std::size_t scratch_bytes = 0;
     void* scratch = impl::PickScratch(workspace_, workspace_size_in_bytes_, workspace_size_in_bytes(), 0, stream_, scratch_bytes);
     iob_routed_options options{};
     options.scale_layout = scale_layout();
+    if (g_idx_or_none && g_idx_or_none->numel() != 0) {
+      // activation order: per-expert row order of the weights, and the (sorted) group of every row
+      INFINI_OPS_CHECK(g_idx_or_none->IsContiguous() && perm_or_none->IsContiguous(),
+                       "`MoeWna16MarlinGemm` requires contiguous `g_idx_or_none` and `perm_or_none`");
+      options.g_idx = static_cast<const int32_t*>(g_idx_or_none->data());
+      options.perm = static_cast<const int32_t*>(perm_or_none->data());
+    }
     impl::Require(
         infiniops_b200_moe_wna16_marlin_gemm_ex(
             a.data(), impl::TypeCode(a.dtype()), static_cast<const int32_t*>(b_q_weight.data()),

@@ -34,6 +34,7 @@
 
 #include <algorithm>
 #include <mutex>
+#include <type_traits>
 #include <unordered_map>
 
 #include "common.cuh"
@@ -87,10 +88,18 @@ __host__ __device__ constexpr int IssuersFor(int tok) { return tok <= 32 ? 3 : t
 __host__ __device__ constexpr bool SplitTokens(int tok) { return tok > 128; }
 // independent accumulators per accumulator stage
 __host__ __device__ constexpr int AccSetsFor(int tok) { return SplitTokens(tok) ? 1 : IssuersFor(tok); }
+__host__ __device__ constexpr int TmemNeedFor(int tok) {
+  return AccStagesFor(tok) * AccSetsFor(tok) * tok + AStagesFor(tok) * kAStageCols;
+}
 __host__ __device__ constexpr int TmemColsFor(int tok) {
-  const int need = AccStagesFor(tok) * AccSetsFor(tok) * tok + AStagesFor(tok) * kAStageCols;
+  const int need = TmemNeedFor(tok);
   return need <= 32 ? 32 : need <= 64 ? 64 : need <= 128 ? 128 : need <= 256 ? 256 : 512;
 }
+// The accumulators and the weight stages (kAStageCols = 64 columns each) share the 512 columns of
+// tensor memory; a ring that does not fit would be addressed past the allocation.
+static_assert(TmemNeedFor(16) <= 512 && TmemNeedFor(32) <= 512 && TmemNeedFor(64) <= 512 && TmemNeedFor(128) <= 512 &&
+                  TmemNeedFor(256) <= 512,
+              "tensor-memory budget");
 
 struct GemmParams {
   const uint32_t* wq;      // [E][K/16][2N]
@@ -1790,6 +1799,48 @@ __global__ void GatherRowsKernel(const T* __restrict__ a, T* __restrict__ gather
   }
 }
 
+// Act-order form of the gather: row `row` of the sorted layout is the token's activations with the
+// columns in the order of its expert's weight rows, gathered[row][k] = a[token][perm[expert][k]]
+// (`perm` = the row order the weights were repacked with; vLLM's `permute_cols`, fused into the gather
+// this GEMM does anyway).  `from_sorted`: `a` already has one row per sorted position.  The scales
+// are read per contiguous group of k, which is what `g_idx` says once the rows are in that order
+// (g_idx[expert][k] == k / group_size); the first row of every routing block checks its expert's
+// `g_idx` and a table of any other form is reported in the status header (code kErrGIdx), not
+// silently misread.
+constexpr int kErrGIdx = 9;
+template <typename T>
+__global__ void GatherPermutedRowsKernel(const T* __restrict__ a, T* __restrict__ gathered,
+                                         const int32_t* __restrict__ sorted_ids, const int32_t* __restrict__ expert_ids,
+                                         const int32_t* __restrict__ num_post_pad, const int32_t* __restrict__ perm,
+                                         const int32_t* __restrict__ g_idx, int k, int top_k, int out_rows, int block_size,
+                                         int group_size, int from_sorted, int* status) {
+  const int rows = *num_post_pad;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const int id = sorted_ids[row];
+    const int expert = expert_ids[row / block_size];
+    T* dst = gathered + static_cast<size_t>(row) * k;
+    if (id < out_rows && expert >= 0) {
+      const T* src = a + static_cast<size_t>(from_sorted ? row : id / top_k) * k;
+      const int32_t* order = perm + static_cast<size_t>(expert) * k;
+      for (int i = threadIdx.x; i < k; i += blockDim.x) {
+        const int from = order[i];
+        dst[i] = from >= 0 && from < k ? src[from] : FromFloat<T>(0.0f);
+      }
+    } else {
+      for (int i = threadIdx.x; i < k; i += blockDim.x) dst[i] = FromFloat<T>(0.0f);
+    }
+    if (expert >= 0 && row % block_size == 0) {
+      const int32_t* groups = g_idx + static_cast<size_t>(expert) * k;
+      bool ok = true;
+      for (int i = threadIdx.x; i < k; i += blockDim.x) ok = ok && groups[i] == i / group_size;
+      if (!ok && atomicCAS(status, 0, kErrGIdx) == 0) {
+        status[1] = expert;
+        __threadfence();
+      }
+    }
+  }
+}
+
 // ---- host side ----------------------------------------------------------------------------------
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -2416,10 +2467,28 @@ extern "C" int infiniops_b200_moe_wna16_marlin_gemm_ex(
   auto s = static_cast<cudaStream_t>(stream);
   auto* base = static_cast<unsigned char*>(scratch);
   const bool a_sorted = options != nullptr && options->a_sorted != 0;
-  const void* gathered = a_sorted ? a : base + plan.gathered_off;
+  const int32_t* perm = options != nullptr ? options->perm : nullptr;
+  const int32_t* g_idx = options != nullptr ? options->g_idx : nullptr;
+  IOB_REQUIRE((perm == nullptr) == (g_idx == nullptr), "%s: requires `g_idx` and `perm` together", op);
+  IOB_REQUIRE(perm == nullptr || num_groups > 1, "%s: activation order needs grouped scales", op);
+  const void* gathered = a_sorted && perm == nullptr ? a : base + plan.gathered_off;
   const int out_rows = static_cast<int>(size_m * top_k);
   const int gather_grid = static_cast<int>(std::min<int64_t>(sorted_cap, 4 * NumSms()));
-  if (a_sorted) {
+  if (perm != nullptr) {
+    auto launch = [&](auto* typed) {
+      using T = std::remove_pointer_t<decltype(typed)>;
+      GatherPermutedRowsKernel<T><<<gather_grid, 256, 0, s>>>(
+          static_cast<const T*>(a), reinterpret_cast<T*>(base + plan.gathered_off), sorted_token_ids, expert_ids,
+          num_tokens_past_padded, perm, g_idx, static_cast<int>(size_k), static_cast<int>(top_k), out_rows,
+          static_cast<int>(moe_block_size), static_cast<int>(size_k / num_groups), a_sorted ? 1 : 0,
+          reinterpret_cast<int*>(base));
+    };
+    if (a_dtype == IOB_BF16) {
+      launch(static_cast<__nv_bfloat16*>(nullptr));
+    } else {
+      launch(static_cast<__half*>(nullptr));
+    }
+  } else if (a_sorted) {
     // `a` already holds one row per sorted position: nothing to gather
   } else if (a_dtype == IOB_BF16) {
     GatherRowsKernel<__nv_bfloat16><<<gather_grid, 256, 0, s>>>(
@@ -2435,7 +2504,8 @@ extern "C" int infiniops_b200_moe_wna16_marlin_gemm_ex(
   const bool pair = tok == 256 && size_n % (2 * kTileN) == 0 && NumSms() >= 2;
   CUtensorMap map;
   // (rows past the end of a caller's sorted buffer read as zeros; the scratch copy has a spare box of rows)
-  if (const int rc = ActivationMap(gathered, a_sorted ? sorted_cap : sorted_cap + tok, size_k, pair ? tok / 2 : tok, a_dtype, &map)) {
+  if (const int rc = ActivationMap(gathered, a_sorted && perm == nullptr ? sorted_cap : sorted_cap + tok, size_k,
+                                   pair ? tok / 2 : tok, a_dtype, &map)) {
     return rc;
   }
   CUtensorMap w_map;
