@@ -37,11 +37,12 @@ class MarlinGemm : public Operator<MarlinGemm> {
     INFINI_OPS_CHECK(size_m_ > 0 && size_n_ > 0 && size_k_ > 0 && size_k_ % 16 == 0 && size_n_ % 64 == 0,
                      "`MarlinGemm` received unsupported dimensions");
     const bool has_zp = b_zeros.has_value();
-    INFINI_OPS_CHECK((b_type_id_ == qtype::kUint4B8 || b_type_id_ == qtype::kUint4) &&
+    INFINI_OPS_CHECK((b_type_id_ == qtype::kUint4B8 || b_type_id_ == qtype::kUint4 || b_type_id_ == qtype::kUint8B128) &&
                          has_zp == (b_type_id_ == qtype::kUint4) && !is_zp_float_,
                      "`MarlinGemm` received an unsupported quantization configuration");
+    const int64_t pack = b_type_id_ == qtype::kUint8B128 ? 4 : 8;  // weights per 32-bit word
     INFINI_OPS_CHECK(b_q_weight.ndim() == 2 && static_cast<int64_t>(b_q_weight.size(0)) == size_k_ / 16 &&
-                         static_cast<int64_t>(b_q_weight.size(1)) == size_n_ * 2 &&
+                         static_cast<int64_t>(b_q_weight.size(1)) == size_n_ * 16 / pack &&
                          b_q_weight.dtype() == DataType::kInt32 && b_q_weight.IsContiguous(),
                      "`MarlinGemm` received invalid packed weights");
     INFINI_OPS_CHECK(b_scales.ndim() == 2 && b_scales.size(0) > 0 && static_cast<int64_t>(b_scales.size(1)) == size_n_ &&

@@ -44,6 +44,7 @@ typedef enum {
  * src/base/moe_wna16_marlin_gemm.h:172-184). */
 #define IOB_QTYPE_UINT4B8 1125899907892224LL /* GPTQ symmetric: w = (q - 8) * s      */
 #define IOB_QTYPE_UINT4 1125899906843648LL   /* AWQ: w = (q - z) * s, z in `b_zeros` */
+#define IOB_QTYPE_UINT8B128 1125899923621888LL /* 8-bit symmetric: w = (q - 128) * s; b_q_weight [.., K/16, 4N] */
 
 /* Text of the last non-OK status returned on the calling thread. */
 const char* infiniops_b200_last_error(void);
@@ -226,6 +227,16 @@ int infiniops_b200_moe_sum(const void* input, int dtype, int64_t num_tokens, int
                            int64_t ids_stride_t, int64_t ids_stride_s, const int32_t* expert_map,
                            int64_t expert_map_size, int64_t expert_map_stride, void* out,
                            void* stream);
+
+/* moe_sum over rows kept in sorted (expert) order: out[t] = sum over s < topk of
+ * input[position[t * topk + s]] (rows of [rows, hidden]; a negative position contributes nothing),
+ * accumulated in fp32 in slot order and rounded once -- the arithmetic of infiniops_b200_moe_sum on
+ * the [num_tokens, topk, hidden] tensor those rows would form.  `position` as written by
+ * iob_routed_options::route_position.  No counterpart in the reference (its layer scatters the
+ * rows first and then calls moe_sum, src/base/moe_sum.h:14-208). */
+int infiniops_b200_moe_gather_sum(const void* input, int dtype, const int32_t* position,
+                                  int64_t num_tokens, int64_t topk, int64_t hidden, void* out,
+                                  void* stream);
 
 /* ---- W4A16 GEMM ------------------------------------------------------------------------------ */
 
@@ -452,12 +463,20 @@ int infiniops_b200_moe_wna16_gemm(const void* input, int dtype, const uint8_t* b
  * activation column perm[e][k] against weight row k.  `g_idx[e][k]` must be the group of row k in
  * that order, i.e. k / group_size (what a provider passes with `is_k_full`); any other table is
  * reported as code 9 in the scratch status word (expert in word 1), not misread.
+ * `out_sorted` together with `mul_topk_weights` (128- or 256-row routing blocks): the rows are
+ * multiplied by their routing weight and still stored as tiles in sorted order; a padding row stores
+ * zeros.  `route_position` (or NULL; int32 [size_m * top_k], a call that gathers, i.e. not `a_sorted`):
+ * receives, for every route that occurs in `sorted_token_ids`, its position there, and -1 for
+ * the others (the call clears the array first, on the stream).  w13 (`out_sorted`, `route_position`) -> silu_and_mul ->
+ * w2 (`a_sorted`, `out_sorted`, weights) -> infiniops_b200_moe_gather_sum is the layer with every
+ * GEMM store a tile store and the scatter folded into the final sum.
  * Zero-initialise the struct.  No counterpart in the reference beyond `g_idx` / `perm`. */
 typedef struct {
   int scale_layout;
   int a_sorted, out_sorted, fuse_silu;
   const int32_t* g_idx;
   const int32_t* perm;
+  int32_t* route_position;
   const int32_t* row_dest;
   void* dest_base[IOB_MAX_PEERS + 1];
   int n_dest;

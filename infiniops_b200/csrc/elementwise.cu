@@ -188,6 +188,49 @@ int LaunchSum(const void* input, void* out, int64_t tokens, const SumArgs& a, cu
   return CheckLaunch("moe_sum launch");
 }
 
+// moe_sum over rows that sit in sorted (expert) order: slot s of token t is row position[t * topk + s]
+// of `in` [rows, hidden]; a negative position contributes nothing.  Same accumulation (fp32, slots in
+// ascending order, one rounding) as moe_sum on the [T, topk, hidden] tensor those rows would form.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+MoeGatherSumKernel(const T* __restrict__ in, const int32_t* __restrict__ position, T* __restrict__ out, int topk,
+                   int64_t hidden, int blocks_per_row) {
+  constexpr int kVec = 16 / sizeof(T);
+  const int64_t token = blockIdx.x / blocks_per_row;
+  const int64_t col = (static_cast<int64_t>(blockIdx.x % blocks_per_row) * kThreads + threadIdx.x) * kVec;
+  if (col >= hidden) return;
+  using P = Pack<T, kVec>;
+  float acc[kVec];
+#pragma unroll
+  for (int i = 0; i < kVec; ++i) acc[i] = 0.0f;
+  for (int slot = 0; slot < topk; ++slot) {
+    const int row = position[token * topk + slot];
+    if (row < 0) continue;
+    const P v = *reinterpret_cast<const P*>(in + static_cast<int64_t>(row) * hidden + col);
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) acc[i] += ToFloat<T>(v.v[i]);
+  }
+  P result;
+#pragma unroll
+  for (int i = 0; i < kVec; ++i) result.v[i] = FromFloat<T>(acc[i]);
+  *reinterpret_cast<P*>(out + token * hidden + col) = result;
+}
+
+template <typename T>
+int LaunchGatherSum(const void* input, const int32_t* position, void* out, int64_t tokens, int64_t topk, int64_t hidden,
+                    cudaStream_t stream) {
+  constexpr int kVec = 16 / sizeof(T);
+  IOB_REQUIRE(hidden % kVec == 0 && reinterpret_cast<uintptr_t>(input) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0,
+              "moe_gather_sum: rows must be 16-byte aligned and `hidden` a multiple of %d", kVec);
+  const int64_t per_block = static_cast<int64_t>(kThreads) * kVec;
+  const int64_t blocks_per_row = (hidden + per_block - 1) / per_block;
+  IOB_REQUIRE(tokens * blocks_per_row <= INT32_MAX, "moe_gather_sum: tensor too large for one launch");
+  MoeGatherSumKernel<T><<<static_cast<unsigned>(tokens * blocks_per_row), kThreads, 0, stream>>>(
+      static_cast<const T*>(input), position, static_cast<T*>(out), static_cast<int>(topk), hidden,
+      static_cast<int>(blocks_per_row));
+  return CheckLaunch("moe_gather_sum launch");
+}
+
 }  // namespace
 }  // namespace iob
 
@@ -231,5 +274,20 @@ extern "C" int infiniops_b200_moe_sum(const void* input, int dtype, int64_t num_
     case IOB_F16: return LaunchSum<__half>(input, out, num_tokens, a, s);
     case IOB_BF16: return LaunchSum<__nv_bfloat16>(input, out, num_tokens, a, s);
     default: return Fail(IOB_INVALID_ARGUMENT, "moe_sum: supports float32, float16 and bfloat16");
+  }
+}
+
+extern "C" int infiniops_b200_moe_gather_sum(const void* input, int dtype, const int32_t* position, int64_t num_tokens,
+                                             int64_t topk, int64_t hidden, void* out, void* stream) {
+  using namespace iob;
+  IOB_REQUIRE(num_tokens >= 0 && topk > 0 && topk <= INT32_MAX && hidden > 0, "moe_gather_sum: invalid extents");
+  if (num_tokens == 0) return IOB_OK;
+  IOB_REQUIRE(input && position && out, "moe_gather_sum: null tensor pointer");
+  auto s = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case IOB_F32: return LaunchGatherSum<float>(input, position, out, num_tokens, topk, hidden, s);
+    case IOB_F16: return LaunchGatherSum<__half>(input, position, out, num_tokens, topk, hidden, s);
+    case IOB_BF16: return LaunchGatherSum<__nv_bfloat16>(input, position, out, num_tokens, topk, hidden, s);
+    default: return Fail(IOB_INVALID_ARGUMENT, "moe_gather_sum: supports float32, float16 and bfloat16");
   }
 }

@@ -56,6 +56,9 @@ constexpr int kMaxBatch = 16;            // problems one batched launch can hold
 
 constexpr int kErrFull = 1, kErrEmpty = 2, kErrAFull = 3, kErrAEmpty = 4, kErrDFull = 5, kErrDEmpty = 6;
 
+// 8-bit weights: a stage of packed weights is 16 KB instead of 8 KB, so the rings are shorter (still
+// multiples of the set and issuer counts of the tile class).
+__host__ __device__ constexpr int StagesFor8(int tok) { return tok <= 32 ? 9 : tok <= 64 ? 6 : 4; }
 __host__ __device__ constexpr int StagesFor(int tok) {
   // As many as fit in 227 KB (decode needs ~90 KB of weights in flight per SM to cover HBM
   // latency at full rate) -- and a multiple of SetsFor(tok), see there.
@@ -75,7 +78,7 @@ __host__ __device__ constexpr int AStagesFor(int tok) { return tok <= 32 ? 6 : t
 // accumulator stages (so the epilogue of one segment overlaps the next); limited by the 512 columns
 __host__ __device__ constexpr int AccStagesFor(int tok) { return tok == 32 || tok > 128 ? 1 : 2; }
 // activations (two swizzle atoms of tok x 128 B) | packed weights 8 KB | 2 scale rows | 2 zero rows
-__host__ __device__ constexpr int StageBytes(int tok) { return tok * 256 + 8192; }
+__host__ __device__ constexpr int StageBytes(int tok, int bits = 4) { return tok * 256 + (bits == 8 ? 16384 : 8192); }
 // MMA-issuing threads.  One thread cannot keep the tensor pipe busy when a stage is only a few
 // hundred cycles of MMA work (its barrier wait and commits are not overlapped), so small token
 // tiles use two or three issuers on alternating stages, each with its own accumulator; the epilogue
@@ -136,6 +139,7 @@ struct GemmParams {
   // in runs of 16 (columns 32b..32b+15 = gate features 16b.., columns 32b+16..32b+31 = the matching up
   // features) and the epilogue stores silu(gate) * up, [rows][N/2], instead of the [rows][N] product.
   int fuse_silu;
+  int bits;                         // 4 or 8: width of a packed weight
   const int2* row_dest;             // null, or per output row: (GPU, row there) the result row is stored to
   void* dest_base[kMaxPeers + 1];   // with `row_dest`: the destination matrix of every GPU (own included)
   const int32_t* sorted_ids;
@@ -473,6 +477,9 @@ __device__ __forceinline__ void TmemWaitSt() { asm volatile("tcgen05.wait::st.sy
 __device__ __forceinline__ void NamedBarrierUnused(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
+__device__ __forceinline__ void LdShared128(uint32_t addr, uint32_t& a, uint32_t& b, uint32_t& c, uint32_t& d) {
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(a), "=r"(b), "=r"(c), "=r"(d) : "r"(addr));
+}
 __device__ __forceinline__ void LdShared64(uint32_t addr, uint32_t& a, uint32_t& b) {
   asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];" : "=r"(a), "=r"(b) : "r"(addr));
 }
@@ -551,6 +558,31 @@ __device__ __forceinline__ uint32_t CentreHigh2(uint32_t word, uint32_t minus_64
   const uint32_t sixteenth = 0x2C002C00u;
   const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&biased), *reinterpret_cast<const __half2*>(&sixteenth),
                             *reinterpret_cast<const __half2*>(&minus_64_zero));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+
+// 8-bit weights: bytes (2 odd, 2 odd + ...) of `word` -- `odd` = 0: bytes 0 and 2 (k = 2t, 2t + 1), `odd` = 1:
+// bytes 1 and 3 (k = 2t + 8, 2t + 9) -- as (q - 128) * scale, both halves in T.  `scale16` is the raw
+// 16-bit scale.
+template <typename T>
+__device__ __forceinline__ uint32_t Dequant8(uint32_t word, int odd, uint32_t scale16);
+template <>
+__device__ __forceinline__ uint32_t Dequant8<__half>(uint32_t word, int odd, uint32_t scale16) {
+  // 0x6400 | q is the float16 1024 + q; minus 1152 = q - 128, exact
+  const uint32_t biased = __byte_perm(word, 0x64646464u, odd ? 0x4341u : 0x4240u);
+  const uint32_t centre = 0x64806480u, scale2 = scale16 * 0x10001u;
+  const __half2 c = __hsub2(*reinterpret_cast<const __half2*>(&biased), *reinterpret_cast<const __half2*>(&centre));
+  const __half2 r = __hmul2(c, *reinterpret_cast<const __half2*>(&scale2));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+template <>
+__device__ __forceinline__ uint32_t Dequant8<__nv_bfloat16>(uint32_t word, int odd, uint32_t scale16) {
+  // eight significant bits do not fit the bfloat16 mantissa trick: go through float32
+  // (0x4B000000 | q = 8388608 + q), centre and scale there, round once to bfloat16
+  const float lo = __uint_as_float(__byte_perm(word, 0x4B000000u, odd ? 0x7541u : 0x7540u)) - 8388736.0f;
+  const float hi = __uint_as_float(__byte_perm(word, 0x4B000000u, odd ? 0x7543u : 0x7542u)) - 8388736.0f;
+  const float s = __uint_as_float(scale16 << 16);
+  const __nv_bfloat162 r = __floats2bfloat162_rn(lo * s, hi * s);
   return *reinterpret_cast<const uint32_t*>(&r);
 }
 
@@ -637,9 +669,9 @@ __device__ __forceinline__ int OwnerOf(long long u, long long total, long long g
 // slot is not held while its weights are being converted; the 8 KB weight stages are freed by
 // the dequantisers.
 constexpr int kPairStages = 6, kPairAStages = 4, kPairSets = 2, kPairActStages = 5;
-template <int kTok, int kSets, bool kPair = false>
+template <int kTok, int kSets, bool kPair = false, int kBits = 4>
 struct Shared {
-  static constexpr int kStages = kPair ? kPairStages : StagesFor(kTok);
+  static constexpr int kStages = kPair ? kPairStages : kBits == 8 ? StagesFor8(kTok) : StagesFor(kTok);
   static constexpr int kAcc = AccStagesFor(kTok);
   uint64_t full[kStages], empty[kStages];
   static constexpr int kAStages = kPair ? kPairAStages : AStagesFor(kTok);
@@ -668,13 +700,20 @@ struct Shared {
 // kBatch: `probs` is a table of `count` dense problems that are worked through as one sequence of
 // units (see BatchTable); otherwise it points to the launch's single problem.  `cur` is the problem
 // the executing thread is currently working on -- every role moves it forward with its own walker.
-template <typename T, int kTok, bool kZeros, bool kMoe, int kSets, bool kLate, bool kPair, bool kBatch, bool kSilu = false>
+template <typename T, int kTok, bool kZeros, bool kMoe, int kSets, bool kLate, bool kPair, bool kBatch, int kEpi = 0, int kBits = 4>
 __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
   static_assert(!kBatch || (!kMoe && !kPair && kLate), "batched launches: dense late-scale tiles only");
-  static_assert(!kSilu || kMoe, "silu_and_mul in the epilogue: routed form only (sorted output)");
+  // kEpi, routed form with sorted output: 1 = silu_and_mul applied by the epilogue, 2 = rows multiplied
+  // by their routing weight.  Variants of their own, so that the other kernels carry none of the code.
+  static_assert(kEpi == 0 || kMoe, "epilogue variants: routed form only (sorted output)");
+  constexpr bool kSilu = kEpi == 1;
+  constexpr bool kWeighted = kEpi == 2;
   const Problem* cur = probs;
   int* const status_word = probs->p.status;  // one status header per launch
-  using Sh = Shared<kTok, kSets, kPair>;
+  using Sh = Shared<kTok, kSets, kPair, kBits>;
+  static_assert(kBits == 4 || (kBits == 8 && !kPair && !kBatch && !kLate && !kZeros && kTok <= 128),
+                "8-bit weights: unpaired tiles with scaled weights, no zero points");
+  constexpr int kWeightBytes = kBits == 8 ? 16384 : 8192;  // packed weights of a stage (128 columns x 128 k)
   constexpr int kStages = Sh::kStages;
   constexpr int kAcc = Sh::kAcc;
   constexpr int kAStages = Sh::kAStages;
@@ -685,10 +724,10 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
   constexpr int kActRows = kPair ? kTok / 2 : kTok;  // activation rows this block loads per stage
   constexpr int kAtomBytes = kActRows * 128;          // one 64-k activation atom
   constexpr int kActBytes = 2 * kAtomBytes;
-  constexpr int kStage = kPair ? 8192 : kActBytes + 8192;  // bytes of a ring slot (kPair: weights only)
+  constexpr int kStage = kPair ? 8192 : kActBytes + kWeightBytes;  // bytes of a ring slot (kPair: weights only)
   constexpr int kWeightsAt = kPair ? 0 : kActBytes;         // where the packed weights sit in a slot
   constexpr int kActStages = Sh::kActStages;
-  static_assert(kStage <= StageBytes(kTok), "stage layout");
+  static_assert(kStage <= StageBytes(kTok, kBits), "stage layout");
   // The lanes of a pass wait for each other, so a pass must stay well below the ring size or the
   // ring would drain between passes.
   constexpr int kProdLanes = kStages >= 8 ? 4 : kStages >= 4 ? 2 : 1;
@@ -716,7 +755,7 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
   [[maybe_unused]] const uint32_t acts_addr = stages_addr + Sh::kStages * 8192;  // kPair: activation ring behind the weight ring
   // behind the rings: two 16-row x 32-column output staging tiles per epilogue warp (8 KB in all)
   [[maybe_unused]] const uint32_t out_stage_addr =
-      stages_addr + (kPair ? Sh::kStages * 8192 + Sh::kActStages * (kTok * 128) : Sh::kStages * StageBytes(kTok));
+      stages_addr + (kPair ? Sh::kStages * 8192 + Sh::kActStages * (kTok * 128) : Sh::kStages * StageBytes(kTok, kBits));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort_flag = &sh.abort_flag;
@@ -854,9 +893,16 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
         const int ks = at.Ks();
         const uint32_t full = SmemAddr(&sh.full[s]);
         // both boxes are always counted in full (rows past M and columns past N arrive as zeros)
-        MbarExpectTx(full, (kPair ? 0 : kActBytes) + 8192);
-        TmaLoad2D(stages_addr + s * kStage + kWeightsAt, &cur->w_map, 2 * tile_of(at.seg.n_tile) * kTileN,
-                  at.expert * (cur->p.k / 16) + ks * 8, full);
+        MbarExpectTx(full, (kPair ? 0 : kActBytes) + kWeightBytes);
+        if constexpr (kBits == 8) {
+          // [K/16, 4N] words: the tile's 512 words per row as two boxes of 256 (one per 64 columns)
+          const int x0 = 4 * tile_of(at.seg.n_tile) * kTileN, y0 = at.expert * (cur->p.k / 16) + ks * 8;
+          TmaLoad2D(stages_addr + s * kStage + kWeightsAt, &cur->w_map, x0, y0, full);
+          TmaLoad2D(stages_addr + s * kStage + kWeightsAt + 8192, &cur->w_map, x0 + 256, y0, full);
+        } else {
+          TmaLoad2D(stages_addr + s * kStage + kWeightsAt, &cur->w_map, 2 * tile_of(at.seg.n_tile) * kTileN,
+                    at.expert * (cur->p.k / 16) + ks * 8, full);
+        }
         // The dequantisers read this stage's scales and zero points with plain loads one stage
         // ahead; pull the lines into L2 now, a whole ring ahead.
         const int n0 = tile_of(at.seg.n_tile) * kTileN;
@@ -1258,7 +1304,39 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
         }
         TcFenceAfter();
       };
-      if constexpr (kLate) {
+      if constexpr (kBits == 8) {
+        // 8-bit weights (uint8b128: w = (q - 128) * s).  Per 16-k slab and 64 columns the thread owns
+        // four adjacent words: [columns c0 | c0 + 8] of its first 16-column block, then of its second;
+        // a word's bytes are k = 2t, 2t + 8, 2t + 1, 2t + 9 (t = lane % 4).  The two 64-column halves
+        // of the tile lie 8 KB apart (one copy each).
+        const uint32_t waddr8 = wbase + (q >> 1) * 8192 + (lane * 8 + 4 * (q & 1)) * 4;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t w8[4][4];
+#pragma unroll
+          for (int kt = 0; kt < 4; ++kt) {
+            LdShared128(waddr8 + (half * 4 + kt) * 1024, w8[kt][0], w8[kt][1], w8[kt][2], w8[kt][3]);
+          }
+          const int row = half * row_step;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint32_t pair = row ? gr.sc[1][h] : gr.sc[0][h];
+            uint32_t regs[16];
+#pragma unroll
+            for (int kt = 0; kt < 4; ++kt) {
+              const uint32_t w0 = w8[kt][2 * h], w1 = w8[kt][2 * h + 1];    // columns c0 and c0 + 8
+              regs[4 * kt + 0] = Dequant8<T>(w0, 0, pair & 0xFFFFu);        // k pair t
+              regs[4 * kt + 1] = Dequant8<T>(w1, 0, pair >> 16);
+              regs[4 * kt + 2] = Dequant8<T>(w0, 1, pair & 0xFFFFu);        // k pair t + 4
+              regs[4 * kt + 3] = Dequant8<T>(w1, 1, pair >> 16);
+            }
+            if (half == 0 && h == 0) before_first_store();
+            if (alive) {
+              TmemStore16(tmem_a + (static_cast<uint32_t>(32 * q + 16 * h) << 16) + a * kAStageCols + half * 32, regs);
+            }
+          }
+        }
+      } else if constexpr (kLate) {
         // Integers only: (q - zero) for the thread's four columns; the scale is applied to the
         // stage's accumulator by the epilogue warps.
         constexpr bool kHalf = Half2Of<T>::kFormat == 0;
@@ -1409,6 +1487,12 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
             }
             return;
           }
+          if constexpr (kWeighted) {
+            const int id = cur->p.sorted_ids[row0 + j];
+            const float w = id < cur->p.out_rows ? cur->p.topk_weights[id] : 0.0f;
+            out[static_cast<size_t>(row0 + j) * cur->p.n + n] = FromFloat<T>(v * w);
+            return;
+          }
           if (cur->p.out_sorted) {
             out[static_cast<size_t>(row0 + j) * cur->p.n + n] = FromFloat<T>(v);
             return;
@@ -1459,6 +1543,19 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
                   const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
                   const T v = SiluMulRounded<T>(mine, other);
                   if (lane < 16) StShared16(buf + j * 32 + lane * 2, *reinterpret_cast<const unsigned short*>(&v));
+                }
+              } else if constexpr (kWeighted) {
+                // lane j fetches the routing weight of row j of the chunk (0 for a padding row)
+                float w_lane = 0.0f;
+                if (lane < 16) {
+                  const int id = cur->p.sorted_ids[row0 + c + lane];
+                  if (id < cur->p.out_rows) w_lane = cur->p.topk_weights[id];
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  const float wj = __shfl_sync(0xffffffffu, w_lane, j);
+                  const T v = FromFloat<T>((__uint_as_float(r[j]) + bias_v) * wj);
+                  StShared16(buf + j * 64 + lane * 2, *reinterpret_cast<const unsigned short*>(&v));
                 }
               } else {
 #pragma unroll
@@ -1743,10 +1840,10 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
 }
 
 // One problem per launch.
-template <typename T, int kTok, bool kZeros, bool kMoe, int kSets, bool kLate, bool kPair = false, bool kSilu = false>
+template <typename T, int kTok, bool kZeros, bool kMoe, int kSets, bool kLate, bool kPair = false, int kEpi = 0, int kBits = 4>
 __global__ void __launch_bounds__((5 + IssuersFor(kTok) + 4 * kSets) * 32, 1)
 W4A16GemmKernel(const __grid_constant__ Problem problem) {
-  GemmBody<T, kTok, kZeros, kMoe, kSets, kLate, kPair, false, kSilu>(&problem, 1);
+  GemmBody<T, kTok, kZeros, kMoe, kSets, kLate, kPair, false, kEpi, kBits>(&problem, 1);
 }
 // A table of dense problems per launch.
 template <typename T, int kTok, bool kZeros, int kSets>
@@ -1784,12 +1881,14 @@ __global__ void BoundedWaitSelfTestKernel(int* status, int* result) {
 template <typename T>
 __global__ void GatherRowsKernel(const T* __restrict__ a, T* __restrict__ gathered,
                                  const int32_t* __restrict__ sorted_ids, const int32_t* __restrict__ num_post_pad,
-                                 int k, int top_k, int out_rows) {
+                                 int k, int top_k, int out_rows, int32_t* __restrict__ position) {
   const int rows = *num_post_pad;
   const int vec_per_row = k / 8;
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const int id = sorted_ids[row];
     uint4* dst = reinterpret_cast<uint4*>(gathered + static_cast<size_t>(row) * k);
+    // by-product for the caller's combine step: where each route sits in sorted order
+    if (position != nullptr && threadIdx.x == 0 && id < out_rows) position[id] = row;
     if (id < out_rows) {
       const uint4* src = reinterpret_cast<const uint4*>(a + static_cast<size_t>(id / top_k) * k);
       for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x) dst[i] = src[i];
@@ -1965,8 +2064,9 @@ int OutputMap(const void* ptr, int64_t rows, int64_t cols, int dtype, CUtensorMa
 }
 
 // Packed weights [E * K/16, 2N] words, box = 8 rows (128 k) x 256 words (128 columns).
-int WeightMap(const void* ptr, int64_t experts, int64_t k, int64_t n, CUtensorMap* out) {
-  return TensorMap2D(ptr, experts * (k / 16), 2 * n, 8, 256, kMapWords, out);
+int WeightMap(const void* ptr, int64_t experts, int64_t k, int64_t n, CUtensorMap* out, int bits = 4) {
+  // (8-bit: [E * K/16, 4N] words; the same 8 x 256 box holds 64 columns, a tile takes two)
+  return TensorMap2D(ptr, experts * (k / 16), (bits == 8 ? 4 : 2) * n, 8, 256, kMapWords, out);
 }
 
 // Shift/multiply form of `ks * 128 / group_size` for the usual group sizes.
@@ -2017,14 +2117,15 @@ ScratchPlan PlanScratch(int64_t tiles, int tok, int64_t gathered_bytes) {
   return plan;
 }
 
-template <typename T, int kTok, bool kZeros, bool kMoe, bool kLate, bool kPair = false, bool kSilu = false>
+template <typename T, int kTok, bool kZeros, bool kMoe, bool kLate, bool kPair = false, int kEpi = 0, int kBits = 4>
 int LaunchVariant(const CUtensorMap& map, const CUtensorMap& w_map, const CUtensorMap& c_map, const GemmParams& p,
                   int grid, cudaStream_t stream) {
   constexpr int kSets = kPair ? kPairSets : SetsFor(kTok);
-  auto kernel = W4A16GemmKernel<T, kTok, kZeros, kMoe, kSets, kLate, kPair, kSilu>;
+  auto kernel = W4A16GemmKernel<T, kTok, kZeros, kMoe, kSets, kLate, kPair, kEpi, kBits>;
   // rings + 8 KB of output staging + slack for the 1024-byte alignment
   constexpr int smem =
-      (kPair ? kPairStages * 8192 + kPairActStages * kTok * 128 : StagesFor(kTok) * StageBytes(kTok)) + 8192 + 1024;
+      (kPair ? kPairStages * 8192 + kPairActStages * kTok * 128
+             : kBits == 8 ? StagesFor8(kTok) * StageBytes(kTok, 8) : StagesFor(kTok) * StageBytes(kTok)) + 8192 + 1024;
   static_assert(smem <= 232448, "shared memory budget");
   static thread_local bool configured[64] = {};
   int device = 0;
@@ -2112,25 +2213,31 @@ int LaunchBatch(int a_dtype, bool zeros, int tok, const BatchTable& table, int g
 
 // Token tiles up to 32 with groups of at least one k-stage take the variant that scales the
 // accumulators instead of the weights.
-template <typename T, int kTok, bool kZeros, bool kMoe, bool kSilu = false>
+template <typename T, int kTok, bool kZeros, bool kMoe, int kEpi = 0>
 int LaunchKernel(const CUtensorMap& map, const CUtensorMap& w_map, const CUtensorMap& c_map, const GemmParams& p, int grid,
                  cudaStream_t stream) {
   // silu_and_mul in the epilogue is a kernel variant of its own (routed form only), so that the
   // kernels without it carry none of its code
-  if constexpr (kMoe && !kSilu) {
-    if (p.fuse_silu) return LaunchKernel<T, kTok, kZeros, kMoe, true>(map, w_map, c_map, p, grid, stream);
+  if constexpr (kEpi == 0 && !kZeros && kTok <= 128) {
+    if (p.bits == 8) return LaunchVariant<T, kTok, kZeros, kMoe, false, false, 0, 8>(map, w_map, c_map, p, grid, stream);
+  }
+  if constexpr (kMoe && kEpi == 0) {
+    if (p.fuse_silu) return LaunchKernel<T, kTok, kZeros, kMoe, 1>(map, w_map, c_map, p, grid, stream);
+    if constexpr (kTok >= 128) {
+      if (p.out_sorted && p.mul_weights) return LaunchKernel<T, kTok, kZeros, kMoe, 2>(map, w_map, c_map, p, grid, stream);
+    }
   }
   // (64-row tiles: dense only -- the routed form, with its many whole tiles per block and its
   // scattered tile-end stores, measured 40 % slower that way than with scaled weights)
   if constexpr (kTok <= 32 || (kTok == 64 && !kMoe)) {
     if (p.group_size >= kBlockK) {
-      return LaunchVariant<T, kTok, kZeros, kMoe, true, false, kSilu>(map, w_map, c_map, p, grid, stream);
+      return LaunchVariant<T, kTok, kZeros, kMoe, true, false, kEpi>(map, w_map, c_map, p, grid, stream);
     }
   }
   if constexpr (kTok == 256) {
-    if (p.pair) return LaunchVariant<T, kTok, kZeros, kMoe, false, true, kSilu>(map, w_map, c_map, p, grid, stream);
+    if (p.pair) return LaunchVariant<T, kTok, kZeros, kMoe, false, true, kEpi>(map, w_map, c_map, p, grid, stream);
   }
-  return LaunchVariant<T, kTok, kZeros, kMoe, false, false, kSilu>(map, w_map, c_map, p, grid, stream);
+  return LaunchVariant<T, kTok, kZeros, kMoe, false, false, kEpi>(map, w_map, c_map, p, grid, stream);
 }
 
 template <typename T, bool kZeros, bool kMoe>
@@ -2158,17 +2265,19 @@ int Dispatch(int a_dtype, bool zeros, int tok, const CUtensorMap& map, const CUt
                : DispatchTok<__half, false, kMoe>(tok, map, w_map, c_map, p, grid, stream);
 }
 
+int BitsOf(int64_t b_type_id) { return b_type_id == IOB_QTYPE_UINT8B128 ? 8 : 4; }
+
 int CheckProblem(const char* op, const void* a, int a_dtype, const void* wq, const void* scales, const void* zeros,
                  int64_t b_type_id, int64_t m, int64_t n, int64_t k, int64_t groups, const void* out) {
   IOB_REQUIRE(a && wq && scales && out, "%s: null tensor pointer", op);
   IOB_REQUIRE(a_dtype == IOB_F16 || a_dtype == IOB_BF16, "%s: requires float16 or bfloat16 `a`", op);
   IOB_REQUIRE(m > 0 && n > 0 && k > 0 && k % 16 == 0 && n % 64 == 0, "%s: received unsupported dimensions", op);
   IOB_REQUIRE(m <= INT32_MAX && n <= INT32_MAX && k <= INT32_MAX, "%s: dimensions exceed int32", op);
-  if (b_type_id != IOB_QTYPE_UINT4B8 && b_type_id != IOB_QTYPE_UINT4) {
-    return Fail(IOB_UNSUPPORTED, "%s: only the 4-bit weight types uint4b8 and uint4 are implemented", op);
+  if (b_type_id != IOB_QTYPE_UINT4B8 && b_type_id != IOB_QTYPE_UINT4 && b_type_id != IOB_QTYPE_UINT8B128) {
+    return Fail(IOB_UNSUPPORTED, "%s: only the weight types uint4b8, uint4 and uint8b128 are implemented", op);
   }
   IOB_REQUIRE((zeros != nullptr) == (b_type_id == IOB_QTYPE_UINT4),
-              "%s: zero points are required for uint4 and not accepted for uint4b8", op);
+              "%s: zero points are required for uint4 and not accepted for uint4b8 / uint8b128", op);
   IOB_REQUIRE(groups > 0 && k % groups == 0, "%s: `size_k` must be a multiple of the number of scale groups", op);
   if (k % kBlockK != 0 || ((k / groups) != 64 && (k / groups) % kBlockK != 0)) {
     return Fail(IOB_UNSUPPORTED, "%s: needs `size_k` to be a multiple of 128 and the group size 64 or a multiple of 128", op);
@@ -2288,7 +2397,9 @@ extern "C" int infiniops_b200_marlin_gemm_placed(const iob_gemm_problem* problem
                                   g.size_k, g.num_groups, g.out)) {
     return rc;
   }
-  const int tok = DenseTokenTile(g.size_m, g.size_n, g.size_k / (g.num_groups > 0 ? g.num_groups : 1));
+  const int bits = BitsOf(b_type_id);
+  int tok = DenseTokenTile(g.size_m, g.size_n, g.size_k / (g.num_groups > 0 ? g.num_groups : 1));
+  if (bits == 8 && tok > 128) tok = 128;  // 8-bit weights: no 256-row tiles (the stage ring would not fit)
   const int64_t n_tiles = (g.size_n + kTileN - 1) / kTileN, m_tiles = (g.size_m + tok - 1) / tok;
   // (the scratch query does not know the group size and answers for the larger plan)
   const ScratchPlan plan = PlanScratch(n_tiles * m_tiles, tok, 0);
@@ -2303,10 +2414,11 @@ extern "C" int infiniops_b200_marlin_gemm_placed(const iob_gemm_problem* problem
   CUtensorMap map;
   if (const int rc = ActivationMap(g.a, g.size_m, g.size_k, pair ? tok / 2 : tok, a_dtype, &map)) return rc;
   CUtensorMap w_map;
-  if (const int rc = WeightMap(g.b_q_weight, 1, g.size_k, g.size_n, &w_map)) return rc;
+  if (const int rc = WeightMap(g.b_q_weight, 1, g.size_k, g.size_n, &w_map, bits)) return rc;
   CUtensorMap c_map;
   if (const int rc = OutputMap(g.out, g.size_m, p.out_ld, a_dtype, &c_map)) return rc;
   p.pair = pair ? 1 : 0;
+  p.bits = bits;
   FillDense(g, static_cast<unsigned char*>(scratch), plan, p);
   const int64_t units = n_tiles * m_tiles * (g.size_k / kBlockK);
   const int grid = pair ? NumSms() : static_cast<int>(units < NumSms() ? units : NumSms());
@@ -2341,6 +2453,7 @@ extern "C" int infiniops_b200_marlin_gemm_batch(const iob_gemm_problem* problems
                                                 size_t scratch_bytes, void* stream) {
   using namespace iob;
   const char* op = "marlin_gemm_batch";
+  IOB_REQUIRE(BitsOf(b_type_id) == 4, "%s: 4-bit weights only; 8-bit problems go through marlin_gemm", op);
   IOB_REQUIRE(problems != nullptr && count > 0, "%s: no problems", op);
   const ScratchPlan plan = PlanScratch(0, 64, 0);
   if (scratch == nullptr || scratch_bytes < plan.total) {
@@ -2467,6 +2580,9 @@ extern "C" int infiniops_b200_moe_wna16_marlin_gemm_ex(
   auto s = static_cast<cudaStream_t>(stream);
   auto* base = static_cast<unsigned char*>(scratch);
   const bool a_sorted = options != nullptr && options->a_sorted != 0;
+  int32_t* position = options != nullptr ? options->route_position : nullptr;
+  IOB_REQUIRE(position == nullptr || (!a_sorted && (options->perm == nullptr)),
+              "%s: `route_position` is written by the plain row gather (not with `a_sorted` or `perm`)", op);
   const int32_t* perm = options != nullptr ? options->perm : nullptr;
   const int32_t* g_idx = options != nullptr ? options->g_idx : nullptr;
   IOB_REQUIRE((perm == nullptr) == (g_idx == nullptr), "%s: requires `g_idx` and `perm` together", op);
@@ -2474,6 +2590,10 @@ extern "C" int infiniops_b200_moe_wna16_marlin_gemm_ex(
   const void* gathered = a_sorted && perm == nullptr ? a : base + plan.gathered_off;
   const int out_rows = static_cast<int>(size_m * top_k);
   const int gather_grid = static_cast<int>(std::min<int64_t>(sorted_cap, 4 * NumSms()));
+  if (position != nullptr &&
+      cudaMemsetAsync(position, 0xFF, static_cast<size_t>(out_rows) * sizeof(int32_t), s) != cudaSuccess) {
+    return Fail(IOB_CUDA_ERROR, "%s: could not clear `route_position`", op);
+  }
   if (perm != nullptr) {
     auto launch = [&](auto* typed) {
       using T = std::remove_pointer_t<decltype(typed)>;
@@ -2493,11 +2613,11 @@ extern "C" int infiniops_b200_moe_wna16_marlin_gemm_ex(
   } else if (a_dtype == IOB_BF16) {
     GatherRowsKernel<__nv_bfloat16><<<gather_grid, 256, 0, s>>>(
         static_cast<const __nv_bfloat16*>(a), reinterpret_cast<__nv_bfloat16*>(base + plan.gathered_off), sorted_token_ids,
-        num_tokens_past_padded, static_cast<int>(size_k), static_cast<int>(top_k), out_rows);
+        num_tokens_past_padded, static_cast<int>(size_k), static_cast<int>(top_k), out_rows, position);
   } else {
     GatherRowsKernel<__half><<<gather_grid, 256, 0, s>>>(static_cast<const __half*>(a), reinterpret_cast<__half*>(base + plan.gathered_off),
                                                         sorted_token_ids, num_tokens_past_padded,
-                                                        static_cast<int>(size_k), static_cast<int>(top_k), out_rows);
+                                                        static_cast<int>(size_k), static_cast<int>(top_k), out_rows, position);
   }
   if (const int rc = CheckLaunch("moe_wna16_marlin_gemm gather launch")) return rc;
   // 256-row routing blocks whose columns pair up run two blocks of a cluster per 256 x 256 tile
@@ -2509,9 +2629,14 @@ extern "C" int infiniops_b200_moe_wna16_marlin_gemm_ex(
     return rc;
   }
   CUtensorMap w_map;
-  if (const int rc = WeightMap(b_q_weight, num_experts, size_k, size_n, &w_map)) return rc;
+  const int bits = BitsOf(b_type_id);
+  IOB_REQUIRE(bits == 4 || (moe_block_size <= 128 && (options == nullptr || !options->fuse_silu) &&
+                            !(options != nullptr && options->out_sorted && mul_topk_weights)),
+              "%s: 8-bit weights take routing blocks up to 128 rows and the plain epilogue", op);
+  if (const int rc = WeightMap(b_q_weight, num_experts, size_k, size_n, &w_map, bits)) return rc;
   GemmParams p{};
   p.pair = pair ? 1 : 0;
+  p.bits = bits;
   p.wq = reinterpret_cast<const uint32_t*>(b_q_weight);
   p.scales = b_scales;
   p.zeros = reinterpret_cast<const uint32_t*>(b_zeros);
@@ -2539,8 +2664,9 @@ extern "C" int infiniops_b200_moe_wna16_marlin_gemm_ex(
                 "%s: `scale_layout` must be 0 (plain) or 1 (provider)", op);
     p.layout = options->scale_layout;
     p.out_sorted = options->out_sorted ? 1 : 0;
-    IOB_REQUIRE(!p.out_sorted || (!mul_topk_weights && options->row_dest == nullptr),
-                "%s: sorted output takes neither routing weights nor a scatter", op);
+    IOB_REQUIRE(!p.out_sorted || options->row_dest == nullptr, "%s: sorted output takes no scatter", op);
+    IOB_REQUIRE(!p.out_sorted || !mul_topk_weights || moe_block_size >= 128,
+                "%s: sorted output with routing weights needs 128- or 256-row routing blocks", op);
     p.fuse_silu = options->fuse_silu ? 1 : 0;
     IOB_REQUIRE(!p.fuse_silu || (p.out_sorted && size_n % 128 == 0),
                 "%s: the fused silu needs sorted output and `size_n` a multiple of 128", op);

@@ -100,12 +100,17 @@ def routing_block(routes: int, num_experts: int) -> int:
     blocks do a quarter of the conversion work (and 256-row blocks run on paired thread blocks).
     The padding (at most block - 1 rows per expert) must stay small against the rows themselves."""
     per_expert = routes / max(1, num_experts)
-    # Measured on a B200 with Mixtral- and DeepSeek-shaped layers.  Many rows per expert: 128-row
-    # blocks beat 64-row ones by 12-37 % from about 256 rows per expert on (256-row blocks on paired
-    # thread blocks come out level with 128-row ones and pad more).  Few rows per expert: a block is
-    # mostly padding, and the GEMM's token tile follows the block, so 16-row blocks win below about 8
-    # rows per expert (by 25-50 %) and 32-row blocks up to about 32.
-    if per_expert >= 192:
+    # Measured on a B200 with Mixtral- and DeepSeek-shaped layers.  With 128- and 256-row blocks both
+    # GEMMs store tiles and each weight is converted once per block of rows: 128-row blocks beat
+    # 64-row ones from about 64 rows per expert on (DeepSeek shape +25 % at 64 rows per expert, +47 %
+    # at 128; Mixtral shape -2 % at 64, +12 % at 128, +30 % at 256), and 256-row blocks (paired
+    # thread blocks) beat 128-row ones from about 640 rows per expert on (+12 % at 768, +11 % at 1024;
+    # -3 % at 512, where they pad too much).  Few rows per expert: a block is mostly padding, and the
+    # GEMM's token tile follows the block, so 16-row blocks win below about 8 rows per expert (by
+    # 25-50 %) and 32-row blocks up to about 32.
+    if per_expert >= 640:
+        return 256
+    if per_expert >= 64:
         return 128
     if per_expert >= 32:
         return 64
@@ -166,22 +171,36 @@ def single_gpu_layer(x, topk_weights, topk_ids, experts: RoutedExperts, stream=N
         capi.moe_align_block_size(topk_ids, None, w.num_experts, block, sorted_ids, expert_ids, npost, stream=stream)
     flat_w = topk_weights.reshape(-1)
     # The intermediates stay in sorted (expert) order -- one row per entry of `sorted_ids` -- so the
-    # first GEMM stores dense tiles and the second reads them in place; only the last result is
-    # scattered to its route.
+    # first GEMM stores dense tiles and the second reads them in place.
+    tiles_only = block >= 128
+    position = None
+    if tiles_only:
+        # 128- / 256-row blocks: the second GEMM stores tiles in sorted order too (rows already
+        # multiplied by their routing weight) and the final sum picks each token's rows by position,
+        # so no GEMM epilogue scatters single rows.  The first GEMM's gather notes the positions.
+        position = experts._buf("L_pos", (t, k), torch.int32, dev)
     h = experts._buf("L_h", (size, w.inter), x.dtype, dev)
     if w.interleaved and (2 * w.inter) % 128 == 0:
         # gate and up meet in the epilogue: the [size, 2I] product is never stored
         capi.moe_wna16_marlin_gemm(x, w.w13, None, w.s13, w.z13, sorted_ids, expert_ids, npost, flat_w, block, k,
                                    False, w.qtype, t, 2 * w.inter, w.hidden, h, stream=stream, out_sorted=True,
-                                   fuse_silu=True)
+                                   fuse_silu=True, route_position=position)
     else:
         g = experts._buf("L_g", (size, 2 * w.inter), x.dtype, dev)
         capi.moe_wna16_marlin_gemm(x, w.w13, None, w.s13, w.z13, sorted_ids, expert_ids, npost, flat_w, block, k,
-                                   False, w.qtype, t, 2 * w.inter, w.hidden, g, stream=stream, out_sorted=True)
+                                   False, w.qtype, t, 2 * w.inter, w.hidden, g, stream=stream, out_sorted=True,
+                                   route_position=position)
         capi.silu_and_mul(g, h, stream=stream)
+    out = experts._buf("L_out", (t, w.hidden), x.dtype, dev)
+    if tiles_only:
+        y = experts._buf("L_ys", (size, w.hidden), x.dtype, dev)
+        capi.moe_wna16_marlin_gemm(h, w.w2, None, w.s2, w.z2, sorted_ids, expert_ids, npost, flat_w, block, 1, True,
+                                   w.qtype, t * k, w.hidden, w.inter, y, stream=stream, a_sorted=True, out_sorted=True)
+        capi.moe_gather_sum(y, position, out, stream=stream)
+        return out
     y = experts._buf("L_y", (t * k, w.hidden), x.dtype, dev)
     capi.moe_wna16_marlin_gemm(h, w.w2, None, w.s2, w.z2, sorted_ids, expert_ids, npost, flat_w, block, 1, True,
                                w.qtype, t * k, w.hidden, w.inter, y, stream=stream, a_sorted=True)
-    out = experts._buf("L_out", (t, w.hidden), x.dtype, dev)
     capi.moe_sum(y.view(t, k, w.hidden), out, stream=stream)
     return out
+

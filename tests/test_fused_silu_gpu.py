@@ -247,3 +247,75 @@ def test_layer_from_logits_equals_the_chain():
     got = moe_layer.layer_from_logits(x, logits, {"kind": "softmax", "top_k": top_k}, runner)
     torch.cuda.synchronize()
     assert torch.equal(got, want)
+
+
+# ---- second GEMM with tile stores + sum by position --------------------------------------------------------
+@pytest.mark.parametrize("block,zeros,with_bias", ((128, False, False), (256, True, True), (256, False, False)))
+def test_tile_store_chain_equals_the_scattered_chain(block, zeros, with_bias):
+    """w2 with `a_sorted` + `out_sorted` + routing weights, then moe_gather_sum by the positions the first
+    GEMM's gather wrote, against w2 scattering rows to their routes followed by moe_sum: same bits.  One
+    token carries an expert id outside the table (its route occurs nowhere in the sort)."""
+    from infiniops_b200 import capi
+
+    tokens, experts, top_k, hidden, inter = 700, 8, 2, 512, 256
+    qtype = capi.QTYPE_UINT4 if zeros else capi.QTYPE_UINT4B8
+    ids = torch.randint(0, experts, (tokens, top_k), dtype=torch.int32, device="cuda")
+    ids[5, 1] = experts + 2
+    tw = torch.rand((tokens, top_k), device="cuda").reshape(-1)
+    w13, s13, z13 = _random_experts(experts, hidden, 2 * inter, zeros, 600 + block)
+    w2, s2, z2 = _random_experts(experts, inter, hidden, zeros, 601 + block)
+    b2 = (torch.randn((experts, hidden), device="cuda") * 0.2).bfloat16() if with_bias else None
+    rows = tokens * top_k
+    size, blocks = omoe.padded_sizes(rows, experts, block)
+    sorted_ids = torch.empty(size, dtype=torch.int32, device="cuda")
+    expert_ids = torch.empty(blocks, dtype=torch.int32, device="cuda")
+    npost = torch.empty(1, dtype=torch.int32, device="cuda")
+    capi.moe_align_block_size(ids, None, experts, block, sorted_ids, expert_ids, npost)
+    x = torch.randn((tokens, hidden), device="cuda").bfloat16()
+
+    position = torch.full((tokens, top_k), 12345, dtype=torch.int32, device="cuda")
+    g = torch.zeros((size, 2 * inter), dtype=torch.bfloat16, device="cuda")
+    capi.moe_wna16_marlin_gemm(x, w13, None, s13, z13, sorted_ids, expert_ids, npost, tw, block, top_k, False, qtype,
+                               tokens, 2 * inter, hidden, g, out_sorted=True, route_position=position)
+    h = torch.empty((size, inter), dtype=torch.bfloat16, device="cuda")
+    capi.silu_and_mul(g, h)
+
+    y = torch.zeros((rows, hidden), dtype=torch.bfloat16, device="cuda")    # the dropped route's row stays zero
+    capi.moe_wna16_marlin_gemm(h, w2, b2, s2, z2, sorted_ids, expert_ids, npost, tw, block, 1, True, qtype, rows, hidden,
+                               inter, y, a_sorted=True)
+    want = torch.empty((tokens, hidden), dtype=torch.bfloat16, device="cuda")
+    capi.moe_sum(y.view(tokens, top_k, hidden), want)
+
+    ys = torch.full((size, hidden), float("nan"), dtype=torch.bfloat16, device="cuda")
+    capi.moe_wna16_marlin_gemm(h, w2, b2, s2, z2, sorted_ids, expert_ids, npost, tw, block, 1, True, qtype, rows, hidden,
+                               inter, ys, a_sorted=True, out_sorted=True)
+    got = torch.empty_like(want)
+    capi.moe_gather_sum(ys, position, got)
+    torch.cuda.synchronize()
+    assert capi.scratch_status(capi.scratch("cuda", 0)) == 0
+    # positions: the inverse of the sort, -1 for the route that was dropped
+    pos = position.cpu().flatten()
+    srt = sorted_ids.cpu().long()
+    assert int(pos[5 * top_k + 1]) == -1 and int((pos < 0).sum()) == 1
+    live = pos >= 0
+    assert torch.equal(srt[pos[live].long()], torch.nonzero(live).flatten())
+    assert not torch.isnan(got.float()).any()
+    assert torch.equal(got, want)
+
+
+def test_sorted_output_with_weights_needs_large_blocks():
+    from infiniops_b200 import capi
+
+    experts, hidden, n, block, tokens = 2, 256, 128, 64, 8
+    w, s, _ = _random_experts(experts, hidden, n, False, 7)
+    ids = torch.zeros((tokens, 1), dtype=torch.int32, device="cuda")
+    size, blocks = omoe.padded_sizes(tokens, experts, block)
+    sorted_ids = torch.empty(size, dtype=torch.int32, device="cuda")
+    expert_ids = torch.empty(blocks, dtype=torch.int32, device="cuda")
+    npost = torch.empty(1, dtype=torch.int32, device="cuda")
+    capi.moe_align_block_size(ids, None, experts, block, sorted_ids, expert_ids, npost)
+    x = torch.randn((tokens, hidden), device="cuda").bfloat16()
+    out = torch.empty((size, n), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(capi.Error, match="128- or 256-row"):
+        capi.moe_wna16_marlin_gemm(x, w, None, s, None, sorted_ids, expert_ids, npost, torch.ones(tokens, device="cuda"),
+                                   block, 1, True, capi.QTYPE_UINT4B8, tokens, n, hidden, out, out_sorted=True)

@@ -117,8 +117,8 @@ def test_rejects_unsupported():
     w = torch.zeros((8, 128), dtype=torch.int32, device="cuda")
     s = torch.zeros((1, 64), dtype=torch.float16, device="cuda")
     out = torch.zeros((4, 64), dtype=torch.float16, device="cuda")
-    with pytest.raises(capi.Error, match="only the 4-bit weight types"):
-        capi.marlin_gemm(a, w, None, s, None, 1125899923621888, 4, 64, 128, out)
+    with pytest.raises(capi.Error, match="only the weight types"):
+        capi.marlin_gemm(a, w, None, s, None, 1125899906844672, 4, 64, 128, out)   # uint8 with zero points
     with pytest.raises(capi.Error, match="zero points are required"):
         capi.marlin_gemm(a, w, None, s, None, capi.QTYPE_UINT4, 4, 64, 128, out)
 
