@@ -170,6 +170,26 @@ __global__ void EpUnpackKernel(const unsigned char* arena, ArenaLayout lay, int 
   }
 }
 
+// Combine step for layers whose second GEMM stores tiles in sorted order (128- / 256-row routing
+// blocks): every result row goes from the local [sorted, hidden] buffer to the arena of the rank its
+// token came from, to the row its route has there -- 16-byte plain stores into peer-mapped memory --
+// and the last block raises the completion flags.  One block per row at a time.
+__global__ void __launch_bounds__(256) EpCombineKernel(const uint4* __restrict__ rows, const int32_t* __restrict__ sorted_ids,
+                                                       const int32_t* __restrict__ num_post_pad,
+                                                       const int2* __restrict__ row_dest, int live_rows, int vec_per_row,
+                                                       PeerSet peers, size_t routed_off, int world, int rank, int* ctrl) {
+  const int total = *num_post_pad;
+  for (int row = blockIdx.x; row < total; row += gridDim.x) {
+    const int id = sorted_ids[row];
+    if (id >= live_rows) continue;
+    const int2 dest = row_dest[id];
+    const uint4* src = rows + static_cast<size_t>(row) * vec_per_row;
+    uint4* dst = reinterpret_cast<uint4*>(peers.arena[dest.x] + routed_off) + static_cast<size_t>(dest.y) * vec_per_row;
+    for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x) dst[i] = src[i];
+  }
+  if (world > 1) SignalWhenGridDone(ctrl, peers, world, rank);
+}
+
 struct Workspace {
   size_t pos, send_count, ids, weights, row_dest, sorted, experts, npost, g, h, gemm, align, total;
   size_t gemm_bytes, align_bytes;
@@ -196,7 +216,8 @@ Workspace PlanWorkspace(const iob_ep_context& c) {
   w.experts = take(static_cast<size_t>(w.blocks) * 4);
   w.npost = take(4);
   // the intermediates stay in sorted (expert) order: one row per position of the sorted id list
-  w.g = take(static_cast<size_t>(w.sorted_size) * 2 * c.inter * 2);
+  // (also holds the second GEMM's [sorted, hidden] result when that is stored as tiles: see the combine step)
+  w.g = take(static_cast<size_t>(w.sorted_size) * std::max<int64_t>(2 * c.inter, c.hidden) * 2);
   w.h = take(static_cast<size_t>(w.sorted_size) * c.inter * 2);
   w.gemm_bytes = std::max(
       infiniops_b200_moe_wna16_marlin_gemm_scratch_bytes(w.rows, 1, 2 * c.inter, c.hidden, c.experts_per_rank, c.moe_block_size),
@@ -321,6 +342,28 @@ extern "C" int infiniops_b200_ep_moe_layer(const iob_ep_context* ctx, const iob_
   signal.flag_slot = c.rank;
   for (int g = 0; g < c.world; ++g) {
     if (g != c.rank) signal.peer_flags[signal.n_peers++] = c.flags[g];
+  }
+  if (c.moe_block_size >= 128) {
+    // tile stores out of the second GEMM too (rows x routing weight, sorted order), then the combine copy
+    iob_routed_options tiles{};
+    tiles.a_sorted = 1;
+    tiles.out_sorted = 1;
+    if (const int rc = infiniops_b200_moe_wna16_marlin_gemm_ex(
+            ws + w.h, c.a_dtype, weights->w2, nullptr, weights->s2, weights->z2, sorted, expert_ids, npost, row_weights,
+            c.moe_block_size, 1, 1, c.b_type_id, w.rows, c.hidden, c.inter, weights->groups2, c.experts_per_rank,
+            w.sorted_size, ws + w.g, &tiles, ws + w.gemm, w.gemm_bytes, stream)) {
+      return rc;
+    }
+    const int vec_per_row = static_cast<int>(c.hidden * 2 / 16);
+    EpCombineKernel<<<static_cast<int>(std::min<int64_t>(w.sorted_size, 8 * NumSms())), 256, 0, s>>>(
+        reinterpret_cast<const uint4*>(ws + w.g), sorted, npost, row_dest, static_cast<int>(w.rows), vec_per_row, peers,
+        lay.routed, c.world, c.rank, c.ctrl);
+    if (const int rc = CheckLaunch("ep combine launch")) return rc;
+    if (c.world > 1) {
+      if (const int rc = infiniops_b200_peer_wait(c.flags[c.rank], c.world, c.rank, c.ctrl + 2, c.ctrl + 3, stream)) return rc;
+    }
+    return infiniops_b200_moe_sum(own + lay.routed, c.a_dtype, tokens, c.top_k, c.hidden, c.top_k * c.hidden, c.hidden, 1,
+                                  nullptr, IOB_I32, 0, 0, nullptr, 0, 0, out, stream);
   }
   iob_routed_options scatter{};
   scatter.row_dest = reinterpret_cast<const int32_t*>(row_dest);

@@ -92,6 +92,16 @@ def _worker(rank, world, port):
         err3 = float((got3.float() - expect_fused[t0:t1].float()).abs().max() / expect_fused.float().abs().max())
         assert err3 <= 1e-2, err3
         ep_fused.close()
+        # ... and with 128-row routing blocks: the second GEMM stores tiles, a copy kernel sends the rows home
+        full.w.interleaved = local.w.interleaved = False
+        ep_tiles = parallel.DeviceExpertParallel(local.w, top_k, tokens // world + 8, dev, 128)
+        for _ in range(2):
+            got4 = ep_tiles(x[t0:t1].contiguous(), ids[t0:t1].contiguous(), weights[t0:t1].contiguous())
+            torch.cuda.synchronize()
+            assert ep_tiles.status() == (0, 0, 0), ep_tiles.status()
+            err4 = float((got4.float() - expect[t0:t1].float()).abs().max() / expect.float().abs().max())
+            assert err4 <= 1e-2, err4
+        ep_tiles.close()
 
         # column-parallel dense linear
         k, n, m = 1024, 1024, 16
@@ -147,8 +157,8 @@ def test_expert_parallel_and_column_parallel_on_two_gpus():
     mp.spawn(_worker, args=(2, _free_port()), nprocs=2, join=True)
 
 
-@pytest.mark.parametrize("interleaved", (False, True))
-def test_device_expert_parallel_world_of_one_against_oracle(interleaved):
+@pytest.mark.parametrize("interleaved,block", ((False, 16), (True, 16), (False, 128), (True, 256)))
+def test_device_expert_parallel_world_of_one_against_oracle(interleaved, block):
     """The device-side expert-parallel layer with this GPU as the only rank, against the oracle chain
     router -> sort -> w13 -> silu_and_mul -> w2 (x weight) -> sum.  One token carries an expert id
     outside the table: its route must contribute nothing.  `interleaved`: w13 is packed with gate and
@@ -159,7 +169,7 @@ def test_device_expert_parallel_world_of_one_against_oracle(interleaved):
     from oracle import moe as omoe
     from oracle import quant as oq
 
-    experts, top_k, hidden, inter, block, tokens = 8, 2, 256, 128, 16, 50
+    experts, top_k, hidden, inter, tokens = 8, 2, 256, 128, 50   # (128- / 256-row blocks: tile stores + combine copy)
     dev = torch.device("cuda", 0)
     gen = torch.Generator().manual_seed(11)
 
