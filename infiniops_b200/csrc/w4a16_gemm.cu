@@ -33,7 +33,6 @@
 #include <cuda.h>
 
 #include <algorithm>
-#include <cstdlib>
 #include <mutex>
 #include <type_traits>
 #include <unordered_map>
@@ -2231,8 +2230,7 @@ int LaunchKernel(const CUtensorMap& map, const CUtensorMap& w_map, const CUtenso
   // (64-row tiles: dense only -- the routed form, with its many whole tiles per block and its
   // scattered tile-end stores, measured 40 % slower that way than with scaled weights)
   if constexpr (kTok <= 32 || (kTok == 64 && !kMoe)) {
-    static const bool late64 = getenv("IOB_LATE64") == nullptr || atoi(getenv("IOB_LATE64")) != 0;  // EXPERIMENT
-    if (p.group_size >= kBlockK && (kTok <= 32 || late64)) {
+    if (p.group_size >= kBlockK) {
       return LaunchVariant<T, kTok, kZeros, kMoe, true, false, kEpi>(map, w_map, c_map, p, grid, stream);
     }
   }
