@@ -19,9 +19,36 @@ oracle standing in for the CUDA operators.
 from __future__ import annotations
 
 import dataclasses
+import time
 
 import torch
 import torch.distributed as dist
+
+
+class CollectiveTimeout(RuntimeError):
+    """A collective of the library formulation did not complete before the host deadline."""
+
+
+# Seconds a collective may take before the caller gets an exception instead of a hang; None waits
+# for ever (the torch.distributed default behaviour).  A rank that never joins -- crashed, or stuck
+# in another step -- otherwise blocks its peers inside the collective with nothing to tell them why.
+DEADLINE_S: float | None = None
+
+
+def _finish(work, what: str, deadline_s: float | None) -> None:
+    """Waits for an asynchronous collective without blocking in the backend: the host polls the work
+    handle and gives up at the deadline.  The communicator is not usable after a timeout (the
+    collective may still be pending on the other ranks); the caller is expected to tear the group down."""
+    limit = DEADLINE_S if deadline_s is None else deadline_s
+    if limit is None:
+        work.wait()
+        return
+    end = time.monotonic() + limit
+    while not work.is_completed():
+        if time.monotonic() > end:
+            raise CollectiveTimeout(f"{what}: not complete after {limit:.3g} s (a rank did not join?)")
+        time.sleep(0.0005)
+    work.wait()   # completed: returns at once; orders the current stream behind the collective (NCCL)
 
 
 # ---- dense: column-parallel -------------------------------------------------------------------------
@@ -48,14 +75,17 @@ def shard_columns(packed, scales, zeros_packed, n: int, rank: int, world: int, s
     return w.contiguous(), scales[:, lo:hi].contiguous(), z
 
 
-def gather_columns(out_local: torch.Tensor, gathered: torch.Tensor | None = None, group=None) -> torch.Tensor:
+def gather_columns(out_local: torch.Tensor, gathered: torch.Tensor | None = None, group=None,
+                   deadline_s: float | None = None) -> torch.Tensor:
     """All-gathers [M, N/g] slices; returns the [g, M, N/g] buffer (rank-major).  `as_matrix` turns it
     into [M, N]."""
     world = dist.get_world_size(group)
     if gathered is None:
         gathered = out_local.new_empty((world, *out_local.shape))
     # flat [g*M, N/g] view: the form every backend accepts
-    dist.all_gather_into_tensor(gathered.view(-1, out_local.shape[-1]), out_local.contiguous(), group=group)
+    work = dist.all_gather_into_tensor(gathered.view(-1, out_local.shape[-1]), out_local.contiguous(), group=group,
+                                       async_op=True)
+    _finish(work, "gather_columns", deadline_s)
     return gathered
 
 
@@ -81,7 +111,7 @@ def experts_per_rank(num_experts: int, world: int) -> int:
     return num_experts // world
 
 
-def plan_dispatch(topk_ids: torch.Tensor, num_experts: int, group=None) -> DispatchPlan:
+def plan_dispatch(topk_ids: torch.Tensor, num_experts: int, group=None, deadline_s: float | None = None) -> DispatchPlan:
     """Sorts this rank's routes by owner of their expert and exchanges the per-rank row counts (the
     one place the host has to read device data: the split sizes of the payload exchange)."""
     world = dist.get_world_size(group)
@@ -90,7 +120,7 @@ def plan_dispatch(topk_ids: torch.Tensor, num_experts: int, group=None) -> Dispa
     order = torch.argsort(dest, stable=True)
     send = torch.bincount(dest, minlength=world).to(torch.int64)
     recv = torch.empty_like(send)
-    dist.all_to_all_single(recv, send, group=group)
+    _finish(dist.all_to_all_single(recv, send, group=group, async_op=True), "plan_dispatch", deadline_s)
     counts = torch.stack((send, recv)).tolist()
     return DispatchPlan(order, counts[0], counts[1])
 
@@ -101,7 +131,7 @@ def _meta_slots(dtype: torch.dtype) -> int:
 
 
 def dispatch(x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, num_experts: int,
-             plan: DispatchPlan, group=None) -> torch.Tensor:
+             plan: DispatchPlan, group=None, deadline_s: float | None = None) -> torch.Tensor:
     """One all-to-all carrying, per route, row `route // k` of x followed by two 32-bit words (expert
     index on the owner, routing weight) packed into spare columns.  Returns the rows this rank has to
     process, [sum(recv), H], and fills `plan.local_expert` / `plan.weights`."""
@@ -115,17 +145,19 @@ def dispatch(x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor
                         topk_weights.reshape(-1)[plan.order].to(torch.float32).view(torch.int32)), dim=1)
     out_buf[:, hidden:] = meta.view(x.dtype).view(-1, 2 * slots)
     in_buf = x.new_empty((sum(plan.recv_counts), hidden + 2 * slots))
-    dist.all_to_all_single(in_buf, out_buf, plan.recv_counts, plan.send_counts, group=group)
+    _finish(dist.all_to_all_single(in_buf, out_buf, plan.recv_counts, plan.send_counts, group=group, async_op=True),
+            "dispatch", deadline_s)
     meta_in = in_buf[:, hidden:].contiguous().view(torch.int32)
     plan.local_expert = meta_in[:, 0].contiguous()
     plan.weights = meta_in[:, 1].contiguous().view(torch.float32)
     return in_buf[:, :hidden].contiguous()
 
 
-def combine(y: torch.Tensor, plan: DispatchPlan, group=None) -> torch.Tensor:
+def combine(y: torch.Tensor, plan: DispatchPlan, group=None, deadline_s: float | None = None) -> torch.Tensor:
     """Inverse of `dispatch`: returns [T*k, H] in flat route order (row t*k + slot)."""
     back = y.new_empty((sum(plan.send_counts), y.shape[1]))
-    dist.all_to_all_single(back, y.contiguous(), plan.send_counts, plan.recv_counts, group=group)
+    _finish(dist.all_to_all_single(back, y.contiguous(), plan.send_counts, plan.recv_counts, group=group, async_op=True),
+            "combine", deadline_s)
     out = torch.empty_like(back)
     out[plan.order] = back
     return out

@@ -135,3 +135,38 @@ def _one_rank_case(parallel, rank, ids, w, dtype):
 
 def test_dispatch_with_an_idle_rank():
     _spawn(_all_to_one_rank)
+
+
+def _late_rank(rank, result):
+    """Rank 1 never enters the collective (it sits out the step on the host, as a crashed or stuck
+    rank would); rank 0 must get an exception at its deadline instead of blocking, and a later
+    collective that both ranks do enter -- on a fresh group -- must still work."""
+    import time
+
+    from infiniops_b200 import parallel
+
+    x = torch.full((3, 4), float(rank))
+    if rank == 0:
+        t0 = time.monotonic()
+        try:
+            parallel.gather_columns(x, deadline_s=0.5)
+            result["outcome"] = "returned"
+        except parallel.CollectiveTimeout as e:
+            result["outcome"] = "timeout"
+            result["message"] = str(e)
+        result["seconds"] = time.monotonic() - t0
+    else:
+        time.sleep(1.5)   # does not join
+    # the ranks learn of the failure on the host (here: simply by both getting past the step) and
+    # continue on a new group; the old communicator is abandoned
+    fresh = dist.new_group(ranks=[0, 1], backend="gloo")
+    got = parallel.as_matrix(parallel.gather_columns(x, group=fresh, deadline_s=20.0))
+    assert torch.equal(got, torch.cat([torch.zeros(3, 4), torch.ones(3, 4)], dim=1))
+
+
+def test_collective_gives_up_at_the_host_deadline():
+    manager = mp.Manager()
+    result = manager.dict()
+    _spawn(_late_rank, result)
+    assert result["outcome"] == "timeout", dict(result)
+    assert "gather_columns" in result["message"] and 0.4 < result["seconds"] < 1.4
