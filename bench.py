@@ -254,10 +254,17 @@ def run_ours(args):
                               max(capi.lib().infiniops_b200_marlin_gemm_scratch_bytes(m, n // world, k)
                                   for _, k, n in SHAPES for m in MS)), dtype=torch.uint8, device=device)
 
+    # How the slices reach the other ranks: stored by the GEMM epilogue tile by tile ("epilogue"), or by one
+    # copy launch behind the GEMMs that sends every slice with whole-warp stores ("broadcast")
+    # (measured: the copy launch costs 8 us more per step at N = 2 and 4 us more at N = 4 than it saves, so the
+    # epilogue stores are the default at every N)
+    gather = "epilogue" if args.gather == "auto" else args.gather
+
     def problem(phase, key, layer_set=None):
         name, m = key
         w = (layer_set or layers)[phase * len(MS) + MS.index(m)][name]
-        peers = [] if group is None else [group.address(r, offsets[phase % 2][key]) for r in group.others()]
+        peers = ([] if group is None or gather == "broadcast" else
+                 [group.address(r, offsets[phase % 2][key]) for r in group.others()])
         return capi.gemm_problem(acts[key], w["marlin"], None, w["scales"], w["zeros"], outs[phase % 2][key], m, w["n"],
                                  w["k"], out_ld=full_n[name], out_col0=rank * w["n"], peer_out=peers)
 
@@ -265,19 +272,37 @@ def run_ours(args):
     singles = [[problem(phase, key) for key in keys] for phase in range(phases)]
     signal = None if group is None else group.signal()
 
+    slice_copies = None
+    if group is not None and gather == "broadcast":
+        def slice_copy(phase, key):
+            name, m = key
+            n_local = full_n[name] // world
+            col_bytes = rank * n_local * 2
+            return capi.peer_copy(outs[phase % 2][key].data_ptr() + col_bytes,
+                                  [group.address(r, offsets[phase % 2][key]) + col_bytes for r in group.others()],
+                                  m, n_local * 2, full_n[name] * 2)
+        slice_copies = [(capi.PeerCopy * len(keys))(*[slice_copy(phase, key) for key in keys]) for phase in range(2)]
+
     def step_batched(phase, stream=None):
-        capi.marlin_gemm_batch(tables[phase], torch.bfloat16, UINT4, scratch, signal=signal, stream=stream)
+        if slice_copies is None:
+            capi.marlin_gemm_batch(tables[phase], torch.bfloat16, UINT4, scratch, signal=signal, stream=stream)
+        else:
+            capi.marlin_gemm_batch(tables[phase], torch.bfloat16, UINT4, scratch, stream=stream)
+            capi.peer_broadcast(slice_copies[phase % 2], world - 1, signal=signal, stream=stream)
         if group is not None:
             group.wait(stream=stream)
-        return 2 + (1 if group is not None else 0)   # two classes of token tile (M <= 16, M = 64): one launch each
+        # two classes of token tile (M <= 16, M = 64), one launch each (+ the slice broadcast) + the flag wait
+        return 2 + (0 if group is None else 1 + (1 if slice_copies is not None else 0))
 
     def step_per_gemm(phase, stream=None):
         for i, g in enumerate(singles[phase]):
-            last = i == len(keys) - 1
+            last = i == len(keys) - 1 and slice_copies is None
             capi.marlin_gemm_placed(g, torch.bfloat16, UINT4, scratch, signal=signal if last else None, stream=stream)
+        if slice_copies is not None:
+            capi.peer_broadcast(slice_copies[phase % 2], world - 1, signal=signal, stream=stream)
         if group is not None:
             group.wait(stream=stream)
-        return len(keys) + (1 if group is not None else 0)
+        return len(keys) + (0 if group is None else 1 + (1 if slice_copies is not None else 0))
 
     def capture(step_fn):
         """The step as CUDA graphs, one per weight-copy phase, so that replays keep rotating the weights."""
@@ -362,8 +387,11 @@ def run_ours(args):
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": WORKLOAD,
                    "parallelism": "single GPU" if world == 1 else
-                   f"column-parallel N-shard x{world}; the GEMM epilogue stores each slice into every rank's "
-                   "full-width result over NVLink (peer-mapped buffers), completion flags + bounded wait per step",
+                   f"column-parallel N-shard x{world}; " +
+                   ("the GEMM epilogue stores each slice into every rank's full-width result over NVLink"
+                    if slice_copies is None else
+                    "one copy launch behind the GEMMs stores every slice into the other ranks' full-width results over NVLink") +
+                   " (peer-mapped buffers), completion flags + bounded wait per step",
                    "l2": f"inputs larger than L2: {copies} full weight copies "
                          f"({copies * layer_bytes / 1e6:.0f} MB per GPU) used in rotation",
                    "launch": "CUDA graph replay of the step; the 16 problems as two batched persistent launches"},
@@ -994,6 +1022,9 @@ def main():
     parser.add_argument("--one-batch", default=None, help="S: the batched step on linears shrunk by S, three times")
     parser.add_argument("--ms", default=None, help="--one-batch: the row counts to include, e.g. 1,4,16")
     parser.add_argument("--gptq", action="store_true", help="--one: GPTQ-symmetric weights instead of AWQ")
+    parser.add_argument("--gather", default="auto", choices=("auto", "epilogue", "broadcast"),
+                        help="N > 1: slices stored to the peers by the GEMM epilogue, or by one copy launch behind the GEMMs "
+                             "(auto: the epilogue)")
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=100)
     parser.add_argument("--warmup", type=int, default=5)

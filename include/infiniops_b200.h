@@ -368,6 +368,24 @@ int infiniops_b200_peer_close(void* ptr);
 int infiniops_b200_peer_wait(const int* flags, int n_slots, int skip_slot, int* wait_epoch,
                              int* status, void* stream);
 
+/* One rectangular slice to send to the other GPUs: `rows` rows of `row_bytes` bytes at a row pitch of
+ * `pitch_bytes`, starting at `src` (local) and going to the same offsets from `dst[r]` (GPU r's
+ * matrix as mapped into this process).  Sizes and addresses are multiples of 16 bytes. */
+#define IOB_MAX_COPIES 16
+typedef struct {
+  const void* src;
+  void* dst[IOB_MAX_PEERS];
+  int64_t rows, row_bytes, pitch_bytes;
+} iob_peer_copy;
+
+/* Sends up to IOB_MAX_COPIES slices to `n_peers` GPUs each in one launch, with whole-warp 16-byte
+ * stores (the coalesced alternative to iob_gemm_problem::peer_out, whose stores leave the GEMM
+ * epilogue as 64-byte pieces; for decode-sized results the extra launch costs more than it saves --
+ * it pays when the slices are large), then raises `signal` (or NULL) the way a GEMM launch does.  The column-parallel step is then: GEMMs with local placement only ->
+ * infiniops_b200_peer_broadcast -> infiniops_b200_peer_wait.  No counterpart in the reference. */
+int infiniops_b200_peer_broadcast(const iob_peer_copy* copies, int count, int n_peers,
+                                  const iob_peer_signal* signal, void* stream);
+
 /* The same dense GEMM for callers that have no device memory to lend and may not allocate any:
  * an engine whose arena already owns the whole GPU, or code that only runs while its host is
  * recording work and cudaMalloc is off limits.  The scratch is a 10 MiB array inside the library

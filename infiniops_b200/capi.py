@@ -72,6 +72,14 @@ class PeerSignal(ctypes.Structure):
                 ("flag_slot", _int)]
 
 
+MAX_COPIES = 16
+
+
+class PeerCopy(ctypes.Structure):
+    """`iob_peer_copy`."""
+    _fields_ = [("src", _vp), ("dst", _vp * MAX_PEERS), ("rows", _i64), ("row_bytes", _i64), ("pitch_bytes", _i64)]
+
+
 class RoutedOptions(ctypes.Structure):
     """`iob_routed_options`."""
     _fields_ = [("scale_layout", _int), ("a_sorted", _int), ("out_sorted", _int), ("fuse_silu", _int),
@@ -122,6 +130,7 @@ PROTOTYPES.update({
     "infiniops_b200_peer_open": (_int, [ctypes.c_char_p, ctypes.POINTER(_vp)]),
     "infiniops_b200_peer_close": (_int, [_vp]),
     "infiniops_b200_peer_wait": (_int, [_vp, _int, _int, _vp, _vp, _vp]),
+    "infiniops_b200_peer_broadcast": (_int, [ctypes.POINTER(PeerCopy), _int, _int, ctypes.POINTER(PeerSignal), _vp]),
 })
 
 _lib = None
@@ -342,6 +351,20 @@ def gemm_problem(a, b_q_weight, b_bias, b_scales, b_zeros, out, size_m, size_n, 
     for i, ptr in enumerate(peer_out):
         g.peer_out[i] = ptr
     return g
+
+
+def peer_copy(src_ptr: int, dst_ptrs, rows: int, row_bytes: int, pitch_bytes: int) -> PeerCopy:
+    c = PeerCopy()
+    c.src, c.rows, c.row_bytes, c.pitch_bytes = src_ptr, rows, row_bytes, pitch_bytes
+    for i, ptr in enumerate(dst_ptrs):
+        c.dst[i] = ptr
+    return c
+
+
+def peer_broadcast(copies, n_peers: int, signal=None, stream=None):
+    """`copies`: a ctypes array `(PeerCopy * n)(...)`, at most MAX_COPIES entries (build it once)."""
+    _check(lib().infiniops_b200_peer_broadcast(copies, len(copies), n_peers,
+                                               None if signal is None else ctypes.byref(signal), _stream(stream)))
 
 
 def problem_array(problems):

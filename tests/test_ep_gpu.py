@@ -144,6 +144,22 @@ def _worker(rank, world, port):
             # each rank's slice equals what the all-gather formulation delivered
             assert torch.equal(full_out, sharded)
             dist.barrier()
+        # the same again with the slices sent by one copy launch behind the GEMM (local placement only)
+        full_out.zero_()
+        dist.barrier()
+        g_local = capi.gemm_problem(a, marlin, None, s, z, full_out, m, n // world, k, out_ld=n, out_col0=rank * (n // world))
+        col_bytes = rank * (n // world) * 2
+        copies = (capi.PeerCopy * 1)(capi.peer_copy(full_out.data_ptr() + col_bytes,
+                                                    [group.address(r, off) + col_bytes for r in group.others()], m,
+                                                    (n // world) * 2, n * 2))
+        for _ in range(2):
+            capi.marlin_gemm_batch(capi.problem_array([g_local]), torch.bfloat16, capi.QTYPE_UINT4, scratch)
+            capi.peer_broadcast(copies, world - 1, signal=group.signal())
+            group.wait()
+            torch.cuda.synchronize()
+            assert group.wait_status() == (0, 0) and capi.scratch_status(scratch) == 0
+            assert torch.equal(full_out, sharded)
+            dist.barrier()
         group.close()
     finally:
         dist.destroy_process_group()
