@@ -465,21 +465,41 @@ def e2e_decode(d, args, layers, acts, keys, full_n, phases):
     import infini.ops
 
     world, device = d.world, d.device
-    host_in = {key: t.cpu().pin_memory() for key, t in acts.items()}
-    host_out = {key: torch.empty((key[1], full_n[key[0]]), dtype=torch.bfloat16).pin_memory() for key in keys}
-    dev_in = {key: torch.empty_like(t) for key, t in acts.items()}
-    dev_out = {key: torch.empty((key[1], full_n[key[0]] // world), dtype=torch.bfloat16, device=device) for key in keys}
+    # One pinned arena for the step's activations and one for its results (and the same on the device),
+    # so that a step moves its inputs in one host -> device copy and its results in one device -> host copy
+    # instead of sixteen small ones each; the operator calls take views of the arenas.
+    def arena(shapes, **kw):
+        sizes = [-(-(r * c) // 128) * 128 for r, c in shapes.values()]   # 256-byte aligned slices
+        flat = torch.empty(sum(sizes), dtype=torch.bfloat16, **kw)
+        views, at = {}, 0
+        for (key, (r, c)), size in zip(shapes.items(), sizes):
+            views[key] = flat[at:at + r * c].view(r, c)
+            at += size
+        return flat, views
+
+    in_shapes = {key: tuple(acts[key].shape) for key in keys}
+    out_shapes = {key: (key[1], full_n[key[0]]) for key in keys}
+    host_in_flat, host_in = arena(in_shapes, pin_memory=True)
+    host_out_flat, host_out = arena(out_shapes, pin_memory=True)
+    dev_in_flat, dev_in = arena(in_shapes, device=device)
+    for key in keys:
+        host_in[key].copy_(acts[key])
+    if world == 1:
+        dev_out_flat, dev_out = arena(out_shapes, device=device)
+    else:
+        dev_out = {key: torch.empty((key[1], full_n[key[0]] // world), dtype=torch.bfloat16, device=device) for key in keys}
+        dev_full_flat, dev_full = arena(out_shapes, device=device)
     gathered = {key: torch.empty((world, key[1], full_n[key[0]] // world), dtype=torch.bfloat16, device=device)
                 for key in keys} if world > 1 else None
     workspace = torch.zeros(432, dtype=torch.int32, device=device)
-    h2d = sum(t.numel() * 2 for t in host_in.values())
-    d2h = sum(t.numel() * 2 for t in host_out.values())
+    h2d = host_in_flat.numel() * 2
+    d2h = host_out_flat.numel() * 2
 
     def step(phase):
         stream = torch.cuda.current_stream().cuda_stream
+        dev_in_flat.copy_(host_in_flat, non_blocking=True)
         for name, m in keys:
             w = layers[phase * len(MS) + MS.index(m)][name]
-            dev_in[(name, m)].copy_(host_in[(name, m)], non_blocking=True)
             infini.ops.marlin_gemm(dev_in[(name, m)], w["marlin"], None, w["scales"], None, None, w["zeros"], None, None,
                                    workspace, UINT4, m, w["n"], w["k"], True, False, True, False, dev_out[(name, m)],
                                    stream=stream)
@@ -487,26 +507,56 @@ def e2e_decode(d, args, layers, acts, keys, full_n, phases):
                 import torch.distributed as dist
 
                 dist.all_gather_into_tensor(gathered[(name, m)].view(-1, w["n"]), dev_out[(name, m)])
-                host_out[(name, m)].copy_(gathered[(name, m)].permute(1, 0, 2).reshape(m, -1), non_blocking=True)
-            else:
-                host_out[(name, m)].copy_(dev_out[(name, m)], non_blocking=True)
+                dev_full[(name, m)].copy_(gathered[(name, m)].permute(1, 0, 2).reshape(m, -1))
+        host_out_flat.copy_(dev_out_flat if world == 1 else dev_full_flat, non_blocking=True)
 
-    for i in range(3):
+    for i in range(max(3, phases)):
         step(i % phases)
+    torch.cuda.synchronize()
     steps = max(3, min(args.steps, 50))
     count = [0]
+    graphs = None
+    if world == 1:
+        # One CUDA graph per weight-copy phase holding the step as the caller issues it: per GEMM a
+        # host -> device copy node, the operator's launch, a device -> host copy node.  (With N > 1 the
+        # step stays eager: it carries an NCCL all-gather per GEMM.)
+        graphs = []
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step(0)   # outside capture first: the operator's per-stream scratch is allocated on first use
+            torch.cuda.synchronize()
+            for phase in range(phases):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    step(phase)
+                graphs.append(g)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        for g in graphs:
+            g.replay()
+        torch.cuda.synchronize()
 
     def run(n):
         for _ in range(n):
-            step(count[0] % phases)
+            if graphs is None:
+                step(count[0] % phases)
+            else:
+                graphs[count[0] % phases].replay()
             count[0] += 1
 
     regions = timed_regions(d, run, steps, 3)
     ms = statistics.median(regions)
+    # what came back to the host must be what the device computed
+    torch.cuda.synchronize()
+    key = keys[-1]
+    assert world > 1 or torch.equal(host_out[key], dev_out[key].cpu()), "e2e: host result differs"
     step_weight_bytes = sum(weight_bytes(k, n) for _, k, n in SHAPES) * len(MS)
     return {"value": step_weight_bytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
             "d2h_bytes_per_step": d2h, "steps": steps, "ms_per_step": ms,
-            "note": "infini.ops.marlin_gemm per GEMM; pinned host activations in, host outputs out"}
+            "note": "infini.ops.marlin_gemm per GEMM; the step's activations in one copy from pinned host memory, its results "
+                    "in one copy back to pinned host memory" +
+                    ("; the step (copies and operator calls) replayed as a CUDA graph" if graphs is not None else "")}
 
 
 # ---------------------------------------------------------------------------------------------------
