@@ -488,6 +488,11 @@ int infiniops_b200_moe_wna16_gemm(const void* input, int dtype, const uint8_t* b
  * the others (the call clears the array first, on the stream).  w13 (`out_sorted`, `route_position`) -> silu_and_mul ->
  * w2 (`a_sorted`, `out_sorted`, weights) -> infiniops_b200_moe_gather_sum is the layer with every
  * GEMM store a tile store and the scatter folded into the final sum.
+ * `block_rows` (or NULL; int32, one entry per routing block): the live rows of every block.  A call
+ * that gathers (not `a_sorted`, no `perm`) writes it; any call given it restricts the MMAs and the
+ * epilogue of a block to its live rows rounded up to 16, so a partly filled last block of an expert
+ * costs tensor-core time for its rows, not for the padding (256-row blocks on paired thread blocks
+ * keep the full extent).  Rows of a sorted output beyond that extent are then left unwritten.  Pass the table the w13 call wrote to the w2 call.
  * Zero-initialise the struct.  No counterpart in the reference beyond `g_idx` / `perm`. */
 typedef struct {
   int scale_layout;
@@ -495,6 +500,7 @@ typedef struct {
   const int32_t* g_idx;
   const int32_t* perm;
   int32_t* route_position;
+  int32_t* block_rows;
   const int32_t* row_dest;
   void* dest_base[IOB_MAX_PEERS + 1];
   int n_dest;

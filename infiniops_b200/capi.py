@@ -83,7 +83,7 @@ class PeerCopy(ctypes.Structure):
 class RoutedOptions(ctypes.Structure):
     """`iob_routed_options`."""
     _fields_ = [("scale_layout", _int), ("a_sorted", _int), ("out_sorted", _int), ("fuse_silu", _int),
-                ("g_idx", _vp), ("perm", _vp), ("route_position", _vp), ("row_dest", _vp),
+                ("g_idx", _vp), ("perm", _vp), ("route_position", _vp), ("block_rows", _vp), ("row_dest", _vp),
                 ("dest_base", _vp * (MAX_PEERS + 1)), ("n_dest", _int),
                 ("signal", ctypes.POINTER(PeerSignal))]
 
@@ -319,7 +319,7 @@ def marlin_gemm_static_scratch(a, b_q_weight, b_bias, b_scales, b_zeros, b_type_
 def moe_wna16_marlin_gemm(a, b_q_weight, b_bias, b_scales, b_zeros, sorted_token_ids, expert_ids,
                           num_tokens_past_padded, topk_weights, moe_block_size, top_k, mul_topk_weights, b_type_id,
                           size_m, size_n, size_k, out, stream=None, scratch_buf=None, scale_layout=0, a_sorted=False,
-                          out_sorted=False, fuse_silu=False, g_idx=None, perm=None, route_position=None):
+                          out_sorted=False, fuse_silu=False, g_idx=None, perm=None, route_position=None, block_rows=None):
     e = b_q_weight.shape[0]
     need = lib().infiniops_b200_moe_wna16_marlin_gemm_scratch_bytes(size_m, top_k, size_n, size_k, e,
                                                                     moe_block_size)
@@ -330,6 +330,7 @@ def moe_wna16_marlin_gemm(a, b_q_weight, b_bias, b_scales, b_zeros, sorted_token
     options.g_idx = None if g_idx is None else g_idx.data_ptr()
     options.perm = None if perm is None else perm.data_ptr()
     options.route_position = None if route_position is None else route_position.data_ptr()
+    options.block_rows = None if block_rows is None else block_rows.data_ptr()
     _check(lib().infiniops_b200_moe_wna16_marlin_gemm_ex(
         _ptr(a), _DTYPE[a.dtype], _ptr(b_q_weight), _ptr(b_bias), _ptr(b_scales), _ptr(b_zeros),
         _ptr(sorted_token_ids), _ptr(expert_ids), _ptr(num_tokens_past_padded), _ptr(topk_weights), moe_block_size,

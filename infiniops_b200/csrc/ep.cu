@@ -191,7 +191,7 @@ __global__ void __launch_bounds__(256) EpCombineKernel(const uint4* __restrict__
 }
 
 struct Workspace {
-  size_t pos, send_count, ids, weights, row_dest, sorted, experts, npost, g, h, gemm, align, total;
+  size_t pos, send_count, ids, weights, row_dest, sorted, experts, npost, live, g, h, gemm, align, total;
   size_t gemm_bytes, align_bytes;
   int64_t rows, sorted_size, blocks;
 };
@@ -216,6 +216,7 @@ Workspace PlanWorkspace(const iob_ep_context& c) {
   w.experts = take(static_cast<size_t>(w.blocks) * 4);
   w.npost = take(4);
   // the intermediates stay in sorted (expert) order: one row per position of the sorted id list
+  w.live = take(static_cast<size_t>(w.blocks + 1) * sizeof(int32_t));
   // (also holds the second GEMM's [sorted, hidden] result when that is stored as tiles: see the combine step)
   w.g = take(static_cast<size_t>(w.sorted_size) * std::max<int64_t>(2 * c.inter, c.hidden) * 2);
   w.h = take(static_cast<size_t>(w.sorted_size) * c.inter * 2);
@@ -319,8 +320,10 @@ extern "C" int infiniops_b200_ep_moe_layer(const iob_ep_context* ctx, const iob_
                                                          w.align_bytes ? ws + w.align : nullptr, w.align_bytes, stream)) {
     return rc;
   }
+  auto* live = reinterpret_cast<int32_t*>(ws + w.live);  // live rows per routing block, noted by the first GEMM's gather
   iob_routed_options first{};
   first.out_sorted = 1;
+  first.block_rows = live;
   const bool fused = weights->w13_interleaved != 0 && (2 * c.inter) % 128 == 0;
   first.fuse_silu = fused ? 1 : 0;
   if (const int rc = infiniops_b200_moe_wna16_marlin_gemm_ex(
@@ -348,6 +351,7 @@ extern "C" int infiniops_b200_ep_moe_layer(const iob_ep_context* ctx, const iob_
     iob_routed_options tiles{};
     tiles.a_sorted = 1;
     tiles.out_sorted = 1;
+    tiles.block_rows = live;
     if (const int rc = infiniops_b200_moe_wna16_marlin_gemm_ex(
             ws + w.h, c.a_dtype, weights->w2, nullptr, weights->s2, weights->z2, sorted, expert_ids, npost, row_weights,
             c.moe_block_size, 1, 1, c.b_type_id, w.rows, c.hidden, c.inter, weights->groups2, c.experts_per_rank,
@@ -371,6 +375,7 @@ extern "C" int infiniops_b200_ep_moe_layer(const iob_ep_context* ctx, const iob_
   for (int g = 0; g < c.world; ++g) scatter.dest_base[g] = peers.arena[g] + lay.routed;
   scatter.signal = c.world > 1 ? &signal : nullptr;
   scatter.a_sorted = 1;
+  scatter.block_rows = live;
   if (const int rc = infiniops_b200_moe_wna16_marlin_gemm_ex(
           ws + w.h, c.a_dtype, weights->w2, nullptr, weights->s2, weights->z2, sorted, expert_ids, npost, row_weights,
           c.moe_block_size, 1, 1, c.b_type_id, w.rows, c.hidden, c.inter, weights->groups2, c.experts_per_rank,

@@ -140,6 +140,9 @@ struct GemmParams {
   // features) and the epilogue stores silu(gate) * up, [rows][N/2], instead of the [rows][N] product.
   int fuse_silu;
   int bits;                         // 4 or 8: width of a packed weight
+  // routed form, optional: live rows of every routing block (the rest of a block is padding).  The
+  // MMAs of a block then cover only its live token columns, rounded up to 16, and so does the epilogue.
+  const int* block_rows;
   const int2* row_dest;             // null, or per output row: (GPU, row there) the result row is stored to
   void* dest_base[kMaxPeers + 1];   // with `row_dest`: the destination matrix of every GPU (own included)
   const int32_t* sorted_ids;
@@ -1065,6 +1068,17 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
           d_addr = kSplit ? tmem_d + acc * kTok + me * kMmaN : tmem_d + (acc * kIssuers + me) * kTok;
         }
         bool issued = false;
+        [[maybe_unused]] uint32_t idesc = kIdesc;
+        if constexpr (kMoe && !kSplit && !kPair) {
+          // (not for paired blocks: their token columns are split between the two blocks' activation
+          // halves, so a shorter extent would not be a prefix of the rows)
+          if (cur->p.block_rows != nullptr) {
+            // token extent of this block's MMAs: its live rows, in steps of 16 (at least 16)
+            const int live = cur->p.block_rows[seg.m_tile];
+            const int n_eff = live >= kMmaN ? kMmaN : live <= 16 ? 16 : (live + 15) & ~15;
+            idesc = (kIdesc & ~(0x3Fu << 17)) | (static_cast<uint32_t>(n_eff >> 3) << 17);
+          }
+        }
         for (int ks = seg.k_begin; ks < seg.k_end; ++ks, ++it) {
           if (!kSplit && static_cast<int>(it % kIssuers) != me) continue;
           last_it = static_cast<int>(it);
@@ -1110,9 +1124,9 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
             const uint64_t desc = desc0 + static_cast<uint64_t>((j >> 2) * (kAtomBytes >> 4) + 2 * (j & 3));
             const uint32_t accumulate = ((issued && !kLate) || j > 0) ? 1u : 0u;
             if constexpr (kPair) {
-              MmaTsPair(d_addr, tmem_a + a * kAStageCols + 8 * j, desc, kIdesc, accumulate);
+              MmaTsPair(d_addr, tmem_a + a * kAStageCols + 8 * j, desc, idesc, accumulate);
             } else {
-              MmaTs(d_addr, tmem_a + a * kAStageCols + 8 * j, desc, kIdesc, accumulate);
+              MmaTs(d_addr, tmem_a + a * kAStageCols + 8 * j, desc, idesc, accumulate);
             }
           }
           issued = true;
@@ -1468,7 +1482,11 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
       const int n = tile_of(seg.n_tile) * kTileN + n_local;
       const bool n_ok = n < cur->p.n;
       const int row0 = kMoe ? seg.m_tile * cur->p.block_size : seg.m_tile * kTok;
-      const int m_valid = kMoe ? cur->p.block_size : min(kTok, cur->p.m - row0);
+      int m_valid = kMoe ? cur->p.block_size : min(kTok, cur->p.m - row0);
+      if constexpr (kMoe && !kSplit && !kPair) {
+        // (only the token columns the block's MMAs wrote: see the issuer)
+        if (cur->p.block_rows != nullptr) m_valid = min(m_valid, max(16, (cur->p.block_rows[seg.m_tile] + 15) & ~15));
+      }
       const bool whole = seg.k_begin == 0 && seg.k_end == seg.k_stages;
       const int n_steps = seg.k_end - seg.k_begin;
       float bias_v = 0.0f;
@@ -1881,12 +1899,19 @@ __global__ void BoundedWaitSelfTestKernel(int* status, int* result) {
 template <typename T>
 __global__ void GatherRowsKernel(const T* __restrict__ a, T* __restrict__ gathered,
                                  const int32_t* __restrict__ sorted_ids, const int32_t* __restrict__ num_post_pad,
-                                 int k, int top_k, int out_rows, int32_t* __restrict__ position) {
+                                 int k, int top_k, int out_rows, int32_t* __restrict__ position,
+                                 int32_t* __restrict__ block_rows, int block_size) {
   const int rows = *num_post_pad;
   const int vec_per_row = k / 8;
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const int id = sorted_ids[row];
     uint4* dst = reinterpret_cast<uint4*>(gathered + static_cast<size_t>(row) * k);
+    // by-product: the live rows of every routing block (they are a prefix of the block: the last live
+    // row is the one followed by padding or by the block's end)
+    if (block_rows != nullptr && threadIdx.x == 0 && id < out_rows) {
+      const int in_block = row % block_size;
+      if (in_block == block_size - 1 || sorted_ids[row + 1] >= out_rows) block_rows[row / block_size] = in_block + 1;
+    }
     // by-product for the caller's combine step: where each route sits in sorted order
     if (position != nullptr && threadIdx.x == 0 && id < out_rows) position[id] = row;
     if (id < out_rows) {
@@ -2583,6 +2608,9 @@ extern "C" int infiniops_b200_moe_wna16_marlin_gemm_ex(
   int32_t* position = options != nullptr ? options->route_position : nullptr;
   IOB_REQUIRE(position == nullptr || (!a_sorted && (options->perm == nullptr)),
               "%s: `route_position` is written by the plain row gather (not with `a_sorted` or `perm`)", op);
+  // live rows per routing block: written by a call that gathers (plain gather), read by any call given it
+  int32_t* block_rows = options != nullptr ? options->block_rows : nullptr;
+  int32_t* block_rows_out = block_rows != nullptr && !a_sorted && (options->perm == nullptr) ? block_rows : nullptr;
   const int32_t* perm = options != nullptr ? options->perm : nullptr;
   const int32_t* g_idx = options != nullptr ? options->g_idx : nullptr;
   IOB_REQUIRE((perm == nullptr) == (g_idx == nullptr), "%s: requires `g_idx` and `perm` together", op);
@@ -2613,11 +2641,13 @@ extern "C" int infiniops_b200_moe_wna16_marlin_gemm_ex(
   } else if (a_dtype == IOB_BF16) {
     GatherRowsKernel<__nv_bfloat16><<<gather_grid, 256, 0, s>>>(
         static_cast<const __nv_bfloat16*>(a), reinterpret_cast<__nv_bfloat16*>(base + plan.gathered_off), sorted_token_ids,
-        num_tokens_past_padded, static_cast<int>(size_k), static_cast<int>(top_k), out_rows, position);
+        num_tokens_past_padded, static_cast<int>(size_k), static_cast<int>(top_k), out_rows, position, block_rows_out,
+        static_cast<int>(moe_block_size));
   } else {
     GatherRowsKernel<__half><<<gather_grid, 256, 0, s>>>(static_cast<const __half*>(a), reinterpret_cast<__half*>(base + plan.gathered_off),
                                                         sorted_token_ids, num_tokens_past_padded,
-                                                        static_cast<int>(size_k), static_cast<int>(top_k), out_rows, position);
+                                                        static_cast<int>(size_k), static_cast<int>(top_k), out_rows, position,
+                                                        block_rows_out, static_cast<int>(moe_block_size));
   }
   if (const int rc = CheckLaunch("moe_wna16_marlin_gemm gather launch")) return rc;
   // 256-row routing blocks whose columns pair up run two blocks of a cluster per 256 x 256 tile
@@ -2637,6 +2667,7 @@ extern "C" int infiniops_b200_moe_wna16_marlin_gemm_ex(
   GemmParams p{};
   p.pair = pair ? 1 : 0;
   p.bits = bits;
+  p.block_rows = block_rows;
   p.wq = reinterpret_cast<const uint32_t*>(b_q_weight);
   p.scales = b_scales;
   p.zeros = reinterpret_cast<const uint32_t*>(b_zeros);

@@ -179,28 +179,32 @@ def single_gpu_layer(x, topk_weights, topk_ids, experts: RoutedExperts, stream=N
         # multiplied by their routing weight) and the final sum picks each token's rows by position,
         # so no GEMM epilogue scatters single rows.  The first GEMM's gather notes the positions.
         position = experts._buf("L_pos", (t, k), torch.int32, dev)
+    # live rows per routing block, noted by the first GEMM's gather: both GEMMs then spend tensor-core
+    # time on a partly filled block in proportion to its rows, not to the block size
+    live = experts._buf("L_rows", (sorted_ids.numel() // block + 1,), torch.int32, dev) if block >= 32 else None
     h = experts._buf("L_h", (size, w.inter), x.dtype, dev)
     if w.interleaved and (2 * w.inter) % 128 == 0:
         # gate and up meet in the epilogue: the [size, 2I] product is never stored
         capi.moe_wna16_marlin_gemm(x, w.w13, None, w.s13, w.z13, sorted_ids, expert_ids, npost, flat_w, block, k,
                                    False, w.qtype, t, 2 * w.inter, w.hidden, h, stream=stream, out_sorted=True,
-                                   fuse_silu=True, route_position=position)
+                                   fuse_silu=True, route_position=position, block_rows=live)
     else:
         g = experts._buf("L_g", (size, 2 * w.inter), x.dtype, dev)
         capi.moe_wna16_marlin_gemm(x, w.w13, None, w.s13, w.z13, sorted_ids, expert_ids, npost, flat_w, block, k,
                                    False, w.qtype, t, 2 * w.inter, w.hidden, g, stream=stream, out_sorted=True,
-                                   route_position=position)
+                                   route_position=position, block_rows=live)
         capi.silu_and_mul(g, h, stream=stream)
     out = experts._buf("L_out", (t, w.hidden), x.dtype, dev)
     if tiles_only:
         y = experts._buf("L_ys", (size, w.hidden), x.dtype, dev)
         capi.moe_wna16_marlin_gemm(h, w.w2, None, w.s2, w.z2, sorted_ids, expert_ids, npost, flat_w, block, 1, True,
-                                   w.qtype, t * k, w.hidden, w.inter, y, stream=stream, a_sorted=True, out_sorted=True)
+                                   w.qtype, t * k, w.hidden, w.inter, y, stream=stream, a_sorted=True, out_sorted=True,
+                                   block_rows=live)
         capi.moe_gather_sum(y, position, out, stream=stream)
         return out
     y = experts._buf("L_y", (t * k, w.hidden), x.dtype, dev)
     capi.moe_wna16_marlin_gemm(h, w.w2, None, w.s2, w.z2, sorted_ids, expert_ids, npost, flat_w, block, 1, True,
-                               w.qtype, t * k, w.hidden, w.inter, y, stream=stream, a_sorted=True)
+                               w.qtype, t * k, w.hidden, w.inter, y, stream=stream, a_sorted=True, block_rows=live)
     capi.moe_sum(y.view(t, k, w.hidden), out, stream=stream)
     return out
 

@@ -319,3 +319,58 @@ def test_sorted_output_with_weights_needs_large_blocks():
     with pytest.raises(capi.Error, match="128- or 256-row"):
         capi.moe_wna16_marlin_gemm(x, w, None, s, None, sorted_ids, expert_ids, npost, torch.ones(tokens, device="cuda"),
                                    block, 1, True, capi.QTYPE_UINT4B8, tokens, n, hidden, out, out_sorted=True)
+
+
+# ---- MMAs and epilogue restricted to the live rows of a routing block ---------------------------------------
+@pytest.mark.parametrize("block,zeros,tokens", ((32, False, 37), (64, True, 150), (128, False, 700), (256, True, 700),
+                                                (256, False, 90)))
+def test_live_row_extent_changes_no_bit(block, zeros, tokens):
+    """With `block_rows` the GEMMs issue their MMAs over a block's live rows (rounded up to 16) instead of
+    the whole block; every live row must come out bit for bit as without it -- scattered and sorted form --
+    and the table itself must hold the number of live rows of every block."""
+    from infiniops_b200 import capi
+
+    experts, top_k, hidden, n = 8, 2, 512, 256
+    qtype = capi.QTYPE_UINT4 if zeros else capi.QTYPE_UINT4B8
+    ids = torch.randint(0, experts, (tokens, top_k), dtype=torch.int32, device="cuda")
+    tw = torch.rand((tokens, top_k), device="cuda").reshape(-1)
+    w, s, z = _random_experts(experts, hidden, n, zeros, 700 + block)
+    rows = tokens * top_k
+    size, blocks = omoe.padded_sizes(rows, experts, block)
+    sorted_ids = torch.empty(size, dtype=torch.int32, device="cuda")
+    expert_ids = torch.empty(blocks, dtype=torch.int32, device="cuda")
+    npost = torch.empty(1, dtype=torch.int32, device="cuda")
+    capi.moe_align_block_size(ids, None, experts, block, sorted_ids, expert_ids, npost)
+    x = torch.randn((tokens, hidden), device="cuda").bfloat16()
+
+    plain = torch.full((rows, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    capi.moe_wna16_marlin_gemm(x, w, None, s, z, sorted_ids, expert_ids, npost, tw, block, top_k, True, qtype, tokens, n,
+                               hidden, plain)
+    live = torch.full((blocks + 1,), -5, dtype=torch.int32, device="cuda")
+    shrunk = torch.full((rows, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    capi.moe_wna16_marlin_gemm(x, w, None, s, z, sorted_ids, expert_ids, npost, tw, block, top_k, True, qtype, tokens, n,
+                               hidden, shrunk, block_rows=live)
+    sorted_plain = torch.zeros((size, n), dtype=torch.bfloat16, device="cuda")
+    capi.moe_wna16_marlin_gemm(x, w, None, s, z, sorted_ids, expert_ids, npost, tw, block, top_k, False, qtype, tokens, n,
+                               hidden, sorted_plain, out_sorted=True)
+    sorted_shrunk = torch.zeros((size, n), dtype=torch.bfloat16, device="cuda")
+    capi.moe_wna16_marlin_gemm(x, w, None, s, z, sorted_ids, expert_ids, npost, tw, block, top_k, False, qtype, tokens, n,
+                               hidden, sorted_shrunk, out_sorted=True, block_rows=live)
+    # a second GEMM reading the sorted rows in place, given the same table
+    w2, s2, z2 = _random_experts(experts, n, hidden, zeros, 701 + block)
+    y_plain = torch.full((rows, hidden), float("nan"), dtype=torch.bfloat16, device="cuda")
+    capi.moe_wna16_marlin_gemm(sorted_plain, w2, None, s2, z2, sorted_ids, expert_ids, npost, tw, block, 1, True, qtype, rows,
+                               hidden, n, y_plain, a_sorted=True)
+    y_shrunk = torch.full((rows, hidden), float("nan"), dtype=torch.bfloat16, device="cuda")
+    capi.moe_wna16_marlin_gemm(sorted_shrunk, w2, None, s2, z2, sorted_ids, expert_ids, npost, tw, block, 1, True, qtype, rows,
+                               hidden, n, y_shrunk, a_sorted=True, block_rows=live)
+    torch.cuda.synchronize()
+    assert capi.scratch_status(capi.scratch("cuda", 0)) == 0
+    total = int(npost.cpu()[0])
+    srt = sorted_ids.cpu().long()[:total].view(-1, block)
+    want_live = (srt < rows).sum(dim=1).to(torch.int32)
+    assert torch.equal(live.cpu()[: total // block], want_live)
+    assert not torch.isnan(shrunk.float()).any() and torch.equal(shrunk, plain)
+    keep = torch.nonzero(sorted_ids[:total].long() < rows).flatten()
+    assert torch.equal(sorted_shrunk[keep], sorted_plain[keep])
+    assert not torch.isnan(y_shrunk.float()).any() and torch.equal(y_shrunk, y_plain)
