@@ -1536,9 +1536,10 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
       };
 
       const bool first_of_block = walk.u - (seg.k_end - seg.k_begin) == u_begin;
-      // partial slot layout: [128 tile columns][kTok tokens], so a thread's tokens are contiguous
+      // partial slot layout: [kTok tokens][128 tile columns] -- a warp's 32 columns of one token are one
+      // 128-byte line, for the stores here and for the loads of the block that sums the tile
       float* my_partial =
-          cur->p.partial + (static_cast<size_t>(2 * blockIdx.x + (first_of_block ? 0 : 1)) * kTileN + n_local) * kTok;
+          cur->p.partial + static_cast<size_t>(2 * blockIdx.x + (first_of_block ? 0 : 1)) * kTileN * kTok + n_local;
       // 16 token columns of this thread's output row, summed over the segment: final values of a
       // whole tile, else this block's partial
       auto finish_chunk = [&](int c, const uint32_t (&r)[16]) {
@@ -1618,9 +1619,7 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < 16; j += 4) {
-            *reinterpret_cast<uint4*>(my_partial + c + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
-          }
+          for (int j = 0; j < 16; ++j) my_partial[(c + j) * kTileN] = __uint_as_float(r[j]);
         }
       };
 
@@ -1774,7 +1773,7 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
             // a block's first segment uses slot 2b, any later one slot 2b + 1
             auto slot_of = [&](int b) -> const float* {
               const bool is_first = RangeStart(b, total_units, grid) >= tile_u0;
-              return cur->p.partial + (static_cast<size_t>(2 * launched_block(b) + (is_first ? 0 : 1)) * kTileN + n_local) * kTok;
+              return cur->p.partial + static_cast<size_t>(2 * launched_block(b) + (is_first ? 0 : 1)) * kTileN * kTok + n_local;
             };
             for (int c = 0; c < m_valid; c += 16) {
               float sum[16];
@@ -1783,23 +1782,18 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
               // two sharers per round: their 8 loads are all in flight together; the additions
               // stay in ascending block order, so the result does not depend on who arrived last
               for (int b = first_block; b <= last_block; b += 2) {
-                float4 v[2][4];
+                float v[2][16];
 #pragma unroll
                 for (int u = 0; u < 2; ++u) {
                   const bool on = b + u <= last_block;
-                  const float4* src = reinterpret_cast<const float4*>(slot_of(on ? b + u : b) + c);
+                  const float* src = slot_of(on ? b + u : b) + c * kTileN;
 #pragma unroll
-                  for (int x = 0; x < 4; ++x) v[u][x] = on ? __ldcg(src + x) : make_float4(0.f, 0.f, 0.f, 0.f);
+                  for (int j = 0; j < 16; ++j) v[u][j] = on ? __ldcg(src + j * kTileN) : 0.0f;
                 }
 #pragma unroll
                 for (int u = 0; u < 2; ++u) {
 #pragma unroll
-                  for (int x = 0; x < 4; ++x) {
-                    sum[4 * x + 0] += v[u][x].x;
-                    sum[4 * x + 1] += v[u][x].y;
-                    sum[4 * x + 2] += v[u][x].z;
-                    sum[4 * x + 3] += v[u][x].w;
-                  }
+                  for (int j = 0; j < 16; ++j) sum[j] += v[u][j];
                 }
               }
 #pragma unroll
