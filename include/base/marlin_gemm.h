@@ -37,10 +37,11 @@ class MarlinGemm : public Operator<MarlinGemm> {
     INFINI_OPS_CHECK(size_m_ > 0 && size_n_ > 0 && size_k_ > 0 && size_k_ % 16 == 0 && size_n_ % 64 == 0,
                      "`MarlinGemm` received unsupported dimensions");
     const bool has_zp = b_zeros.has_value();
-    INFINI_OPS_CHECK((b_type_id_ == qtype::kUint4B8 || b_type_id_ == qtype::kUint4 || b_type_id_ == qtype::kUint8B128) &&
-                         has_zp == (b_type_id_ == qtype::kUint4) && !is_zp_float_,
+    INFINI_OPS_CHECK((b_type_id_ == qtype::kUint4B8 || b_type_id_ == qtype::kUint4 || b_type_id_ == qtype::kUint8B128 ||
+                      b_type_id_ == qtype::kUint8) &&
+                         has_zp == (b_type_id_ == qtype::kUint4 || b_type_id_ == qtype::kUint8) && !is_zp_float_,
                      "`MarlinGemm` received an unsupported quantization configuration");
-    const int64_t pack = b_type_id_ == qtype::kUint8B128 ? 4 : 8;  // weights per 32-bit word
+    const int64_t pack = (b_type_id_ == qtype::kUint8B128 || b_type_id_ == qtype::kUint8) ? 4 : 8;  // weights per 32-bit word
     INFINI_OPS_CHECK(b_q_weight.ndim() == 2 && static_cast<int64_t>(b_q_weight.size(0)) == size_k_ / 16 &&
                          static_cast<int64_t>(b_q_weight.size(1)) == size_n_ * 16 / pack &&
                          b_q_weight.dtype() == DataType::kInt32 && b_q_weight.IsContiguous(),
@@ -56,7 +57,7 @@ class MarlinGemm : public Operator<MarlinGemm> {
     }
     if (b_zeros) {
       INFINI_OPS_CHECK(b_zeros->ndim() == 2 && b_zeros->size(0) == b_scales.size(0) &&
-                           static_cast<int64_t>(b_zeros->size(1)) == size_n_ / 8 &&
+                           static_cast<int64_t>(b_zeros->size(1)) == size_n_ / pack &&
                            b_zeros->dtype() == DataType::kInt32 && b_zeros->IsContiguous(),
                        "`MarlinGemm` received invalid zero points");
     }

@@ -45,6 +45,7 @@ typedef enum {
 #define IOB_QTYPE_UINT4B8 1125899907892224LL /* GPTQ symmetric: w = (q - 8) * s      */
 #define IOB_QTYPE_UINT4 1125899906843648LL   /* AWQ: w = (q - z) * s, z in `b_zeros` */
 #define IOB_QTYPE_UINT8B128 1125899923621888LL /* 8-bit symmetric: w = (q - 128) * s; b_q_weight [.., K/16, 4N] */
+#define IOB_QTYPE_UINT8 1125899906844672LL     /* 8-bit with zero points: w = (q - z) * s; b_zeros [.., G, N/4], byte n % 4 of word n / 4 */
 
 /* Text of the last non-OK status returned on the calling thread. */
 const char* infiniops_b200_last_error(void);

@@ -17,8 +17,9 @@ namespace infini::ops {
 
 namespace impl {
 inline void RequireFourBit(int64_t b_type_id, const char* op) {
-  if (b_type_id != qtype::kUint4B8 && b_type_id != qtype::kUint4 && b_type_id != qtype::kUint8B128) {
-    std::fprintf(stderr, "`%s`: only the weight types uint4b8, uint4 and uint8b128 are implemented in this build\n", op);
+  if (b_type_id != qtype::kUint4B8 && b_type_id != qtype::kUint4 && b_type_id != qtype::kUint8B128 &&
+      b_type_id != qtype::kUint8) {
+    std::fprintf(stderr, "`%s`: only the weight types uint4b8, uint4, uint8b128 and uint8 are implemented in this build\n", op);
     std::fflush(stderr);
     std::abort();
   }

@@ -568,22 +568,23 @@ __device__ __forceinline__ uint32_t CentreHigh2(uint32_t word, uint32_t minus_64
 // bytes 1 and 3 (k = 2t + 8, 2t + 9) -- as (q - 128) * scale, both halves in T.  `scale16` is the raw
 // 16-bit scale.
 template <typename T>
-__device__ __forceinline__ uint32_t Dequant8(uint32_t word, int odd, uint32_t scale16);
+__device__ __forceinline__ uint32_t Dequant8(uint32_t word, int odd, uint32_t scale16, uint32_t zero);
 template <>
-__device__ __forceinline__ uint32_t Dequant8<__half>(uint32_t word, int odd, uint32_t scale16) {
-  // 0x6400 | q is the float16 1024 + q; minus 1152 = q - 128, exact
+__device__ __forceinline__ uint32_t Dequant8<__half>(uint32_t word, int odd, uint32_t scale16, uint32_t zero) {
+  // 0x6400 | q is the float16 1024 + q; minus (1024 + zero) = q - zero, exact
   const uint32_t biased = __byte_perm(word, 0x64646464u, odd ? 0x4341u : 0x4240u);
-  const uint32_t centre = 0x64806480u, scale2 = scale16 * 0x10001u;
+  const uint32_t centre = (0x6400u | zero) * 0x10001u, scale2 = scale16 * 0x10001u;
   const __half2 c = __hsub2(*reinterpret_cast<const __half2*>(&biased), *reinterpret_cast<const __half2*>(&centre));
   const __half2 r = __hmul2(c, *reinterpret_cast<const __half2*>(&scale2));
   return *reinterpret_cast<const uint32_t*>(&r);
 }
 template <>
-__device__ __forceinline__ uint32_t Dequant8<__nv_bfloat16>(uint32_t word, int odd, uint32_t scale16) {
+__device__ __forceinline__ uint32_t Dequant8<__nv_bfloat16>(uint32_t word, int odd, uint32_t scale16, uint32_t zero) {
   // eight significant bits do not fit the bfloat16 mantissa trick: go through float32
   // (0x4B000000 | q = 8388608 + q), centre and scale there, round once to bfloat16
-  const float lo = __uint_as_float(__byte_perm(word, 0x4B000000u, odd ? 0x7541u : 0x7540u)) - 8388736.0f;
-  const float hi = __uint_as_float(__byte_perm(word, 0x4B000000u, odd ? 0x7543u : 0x7542u)) - 8388736.0f;
+  const float centre = __uint_as_float(0x4B000000u | zero);
+  const float lo = __uint_as_float(__byte_perm(word, 0x4B000000u, odd ? 0x7541u : 0x7540u)) - centre;
+  const float hi = __uint_as_float(__byte_perm(word, 0x4B000000u, odd ? 0x7543u : 0x7542u)) - centre;
   const float s = __uint_as_float(scale16 << 16);
   const __nv_bfloat162 r = __floats2bfloat162_rn(lo * s, hi * s);
   return *reinterpret_cast<const uint32_t*>(&r);
@@ -714,8 +715,8 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
   const Problem* cur = probs;
   int* const status_word = probs->p.status;  // one status header per launch
   using Sh = Shared<kTok, kSets, kPair, kBits>;
-  static_assert(kBits == 4 || (kBits == 8 && !kPair && !kBatch && !kLate && !kZeros && kTok <= 128),
-                "8-bit weights: unpaired tiles with scaled weights, no zero points");
+  static_assert(kBits == 4 || (kBits == 8 && !kPair && !kBatch && !kLate && kTok <= 128),
+                "8-bit weights: unpaired tiles with scaled weights");
   constexpr int kWeightBytes = kBits == 8 ? 16384 : 8192;  // packed weights of a stage (128 columns x 128 k)
   constexpr int kStages = Sh::kStages;
   constexpr int kAcc = Sh::kAcc;
@@ -1253,6 +1254,17 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
       // lane / 4 of words x, y, z, w = this thread's columns +0, +8, +16, +24), so that the
       // conversion code below is the same for both.
       auto load_zeros = [&](uint32_t row) -> uint4 {
+        if constexpr (kBits == 8) {
+          // 8-bit zero points: one byte per column ([G, N/4] words, byte n % 4 of word n / 4); the four
+          // bytes of this thread's columns +0, +8, +16, +24 packed into x (plain layout only)
+          const unsigned char* zrow = reinterpret_cast<const unsigned char*>(cur->p.zeros) +
+                                      (static_cast<size_t>(c.expert) * cur->p.groups + row) * static_cast<uint32_t>(gmap.n) +
+                                      tile_of(c.seg.n_tile) * kTileN + col;
+          uint32_t packed = 0;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) packed |= static_cast<uint32_t>(__ldg(zrow + 8 * j)) << (8 * j);
+          return make_uint4(packed, 0, 0, 0);
+        }
         if (zword == nullptr) return LdGlobalV4Here(zbase + static_cast<size_t>(row) * static_cast<uint32_t>(gmap.n / 32));
         uint32_t w;
         asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(w) : "l"(zword + static_cast<size_t>(row) * static_cast<uint32_t>(gmap.n / 8)));
@@ -1335,14 +1347,21 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             const uint32_t pair = row ? gr.sc[1][h] : gr.sc[0][h];
+            // zero points of columns c0 and c0 + 8 (128 for the symmetric type)
+            uint32_t z0 = 128, z1 = 128;
+            if constexpr (kZeros) {
+              const uint32_t zp = row ? gr.zp[1].x : gr.zp[0].x;
+              z0 = (zp >> (16 * h)) & 0xFFu;
+              z1 = (zp >> (16 * h + 8)) & 0xFFu;
+            }
             uint32_t regs[16];
 #pragma unroll
             for (int kt = 0; kt < 4; ++kt) {
               const uint32_t w0 = w8[kt][2 * h], w1 = w8[kt][2 * h + 1];    // columns c0 and c0 + 8
-              regs[4 * kt + 0] = Dequant8<T>(w0, 0, pair & 0xFFFFu);        // k pair t
-              regs[4 * kt + 1] = Dequant8<T>(w1, 0, pair >> 16);
-              regs[4 * kt + 2] = Dequant8<T>(w0, 1, pair & 0xFFFFu);        // k pair t + 4
-              regs[4 * kt + 3] = Dequant8<T>(w1, 1, pair >> 16);
+              regs[4 * kt + 0] = Dequant8<T>(w0, 0, pair & 0xFFFFu, z0);    // k pair t
+              regs[4 * kt + 1] = Dequant8<T>(w1, 0, pair >> 16, z1);
+              regs[4 * kt + 2] = Dequant8<T>(w0, 1, pair & 0xFFFFu, z0);    // k pair t + 4
+              regs[4 * kt + 3] = Dequant8<T>(w1, 1, pair >> 16, z1);
             }
             if (half == 0 && h == 0) before_first_store();
             if (alive) {
@@ -2237,7 +2256,7 @@ int LaunchKernel(const CUtensorMap& map, const CUtensorMap& w_map, const CUtenso
                  cudaStream_t stream) {
   // silu_and_mul in the epilogue is a kernel variant of its own (routed form only), so that the
   // kernels without it carry none of its code
-  if constexpr (kEpi == 0 && !kZeros && kTok <= 128) {
+  if constexpr (kEpi == 0 && kTok <= 128) {
     if (p.bits == 8) return LaunchVariant<T, kTok, kZeros, kMoe, false, false, 0, 8>(map, w_map, c_map, p, grid, stream);
   }
   if constexpr (kMoe && kEpi == 0) {
@@ -2284,7 +2303,7 @@ int Dispatch(int a_dtype, bool zeros, int tok, const CUtensorMap& map, const CUt
                : DispatchTok<__half, false, kMoe>(tok, map, w_map, c_map, p, grid, stream);
 }
 
-int BitsOf(int64_t b_type_id) { return b_type_id == IOB_QTYPE_UINT8B128 ? 8 : 4; }
+int BitsOf(int64_t b_type_id) { return b_type_id == IOB_QTYPE_UINT8B128 || b_type_id == IOB_QTYPE_UINT8 ? 8 : 4; }
 
 int CheckProblem(const char* op, const void* a, int a_dtype, const void* wq, const void* scales, const void* zeros,
                  int64_t b_type_id, int64_t m, int64_t n, int64_t k, int64_t groups, const void* out) {
@@ -2292,11 +2311,12 @@ int CheckProblem(const char* op, const void* a, int a_dtype, const void* wq, con
   IOB_REQUIRE(a_dtype == IOB_F16 || a_dtype == IOB_BF16, "%s: requires float16 or bfloat16 `a`", op);
   IOB_REQUIRE(m > 0 && n > 0 && k > 0 && k % 16 == 0 && n % 64 == 0, "%s: received unsupported dimensions", op);
   IOB_REQUIRE(m <= INT32_MAX && n <= INT32_MAX && k <= INT32_MAX, "%s: dimensions exceed int32", op);
-  if (b_type_id != IOB_QTYPE_UINT4B8 && b_type_id != IOB_QTYPE_UINT4 && b_type_id != IOB_QTYPE_UINT8B128) {
-    return Fail(IOB_UNSUPPORTED, "%s: only the weight types uint4b8, uint4 and uint8b128 are implemented", op);
+  if (b_type_id != IOB_QTYPE_UINT4B8 && b_type_id != IOB_QTYPE_UINT4 && b_type_id != IOB_QTYPE_UINT8B128 &&
+      b_type_id != IOB_QTYPE_UINT8) {
+    return Fail(IOB_UNSUPPORTED, "%s: only the weight types uint4b8, uint4, uint8b128 and uint8 are implemented", op);
   }
-  IOB_REQUIRE((zeros != nullptr) == (b_type_id == IOB_QTYPE_UINT4),
-              "%s: zero points are required for uint4 and not accepted for uint4b8 / uint8b128", op);
+  IOB_REQUIRE((zeros != nullptr) == (b_type_id == IOB_QTYPE_UINT4 || b_type_id == IOB_QTYPE_UINT8),
+              "%s: zero points are required for uint4 / uint8 and not accepted for uint4b8 / uint8b128", op);
   IOB_REQUIRE(groups > 0 && k % groups == 0, "%s: `size_k` must be a multiple of the number of scale groups", op);
   if (k % kBlockK != 0 || ((k / groups) != 64 && (k / groups) % kBlockK != 0)) {
     return Fail(IOB_UNSUPPORTED, "%s: needs `size_k` to be a multiple of 128 and the group size 64 or a multiple of 128", op);
@@ -2417,6 +2437,8 @@ extern "C" int infiniops_b200_marlin_gemm_placed(const iob_gemm_problem* problem
     return rc;
   }
   const int bits = BitsOf(b_type_id);
+  IOB_REQUIRE(!(bits == 8 && g.b_zeros != nullptr && g.scale_layout != 0),
+              "%s: 8-bit zero points are read in the plain layout only", op);
   int tok = DenseTokenTile(g.size_m, g.size_n, g.size_k / (g.num_groups > 0 ? g.num_groups : 1));
   if (bits == 8 && tok > 128) tok = 128;  // 8-bit weights: no 256-row tiles (the stage ring would not fit)
   const int64_t n_tiles = (g.size_n + kTileN - 1) / kTileN, m_tiles = (g.size_m + tok - 1) / tok;
@@ -2654,6 +2676,8 @@ extern "C" int infiniops_b200_moe_wna16_marlin_gemm_ex(
   }
   CUtensorMap w_map;
   const int bits = BitsOf(b_type_id);
+  IOB_REQUIRE(!(bits == 8 && b_zeros != nullptr && options != nullptr && options->scale_layout != 0),
+              "%s: 8-bit zero points are read in the plain layout only", op);
   IOB_REQUIRE(bits == 4 || (moe_block_size <= 128 && (options == nullptr || !options->fuse_silu) &&
                             !(options != nullptr && options->out_sorted && mul_topk_weights)),
               "%s: 8-bit weights take routing blocks up to 128 rows and the plain epilogue", op);

@@ -118,7 +118,7 @@ def test_rejects_unsupported():
     s = torch.zeros((1, 64), dtype=torch.float16, device="cuda")
     out = torch.zeros((4, 64), dtype=torch.float16, device="cuda")
     with pytest.raises(capi.Error, match="only the weight types"):
-        capi.marlin_gemm(a, w, None, s, None, 1125899906844672, 4, 64, 128, out)   # uint8 with zero points
+        capi.marlin_gemm(a, w, None, s, None, 1125899906908928, 4, 64, 128, out)   # int4 (signed)
     with pytest.raises(capi.Error, match="zero points are required"):
         capi.marlin_gemm(a, w, None, s, None, capi.QTYPE_UINT4, 4, 64, 128, out)
 

@@ -16,6 +16,13 @@ from tests.helpers import rel_max_err
 pytestmark = pytest.mark.gpu
 TOL = 1e-2
 UINT8B128 = 1125899923621888
+UINT8 = 1125899906844672
+
+
+def _pack_zeros8(zeros: np.ndarray) -> np.ndarray:
+    """[G, N] bytes -> int32 [G, N/4]: byte n % 4 of word n / 4 (little endian), the 8-bit form of the
+    reference's zero-point packing (pack factor 4, src/base/moe_wna16_marlin_gemm.h:231-240)."""
+    return np.ascontiguousarray(zeros.astype(np.uint8)).view(np.int32)
 
 
 def _weights(k, n, group, dtype, seed):
@@ -132,3 +139,53 @@ def test_8bit_weights_through_the_operator_api():
                            tokens, n, k, True, False, True, False, dense_out, stream=stream)
     torch.cuda.synchronize()
     assert rel_max_err(dense_out, x.float() @ oq.dequantize(qs[0], ss[0], None, 8)) <= TOL
+
+
+@pytest.mark.parametrize("dtype", (torch.bfloat16, torch.float16))
+@pytest.mark.parametrize("m,k,n,group", ((3, 512, 256, 128), (40, 1024, 320, 128), (100, 512, 128, 64)))
+def test_dense_gemm_with_8bit_weights_and_zero_points(dtype, m, k, n, group):
+    from infiniops_b200 import capi
+
+    q, scales, marlin = _weights(k, n, group, dtype, 8300 + m)
+    zeros = torch.randint(0, 256, (k // group, n), generator=torch.Generator().manual_seed(m + 1), dtype=torch.int32) \
+        .numpy().astype(np.uint8)
+    a = torch.randn((m, k), generator=torch.Generator().manual_seed(m)).to(dtype)
+    out = torch.full((m, n), float("nan"), dtype=dtype, device="cuda")
+    capi.marlin_gemm(a.cuda(), marlin, None, scales.cuda(), torch.from_numpy(_pack_zeros8(zeros)).cuda(), UINT8, m, n, k, out)
+    torch.cuda.synchronize()
+    assert capi.scratch_status(capi.scratch("cuda", 0)) == 0
+    ref = a.float() @ oq.dequantize(q, scales, zeros, 8)
+    assert not torch.isnan(out.float()).any()
+    assert rel_max_err(out, ref) <= TOL
+
+
+def test_routed_gemm_with_8bit_weights_and_zero_points():
+    from infiniops_b200 import capi
+
+    tokens, experts, top_k, k, n, block, dtype = 70, 4, 2, 512, 256, 32, torch.bfloat16
+    qs, ss, ws = zip(*[_weights(k, n, 128, dtype, 8400 + e) for e in range(experts)])
+    gen = torch.Generator().manual_seed(12)
+    zs = [torch.randint(0, 256, (k // 128, n), generator=gen, dtype=torch.int32).numpy().astype(np.uint8) for _ in range(experts)]
+    words, scales = torch.stack(ws), torch.stack(ss).cuda()
+    zp = torch.stack([torch.from_numpy(_pack_zeros8(z)) for z in zs]).cuda()
+    ids = torch.randint(0, experts, (tokens, top_k), generator=gen, dtype=torch.int32)
+    x = torch.randn((tokens, k), generator=gen).to(dtype)
+    tw = torch.rand(tokens * top_k, generator=gen)
+    rows = tokens * top_k
+    size, blocks = omoe.padded_sizes(rows, experts, block)
+    sorted_ids = torch.empty(size, dtype=torch.int32, device="cuda")
+    expert_ids = torch.empty(blocks, dtype=torch.int32, device="cuda")
+    npost = torch.empty(1, dtype=torch.int32, device="cuda")
+    capi.moe_align_block_size(ids.cuda(), None, experts, block, sorted_ids, expert_ids, npost)
+    out = torch.full((rows, n), float("nan"), dtype=dtype, device="cuda")
+    capi.moe_wna16_marlin_gemm(x.cuda(), words, None, scales, zp, sorted_ids, expert_ids, npost, tw.cuda(), block, top_k,
+                               True, UINT8, tokens, n, k, out)
+    torch.cuda.synchronize()
+    assert capi.scratch_status(capi.scratch("cuda", 0)) == 0
+    ref = torch.zeros((rows, n))
+    for t in range(tokens):
+        for j in range(top_k):
+            e = int(ids[t, j])
+            ref[t * top_k + j] = (x[t].float() @ oq.dequantize(qs[e], ss[e], zs[e], 8)) * tw[t * top_k + j]
+    assert not torch.isnan(out.float()).any()
+    assert rel_max_err(out, ref) <= TOL
