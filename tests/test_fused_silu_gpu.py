@@ -206,7 +206,7 @@ def test_softmax_router_and_sort_in_one_call(tokens, experts, top_k, block, dtyp
         assert torch.equal(a, b)
     # and the sort itself against the oracle
     rs, re, rn = omoe.moe_align_block_size(i1.cpu().numpy(), None, experts, block)
-    assert np.array_equal(s1.cpu().numpy(), rs) and np.array_equal(e1.cpu().numpy(), re) and int(n1.cpu()[0]) == int(rn)
+    assert np.array_equal(s1.cpu().numpy(), rs) and np.array_equal(e1.cpu().numpy(), re) and int(n1.cpu()[0]) == int(rn[0])
 
 
 @pytest.mark.parametrize("tokens,block,dtype", ((16, 16, torch.float32), (128, 16, torch.float32), (64, 32, torch.bfloat16),

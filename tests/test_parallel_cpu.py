@@ -137,7 +137,7 @@ def test_dispatch_with_an_idle_rank():
     _spawn(_all_to_one_rank)
 
 
-def _late_rank(rank, result):
+def _late_rank(rank, result_path):
     """Rank 1 never enters the collective (it sits out the step on the host, as a crashed or stuck
     rank would); rank 0 must get an exception at its deadline instead of blocking, and a later
     collective that both ranks do enter -- on a fresh group -- must still work."""
@@ -145,8 +145,11 @@ def _late_rank(rank, result):
 
     from infiniops_b200 import parallel
 
+    import json
+
     x = torch.full((3, 4), float(rank))
     if rank == 0:
+        result = {}
         t0 = time.monotonic()
         try:
             parallel.gather_columns(x, deadline_s=0.5)
@@ -155,6 +158,8 @@ def _late_rank(rank, result):
             result["outcome"] = "timeout"
             result["message"] = str(e)
         result["seconds"] = time.monotonic() - t0
+        with open(result_path, "w") as f:
+            json.dump(result, f)
     else:
         time.sleep(1.5)   # does not join
     # the ranks learn of the failure on the host (here: simply by both getting past the step) and
@@ -164,9 +169,11 @@ def _late_rank(rank, result):
     assert torch.equal(got, torch.cat([torch.zeros(3, 4), torch.ones(3, 4)], dim=1))
 
 
-def test_collective_gives_up_at_the_host_deadline():
-    manager = mp.Manager()
-    result = manager.dict()
-    _spawn(_late_rank, result)
-    assert result["outcome"] == "timeout", dict(result)
+def test_collective_gives_up_at_the_host_deadline(tmp_path):
+    import json
+
+    path = tmp_path / "rank0.json"
+    _spawn(_late_rank, str(path))
+    result = json.loads(path.read_text())
+    assert result["outcome"] == "timeout", result
     assert "gather_columns" in result["message"] and 0.4 < result["seconds"] < 1.4
