@@ -674,7 +674,8 @@ def moe_layer_time(d, cfg, tokens, steps, warmup, block=64, fuse=None):
     fused = False
     block_arg = block
     if block == 0:
-        block = moe_layer.routing_block(t_local * d.world * cfg["top_k"] // d.world, weights.num_experts)
+        block = moe_layer.routing_block(t_local * d.world * cfg["top_k"] // d.world, weights.num_experts,
+                                        cfg["hidden"] * cfg["inter"])
         # (silu_and_mul inside the first GEMM's epilogue -- `--moe-fuse silu` -- is not part of this arm:
         # it measured 2-4 % slower than the separate pass at every size once all GEMM stores are tiles)
     if fuse is not None:

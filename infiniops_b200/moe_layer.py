@@ -93,13 +93,19 @@ class RoutedExperts:
         return out
 
 
-def routing_block(routes: int, num_experts: int) -> int:
-    """Rows per routing block for a layer with `routes` routed rows over `num_experts` experts.  The
-    reference's operators take 8..64; the sort and the GEMMs of this library also take 128 and 256,
-    and the GEMM converts each weight once per block of rows -- so with many rows per expert larger
-    blocks do a quarter of the conversion work (and 256-row blocks run on paired thread blocks).
-    The padding (at most block - 1 rows per expert) must stay small against the rows themselves."""
+def routing_block(routes: int, num_experts: int, expert_elems: int | None = None) -> int:
+    """Rows per routing block for a layer with `routes` routed rows over `num_experts` experts
+    (`expert_elems`: hidden x intermediate size of one expert, if known).  The reference's operators
+    take 8..64; the sort and the GEMMs of this library also take 128 and 256, and the GEMM converts
+    each weight once per block of rows -- so with many rows per expert larger blocks do a quarter of
+    the conversion work (and 256-row blocks run on paired thread blocks).  The padding (at most
+    block - 1 rows per expert) must stay small against the rows themselves."""
     per_expert = routes / max(1, num_experts)
+    # Small experts (DeepSeek shape: 7168 x 2048 against Mixtral's 4096 x 14336) have short tiles, whose
+    # fixed cost a larger block amortises: their best block sits one step higher at every point measured
+    # below 640 rows per expert (T = 512: 64 rows beat 32 by 7 %, T = 1024: 128 beat 64 by 10 %).
+    if expert_elems is not None and expert_elems < (32 << 20) and per_expert < 320:
+        per_expert *= 2
     # Measured on a B200 with Mixtral- and DeepSeek-shaped layers.  With 128- and 256-row blocks both
     # GEMMs store tiles and each weight is converted once per block of rows: 128-row blocks beat
     # 64-row ones from about 64 rows per expert on (DeepSeek shape +25 % at 64 rows per expert, +47 %
