@@ -41,3 +41,45 @@ def test_argument_validation_without_gpu():
     assert rc == 1 and b"at least two experts per group" in lib.infiniops_b200_last_error()
     rc = lib.infiniops_b200_moe_align_block_size(None, None, 0, 2000, 4, None, 0, None, 0, None, None, 0, None)
     assert rc == 1 and b"[1, 1023]" in lib.infiniops_b200_last_error()
+
+
+def test_ctypes_structs_match_the_header(tmp_path):
+    """Every struct of the C ABI as a C compiler lays it out (size and field offsets) against its ctypes
+    mirror in `capi`: a field added on one side only would otherwise shift every later argument silently."""
+    import subprocess
+
+    from infiniops_b200 import capi
+
+    mirrors = {
+        "iob_gemm_problem": (capi.GemmProblem, ("a", "b_q_weight", "b_bias", "b_scales", "b_zeros", "out", "size_m", "size_n",
+                                                "size_k", "num_groups", "out_ld", "out_col0", "n_peers", "peer_out",
+                                                "scale_layout")),
+        "iob_peer_signal": (capi.PeerSignal, ("done_counter", "epoch", "n_peers", "peer_flags", "flag_slot")),
+        "iob_routed_options": (capi.RoutedOptions, ("scale_layout", "a_sorted", "out_sorted", "fuse_silu", "g_idx", "perm",
+                                                    "route_position", "block_rows", "row_dest", "dest_base", "n_dest",
+                                                    "signal")),
+        "iob_ep_context": (capi.EpContext, ("world", "rank", "top_k", "hidden", "inter", "experts_per_rank", "capacity",
+                                            "moe_block_size", "a_dtype", "b_type_id", "arena", "flags", "ctrl")),
+        "iob_expert_weights": (capi.ExpertWeightsC, ("w13", "s13", "z13", "groups13", "w2", "s2", "z2", "groups2",
+                                                     "w13_interleaved")),
+        "iob_peer_copy": (capi.PeerCopy, ("src", "dst", "rows", "row_bytes", "pitch_bytes")),
+    }
+    lines = ['#include <stddef.h>', '#include <stdio.h>', '#include "infiniops_b200.h"', "int main(void) {"]
+    for name, (_, fields) in mirrors.items():
+        lines.append(f'  printf("{name} %zu", sizeof({name}));')
+        for f in fields:
+            lines.append(f'  printf(" %zu", offsetof({name}, {f}));')
+        lines.append('  printf("\\n");')
+    lines += ["  return 0;", "}"]
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run(["gcc", "-I", str(ROOT / "include"), str(src), "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.strip().splitlines()
+    for line in out:
+        name, size, *offsets = line.split()
+        mirror, fields = mirrors[name]
+        assert ctypes.sizeof(mirror) == int(size), f"{name}: size {ctypes.sizeof(mirror)} != {size}"
+        assert [f for f, _ in mirror._fields_] == list(fields), f"{name}: field list differs"
+        for f, off in zip(fields, offsets):
+            assert getattr(mirror, f).offset == int(off), f"{name}.{f}: offset {getattr(mirror, f).offset} != {off}"

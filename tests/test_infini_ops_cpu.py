@@ -90,3 +90,23 @@ def test_validation_aborts_with_the_reference_message(ops, message):
     result = subprocess.run([sys.executable, "-c", script], capture_output=True, text=True)
     assert result.returncode != 0
     assert message in result.stderr, result.stderr[-400:]
+
+
+def test_routing_block_rule_and_gate_up_interleave():
+    """Host-side helpers of the MoE layer: the routing block chosen from the rows per expert, and the
+    column order for the fused silu epilogue."""
+    from infiniops_b200 import moe_layer
+
+    mixtral, deepseek = 4096 * 14336, 7168 * 2048
+    picks = [moe_layer.routing_block(t * 2, 8, mixtral) for t in (1, 16, 64, 128, 256, 1024, 4096)]
+    assert picks == [16, 16, 32, 64, 128, 128, 256]
+    picks = [moe_layer.routing_block(t * 8, 256, deepseek) for t in (16, 64, 256, 512, 1024, 8192)]
+    assert picks == [16, 16, 32, 64, 128, 128]
+    assert moe_layer.routing_block(0, 8) == 16 and moe_layer.routing_block(10**6, 1) == 256
+
+    idx = moe_layer.gate_up_interleave(64)
+    assert sorted(idx.tolist()) == list(range(128))
+    assert idx[:16].tolist() == list(range(16)) and idx[16:32].tolist() == list(range(64, 80))
+    assert idx[32:48].tolist() == list(range(16, 32))
+    with pytest.raises(ValueError):
+        moe_layer.gate_up_interleave(40)
