@@ -63,8 +63,15 @@ class MarlinGemm : public Operator<MarlinGemm> {
     }
     INFINI_OPS_CHECK(!a_scales && !global_scale, "`MarlinGemm` does not take activation or global scales for 16-bit `a`");
     INFINI_OPS_CHECK(g_idx.has_value() == perm.has_value(), "`MarlinGemm` requires `g_idx` and `perm` together");
-    INFINI_OPS_CHECK(!g_idx || (g_idx->numel() == 0 && perm->numel() == 0),
-                     "`MarlinGemm` act-order (`g_idx` / `perm`) is not implemented");
+    if (g_idx && (g_idx->numel() != 0 || perm->numel() != 0)) {
+      // activation order: one int32 entry per weight row
+      for (const auto* t : {&*g_idx, &*perm}) {
+        INFINI_OPS_CHECK(t->ndim() == 1 && static_cast<int64_t>(t->size(0)) == size_k_ && t->dtype() == DataType::kInt32 &&
+                             t->IsContiguous() && SameDevice(*t, a),
+                         "`MarlinGemm` requires contiguous int32 `g_idx` and `perm` of `size_k` entries");
+      }
+      INFINI_OPS_CHECK(b_scales.size(0) > 1, "`MarlinGemm` act-order needs grouped scales");
+    }
     INFINI_OPS_CHECK(workspace.ndim() == 1 && workspace.dtype() == DataType::kInt32 && workspace.IsContiguous(),
                      "`MarlinGemm` requires an int32 workspace");
     INFINI_OPS_CHECK(out.shape() == Tensor::Shape({static_cast<Tensor::Size>(size_m_), static_cast<Tensor::Size>(size_n_)}) &&

@@ -266,6 +266,8 @@ int infiniops_b200_gemm_scratch_prepare(void* scratch, size_t scratch_bytes, voi
 /* Bytes of scratch the dense GEMM needs for an [M, K] x [K, N] problem on the current
  * device (partial sums of K-split tiles and their arrival counters). */
 size_t infiniops_b200_marlin_gemm_scratch_bytes(int64_t size_m, int64_t size_n, int64_t size_k);
+/* The same with room for the column-permuted copy of `a` that a problem with `g_idx` / `perm` makes. */
+size_t infiniops_b200_marlin_gemm_act_order_scratch_bytes(int64_t size_m, int64_t size_n, int64_t size_k);
 
 /* C[M, N] = A[M, K] * dequant(W)[K, N] (+ bias[N]), fp32 accumulation, C in A's type.
  * a: [M, K] F16/BF16 row-major.  b_q_weight: Marlin layout int32 [K/16, 2N] as produced by
@@ -308,6 +310,14 @@ typedef struct {
   int n_peers;
   void* peer_out[IOB_MAX_PEERS];
   int scale_layout; /* 0 = plain scales / zero points, 1 = vLLM Marlin layouts (see iob_routed_options) */
+  /* Activation order (both or neither; int32 [size_k]): `perm` is the row order the weights were
+   * repacked with (gptq_marlin_repack's `perm`), the GEMM reads activation column perm[k] against
+   * weight row k; `g_idx[k]` must be the group of row k in that order (k / group_size), any other
+   * table is reported as code 9 in the scratch status header.  Needs
+   * infiniops_b200_marlin_gemm_act_order_scratch_bytes of scratch (a permuted copy of `a`); not
+   * accepted by the batch entry. */
+  const int32_t* g_idx;
+  const int32_t* perm;
 } iob_gemm_problem;
 
 /* Completion signal of a launch towards the other GPUs.  When the last thread block of the launch

@@ -32,7 +32,10 @@ class Operator<MarlinGemm, Device::Type::kNvidia, 0> : public MarlinGemm {
   using MarlinGemm::MarlinGemm;
 
   std::size_t workspace_size_in_bytes() const override {
-    return infiniops_b200_marlin_gemm_scratch_bytes(size_m_, size_n_, size_k_);
+    // (activation order keeps a column-permuted copy of `a` in the scratch as well)
+    const auto& perm = optionals_[5];
+    return perm && perm->numel() != 0 ? infiniops_b200_marlin_gemm_act_order_scratch_bytes(size_m_, size_n_, size_k_)
+                                      : infiniops_b200_marlin_gemm_scratch_bytes(size_m_, size_n_, size_k_);
   }
 
   void operator()(const Tensor a, const Tensor b_q_weight, std::optional<Tensor> b_bias, const Tensor b_scales,
@@ -60,6 +63,10 @@ class Operator<MarlinGemm, Device::Type::kNvidia, 0> : public MarlinGemm {
     problem.size_k = size_k;
     problem.num_groups = static_cast<int64_t>(b_scales.size(0));
     problem.scale_layout = scale_layout();
+    if (perm && perm->numel() != 0) {
+      problem.g_idx = static_cast<const int32_t*>(g_idx->data());
+      problem.perm = static_cast<const int32_t*>(perm->data());
+    }
     impl::Require(infiniops_b200_marlin_gemm_placed(&problem, impl::TypeCode(a.dtype()), b_type_id, nullptr, scratch,
                                                     scratch_bytes, stream_),
                   kName);

@@ -45,6 +45,7 @@ PROTOTYPES = {
                                       _i64, _i64, _vp, _vp]),
     "infiniops_b200_scratch_status": (_int, [_vp, _vp]),
     "infiniops_b200_marlin_gemm_scratch_bytes": (_sz, [_i64, _i64, _i64]),
+    "infiniops_b200_marlin_gemm_act_order_scratch_bytes": (_sz, [_i64, _i64, _i64]),
     "infiniops_b200_marlin_gemm": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _vp, _vp,
                                           _sz, _vp]),
     "infiniops_b200_marlin_gemm_static_scratch": (_int, [_vp, _int, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64,
@@ -63,7 +64,7 @@ class GemmProblem(ctypes.Structure):
     _fields_ = [("a", _vp), ("b_q_weight", _vp), ("b_bias", _vp), ("b_scales", _vp), ("b_zeros", _vp), ("out", _vp),
                 ("size_m", _i64), ("size_n", _i64), ("size_k", _i64), ("num_groups", _i64),
                 ("out_ld", _i64), ("out_col0", _i64), ("n_peers", _int), ("peer_out", _vp * MAX_PEERS),
-                ("scale_layout", _int)]
+                ("scale_layout", _int), ("g_idx", _vp), ("perm", _vp)]
 
 
 class PeerSignal(ctypes.Structure):
@@ -299,12 +300,24 @@ def scratch_status(buf, stream=None) -> int:
 
 
 def marlin_gemm(a, b_q_weight, b_bias, b_scales, b_zeros, b_type_id, size_m, size_n, size_k, out, stream=None,
-                scratch_buf=None):
-    need = lib().infiniops_b200_marlin_gemm_scratch_bytes(size_m, size_n, size_k)
+                scratch_buf=None, g_idx=None, perm=None):
+    """`g_idx` / `perm` (int32 [size_k], both or neither): activation order."""
+    if perm is None and g_idx is None:
+        need = lib().infiniops_b200_marlin_gemm_scratch_bytes(size_m, size_n, size_k)
+        buf = scratch_buf if scratch_buf is not None else scratch(a.device, need)
+        _check(lib().infiniops_b200_marlin_gemm(_ptr(a), _DTYPE[a.dtype], _ptr(b_q_weight), _ptr(b_bias),
+                                                _ptr(b_scales), _ptr(b_zeros), b_type_id, size_m, size_n, size_k,
+                                                b_scales.shape[-2], _ptr(out), _ptr(buf), buf.numel(), _stream(stream)))
+        return
+    need = lib().infiniops_b200_marlin_gemm_act_order_scratch_bytes(size_m, size_n, size_k)
     buf = scratch_buf if scratch_buf is not None else scratch(a.device, need)
-    _check(lib().infiniops_b200_marlin_gemm(_ptr(a), _DTYPE[a.dtype], _ptr(b_q_weight), _ptr(b_bias), _ptr(b_scales),
-                                            _ptr(b_zeros), b_type_id, size_m, size_n, size_k, b_scales.shape[-2],
-                                            _ptr(out), _ptr(buf), buf.numel(), _stream(stream)))
+    problem = GemmProblem()
+    problem.a, problem.b_q_weight, problem.b_bias = a.data_ptr(), b_q_weight.data_ptr(), _ptr(b_bias)
+    problem.b_scales, problem.b_zeros, problem.out = b_scales.data_ptr(), _ptr(b_zeros), out.data_ptr()
+    problem.size_m, problem.size_n, problem.size_k, problem.num_groups = size_m, size_n, size_k, b_scales.shape[-2]
+    problem.g_idx, problem.perm = _ptr(g_idx), _ptr(perm)
+    _check(lib().infiniops_b200_marlin_gemm_placed(ctypes.byref(problem), _DTYPE[a.dtype], b_type_id, None, _ptr(buf),
+                                                   buf.numel(), _stream(stream)))
 
 
 def marlin_gemm_static_scratch(a, b_q_weight, b_bias, b_scales, b_zeros, b_type_id, size_m, size_n, size_k, out,

@@ -1978,6 +1978,29 @@ __global__ void GatherPermutedRowsKernel(const T* __restrict__ a, T* __restrict_
   }
 }
 
+// Act-order for the dense GEMM: permuted[row][k] = a[row][perm[k]], one table for the whole matrix;
+// block 0 checks `g_idx` as above (status header: code kErrGIdx, detail -1).
+template <typename T>
+__global__ void PermuteColumnsKernel(const T* __restrict__ a, T* __restrict__ permuted, const int32_t* __restrict__ perm,
+                                     const int32_t* __restrict__ g_idx, int m, int k, int group_size, int* status) {
+  for (int row = blockIdx.x; row < m; row += gridDim.x) {
+    const T* src = a + static_cast<size_t>(row) * k;
+    T* dst = permuted + static_cast<size_t>(row) * k;
+    for (int i = threadIdx.x; i < k; i += blockDim.x) {
+      const int from = perm[i];
+      dst[i] = from >= 0 && from < k ? src[from] : FromFloat<T>(0.0f);
+    }
+  }
+  if (blockIdx.x == 0) {
+    bool ok = true;
+    for (int i = threadIdx.x; i < k; i += blockDim.x) ok = ok && g_idx[i] == i / group_size;
+    if (!ok && atomicCAS(status, 0, kErrGIdx) == 0) {
+      status[1] = -1;
+      __threadfence();
+    }
+  }
+}
+
 // ---- host side ----------------------------------------------------------------------------------
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -2367,6 +2390,13 @@ extern "C" size_t infiniops_b200_marlin_gemm_scratch_bytes(int64_t size_m, int64
   return PlanScratch(tiles, tok, 0).total;
 }
 
+extern "C" size_t infiniops_b200_marlin_gemm_act_order_scratch_bytes(int64_t size_m, int64_t size_n, int64_t size_k) {
+  using namespace iob;
+  const int tok = TokenTile(size_m);
+  const int64_t tiles = ((size_n + kTileN - 1) / kTileN) * ((size_m + tok - 1) / tok);
+  return PlanScratch(tiles, tok, size_m * size_k * 2).total;
+}
+
 namespace iob {
 namespace {
 
@@ -2443,17 +2473,40 @@ extern "C" int infiniops_b200_marlin_gemm_placed(const iob_gemm_problem* problem
   if (bits == 8 && tok > 128) tok = 128;  // 8-bit weights: no 256-row tiles (the stage ring would not fit)
   const int64_t n_tiles = (g.size_n + kTileN - 1) / kTileN, m_tiles = (g.size_m + tok - 1) / tok;
   // (the scratch query does not know the group size and answers for the larger plan)
-  const ScratchPlan plan = PlanScratch(n_tiles * m_tiles, tok, 0);
+  IOB_REQUIRE((g.perm == nullptr) == (g.g_idx == nullptr), "%s: requires `g_idx` and `perm` together", op);
+  IOB_REQUIRE(g.perm == nullptr || g.num_groups > 1, "%s: activation order needs grouped scales", op);
+  const ScratchPlan plan = PlanScratch(n_tiles * m_tiles, tok, g.perm != nullptr ? g.size_m * g.size_k * 2 : 0);
   if (scratch == nullptr || scratch_bytes < plan.total) {
     return Fail(IOB_SCRATCH_TOO_SMALL, "%s: needs %zu bytes of scratch, got %zu", op, plan.total, scratch_bytes);
   }
   GemmParams p{};
   if (const int rc = SetPlacement(op, g, p)) return rc;
   if (const int rc = SetSignal(op, signal, p)) return rc;
+  const void* activations = g.a;
+  if (g.perm != nullptr) {
+    // Activation order: the weight rows are in `perm` order, so the GEMM runs on a copy of `a` with
+    // its columns in that order (kept in the scratch buffer, behind the split-K partial sums).
+    unsigned char* base = static_cast<unsigned char*>(scratch);
+    const int rows_grid = static_cast<int>(std::min<int64_t>(g.size_m, 4 * NumSms()));
+    auto launch = [&](auto* typed) {
+      using T = std::remove_pointer_t<decltype(typed)>;
+      PermuteColumnsKernel<T><<<rows_grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+          static_cast<const T*>(g.a), reinterpret_cast<T*>(base + plan.gathered_off), g.perm, g.g_idx,
+          static_cast<int>(g.size_m), static_cast<int>(g.size_k), static_cast<int>(g.size_k / g.num_groups),
+          reinterpret_cast<int*>(base));
+    };
+    if (a_dtype == IOB_BF16) {
+      launch(static_cast<__nv_bfloat16*>(nullptr));
+    } else {
+      launch(static_cast<__half*>(nullptr));
+    }
+    if (const int rc = CheckLaunch("marlin_gemm column permutation launch")) return rc;
+    activations = base + plan.gathered_off;
+  }
   // Prefill-sized problems whose columns pair up run two blocks per 256 x 256 output tile.
   const bool pair = tok == 256 && g.size_n % (2 * kTileN) == 0 && NumSms() >= 2;
   CUtensorMap map;
-  if (const int rc = ActivationMap(g.a, g.size_m, g.size_k, pair ? tok / 2 : tok, a_dtype, &map)) return rc;
+  if (const int rc = ActivationMap(activations, g.size_m, g.size_k, pair ? tok / 2 : tok, a_dtype, &map)) return rc;
   CUtensorMap w_map;
   if (const int rc = WeightMap(g.b_q_weight, 1, g.size_k, g.size_n, &w_map, bits)) return rc;
   CUtensorMap c_map;
@@ -2519,6 +2572,7 @@ extern "C" int infiniops_b200_marlin_gemm_batch(const iob_gemm_problem* problems
       return Fail(IOB_UNSUPPORTED, "%s: problem %d: batched launches take at most 64 rows and group sizes that are "
                   "multiples of 128; use marlin_gemm", op, i);
     }
+    IOB_REQUIRE(g.perm == nullptr && g.g_idx == nullptr, "%s: problem %d: activation order goes through marlin_gemm", op, i);
     const int cls = g.size_m <= 16 ? 0 : g.size_m <= 32 ? 1 : 2;
     order[cls][n_of[cls]++] = i;
   }

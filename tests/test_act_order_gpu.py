@@ -1,4 +1,4 @@
-"""GPU: activation order (`g_idx` / `perm`) in the routed Marlin GEMM.
+"""GPU: activation order (`g_idx` / `perm`) in the routed and the dense Marlin GEMM.
 
 A GPTQ act-order checkpoint stores, per expert, weights [K, N] whose row k belongs to scale group
 g_idx[k] (groups scattered over the rows).  The provider's preparation sorts the rows by group --
@@ -145,3 +145,64 @@ def test_operator_api_takes_activation_order():
     # all-zero words are q = 0, i.e. the weight -8 * 0.25 = -2 everywhere
     want = (a.float().sum(dim=1, keepdim=True) * -2.0).repeat_interleave(top_k, dim=0).expand(routes, n)
     assert rel_max_err(out, want) <= 2e-2
+
+
+@pytest.mark.parametrize("m,k,n,dtype", ((1, 512, 256, torch.bfloat16), (48, 1024, 384, torch.float16),
+                                         (200, 512, 512, torch.bfloat16), (300, 2048, 256, torch.bfloat16)))
+def test_dense_gemm_with_activation_order(m, k, n, dtype):
+    """All token tiles (16 .. 256 rows, the paired kernel at n % 256 == 0 included) read the permuted copy."""
+    from infiniops_b200 import capi
+
+    qs, gs, ss, words, scales, perm, g_sorted = _act_order_experts(1, k, n, 40 + m)
+    x = torch.randn((m, k), generator=torch.Generator().manual_seed(m)).to(dtype)
+    ref = x.float() @ _dequant_scattered(qs[0], gs[0], ss[0].to(dtype))
+    out = torch.full((m, n), float("nan"), dtype=dtype, device="cuda")
+    capi.marlin_gemm(x.cuda(), words[0], None, scales[0].to(dtype).contiguous(), None, capi.QTYPE_UINT4B8, m, n, k, out,
+                     g_idx=g_sorted[0].contiguous(), perm=perm[0].contiguous())
+    torch.cuda.synchronize()
+    assert capi.scratch_status(capi.scratch("cuda", 0)) == 0
+    assert not torch.isnan(out.float()).any()
+    assert rel_max_err(out, ref) <= TOL
+    # identical to the plain GEMM on activations permuted by hand
+    plain = torch.empty_like(out)
+    capi.marlin_gemm(x[:, perm[0].cpu().long()].contiguous().cuda(), words[0], None, scales[0].to(dtype).contiguous(), None,
+                     capi.QTYPE_UINT4B8, m, n, k, plain)
+    torch.cuda.synchronize()
+    assert torch.equal(out, plain)
+
+
+def test_dense_gemm_reports_an_unsorted_g_idx_and_refuses_half_a_pair():
+    from infiniops_b200 import capi
+
+    m, k, n = 8, 256, 128
+    qs, gs, ss, words, scales, perm, g_sorted = _act_order_experts(1, k, n, 6)
+    x = torch.randn((m, k), device="cuda").bfloat16()
+    out = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    capi.marlin_gemm(x, words[0], None, scales[0].contiguous(), None, capi.QTYPE_UINT4B8, m, n, k, out,
+                     g_idx=gs[0].cuda(), perm=perm[0].contiguous())
+    torch.cuda.synchronize()
+    buf = capi.scratch("cuda", 0)
+    assert capi.scratch_status(buf) == 9
+    capi.lib().infiniops_b200_gemm_scratch_prepare(buf.data_ptr(), buf.numel(), None)
+    torch.cuda.synchronize()
+    assert capi.scratch_status(buf) == 0
+    with pytest.raises(capi.Error, match="together"):
+        capi.marlin_gemm(x, words[0], None, scales[0].contiguous(), None, capi.QTYPE_UINT4B8, m, n, k, out,
+                         perm=perm[0].contiguous())
+
+
+def test_dense_operator_api_takes_activation_order():
+    import infini.ops
+
+    m, k, n = 24, 512, 256
+    qs, gs, ss, words, scales, perm, g_sorted = _act_order_experts(1, k, n, 8)
+    x = torch.randn((m, k), generator=torch.Generator().manual_seed(2)).bfloat16()
+    out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    workspace = torch.zeros(432, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    infini.ops.marlin_gemm(x.cuda(), words[0], None, scales[0].contiguous(), None, None, None, g_sorted[0].contiguous(),
+                           perm[0].contiguous(), workspace, 1125899907892224, m, n, k, True, False, True, False, out,
+                           stream=stream)
+    torch.cuda.synchronize()
+    ref = x.float() @ _dequant_scattered(qs[0], gs[0], ss[0])
+    assert rel_max_err(out, ref) <= TOL

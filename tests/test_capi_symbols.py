@@ -53,7 +53,7 @@ def test_ctypes_structs_match_the_header(tmp_path):
     mirrors = {
         "iob_gemm_problem": (capi.GemmProblem, ("a", "b_q_weight", "b_bias", "b_scales", "b_zeros", "out", "size_m", "size_n",
                                                 "size_k", "num_groups", "out_ld", "out_col0", "n_peers", "peer_out",
-                                                "scale_layout")),
+                                                "scale_layout", "g_idx", "perm")),
         "iob_peer_signal": (capi.PeerSignal, ("done_counter", "epoch", "n_peers", "peer_flags", "flag_slot")),
         "iob_routed_options": (capi.RoutedOptions, ("scale_layout", "a_sorted", "out_sorted", "fuse_silu", "g_idx", "perm",
                                                     "route_position", "block_rows", "row_dest", "dest_base", "n_dest",
