@@ -15,7 +15,8 @@ Metric: weight-stream bandwidth = int4 weight bytes of the GEMMs of a step / tim
               repeated; the median is reported with the spread.
 * `e2e`       the same GEMMs issued one by one through the operator API (`infini.ops.marlin_gemm`)
               with HOST activations and outputs: pinned host -> device copy of A and device -> host
-              copy of C inside the timed region (weights are model state and stay on the device).
+              copy of C inside the timed region (weights are model state and stay on the device);
+              on one GPU consecutive steps alternate between two sets of buffers and streams.
 * `roofline`  algorithmic bytes of the GEMM launches in the timed region / their time, against
               the measured HBM copy bandwidth of this machine pool.
 * `cpu_baseline`  the reference's CPU formulation (fp32 dequantise, then matmul) on the host
@@ -479,84 +480,109 @@ def e2e_decode(d, args, layers, acts, keys, full_n, phases):
 
     in_shapes = {key: tuple(acts[key].shape) for key in keys}
     out_shapes = {key: (key[1], full_n[key[0]]) for key in keys}
-    host_in_flat, host_in = arena(in_shapes, pin_memory=True)
-    host_out_flat, host_out = arena(out_shapes, pin_memory=True)
-    dev_in_flat, dev_in = arena(in_shapes, device=device)
-    for key in keys:
-        host_in[key].copy_(acts[key])
-    if world == 1:
-        dev_out_flat, dev_out = arena(out_shapes, device=device)
-    else:
-        dev_out = {key: torch.empty((key[1], full_n[key[0]] // world), dtype=torch.bfloat16, device=device) for key in keys}
-        dev_full_flat, dev_full = arena(out_shapes, device=device)
-    gathered = {key: torch.empty((world, key[1], full_n[key[0]] // world), dtype=torch.bfloat16, device=device)
-                for key in keys} if world > 1 else None
-    workspace = torch.zeros(432, dtype=torch.int32, device=device)
-    h2d = host_in_flat.numel() * 2
-    d2h = host_out_flat.numel() * 2
 
-    def step(phase):
+    class Lane:
+        """One set of step buffers: pinned host arenas, their device twins, and (N = 1) a stream of its own."""
+
+        def __init__(self):
+            self.host_in_flat, self.host_in = arena(in_shapes, pin_memory=True)
+            self.host_out_flat, self.host_out = arena(out_shapes, pin_memory=True)
+            self.dev_in_flat, self.dev_in = arena(in_shapes, device=device)
+            for key in keys:
+                self.host_in[key].copy_(acts[key])
+            if world == 1:
+                self.dev_out_flat, self.dev_out = arena(out_shapes, device=device)
+            else:
+                self.dev_out = {key: torch.empty((key[1], full_n[key[0]] // world), dtype=torch.bfloat16, device=device)
+                                for key in keys}
+                self.dev_full_flat, self.dev_full = arena(out_shapes, device=device)
+            self.gathered = {key: torch.empty((world, key[1], full_n[key[0]] // world), dtype=torch.bfloat16, device=device)
+                             for key in keys} if world > 1 else None
+            self.workspace = torch.zeros(432, dtype=torch.int32, device=device)
+            self.stream = torch.cuda.Stream() if world == 1 else None
+            self.graphs = None
+
+    # N = 1: two lanes, so that a step's copies overlap the GEMMs of the step before / after it on the
+    # other lane (what a host that double-buffers its requests does); every step still moves its own
+    # inputs in and its own results out inside the timed region.
+    lanes = [Lane() for _ in range(2 if world == 1 else 1)]
+    h2d = lanes[0].host_in_flat.numel() * 2
+    d2h = lanes[0].host_out_flat.numel() * 2
+
+    def step(lane, phase):
         stream = torch.cuda.current_stream().cuda_stream
-        dev_in_flat.copy_(host_in_flat, non_blocking=True)
+        lane.dev_in_flat.copy_(lane.host_in_flat, non_blocking=True)
         for name, m in keys:
             w = layers[phase * len(MS) + MS.index(m)][name]
-            infini.ops.marlin_gemm(dev_in[(name, m)], w["marlin"], None, w["scales"], None, None, w["zeros"], None, None,
-                                   workspace, UINT4, m, w["n"], w["k"], True, False, True, False, dev_out[(name, m)],
-                                   stream=stream)
+            infini.ops.marlin_gemm(lane.dev_in[(name, m)], w["marlin"], None, w["scales"], None, None, w["zeros"], None,
+                                   None, lane.workspace, UINT4, m, w["n"], w["k"], True, False, True, False,
+                                   lane.dev_out[(name, m)], stream=stream)
             if world > 1:
                 import torch.distributed as dist
 
-                dist.all_gather_into_tensor(gathered[(name, m)].view(-1, w["n"]), dev_out[(name, m)])
-                dev_full[(name, m)].copy_(gathered[(name, m)].permute(1, 0, 2).reshape(m, -1))
-        host_out_flat.copy_(dev_out_flat if world == 1 else dev_full_flat, non_blocking=True)
+                dist.all_gather_into_tensor(lane.gathered[(name, m)].view(-1, w["n"]), lane.dev_out[(name, m)])
+                lane.dev_full[(name, m)].copy_(lane.gathered[(name, m)].permute(1, 0, 2).reshape(m, -1))
+        lane.host_out_flat.copy_(lane.dev_out_flat if world == 1 else lane.dev_full_flat, non_blocking=True)
 
     for i in range(max(3, phases)):
-        step(i % phases)
+        step(lanes[0], i % phases)
     torch.cuda.synchronize()
     steps = max(3, min(args.steps, 50))
     count = [0]
-    graphs = None
     if world == 1:
-        # One CUDA graph per weight-copy phase holding the step as the caller issues it: per GEMM a
-        # host -> device copy node, the operator's launch, a device -> host copy node.  (With N > 1 the
-        # step stays eager: it carries an NCCL all-gather per GEMM.)
-        graphs = []
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            step(0)   # outside capture first: the operator's per-stream scratch is allocated on first use
-            torch.cuda.synchronize()
-            for phase in range(phases):
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, stream=side):
-                    step(phase)
-                graphs.append(g)
-        torch.cuda.current_stream().wait_stream(side)
-        torch.cuda.synchronize()
-        for g in graphs:
-            g.replay()
+        # One CUDA graph per lane and weight-copy phase holding the step as the caller issues it: a
+        # host -> device copy node, the operator's sixteen launches, a device -> host copy node.  Each
+        # lane is captured on its own stream: the operator keeps its split-K scratch per stream, so the
+        # two lanes' GEMMs never share one.  (With N > 1 the step stays eager: it carries an NCCL
+        # all-gather per GEMM.)
+        for lane in lanes:
+            lane.stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(lane.stream):
+                step(lane, 0)   # outside capture first: the operator's per-stream scratch is allocated on first use
+                torch.cuda.synchronize()
+                lane.graphs = []
+                for phase in range(phases):
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=lane.stream):
+                        step(lane, phase)
+                    lane.graphs.append(g)
+            torch.cuda.current_stream().wait_stream(lane.stream)
         torch.cuda.synchronize()
 
     def run(n):
+        if world > 1:
+            for _ in range(n):
+                step(lanes[0], count[0] % phases)
+                count[0] += 1
+            return
+        # the timing events sit on the current stream: the lanes start after it and it ends after them
+        main = torch.cuda.current_stream()
+        for lane in lanes:
+            lane.stream.wait_stream(main)
         for _ in range(n):
-            if graphs is None:
-                step(count[0] % phases)
-            else:
-                graphs[count[0] % phases].replay()
+            lane = lanes[count[0] % len(lanes)]
+            with torch.cuda.stream(lane.stream):
+                lane.graphs[count[0] % phases].replay()
             count[0] += 1
+        for lane in lanes:
+            main.wait_stream(lane.stream)
 
+    run(2 * len(lanes))
+    torch.cuda.synchronize()
     regions = timed_regions(d, run, steps, 3)
     ms = statistics.median(regions)
     # what came back to the host must be what the device computed
     torch.cuda.synchronize()
     key = keys[-1]
-    assert world > 1 or torch.equal(host_out[key], dev_out[key].cpu()), "e2e: host result differs"
+    for lane in lanes:
+        assert world > 1 or torch.equal(lane.host_out[key], lane.dev_out[key].cpu()), "e2e: host result differs"
     step_weight_bytes = sum(weight_bytes(k, n) for _, k, n in SHAPES) * len(MS)
     return {"value": step_weight_bytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
             "d2h_bytes_per_step": d2h, "steps": steps, "ms_per_step": ms,
             "note": "infini.ops.marlin_gemm per GEMM; the step's activations in one copy from pinned host memory, its results "
                     "in one copy back to pinned host memory" +
-                    ("; the step (copies and operator calls) replayed as a CUDA graph" if graphs is not None else "")}
+                    ("; the step (copies and operator calls) replayed as a CUDA graph, steps alternating between two "
+                     "sets of buffers and streams so that one step's copies overlap the other's GEMMs" if world == 1 else "")}
 
 
 # ---------------------------------------------------------------------------------------------------
