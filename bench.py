@@ -372,7 +372,10 @@ def run_ours(args):
         del graphs16
 
     # ---- end to end through the operator call with host buffers -------------------------------
-    e2e = e2e_decode(d, args, layers, acts, keys, full_n, phases)
+    multi = None if group is None else {"group": group, "offsets": offsets, "outs": outs, "signal": signal,
+                                        "scratch": scratch, "set_bytes": set_bytes}
+    e2e = e2e_decode(d, args, layers, acts, keys, full_n, phases, multi)
+    check_status("end-to-end step")
 
     step_weight_bytes = sum(weight_bytes(k, n) for _, k, n in SHAPES) * len(MS)
     step_algo_bytes = sum(algorithmic_bytes(m, k, n // world) for _, k, n in SHAPES for m in MS)  # per GPU
@@ -459,13 +462,17 @@ def check_gathered(d, capi, layers, acts, keys, gathered, phase, scratch, full_n
     return d.all_true(ok)
 
 
-def e2e_decode(d, args, layers, acts, keys, full_n, phases):
-    """The step through the public operator (`infini.ops.marlin_gemm`), one call per GEMM, with pinned
-    host activations copied in and the full-width result copied out to pinned host memory, inside the
-    timed region.  With N > 1 the slices are all-gathered (NCCL) between the GEMM and the copy out."""
+def e2e_decode(d, args, layers, acts, keys, full_n, phases, multi=None):
+    """The step with pinned host activations copied in and the full-width result copied out to pinned host
+    memory, inside the timed region.  One GPU: through the public operator (`infini.ops.marlin_gemm`), one
+    call per GEMM.  N > 1 (the reference's operator has no placement arguments and the reference no
+    communication layer): one C-ABI call per GEMM (`infiniops_b200_marlin_gemm_placed`), whose epilogue
+    stores the rank's slice into every rank's full-width result; then the bounded flag wait and the copy out."""
     import infini.ops
 
     world, device = d.world, d.device
+    if multi is not None:
+        return e2e_decode_placed(d, args, layers, acts, keys, full_n, phases, multi)
     # One pinned arena for the step's activations and one for its results (and the same on the device),
     # so that a step moves its inputs in one host -> device copy and its results in one device -> host copy
     # instead of sixteen small ones each; the operator calls take views of the arenas.
@@ -583,6 +590,130 @@ def e2e_decode(d, args, layers, acts, keys, full_n, phases):
                     "in one copy back to pinned host memory" +
                     ("; the step (copies and operator calls) replayed as a CUDA graph, steps alternating between two "
                      "sets of buffers and streams so that one step's copies overlap the other's GEMMs" if world == 1 else "")}
+
+
+def e2e_decode_placed(d, args, layers, acts, keys, full_n, phases, multi):
+    """`e2e` at N > 1: host activations in (one pinned copy), sixteen placed GEMM calls whose epilogues
+    store into every rank's result set, the flag wait, the full-width results out (one pinned copy).
+
+    Three streams per rank -- copy in, GEMMs, copy out -- with two input buffers and the two result sets
+    of the device-resident step, which alternate with the step.  What orders them (step i, set s = i % 2):
+      * copy in (i) overwrites input buffer s, last read by the GEMMs of step i - 2;
+      * set s is written by every rank's GEMMs (i), copied out by (i), and written again by the GEMMs
+        (i + 2) -- the peers' as soon as this rank has signalled step i + 1.  So the copy out (i) must be
+        over before this rank's last GEMM of step i + 1, the one that raises the signal: the step is two
+        CUDA graphs per weight-copy phase, fifteen GEMMs / the last GEMM + flag wait, with the wait for
+        the copy out (i - 1) between them."""
+    from infiniops_b200 import capi
+
+    world, rank, device = d.world, d.rank, d.device
+    group, offsets, outs, signal, scratch = (multi[k] for k in ("group", "offsets", "outs", "signal", "scratch"))
+    sizes = [-(-(m * acts[(name, m)].shape[1]) // 128) * 128 for name, m in keys]
+    host_in = torch.empty(sum(sizes), dtype=torch.bfloat16, pin_memory=True)
+    dev_in = [torch.empty(sum(sizes), dtype=torch.bfloat16, device=device) for _ in range(2)]
+    views, at = [{}, {}], 0
+    for key, size in zip(keys, sizes):
+        r, c = acts[key].shape
+        for s in range(2):
+            views[s][key] = dev_in[s][at:at + r * c].view(r, c)
+        host_in[at:at + r * c].view(r, c).copy_(acts[key])
+        at += size
+    # a result set is one contiguous piece of the arena (carved key by key, 256-byte aligned)
+    sets = [group.local(offsets[s][keys[0]], (multi["set_bytes"],), torch.uint8) for s in range(2)]
+    host_out = [torch.empty(multi["set_bytes"], dtype=torch.uint8, pin_memory=True) for _ in range(2)]
+    assert phases % 2 == 0   # so that a phase always meets the same buffers: phase % 2 == step % 2
+
+    def problem(phase, key):
+        name, m = key
+        w = layers[phase * len(MS) + MS.index(m)][name]
+        peers = [group.address(r, offsets[phase % 2][key]) for r in group.others()]
+        return capi.gemm_problem(views[phase % 2][key], w["marlin"], None, w["scales"], w["zeros"], outs[phase % 2][key],
+                                 m, w["n"], w["k"], out_ld=full_n[name], out_col0=rank * w["n"], peer_out=peers)
+
+    problems = [[problem(phase, key) for key in keys] for phase in range(phases)]
+
+    def gemms(phase, part, stream=None):
+        """part 0: all GEMMs but the last; part 1: the last one (it raises the signal) and the flag wait."""
+        todo = problems[phase][:-1] if part == 0 else problems[phase][-1:]
+        for g in todo:
+            capi.marlin_gemm_placed(g, torch.bfloat16, UINT4, scratch, signal=signal if part == 1 else None, stream=stream)
+        if part == 1:
+            group.wait(stream=stream)
+
+    for phase in range(phases):   # outside any graph first, one stream, copies in step order
+        dev_in[phase % 2].copy_(host_in, non_blocking=True)
+        gemms(phase, 0)
+        gemms(phase, 1)
+        host_out[phase % 2].copy_(sets[phase % 2], non_blocking=True)
+    torch.cuda.synchronize()
+    d.barrier()
+    copy_in, compute, copy_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+    graphs = []
+    compute.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(compute):
+        for phase in range(phases):
+            pair = []
+            for part in range(2):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=compute):
+                    gemms(phase, part, stream=compute.cuda_stream)
+                pair.append(g)
+            graphs.append(pair)
+    torch.cuda.current_stream().wait_stream(compute)
+    torch.cuda.synchronize()
+    # (captured graphs have not run: every rank has signalled and waited `phases` times so far)
+    in_done = [torch.cuda.Event() for _ in range(2)]
+    gemm_done = [torch.cuda.Event() for _ in range(2)]
+    out_done = [torch.cuda.Event() for _ in range(2)]
+    for e in in_done + gemm_done + out_done:
+        e.record()
+    torch.cuda.synchronize()
+    count = [0]
+
+    def run(n):
+        main = torch.cuda.current_stream()
+        for st in (copy_in, compute, copy_out):
+            st.wait_stream(main)
+        for _ in range(n):
+            i = count[0]
+            s, phase = i % 2, i % phases
+            copy_in.wait_event(gemm_done[s])          # the GEMMs of step i - 2 have read input buffer s
+            with torch.cuda.stream(copy_in):
+                dev_in[s].copy_(host_in, non_blocking=True)
+                in_done[s].record()
+            compute.wait_event(in_done[s])
+            with torch.cuda.stream(compute):
+                graphs[phase][0].replay()
+            # set 1 - s (step i - 1) is on the host before this rank's signal lets the peers write it again
+            # (and this rank's own GEMMs of step i + 1 follow this point in the stream)
+            compute.wait_event(out_done[1 - s])
+            with torch.cuda.stream(compute):
+                graphs[phase][1].replay()
+                gemm_done[s].record()
+            copy_out.wait_event(gemm_done[s])
+            with torch.cuda.stream(copy_out):
+                host_out[s].copy_(sets[s], non_blocking=True)
+                out_done[s].record()
+            count[0] += 1
+        for st in (copy_in, compute, copy_out):
+            main.wait_stream(st)
+
+    run(phases)
+    torch.cuda.synchronize()
+    steps = max(3, min(args.steps, 50))
+    regions = timed_regions(d, run, steps, 3)
+    ms = statistics.median(regions)
+    torch.cuda.synchronize()
+    last = (count[0] - 1) % 2
+    assert torch.equal(host_out[last], sets[last].cpu()), "e2e: host result differs"
+    step_weight_bytes = sum(weight_bytes(k, n) for _, k, n in SHAPES) * len(MS)
+    return {"value": step_weight_bytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": host_in.numel() * 2,
+            "d2h_bytes_per_step": multi["set_bytes"], "steps": steps, "ms_per_step": ms,
+            "note": "per rank: the step's activations in one copy from pinned host memory, one "
+                    "infiniops_b200_marlin_gemm_placed call per GEMM (the epilogue stores the slice into every rank's "
+                    "full-width result), the bounded flag wait, the full-width results in one copy back to pinned host "
+                    "memory; GEMMs replayed as CUDA graphs, the copies on streams of their own beside the neighbouring "
+                    "steps' GEMMs"}
 
 
 # ---------------------------------------------------------------------------------------------------
