@@ -16,7 +16,9 @@ Metric: weight-stream bandwidth = int4 weight bytes of the GEMMs of a step / tim
 * `e2e`       the same GEMMs issued one by one through the operator API (`infini.ops.marlin_gemm`)
               with HOST activations and outputs: pinned host -> device copy of A and device -> host
               copy of C inside the timed region (weights are model state and stay on the device);
-              on one GPU consecutive steps alternate between two sets of buffers and streams.
+              on one GPU consecutive steps alternate between two sets of buffers and streams.  With
+              N > 1: one placed C-ABI GEMM call per GEMM (epilogue peer stores), every rank copying the
+              full-width results out; copies and GEMMs on streams of their own.
 * `roofline`  algorithmic bytes of the GEMM launches in the timed region / their time, against
               the measured HBM copy bandwidth of this machine pool.
 * `cpu_baseline`  the reference's CPU formulation (fp32 dequantise, then matmul) on the host
