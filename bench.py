@@ -16,7 +16,7 @@ Metric: weight-stream bandwidth = int4 weight bytes of the GEMMs of a step / tim
 * `e2e`       the same GEMMs issued one by one through the operator API (`infini.ops.marlin_gemm`)
               with HOST activations and outputs: pinned host -> device copy of A and device -> host
               copy of C inside the timed region (weights are model state and stay on the device);
-              on one GPU consecutive steps alternate between two sets of buffers and streams.  With
+              on one GPU consecutive steps alternate between three sets of buffers and streams.  With
               N > 1: one placed C-ABI GEMM call per GEMM (epilogue peer stores), every rank copying the
               full-width results out; copies and GEMMs on streams of their own.
 * `roofline`  algorithmic bytes of the GEMM launches in the timed region / their time, against
@@ -510,11 +510,13 @@ def e2e_decode(d, args, layers, acts, keys, full_n, phases, multi=None):
             self.workspace = torch.zeros(432, dtype=torch.int32, device=device)
             self.stream = torch.cuda.Stream() if world == 1 else None
             self.graphs = None
+            self.last_phase = 0
 
-    # N = 1: two lanes, so that a step's copies overlap the GEMMs of the step before / after it on the
-    # other lane (what a host that double-buffers its requests does); every step still moves its own
-    # inputs in and its own results out inside the timed region.
-    lanes = [Lane() for _ in range(2 if world == 1 else 1)]
+    # N = 1: several lanes (three by default), so that a step's copies overlap the GEMMs of the steps
+    # before / after it on the other lanes, and the blocks of one lane's next GEMM fill the SMs that the
+    # tail of another lane's GEMM leaves idle (what a host with a few requests in flight does); every
+    # step still moves its own inputs in and its own results out inside the timed region.
+    lanes = [Lane() for _ in range(max(1, args.e2e_lanes) if world == 1 else 1)]
     h2d = lanes[0].host_in_flat.numel() * 2
     d2h = lanes[0].host_out_flat.numel() * 2
 
@@ -572,6 +574,7 @@ def e2e_decode(d, args, layers, acts, keys, full_n, phases, multi=None):
             lane = lanes[count[0] % len(lanes)]
             with torch.cuda.stream(lane.stream):
                 lane.graphs[count[0] % phases].replay()
+            lane.last_phase = count[0] % phases
             count[0] += 1
         for lane in lanes:
             main.wait_stream(lane.stream)
@@ -585,13 +588,23 @@ def e2e_decode(d, args, layers, acts, keys, full_n, phases, multi=None):
     key = keys[-1]
     for lane in lanes:
         assert world > 1 or torch.equal(lane.host_out[key], lane.dev_out[key].cpu()), "e2e: host result differs"
+        if world == 1:
+            # ... and what a lone call of the same GEMM computes (the lanes' launches ran side by side)
+            from infiniops_b200 import capi
+
+            for name, m in (keys[0], keys[-1]):
+                w = layers[lane.last_phase * len(MS) + MS.index(m)][name]
+                alone = torch.empty_like(lane.dev_out[(name, m)])
+                capi.marlin_gemm(acts[(name, m)], w["marlin"], None, w["scales"], w["zeros"], UINT4, m, w["n"], w["k"], alone)
+                assert torch.equal(alone, lane.dev_out[(name, m)]), "e2e: result differs from the GEMM run alone"
     step_weight_bytes = sum(weight_bytes(k, n) for _, k, n in SHAPES) * len(MS)
     return {"value": step_weight_bytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
             "d2h_bytes_per_step": d2h, "steps": steps, "ms_per_step": ms,
             "note": "infini.ops.marlin_gemm per GEMM; the step's activations in one copy from pinned host memory, its results "
                     "in one copy back to pinned host memory" +
-                    ("; the step (copies and operator calls) replayed as a CUDA graph, steps alternating between two "
-                     "sets of buffers and streams so that one step's copies overlap the other's GEMMs" if world == 1 else "")}
+                    (f"; the step (copies and operator calls) replayed as a CUDA graph, steps alternating between {len(lanes)} "
+                     "sets of buffers and streams so that one step's copies and launch tails overlap the others' GEMMs"
+                     if world == 1 else "")}
 
 
 def e2e_decode_placed(d, args, layers, acts, keys, full_n, phases, multi):
@@ -1235,6 +1248,8 @@ def main():
     parser.add_argument("--gather", default="auto", choices=("auto", "epilogue", "broadcast"),
                         help="N > 1: slices stored to the peers by the GEMM epilogue, or by one copy launch behind the GEMMs "
                              "(auto: the epilogue)")
+    parser.add_argument("--e2e-lanes", type=int, default=3,
+                        help="N = 1: sets of step buffers (each with its stream) the end-to-end leg alternates between")
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=100)
     parser.add_argument("--warmup", type=int, default=5)
