@@ -272,6 +272,16 @@ def run_ours(args):
                                  w["k"], out_ld=full_n[name], out_col0=rank * w["n"], peer_out=peers)
 
     tables = [capi.problem_array([problem(phase, key) for key in keys]) for phase in range(phases)]
+    # One GPU: the step as two batch calls side by side -- the M = 64 problems on the step's stream, the
+    # M <= 16 problems on a second one, each call with its own scratch -- instead of one call whose two
+    # launches follow each other: the second call's blocks take the SMs as the first's blocks leave them
+    # and so work through the first launch's split-K hand-over instead of waiting for its end.
+    side_by_side = group is None and args.decode_streams == 2
+    if side_by_side:
+        wide = [capi.problem_array([problem(phase, key) for key in keys if key[1] > 32]) for phase in range(phases)]
+        narrow = [capi.problem_array([problem(phase, key) for key in keys if key[1] <= 32]) for phase in range(phases)]
+        scratch_b = torch.zeros_like(scratch)
+        branch = torch.cuda.Stream()
     singles = [[problem(phase, key) for key in keys] for phase in range(phases)]
     signal = None if group is None else group.signal()
 
@@ -287,6 +297,13 @@ def run_ours(args):
         slice_copies = [(capi.PeerCopy * len(keys))(*[slice_copy(phase, key) for key in keys]) for phase in range(2)]
 
     def step_batched(phase, stream=None):
+        if side_by_side:
+            here = torch.cuda.current_stream()   # (under capture: the capturing stream, which `stream` names)
+            branch.wait_stream(here)
+            capi.marlin_gemm_batch(wide[phase], torch.bfloat16, UINT4, scratch, stream=here.cuda_stream)
+            capi.marlin_gemm_batch(narrow[phase], torch.bfloat16, UINT4, scratch_b, stream=branch.cuda_stream)
+            here.wait_stream(branch)
+            return 2
         if slice_copies is None:
             capi.marlin_gemm_batch(tables[phase], torch.bfloat16, UINT4, scratch, signal=signal, stream=stream)
         else:
@@ -330,6 +347,9 @@ def run_ours(args):
         torch.cuda.synchronize()
         assert capi.scratch_status(scratch) == 0, f"{what}: a GEMM kernel gave up on a wait: " \
                                                   f"{scratch[:192].view(torch.int32).tolist()}"
+        if side_by_side:
+            assert capi.scratch_status(scratch_b) == 0, f"{what}: a GEMM kernel gave up on a wait: " \
+                                                        f"{scratch_b[:192].view(torch.int32).tolist()}"
         if group is not None:
             assert group.wait_status() == (0, 0), f"{what}: a wait for a peer's completion flag ran out: {group.wait_status()}"
 
@@ -400,7 +420,8 @@ def run_ours(args):
                    " (peer-mapped buffers), completion flags + bounded wait per step",
                    "l2": f"inputs larger than L2: {copies} full weight copies "
                          f"({copies * layer_bytes / 1e6:.0f} MB per GPU) used in rotation",
-                   "launch": "CUDA graph replay of the step; the 16 problems as two batched persistent launches"},
+                   "launch": "CUDA graph replay of the step; the 16 problems as two batched persistent launches" +
+                             (", side by side on two streams" if side_by_side else "")},
         "timing": dict(spread_of(regions), unit="ms per step", note=f"{repeats} timed regions of {args.steps} steps, "
                        "CUDA events, max over ranks per region; `ms_per_step` is the median"),
         "e2e": e2e,
@@ -1248,6 +1269,9 @@ def main():
     parser.add_argument("--gather", default="auto", choices=("auto", "epilogue", "broadcast"),
                         help="N > 1: slices stored to the peers by the GEMM epilogue, or by one copy launch behind the GEMMs "
                              "(auto: the epilogue)")
+    parser.add_argument("--decode-streams", type=int, default=2, choices=(1, 2),
+                        help="N = 1: 2 = the step's two batch calls (M = 64 / M <= 16) side by side on two streams, "
+                             "1 = one call, its launches one after the other")
     parser.add_argument("--e2e-lanes", type=int, default=3,
                         help="N = 1: sets of step buffers (each with its stream) the end-to-end leg alternates between")
     parser.add_argument("--gpus", type=int, default=1)
