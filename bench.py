@@ -492,10 +492,12 @@ def e2e_decode(d, args, layers, acts, keys, full_n, phases, multi=None):
     communication layer): one C-ABI call per GEMM (`infiniops_b200_marlin_gemm_placed`), whose epilogue
     stores the rank's slice into every rank's full-width result; then the bounded flag wait and the copy out."""
     import infini.ops
+    from infiniops_b200 import capi
 
-    world, device = d.world, d.device
     if multi is not None:
         return e2e_decode_placed(d, args, layers, acts, keys, full_n, phases, multi)
+    assert d.world == 1
+    device = d.device
     # One pinned arena for the step's activations and one for its results (and the same on the device),
     # so that a step moves its inputs in one host -> device copy and its results in one device -> host copy
     # instead of sixteen small ones each; the operator calls take views of the arenas.
@@ -512,32 +514,25 @@ def e2e_decode(d, args, layers, acts, keys, full_n, phases, multi=None):
     out_shapes = {key: (key[1], full_n[key[0]]) for key in keys}
 
     class Lane:
-        """One set of step buffers: pinned host arenas, their device twins, and (N = 1) a stream of its own."""
+        """One set of step buffers (pinned host arenas and their device twins) with a stream of its own."""
 
         def __init__(self):
             self.host_in_flat, self.host_in = arena(in_shapes, pin_memory=True)
             self.host_out_flat, self.host_out = arena(out_shapes, pin_memory=True)
             self.dev_in_flat, self.dev_in = arena(in_shapes, device=device)
+            self.dev_out_flat, self.dev_out = arena(out_shapes, device=device)
             for key in keys:
                 self.host_in[key].copy_(acts[key])
-            if world == 1:
-                self.dev_out_flat, self.dev_out = arena(out_shapes, device=device)
-            else:
-                self.dev_out = {key: torch.empty((key[1], full_n[key[0]] // world), dtype=torch.bfloat16, device=device)
-                                for key in keys}
-                self.dev_full_flat, self.dev_full = arena(out_shapes, device=device)
-            self.gathered = {key: torch.empty((world, key[1], full_n[key[0]] // world), dtype=torch.bfloat16, device=device)
-                             for key in keys} if world > 1 else None
             self.workspace = torch.zeros(432, dtype=torch.int32, device=device)
-            self.stream = torch.cuda.Stream() if world == 1 else None
+            self.stream = torch.cuda.Stream()
             self.graphs = None
             self.last_phase = 0
 
-    # N = 1: several lanes (three by default), so that a step's copies overlap the GEMMs of the steps
-    # before / after it on the other lanes, and the blocks of one lane's next GEMM fill the SMs that the
-    # tail of another lane's GEMM leaves idle (what a host with a few requests in flight does); every
-    # step still moves its own inputs in and its own results out inside the timed region.
-    lanes = [Lane() for _ in range(max(1, args.e2e_lanes) if world == 1 else 1)]
+    # Several lanes (three by default), so that a step's copies overlap the GEMMs of the steps before /
+    # after it on the other lanes, and the blocks of one lane's next GEMM fill the SMs that the tail of
+    # another lane's GEMM leaves idle (what a host with a few requests in flight does); every step still
+    # moves its own inputs in and its own results out inside the timed region.
+    lanes = [Lane() for _ in range(max(1, args.e2e_lanes))]
     h2d = lanes[0].host_in_flat.numel() * 2
     d2h = lanes[0].host_out_flat.numel() * 2
 
@@ -549,44 +544,32 @@ def e2e_decode(d, args, layers, acts, keys, full_n, phases, multi=None):
             infini.ops.marlin_gemm(lane.dev_in[(name, m)], w["marlin"], None, w["scales"], None, None, w["zeros"], None,
                                    None, lane.workspace, UINT4, m, w["n"], w["k"], True, False, True, False,
                                    lane.dev_out[(name, m)], stream=stream)
-            if world > 1:
-                import torch.distributed as dist
-
-                dist.all_gather_into_tensor(lane.gathered[(name, m)].view(-1, w["n"]), lane.dev_out[(name, m)])
-                lane.dev_full[(name, m)].copy_(lane.gathered[(name, m)].permute(1, 0, 2).reshape(m, -1))
-        lane.host_out_flat.copy_(lane.dev_out_flat if world == 1 else lane.dev_full_flat, non_blocking=True)
+        lane.host_out_flat.copy_(lane.dev_out_flat, non_blocking=True)
 
     for i in range(max(3, phases)):
         step(lanes[0], i % phases)
     torch.cuda.synchronize()
     steps = max(3, min(args.steps, 50))
     count = [0]
-    if world == 1:
-        # One CUDA graph per lane and weight-copy phase holding the step as the caller issues it: a
-        # host -> device copy node, the operator's sixteen launches, a device -> host copy node.  Each
-        # lane is captured on its own stream: the operator keeps its split-K scratch per stream, so the
-        # two lanes' GEMMs never share one.  (With N > 1 the step stays eager: it carries an NCCL
-        # all-gather per GEMM.)
-        for lane in lanes:
-            lane.stream.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(lane.stream):
-                step(lane, 0)   # outside capture first: the operator's per-stream scratch is allocated on first use
-                torch.cuda.synchronize()
-                lane.graphs = []
-                for phase in range(phases):
-                    g = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(g, stream=lane.stream):
-                        step(lane, phase)
-                    lane.graphs.append(g)
-            torch.cuda.current_stream().wait_stream(lane.stream)
-        torch.cuda.synchronize()
+    # One CUDA graph per lane and weight-copy phase holding the step as the caller issues it: a
+    # host -> device copy node, the operator's sixteen launches, a device -> host copy node.  Each
+    # lane is captured on its own stream: the operator keeps its split-K scratch per stream, so the
+    # lanes' GEMMs never share one.
+    for lane in lanes:
+        lane.stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(lane.stream):
+            step(lane, 0)   # outside capture first: the operator's per-stream scratch is allocated on first use
+            torch.cuda.synchronize()
+            lane.graphs = []
+            for phase in range(phases):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=lane.stream):
+                    step(lane, phase)
+                lane.graphs.append(g)
+        torch.cuda.current_stream().wait_stream(lane.stream)
+    torch.cuda.synchronize()
 
     def run(n):
-        if world > 1:
-            for _ in range(n):
-                step(lanes[0], count[0] % phases)
-                count[0] += 1
-            return
         # the timing events sit on the current stream: the lanes start after it and it ends after them
         main = torch.cuda.current_stream()
         for lane in lanes:
@@ -604,28 +587,23 @@ def e2e_decode(d, args, layers, acts, keys, full_n, phases, multi=None):
     torch.cuda.synchronize()
     regions = timed_regions(d, run, steps, 3)
     ms = statistics.median(regions)
-    # what came back to the host must be what the device computed
     torch.cuda.synchronize()
-    key = keys[-1]
     for lane in lanes:
-        assert world > 1 or torch.equal(lane.host_out[key], lane.dev_out[key].cpu()), "e2e: host result differs"
-        if world == 1:
-            # ... and what a lone call of the same GEMM computes (the lanes' launches ran side by side)
-            from infiniops_b200 import capi
-
-            for name, m in (keys[0], keys[-1]):
-                w = layers[lane.last_phase * len(MS) + MS.index(m)][name]
-                alone = torch.empty_like(lane.dev_out[(name, m)])
-                capi.marlin_gemm(acts[(name, m)], w["marlin"], None, w["scales"], w["zeros"], UINT4, m, w["n"], w["k"], alone)
-                assert torch.equal(alone, lane.dev_out[(name, m)]), "e2e: result differs from the GEMM run alone"
+        # what came back to the host must be what the device computed ...
+        assert torch.equal(lane.host_out[keys[-1]], lane.dev_out[keys[-1]].cpu()), "e2e: host result differs"
+        # ... and what a lone call of the same GEMM computes (the lanes' launches ran side by side)
+        for name, m in (keys[0], keys[-1]):
+            w = layers[lane.last_phase * len(MS) + MS.index(m)][name]
+            alone = torch.empty_like(lane.dev_out[(name, m)])
+            capi.marlin_gemm(acts[(name, m)], w["marlin"], None, w["scales"], w["zeros"], UINT4, m, w["n"], w["k"], alone)
+            assert torch.equal(alone, lane.dev_out[(name, m)]), "e2e: result differs from the GEMM run alone"
     step_weight_bytes = sum(weight_bytes(k, n) for _, k, n in SHAPES) * len(MS)
     return {"value": step_weight_bytes / (ms * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
             "d2h_bytes_per_step": d2h, "steps": steps, "ms_per_step": ms,
             "note": "infini.ops.marlin_gemm per GEMM; the step's activations in one copy from pinned host memory, its results "
-                    "in one copy back to pinned host memory" +
-                    (f"; the step (copies and operator calls) replayed as a CUDA graph, steps alternating between {len(lanes)} "
-                     "sets of buffers and streams so that one step's copies and launch tails overlap the others' GEMMs"
-                     if world == 1 else "")}
+                    f"in one copy back to pinned host memory; the step (copies and operator calls) replayed as a CUDA graph, "
+                    f"steps alternating between {len(lanes)} sets of buffers and streams so that one step's copies and "
+                    "launch tails overlap the others' GEMMs"}
 
 
 def e2e_decode_placed(d, args, layers, acts, keys, full_n, phases, multi):
