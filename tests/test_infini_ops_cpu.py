@@ -77,6 +77,14 @@ _CASES = {
         infini.ops.MoeWna16MarlinGemm(h(2, 128), i32(2, 8, 128), None, h(2, 1, 64), None, None, None, None, None,
                                       i32(16), i32(64), i32(4), i32(1), Fake(torch.zeros(4)), 24, 2, False,
                                       1125899907892224, 2, 64, 128, True, False, True, False, -1, -1, -1, h(4, 64))""",
+    "requires contiguous int32 `g_idx` and `perm` of `size_k` entries": """
+        h = lambda *s: Fake(torch.zeros(s, dtype=torch.float16))
+        infini.ops.MarlinGemm(h(2, 256), i32(16, 128), None, h(2, 64), None, None, None, i32(256), i32(128), i32(16),
+                              1125899907892224, 2, 64, 256, True, False, True, False, h(2, 64))""",
+    "act-order needs grouped scales": """
+        h = lambda *s: Fake(torch.zeros(s, dtype=torch.float16))
+        infini.ops.MarlinGemm(h(2, 256), i32(16, 128), None, h(1, 64), None, None, None, i32(256), i32(256), i32(16),
+                              1125899907892224, 2, 64, 256, True, False, True, False, h(2, 64))""",
     "has no implementation 16": """
         infini.ops.SiluAndMul(Fake(torch.zeros((2, 8))), Fake(torch.zeros((2, 4))), implementation_index=16)""",
 }
