@@ -38,10 +38,10 @@ class MarlinGemm : public Operator<MarlinGemm> {
                      "`MarlinGemm` received unsupported dimensions");
     const bool has_zp = b_zeros.has_value();
     INFINI_OPS_CHECK((b_type_id_ == qtype::kUint4B8 || b_type_id_ == qtype::kUint4 || b_type_id_ == qtype::kUint8B128 ||
-                      b_type_id_ == qtype::kUint8) &&
+                      b_type_id_ == qtype::kUint8 || b_type_id_ == qtype::kFloat8E4M3Fn) &&
                          has_zp == (b_type_id_ == qtype::kUint4 || b_type_id_ == qtype::kUint8) && !is_zp_float_,
                      "`MarlinGemm` received an unsupported quantization configuration");
-    const int64_t pack = (b_type_id_ == qtype::kUint8B128 || b_type_id_ == qtype::kUint8) ? 4 : 8;  // weights per 32-bit word
+    const int64_t pack = (b_type_id_ == qtype::kUint8B128 || b_type_id_ == qtype::kUint8 || b_type_id_ == qtype::kFloat8E4M3Fn) ? 4 : 8;  // weights per 32-bit word
     INFINI_OPS_CHECK(b_q_weight.ndim() == 2 && static_cast<int64_t>(b_q_weight.size(0)) == size_k_ / 16 &&
                          static_cast<int64_t>(b_q_weight.size(1)) == size_n_ * 16 / pack &&
                          b_q_weight.dtype() == DataType::kInt32 && b_q_weight.IsContiguous(),

@@ -46,6 +46,7 @@ typedef enum {
 #define IOB_QTYPE_UINT4 1125899906843648LL   /* AWQ: w = (q - z) * s, z in `b_zeros` */
 #define IOB_QTYPE_UINT8B128 1125899923621888LL /* 8-bit symmetric: w = (q - 128) * s; b_q_weight [.., K/16, 4N] */
 #define IOB_QTYPE_UINT8 1125899906844672LL     /* 8-bit with zero points: w = (q - z) * s; b_zeros [.., G, N/4], byte n % 4 of word n / 4 */
+#define IOB_QTYPE_FLOAT8_E4M3FN 2814749767172868LL /* 8-bit float weights: w = float8_e4m3fn(byte) * s; layout as uint8b128, no zero points */
 
 /* Text of the last non-OK status returned on the calling thread. */
 const char* infiniops_b200_last_error(void);

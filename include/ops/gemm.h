@@ -18,8 +18,10 @@ namespace infini::ops {
 namespace impl {
 inline void RequireFourBit(int64_t b_type_id, const char* op) {
   if (b_type_id != qtype::kUint4B8 && b_type_id != qtype::kUint4 && b_type_id != qtype::kUint8B128 &&
-      b_type_id != qtype::kUint8) {
-    std::fprintf(stderr, "`%s`: only the weight types uint4b8, uint4, uint8b128 and uint8 are implemented in this build\n", op);
+      b_type_id != qtype::kUint8 && b_type_id != qtype::kFloat8E4M3Fn) {
+    std::fprintf(stderr,
+                 "`%s`: only the weight types uint4b8, uint4, uint8b128, uint8 and float8_e4m3fn are implemented in this build\n",
+                 op);
     std::fflush(stderr);
     std::abort();
   }

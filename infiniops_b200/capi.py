@@ -17,6 +17,9 @@ _LIB_PATH = pathlib.Path(__file__).resolve().parent / "lib" / "libinfiniops_b200
 F32, F16, BF16, I32, I64, U32 = range(6)
 QTYPE_UINT4B8 = 1125899907892224
 QTYPE_UINT4 = 1125899906843648
+QTYPE_UINT8B128 = 1125899923621888
+QTYPE_UINT8 = 1125899906844672
+QTYPE_FLOAT8_E4M3FN = 2814749767172868
 
 _DTYPE = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16, torch.int32: I32,
           torch.int64: I64, torch.uint32: U32}

@@ -140,6 +140,7 @@ struct GemmParams {
   // features) and the epilogue stores silu(gate) * up, [rows][N/2], instead of the [rows][N] product.
   int fuse_silu;
   int bits;                         // 4 or 8: width of a packed weight
+  int fp8;                          // 8-bit weights are float8_e4m3fn bytes (no zero point)
   // routed form, optional: live rows of every routing block (the rest of a block is padding).  The
   // MMAs of a block then cover only its live token columns, rounded up to 16, and so does the epilogue.
   const int* block_rows;
@@ -586,6 +587,32 @@ __device__ __forceinline__ uint32_t Dequant8<__nv_bfloat16>(uint32_t word, int o
   const float lo = __uint_as_float(__byte_perm(word, 0x4B000000u, odd ? 0x7541u : 0x7540u)) - centre;
   const float hi = __uint_as_float(__byte_perm(word, 0x4B000000u, odd ? 0x7543u : 0x7542u)) - centre;
   const float s = __uint_as_float(scale16 << 16);
+  const __nv_bfloat162 r = __floats2bfloat162_rn(lo * s, hi * s);
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+
+// 8-bit floating-point weights (float8_e4m3fn; same byte positions as Dequant8): value * scale in T.
+// The byte's exponent and mantissa go where T keeps its own, which leaves the exponent bias of the narrow
+// type (7) in place of T's: a power of two, multiplied back in exactly (subnormal bytes become
+// subnormals of T and come out right the same way).  The type's two NaN bytes are not weights.
+template <typename T>
+__device__ __forceinline__ uint32_t DequantF8(uint32_t word, int odd, uint32_t scale16);
+template <>
+__device__ __forceinline__ uint32_t DequantF8<__half>(uint32_t word, int odd, uint32_t scale16) {
+  const uint32_t v = __byte_perm(word, 0u, odd ? 0x3414u : 0x2404u);   // the two bytes as the high bytes of the halves
+  const uint32_t h = (v & 0x80008000u) | ((v >> 1) & 0x3F803F80u);
+  const uint32_t two8 = 0x5C005C00u, scale2 = scale16 * 0x10001u;       // 256 = 2^(15 - 7)
+  const __half2 c = __hmul2(*reinterpret_cast<const __half2*>(&h), *reinterpret_cast<const __half2*>(&two8));
+  const __half2 r = __hmul2(c, *reinterpret_cast<const __half2*>(&scale2));
+  return *reinterpret_cast<const uint32_t*>(&r);
+}
+template <>
+__device__ __forceinline__ uint32_t DequantF8<__nv_bfloat16>(uint32_t word, int odd, uint32_t scale16) {
+  const uint32_t v = __byte_perm(word, 0u, odd ? 0x3414u : 0x2404u);
+  const uint32_t h = (v & 0x80008000u) | ((v >> 4) & 0x07F007F0u);
+  const float two120 = __uint_as_float(0x7B800000u);                    // 2^(127 - 7)
+  const float s = __uint_as_float(scale16 << 16);
+  const float lo = __uint_as_float(h << 16) * two120, hi = __uint_as_float(h & 0xFFFF0000u) * two120;
   const __nv_bfloat162 r = __floats2bfloat162_rn(lo * s, hi * s);
   return *reinterpret_cast<const uint32_t*>(&r);
 }
@@ -1331,7 +1358,7 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
         TcFenceAfter();
       };
       if constexpr (kBits == 8) {
-        // 8-bit weights (uint8b128: w = (q - 128) * s).  Per 16-k slab and 64 columns the thread owns
+        // 8-bit weights (uint8b128: w = (q - 128) * s; uint8: (q - z) * s; float8_e4m3fn: float8(q) * s).  Per 16-k slab and 64 columns the thread owns
         // four adjacent words: [columns c0 | c0 + 8] of its first 16-column block, then of its second;
         // a word's bytes are k = 2t, 2t + 8, 2t + 1, 2t + 9 (t = lane % 4).  The two 64-column halves
         // of the tile lie 8 KB apart (one copy each).
@@ -1358,10 +1385,22 @@ __device__ __forceinline__ void GemmBody(const Problem* probs, int count) {
 #pragma unroll
             for (int kt = 0; kt < 4; ++kt) {
               const uint32_t w0 = w8[kt][2 * h], w1 = w8[kt][2 * h + 1];    // columns c0 and c0 + 8
-              regs[4 * kt + 0] = Dequant8<T>(w0, 0, pair & 0xFFFFu, z0);    // k pair t
-              regs[4 * kt + 1] = Dequant8<T>(w1, 0, pair >> 16, z1);
-              regs[4 * kt + 2] = Dequant8<T>(w0, 1, pair & 0xFFFFu, z0);    // k pair t + 4
-              regs[4 * kt + 3] = Dequant8<T>(w1, 1, pair >> 16, z1);
+              bool done = false;
+              if constexpr (!kZeros) {
+                if (cur->p.fp8) {
+                  regs[4 * kt + 0] = DequantF8<T>(w0, 0, pair & 0xFFFFu);
+                  regs[4 * kt + 1] = DequantF8<T>(w1, 0, pair >> 16);
+                  regs[4 * kt + 2] = DequantF8<T>(w0, 1, pair & 0xFFFFu);
+                  regs[4 * kt + 3] = DequantF8<T>(w1, 1, pair >> 16);
+                  done = true;
+                }
+              }
+              if (!done) {
+                regs[4 * kt + 0] = Dequant8<T>(w0, 0, pair & 0xFFFFu, z0);    // k pair t
+                regs[4 * kt + 1] = Dequant8<T>(w1, 0, pair >> 16, z1);
+                regs[4 * kt + 2] = Dequant8<T>(w0, 1, pair & 0xFFFFu, z0);    // k pair t + 4
+                regs[4 * kt + 3] = Dequant8<T>(w1, 1, pair >> 16, z1);
+              }
             }
             if (half == 0 && h == 0) before_first_store();
             if (alive) {
@@ -2326,7 +2365,9 @@ int Dispatch(int a_dtype, bool zeros, int tok, const CUtensorMap& map, const CUt
                : DispatchTok<__half, false, kMoe>(tok, map, w_map, c_map, p, grid, stream);
 }
 
-int BitsOf(int64_t b_type_id) { return b_type_id == IOB_QTYPE_UINT8B128 || b_type_id == IOB_QTYPE_UINT8 ? 8 : 4; }
+int BitsOf(int64_t b_type_id) {
+  return b_type_id == IOB_QTYPE_UINT8B128 || b_type_id == IOB_QTYPE_UINT8 || b_type_id == IOB_QTYPE_FLOAT8_E4M3FN ? 8 : 4;
+}
 
 int CheckProblem(const char* op, const void* a, int a_dtype, const void* wq, const void* scales, const void* zeros,
                  int64_t b_type_id, int64_t m, int64_t n, int64_t k, int64_t groups, const void* out) {
@@ -2335,11 +2376,12 @@ int CheckProblem(const char* op, const void* a, int a_dtype, const void* wq, con
   IOB_REQUIRE(m > 0 && n > 0 && k > 0 && k % 16 == 0 && n % 64 == 0, "%s: received unsupported dimensions", op);
   IOB_REQUIRE(m <= INT32_MAX && n <= INT32_MAX && k <= INT32_MAX, "%s: dimensions exceed int32", op);
   if (b_type_id != IOB_QTYPE_UINT4B8 && b_type_id != IOB_QTYPE_UINT4 && b_type_id != IOB_QTYPE_UINT8B128 &&
-      b_type_id != IOB_QTYPE_UINT8) {
-    return Fail(IOB_UNSUPPORTED, "%s: only the weight types uint4b8, uint4, uint8b128 and uint8 are implemented", op);
+      b_type_id != IOB_QTYPE_UINT8 && b_type_id != IOB_QTYPE_FLOAT8_E4M3FN) {
+    return Fail(IOB_UNSUPPORTED,
+                "%s: only the weight types uint4b8, uint4, uint8b128, uint8 and float8_e4m3fn are implemented", op);
   }
   IOB_REQUIRE((zeros != nullptr) == (b_type_id == IOB_QTYPE_UINT4 || b_type_id == IOB_QTYPE_UINT8),
-              "%s: zero points are required for uint4 / uint8 and not accepted for uint4b8 / uint8b128", op);
+              "%s: zero points are required for uint4 / uint8 and not accepted for uint4b8 / uint8b128 / float8_e4m3fn", op);
   IOB_REQUIRE(groups > 0 && k % groups == 0, "%s: `size_k` must be a multiple of the number of scale groups", op);
   if (k % kBlockK != 0 || ((k / groups) != 64 && (k / groups) % kBlockK != 0)) {
     return Fail(IOB_UNSUPPORTED, "%s: needs `size_k` to be a multiple of 128 and the group size 64 or a multiple of 128", op);
@@ -2469,6 +2511,8 @@ extern "C" int infiniops_b200_marlin_gemm_placed(const iob_gemm_problem* problem
   const int bits = BitsOf(b_type_id);
   IOB_REQUIRE(!(bits == 8 && g.b_zeros != nullptr && g.scale_layout != 0),
               "%s: 8-bit zero points are read in the plain layout only", op);
+  IOB_REQUIRE(!(b_type_id == IOB_QTYPE_FLOAT8_E4M3FN && g.scale_layout != 0),
+              "%s: float8_e4m3fn weights take their scales in the plain layout only", op);
   int tok = DenseTokenTile(g.size_m, g.size_n, g.size_k / (g.num_groups > 0 ? g.num_groups : 1));
   if (bits == 8 && tok > 128) tok = 128;  // 8-bit weights: no 256-row tiles (the stage ring would not fit)
   const int64_t n_tiles = (g.size_n + kTileN - 1) / kTileN, m_tiles = (g.size_m + tok - 1) / tok;
@@ -2513,6 +2557,7 @@ extern "C" int infiniops_b200_marlin_gemm_placed(const iob_gemm_problem* problem
   if (const int rc = OutputMap(g.out, g.size_m, p.out_ld, a_dtype, &c_map)) return rc;
   p.pair = pair ? 1 : 0;
   p.bits = bits;
+  p.fp8 = b_type_id == IOB_QTYPE_FLOAT8_E4M3FN ? 1 : 0;
   FillDense(g, static_cast<unsigned char*>(scratch), plan, p);
   const int64_t units = n_tiles * m_tiles * (g.size_k / kBlockK);
   const int grid = pair ? NumSms() : static_cast<int>(units < NumSms() ? units : NumSms());
@@ -2732,6 +2777,8 @@ extern "C" int infiniops_b200_moe_wna16_marlin_gemm_ex(
   const int bits = BitsOf(b_type_id);
   IOB_REQUIRE(!(bits == 8 && b_zeros != nullptr && options != nullptr && options->scale_layout != 0),
               "%s: 8-bit zero points are read in the plain layout only", op);
+  IOB_REQUIRE(!(b_type_id == IOB_QTYPE_FLOAT8_E4M3FN && options != nullptr && options->scale_layout != 0),
+              "%s: float8_e4m3fn weights take their scales in the plain layout only", op);
   IOB_REQUIRE(bits == 4 || (moe_block_size <= 128 && (options == nullptr || !options->fuse_silu) &&
                             !(options != nullptr && options->out_sorted && mul_topk_weights)),
               "%s: 8-bit weights take routing blocks up to 128 rows and the plain epilogue", op);
@@ -2739,6 +2786,7 @@ extern "C" int infiniops_b200_moe_wna16_marlin_gemm_ex(
   GemmParams p{};
   p.pair = pair ? 1 : 0;
   p.bits = bits;
+  p.fp8 = b_type_id == IOB_QTYPE_FLOAT8_E4M3FN ? 1 : 0;
   p.block_rows = block_rows;
   p.wq = reinterpret_cast<const uint32_t*>(b_q_weight);
   p.scales = b_scales;
