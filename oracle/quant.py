@@ -242,6 +242,19 @@ def dequantize(q, scales, zeros=None, num_bits: int = 4) -> torch.Tensor:
     return (qf - zp) * s
 
 
+def dequantize_float8(q, scales) -> torch.Tensor:
+    """fp32 weights [K, N] = float8_e4m3fn(byte) * scale, scale per group along K.
+
+    q: [K, N] bytes, each the bit pattern of a float8_e4m3fn number (the weight type the operator
+    accepts as `kFloat8E4M3Fn`, four weights per 32-bit word: src/base/moe_wna16_marlin_gemm.h:172-200);
+    scales: [G, N].  The reference's tests hold no float8 case: this follows the type's definition
+    (torch's own conversion) and the grouped-scale rule of `dequantize` above.
+    """
+    values = torch.from_numpy(np.ascontiguousarray(_as_np(q).astype(np.uint8))).view(torch.float8_e4m3fn).float()
+    s = torch.as_tensor(scales).float().cpu()
+    return values * s.repeat_interleave(values.shape[0] // s.shape[0], dim=0)
+
+
 def w4a16_gemm(a, q, scales, zeros=None, num_bits: int = 4, bias=None) -> torch.Tensor:
     """fp32 [M, N] = a.float() @ dequantize(q) (+ bias); fp32 accumulate.
 

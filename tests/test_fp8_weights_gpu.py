@@ -30,9 +30,7 @@ def _weights(k, n, group, dtype, seed):
     packed = torch.from_numpy(oq.gptq_pack(q, 8)).cuda()
     marlin = torch.empty((k // 16, 4 * n), dtype=torch.int32, device="cuda")
     capi.gptq_marlin_repack(packed, None, k, n, 8, False, marlin)
-    values = torch.from_numpy(q.copy()).view(torch.float8_e4m3fn).float()
-    dense = values * scales.float().repeat_interleave(k // groups, dim=0)
-    return dense, scales, marlin
+    return oq.dequantize_float8(q, scales), scales, marlin
 
 
 def test_every_byte_value_converts_exactly():
@@ -52,7 +50,7 @@ def test_every_byte_value_converts_exactly():
         out = torch.full((k, n), float("nan"), dtype=dtype, device="cuda")
         capi.marlin_gemm(a, marlin, None, scales, None, FLOAT8_E4M3FN, k, n, k, out)
         torch.cuda.synchronize()
-        want = torch.from_numpy(q.copy()).view(torch.float8_e4m3fn).float()
+        want = oq.dequantize_float8(q, torch.ones((1, n)))
         assert torch.equal(out.float().cpu(), want.to(dtype).float())
 
 

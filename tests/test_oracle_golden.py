@@ -167,3 +167,17 @@ def test_moe_mm_data_oracle_shapes(golden):
         valid = int(((ids >= 0) & (ids < experts)).sum())
         assert offsets[-1] == valid and sorted(out_perm[(ids.reshape(-1) >= 0) & (ids.reshape(-1) < experts)].tolist()) == list(range(valid))
         assert (scale is not None) == bool(blockscale)
+
+
+def test_float8_dequantisation_known_values():
+    """float8_e4m3fn bytes by the type's definition: bias 7, three mantissa bits, subnormals below 2**-6,
+    largest finite value 448."""
+    import numpy as np
+    import torch
+
+    from oracle import quant as oq
+
+    q = np.array([[0x38, 0x40, 0x7E, 0x01, 0xB8, 0x08, 0x07, 0x00]], dtype=np.uint8).T.repeat(2, axis=1)
+    got = oq.dequantize_float8(q, torch.tensor([[1.0, 0.5]]))
+    want = torch.tensor([1.0, 2.0, 448.0, 2.0**-9, -1.0, 2.0**-6, 7 * 2.0**-9, 0.0])
+    assert torch.equal(got[:, 0], want) and torch.equal(got[:, 1], want * 0.5)
