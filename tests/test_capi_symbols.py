@@ -83,3 +83,23 @@ def test_ctypes_structs_match_the_header(tmp_path):
         assert [f for f, _ in mirror._fields_] == list(fields), f"{name}: field list differs"
         for f, off in zip(fields, offsets):
             assert getattr(mirror, f).offset == int(off), f"{name}.{f}: offset {getattr(mirror, f).offset} != {off}"
+
+
+def test_weight_type_ids_agree_between_header_bindings_and_operator_layer():
+    """The vLLM scalar-type ids appear three times (C header, ctypes constants, C++ operator layer): one
+    list, compared number by number."""
+    import re
+
+    from infiniops_b200 import capi
+
+    header = (ROOT / "include" / "infiniops_b200.h").read_text()
+    in_header = {name: int(value) for name, value in re.findall(r"#define IOB_QTYPE_(\w+) (\d+)LL", header)}
+    assert set(in_header) == {"UINT4B8", "UINT4", "UINT8B128", "UINT8", "FLOAT8_E4M3FN"}
+    for name, value in in_header.items():
+        assert getattr(capi, "QTYPE_" + name) == value, name
+    base = (ROOT / "include" / "base" / "moe_wna16_marlin_gemm.h").read_text()
+    in_base = {name: int(value) for name, value in re.findall(r"k(\w+) = (\d+)", base)}
+    spelled = {"UINT4B8": "Uint4B8", "UINT4": "Uint4", "UINT8B128": "Uint8B128", "UINT8": "Uint8",
+               "FLOAT8_E4M3FN": "Float8E4M3Fn"}
+    for name, value in in_header.items():
+        assert in_base[spelled[name]] == value, name
